@@ -1,0 +1,134 @@
+"""The numpy oracle against golden outputs produced by the reference itself (tests/golden/make_golden.py)."""
+import numpy as np
+import pytest
+
+from oracle import attn as oattn
+from oracle import kv as okv
+from oracle import model as om
+from tests import golden_inputs as gi
+from tests.helpers import build_model, golden, oracle_weights
+
+
+def test_quantiser_bit_exact():
+    g = golden("quant")
+    for name, x in gi.quant_cases().items():
+        assert gi.sha(x) == str(g[name + ".in_sha"])
+        q, s = okv.quantize_kv(x)
+        assert np.array_equal(q, g[name + ".q"]), name
+        assert np.array_equal(s.view(np.uint16), g[name + ".s"]), name
+    x, idx = gi.kv_write_case()
+    cache = np.zeros((4, 2, 16, 64), np.int8)
+    sc = np.zeros((4, 2, 16), np.float16)
+    okv.kv_write(cache, sc, idx, x)
+    assert np.array_equal(cache, g["kv_write.cache"])
+    assert np.array_equal(sc.view(np.uint16), g["kv_write.scale"])
+
+
+def test_quantiser_properties():
+    # tests/test_math_kernels.py:115-121: |dequant - x| <= scale / 2, zero rows stay zero
+    x = gi.quant_cases()["normal_hd128"]
+    q, s = okv.quantize_kv(x)
+    err = np.abs(okv.dequantize_kv(q, s) - x)
+    assert err.max() <= (s.astype(np.float32) * 0.5 + 1e-3).max()
+    assert (q[0, 0] == 0).all() and s[0, 0] == 0
+
+
+def test_config1_attention():
+    g = golden("attn")
+    c = gi.config1()
+    assert np.array_equal(c["lens"], g["config1.lens"]) and int(c["lens"].sum()) == 4790
+    kq, ks = okv.quantize_kv(c["k"])
+    vq, vs = okv.quantize_kv(c["v"])
+    for n, a in (("kq", kq), ("ks", ks), ("vq", vq), ("vs", vs)):
+        assert gi.sha(a) == str(g[f"config1.{n}_sha"]), n
+    pos, starts = c["lens"] - 1, np.zeros(16, np.int64)
+    out = oattn.decode_attention_ref(c["q"], kq, vq, pos, starts, 0.14125, k_scale=ks, v_scale=vs)
+    np.testing.assert_allclose(out, g["config1.global"], atol=2e-6, rtol=1e-5)
+    out = oattn.decode_attention_ref(c["q"], kq[:, :, :256], vq[:, :, :256], pos, starts, 0.14125, window=256,
+                                     ring=True, k_scale=ks[:, :, :256], v_scale=vs[:, :, :256])
+    np.testing.assert_allclose(out, g["config1.local"], atol=2e-6, rtol=1e-5)
+    assert int(oattn.attention_key_counts(pos, starts).sum()) * 132 == 632280
+
+
+@pytest.mark.parametrize("name", sorted(gi.attn_cases()))
+def test_attention_grid(name):
+    g = golden("attn")
+    c = gi.attn_cases()[name]
+    assert gi.sha(c["q"], c["k"], c["v"], c["pos"], c["starts"]) == str(g[name + ".in_sha"])
+    if c["int8"]:
+        kq, ks = okv.quantize_kv(c["k"])
+        vq, vs = okv.quantize_kv(c["v"])
+    else:
+        kq, ks, vq, vs = c["k"], None, c["v"], None
+    out = oattn.decode_attention_ref(c["q"], kq, vq, c["pos"], c["starts"], c["scale"], window=c["window"],
+                                     ring=c["ring"], k_scale=ks, v_scale=vs)
+    np.testing.assert_allclose(out, g[name], atol=3e-6, rtol=1e-5)
+
+
+@pytest.mark.parametrize("name", sorted(gi.model_specs()))
+def test_model_teacher_forced(name):
+    g = golden("model")
+    spec = gi.model_specs()[name]
+    m = build_model(spec)
+    assert gi.state_sha(m.state_dict()) == str(g[name + ".weights_sha"])
+    W = oracle_weights(m)
+    idx, starts, cont, max_len = gi.teacher_inputs(spec)
+    st = om.State(m.cfg, idx.shape[0], max_len)
+    outs = [om.prefill(W, m.cfg, idx, starts, st)]
+    for t in range(cont.shape[1]):
+        outs.append(om.decode_step(W, m.cfg, cont[:, t], st))
+    lg = np.stack(outs, 1)
+    cols = gi.logit_columns(spec, lg.shape[-1])
+    # an int8 value on a rounding boundary can flip by one step (summation order), which moves logits by ~1e-3
+    d = np.abs(lg[..., cols] - g[name + ".logits"])
+    assert d.max() < 5e-3 and np.median(d) < 1e-4, (d.max(), np.median(d))
+    np.testing.assert_allclose(lg.max(-1), g[name + ".max"], atol=5e-3)
+    assert (lg.argmax(-1) == g[name + ".argmax"]).mean() > 0.99
+    assert np.array_equal(st.pos, g[name + ".pos"])
+    # int8 cache bytes: fp32 matmul summation order differs between numpy and torch, so a value sitting on a rounding
+    # boundary may move by one step; everything else must be identical
+    for l in spec["cache_layers"]:
+        for key, arr in ((f"k{l}", st.k[l]), (f"v{l}", st.v[l])):
+            ref = g[f"{name}.{key}"]
+            d = np.abs(arr.astype(np.int16) - ref.astype(np.int16))
+            assert d.max() <= 1 and (d != 0).mean() < 2e-3, (key, d.max(), (d != 0).mean())
+        for key, arr in ((f"ks{l}", st.k_scale[l]), (f"vs{l}", st.v_scale[l])):
+            ref = g[f"{name}.{key}"].view(np.float16).astype(np.float32)
+            np.testing.assert_allclose(arr.astype(np.float32), ref, rtol=2e-3, atol=1e-7)
+
+
+def test_generate_and_continuous_token_streams():
+    g = golden("model")
+    spec = gi.model_specs()["tiny"]
+    m = build_model(spec)
+    W = oracle_weights(m)
+    ge = spec["generate"]
+    assert om.generate(W, m.cfg, ge["prompts"], ge["max_new"], eos_id=ge["eos_id"]) == \
+        gi.unpack_lists(g["tiny.generate"])
+    c = spec["continuous"]
+    res = om.generate_continuous(W, m.cfg, c["prompts"], c["max_new"], c["batch"], eos_id=c["eos_id"],
+                                 check_every=c["check_every"], target_lens=c["target_lens"])
+    ref = gi.unpack_lists(g["tiny.continuous"])
+    assert res == ref
+    assert [len(r) for r in res] == c["target_lens"]
+
+
+def test_samplers():
+    g = golden("sampler")
+    x, u, cap, temps = gi.fused_sample_case()
+    assert gi.sha(x, u) == str(g["fused.in_sha"])
+    for t in temps:
+        tok, lp = om.fused_sample_ref(x, u, cap, t)
+        ref_tok = g[f"fused.tok.T{t}"]
+        # the flat fp32 cumsum is order sensitive: allow a neighbouring index, require the log-prob of an equal token
+        assert (np.abs(tok - ref_tok) <= 1).all() and (tok == ref_tok).mean() >= 0.75
+        same = tok == ref_tok
+        np.testing.assert_allclose(lp[same], g[f"fused.lp.T{t}"][same], atol=2e-5)
+    lg, temp, top_p, _ = gi.top_p_case()
+    keep = om.top_p_keep(lg, temp, top_p)
+    seen = g["top_p.support"]
+    assert not (seen & ~keep).any()          # the reference never draws outside the oracle's nucleus
+    z = lg / temp
+    p = np.exp(z - z.max(-1, keepdims=True))
+    p /= p.sum(-1, keepdims=True)
+    assert not (keep & ~seen & (p > 5e-3)).any()  # and draws every nucleus token that is not vanishingly rare
