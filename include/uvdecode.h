@@ -1,0 +1,126 @@
+/*
+ * uvdecode.h -- C ABI of libuvdecode.so: the UV-50M rollout-decode hot path as hand-written sm_100a CUDA kernels.
+ *
+ * The reference (hliuson/ultraviolet) is pure Python and has no FFI; its one native boundary on this path is the
+ * NVRTC launch `torch.cuda._compile_kernel(...)(grid, block, args=[...])` (ultraviolet/kernels/decode_attn_cuda.py:
+ * 300-305).  Each entry point below replaces one reference Python function (cited per function) and is what a
+ * ctypes / cffi binding on the reference side would call.
+ *
+ * Conventions
+ *   - every pointer is a DEVICE pointer unless its name starts with "h_"; the library never allocates, frees or
+ *     synchronises; all work is enqueued on `stream` (a cudaStream_t passed as void*; NULL = the legacy default
+ *     stream), so every call is CUDA-graph capturable;
+ *   - return value: 0 on success, a negative UV_ERR_* code on an argument error (nothing is launched), or
+ *     UV_ERR_CUDA with the CUDA error retrievable through uv_last_cuda_error();
+ *   - dtype codes: UV_F32 / UV_F16 / UV_BF16 / UV_I8;
+ *   - strides are in ELEMENTS of the tensor they describe; the innermost (head_dim) dimension is contiguous;
+ *   - no global mutable state apart from a per-thread last-error slot: calls are re-entrant per device/stream.
+ */
+#ifndef UVDECODE_H_
+#define UVDECODE_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define UV_ABI_VERSION 1
+
+enum { UV_F32 = 0, UV_F16 = 1, UV_BF16 = 2, UV_I8 = 3 };
+
+enum {
+  UV_OK = 0,
+  UV_ERR_ARG = -1,        /* null pointer / negative size / unsupported combination */
+  UV_ERR_DTYPE = -2,      /* dtype code not supported by this entry point */
+  UV_ERR_SHAPE = -3,      /* head_dim / group size / vocabulary outside the compiled set */
+  UV_ERR_ALIGN = -4,      /* pointer or stride alignment requirement not met */
+  UV_ERR_WORKSPACE = -5,  /* workspace missing or too small */
+  UV_ERR_CUDA = -6        /* a CUDA runtime call failed; see uv_last_cuda_error() */
+};
+
+int uv_abi_version(void);
+const char* uv_error_string(int code);
+int uv_last_cuda_error(void); /* cudaError_t of the last UV_ERR_CUDA on this host thread */
+
+/* ---------------------------------------------------------------------------------------------------------------
+ * (b) KV quantise + append.  Replaces quantize_kv + kv_write (ultraviolet/kernels/kv_quant.py:12-36) and the two
+ * kv_write calls per layer of decode_step_fast (ultraviolet/kernels/fast_decode.py:316-317).
+ *
+ * Quantiser (bit-exact with kv_quant.py:12-19): scale16 = fp16_rne(max|x| / 127) (fp32 division); q = clamp(
+ * rint(x / max(float(scale16), 1e-30)), -127, 127) with a true fp32 division and round-half-even.
+ *
+ * uv_kv_quant_scatter: n_rows vectors x[i] (hd elements, row stride x_stride) are quantised and written to row
+ * flat_idx[i] of the flat (rows, hd) int8 view `cache` and element flat_idx[i] of `scale` (fp16 bits).
+ * flat_idx == NULL means the identity (plain quantize_kv into contiguous outputs).  n_cache_rows bounds flat_idx;
+ * out-of-range indices are skipped and counted in *oob_count (optional device int, may be NULL).
+ */
+int uv_kv_quant_scatter(const void* x, int x_dtype, int64_t x_stride, int64_t n_rows, int hd,
+                        int8_t* cache, uint16_t* scale, const int64_t* flat_idx, int64_t n_cache_rows,
+                        int* oob_count, void* stream);
+
+/* uv_kv_append: the decode-time form.  For every slot-row b < B and kv head h < KH, quantise k_new[b,h,:] and
+ * v_new[b,h,:] and store them at cache slot (ring ? pos[b] % S : pos[b]) of row (b*KH + h) in caches laid out
+ * (B, KH, S, hd) int8 / (B, KH, S) fp16 (kv_quant.py:3-4).  Rows whose slot falls outside [0, S) are skipped and
+ * counted in *oob_count.  k_new / v_new: (B, KH, hd) with row strides in elements between consecutive (b, h). */
+int uv_kv_append(const void* k_new, const void* v_new, int dtype, int64_t k_stride, int64_t v_stride,
+                 int8_t* k_cache, int8_t* v_cache, uint16_t* k_scale, uint16_t* v_scale,
+                 const int64_t* pos, int B, int KH, int hd, int S, int ring, int* oob_count, void* stream);
+
+/* ---------------------------------------------------------------------------------------------------------------
+ * (c) Split-K single-query decode attention over the slot-indexed cache.  Replaces decode_attention / _launch /
+ * _split_kernel / _combine_kernel (ultraviolet/kernels/decode_attn.py:24-230) and decode_attn_cuda.launch
+ * (ultraviolet/kernels/decode_attn_cuda.py:273-309).
+ *
+ * Row b attends to the keys at absolute positions lo_b..pos_b, lo_b = max(starts_b, pos_b - window + 1, 0)
+ * (window 0 = unlimited); position t lives in slot t % S when ring, else slot t.  Query head h*G+g uses kv head h.
+ * out[b, h*G+g, :] = softmax_t(scale * q.K_t * ks_t) . (V_t * vs_t).
+ *
+ * Optional fused epilogue (Attention.post up to the output projection, ultraviolet/model.py:322-333), applied
+ * when the pointers are non-NULL: XSA  z -= xsa_alpha[head] * (z . vhat) * vhat with vhat = v_cur / max(|v_cur|,
+ * xsa_eps) from the CURRENT token's unquantised v, then the head gate z *= 2*sigmoid(gate_x[b, :gate_ch] .
+ * gate_w[head, :gate_ch]).
+ */
+typedef struct uv_attn_args {
+  const void* q;          /* (B, H, hd) */
+  int q_dtype;            /* UV_F16 | UV_BF16 */
+  int64_t sqb, sqh;
+  const void* k_cache;    /* (B, KH, S, hd) */
+  const void* v_cache;
+  int kv_dtype;           /* UV_I8 (with scales) */
+  int64_t skb, skh, sks, svb, svh, svs;
+  const uint16_t* k_scale; /* (B, KH, S) fp16 bits */
+  const uint16_t* v_scale;
+  int64_t ssb, ssh, stb, sth;
+  const int64_t* pos;     /* (B,) position of the newest key (already in the cache) */
+  const int64_t* starts;  /* (B,) first valid position */
+  void* out;              /* (B, H, hd) in q_dtype */
+  int64_t sob, soh;
+  int B, H, KH, hd, S;
+  int window, ring;
+  float scale;
+  int num_splits;         /* >= 1; > 1 needs workspace */
+  void* workspace;        /* uv_decode_attn_workspace_bytes() bytes, 16-byte aligned */
+  size_t workspace_bytes;
+  /* fused epilogue, all optional */
+  const void* v_cur;      /* (B, KH, hd) q_dtype, row stride v_cur_stride elements between (b, h) vectors */
+  int64_t v_cur_stride;
+  const float* xsa_alpha; /* (H,) fp32, already tanh'ed (Attention.fuse, model.py:298-299) */
+  float xsa_eps;
+  const void* gate_x;     /* (B, >= gate_ch) q_dtype, row stride gate_x_stride */
+  int64_t gate_x_stride;
+  const void* gate_w;     /* (H, gate_ch) q_dtype contiguous */
+  int gate_ch;
+} uv_attn_args;
+
+size_t uv_decode_attn_workspace_bytes(int B, int KH, int G, int hd, int num_splits);
+/* Split count for (B*KH) cache rows of at most ctx keys on a device with n_sm SMs (role of default_splits,
+ * decode_attn.py:121-129, retuned for 148-SM parts with 64-key TMA tiles). */
+int uv_default_splits(int n_bk, int ctx, int n_sm);
+int uv_decode_attn(const uv_attn_args* args, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* UVDECODE_H_ */

@@ -1,0 +1,86 @@
+"""ctypes binding of libuvdecode.so (declared in include/uvdecode.h).
+
+The library is the product: there is no Python or torch fallback for any entry point.  ``lib()`` raises if the
+shared object is missing instead of degrading silently.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import threading
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libuvdecode.so")
+
+UV_F32, UV_F16, UV_BF16, UV_I8 = 0, 1, 2, 3
+UV_ABI_VERSION = 1
+
+_lock = threading.Lock()
+_lib = None
+
+
+class UvError(RuntimeError):
+    pass
+
+
+class AttnArgs(C.Structure):
+    _fields_ = [
+        ("q", C.c_void_p), ("q_dtype", C.c_int), ("sqb", C.c_int64), ("sqh", C.c_int64),
+        ("k_cache", C.c_void_p), ("v_cache", C.c_void_p), ("kv_dtype", C.c_int),
+        ("skb", C.c_int64), ("skh", C.c_int64), ("sks", C.c_int64),
+        ("svb", C.c_int64), ("svh", C.c_int64), ("svs", C.c_int64),
+        ("k_scale", C.c_void_p), ("v_scale", C.c_void_p),
+        ("ssb", C.c_int64), ("ssh", C.c_int64), ("stb", C.c_int64), ("sth", C.c_int64),
+        ("pos", C.c_void_p), ("starts", C.c_void_p),
+        ("out", C.c_void_p), ("sob", C.c_int64), ("soh", C.c_int64),
+        ("B", C.c_int), ("H", C.c_int), ("KH", C.c_int), ("hd", C.c_int), ("S", C.c_int),
+        ("window", C.c_int), ("ring", C.c_int), ("scale", C.c_float), ("num_splits", C.c_int),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
+        ("v_cur", C.c_void_p), ("v_cur_stride", C.c_int64), ("xsa_alpha", C.c_void_p), ("xsa_eps", C.c_float),
+        ("gate_x", C.c_void_p), ("gate_x_stride", C.c_int64), ("gate_w", C.c_void_p), ("gate_ch", C.c_int),
+    ]
+
+
+# name -> (restype, argtypes); every symbol include/uvdecode.h declares
+SIGNATURES = {
+    "uv_abi_version": (C.c_int, []),
+    "uv_error_string": (C.c_char_p, [C.c_int]),
+    "uv_last_cuda_error": (C.c_int, []),
+    "uv_kv_quant_scatter": (C.c_int, [C.c_void_p, C.c_int, C.c_int64, C.c_int64, C.c_int, C.c_void_p, C.c_void_p,
+                                      C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p]),
+    "uv_kv_append": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int64, C.c_int64, C.c_void_p, C.c_void_p,
+                               C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
+                               C.c_void_p, C.c_void_p]),
+    "uv_decode_attn_workspace_bytes": (C.c_size_t, [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int]),
+    "uv_default_splits": (C.c_int, [C.c_int, C.c_int, C.c_int]),
+    "uv_decode_attn": (C.c_int, [C.POINTER(AttnArgs), C.c_void_p]),
+}
+
+
+def lib() -> C.CDLL:
+    """Load libuvdecode.so once; raise loudly if it has not been built (python -m ultraviolet_b200.build)."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    with _lock:
+        if _lib is None:
+            if not os.path.exists(LIB_PATH):
+                raise UvError(f"{LIB_PATH} is missing: build it with `python -m ultraviolet_b200.build` "
+                              "(nvcc, sm_100a). There is no fallback path.")
+            h = C.CDLL(LIB_PATH)
+            for name, (res, args) in SIGNATURES.items():
+                fn = getattr(h, name)  # AttributeError if the library does not export a declared symbol
+                fn.restype, fn.argtypes = res, args
+            if h.uv_abi_version() != UV_ABI_VERSION:
+                raise UvError(f"libuvdecode ABI {h.uv_abi_version()} != binding {UV_ABI_VERSION}: rebuild")
+            _lib = h
+    return _lib
+
+
+def check(code: int, what: str) -> None:
+    if code != 0:
+        h = lib()
+        msg = h.uv_error_string(code).decode()
+        if code == -6:
+            msg += f" [cudaError {h.uv_last_cuda_error()}]"
+        raise UvError(f"{what}: {msg} (code {code})")

@@ -1,0 +1,24 @@
+// Library-level entry points: ABI version, error strings, per-thread CUDA error slot.
+#include "common.cuh"
+
+namespace uv {
+static thread_local int g_last_cuda_error = 0;
+void set_last_cuda_error(int e) { g_last_cuda_error = e; }
+}  // namespace uv
+
+extern "C" int uv_abi_version(void) { return UV_ABI_VERSION; }
+
+extern "C" int uv_last_cuda_error(void) { return uv::g_last_cuda_error; }
+
+extern "C" const char* uv_error_string(int code) {
+  switch (code) {
+    case UV_OK: return "ok";
+    case UV_ERR_ARG: return "invalid argument (null pointer, negative size or inconsistent options)";
+    case UV_ERR_DTYPE: return "dtype not supported by this entry point";
+    case UV_ERR_SHAPE: return "shape outside the compiled set (head_dim, group size or vocabulary)";
+    case UV_ERR_ALIGN: return "pointer or stride alignment requirement not met";
+    case UV_ERR_WORKSPACE: return "workspace missing or too small";
+    case UV_ERR_CUDA: return "CUDA runtime error (see uv_last_cuda_error)";
+    default: return "unknown error code";
+  }
+}

@@ -1,0 +1,718 @@
+// Split-K single-query (flash-decode) attention over the slot-indexed int8 KV cache, sm_100a.
+//
+// Work decomposition: one CTA per (cache row b, kv head h, split).  The row's valid positions [lo, hi] are cut into
+// 64-key tiles aligned to multiples of 64 in position space; a split owns a contiguous run of tiles.  Tiles stream
+// HBM -> shared memory through the bulk-copy (TMA) engine into a 4-stage ring (cp.async.bulk + mbarrier
+// complete_tx), K / V / both scale vectors as four linear copies per tile, trimmed to the row's valid range at
+// 8-key granularity.  Caches whose geometry breaks the 16-byte rules of the bulk engine (row length not a multiple
+// of 8 slots, ring length not a multiple of 64, unaligned views) take a plain-load path with the same shared
+// memory layout.
+//
+// Math: the G query heads of a kv group form the M rows of warp-level tensor-core tiles (mma.sync.m16n8k16, fp16
+// inputs, fp32 accumulate; G <= 8 leaves rows 8..15 zero, G <= 16 uses them).  S = Q K^T has keys as the N
+// dimension, so its accumulators are already the A fragment of P for O += P V: no transposition of P.  int8 K and
+// V are dequantised in registers (xor 0x80 + byte permute into the mantissa of 1024.0, minus 1152), V through a
+// 4x4 byte transpose that rides on the same permutes.  The per-key K scale multiplies the S columns, the V scale is
+// folded into P.  Head dims are consumed in a permuted order that Q shares (dot products are order free) so every
+// lane reads contiguous 16-byte pieces of a key row.
+//
+// Each of the 4 warps owns 16 keys of every tile with its own online-softmax state; states are merged through
+// shared memory with log-sum-exp weights, and splits > 1 are merged by a second small kernel.
+#include "common.cuh"
+
+namespace uv {
+
+constexpr int TILE = 64;
+constexpr int NSTAGE = 4;
+constexpr int NWARP = 4;
+constexpr int NTHREAD = NWARP * 32;
+constexpr unsigned long long WAIT_NS = 200ull * 1000 * 1000;  // a tile that has not landed after 200 ms is abandoned
+constexpr float LOG2E = 1.4426950408889634f;
+
+struct AttnParams {
+  const void* q;
+  const int8_t* k;
+  const int8_t* v;
+  const __half* ks;
+  const __half* vs;
+  const int64_t* pos;
+  const int64_t* starts;
+  void* out;
+  float* ws_o;
+  float* ws_m;
+  float* ws_l;
+  int* status;
+  int64_t sqb, sqh, skb, skh, sks, svb, svh, svs, ssb, ssh, stb, sth, sob, soh;
+  int B, H, KH, G, S, window, ring, splits;
+  float scale_log2;
+  // fused epilogue
+  const void* v_cur;
+  int64_t v_cur_stride;
+  const float* xsa_alpha;
+  float xsa_eps;
+  const void* gate_x;
+  int64_t gate_x_stride;
+  const void* gate_w;
+  int gate_ch;
+};
+
+// ------------------------------------------------------------------------------------------------ PTX wrappers
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void fence_barrier_init() {
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+               "l"(src), "r"(bytes), "r"(bar)
+               : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ unsigned long long global_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+// Poll with a wall-clock bound: never an unbounded spin.  false = the expected bytes did not arrive in WAIT_NS.
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity) {
+  unsigned long long t_begin = 0;
+  for (int i = 0;; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((i & 127) == 127) {
+      const unsigned long long now = global_ns();
+      if (t_begin == 0) t_begin = now;
+      else if (now - t_begin > WAIT_NS) return false;
+    }
+  }
+}
+
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ uint32_t pack_h2(float lo, float hi) {
+  __half2 h = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+__device__ __forceinline__ void mma16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                         uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+// two bytes (already xor 0x80) selected from x -> half2 of the signed values: 0x64xx is 1024 + xx, minus 1152
+__device__ __forceinline__ uint32_t bias_pair(uint32_t x, uint32_t sel) {
+  uint32_t w = __byte_perm(x, 0x64646464u, sel);
+  __half2 h = __hsub2(*reinterpret_cast<__half2*>(&w), __half2half2(__ushort_as_half(0x6480)));
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+
+template <typename QT> __device__ __forceinline__ uint32_t q_pair(const QT* p);
+template <> __device__ __forceinline__ uint32_t q_pair<__half>(const __half* p) {
+  return *reinterpret_cast<const uint32_t*>(p);
+}
+template <> __device__ __forceinline__ uint32_t q_pair<__nv_bfloat16>(const __nv_bfloat16* p) {
+  return pack_h2(__bfloat162float(p[0]), __bfloat162float(p[1]));
+}
+
+// ------------------------------------------------------------------------------------------------ row finalisation
+// One warp holds z (one query head's output, lane owns dims lane + 32*i), applies the optional XSA / head-gate
+// epilogue with the reference's rounding points (Attention.post, ultraviolet/model.py:322-333) and stores it.
+template <typename QT, int HD>
+__device__ __forceinline__ void finalize_row(float (&z)[(HD + 31) / 32], int lane, int b, int head, int kvh,
+                                             const AttnParams& P) {
+  constexpr int EPL = (HD + 31) / 32;
+  const bool act = (HD >= 32) || lane < HD;
+#pragma unroll
+  for (int i = 0; i < EPL; ++i) z[i] = rnd<QT>(z[i]);  // the attention output itself is in the activation dtype
+  if (P.xsa_alpha != nullptr) {
+    const QT* vc = static_cast<const QT*>(P.v_cur) + ((int64_t)b * P.KH + kvh) * P.v_cur_stride;
+    float vv[EPL], n2 = 0.f;
+#pragma unroll
+    for (int i = 0; i < EPL; ++i) {
+      vv[i] = act ? to_f32<QT>(vc[lane + 32 * i]) : 0.f;
+      n2 += vv[i] * vv[i];
+    }
+    n2 = warp_sum(n2);
+    const float inv = 1.0f / fmaxf(sqrtf(n2), P.xsa_eps);
+    float dot = 0.f;
+#pragma unroll
+    for (int i = 0; i < EPL; ++i) {
+      vv[i] *= inv;
+      dot += z[i] * vv[i];
+    }
+    dot = warp_sum(dot);
+    const float a = P.xsa_alpha[head];
+#pragma unroll
+    for (int i = 0; i < EPL; ++i) z[i] = rnd<QT>(z[i] - a * dot * vv[i]);
+  }
+  if (P.gate_w != nullptr) {
+    const QT* gx = static_cast<const QT*>(P.gate_x) + (int64_t)b * P.gate_x_stride;
+    const QT* gw = static_cast<const QT*>(P.gate_w) + (int64_t)head * P.gate_ch;
+    float acc = 0.f;
+    for (int ch = lane; ch < P.gate_ch; ch += 32) acc += to_f32<QT>(gx[ch]) * to_f32<QT>(gw[ch]);
+    acc = rnd<QT>(warp_sum(acc));
+    const float g = rnd<QT>(2.0f * rnd<QT>(1.0f / (1.0f + __expf(-acc))));
+#pragma unroll
+    for (int i = 0; i < EPL; ++i) z[i] = rnd<QT>(z[i] * g);
+  }
+  QT* o = static_cast<QT*>(P.out) + (int64_t)b * P.sob + (int64_t)head * P.soh;
+#pragma unroll
+  for (int i = 0; i < EPL; ++i)
+    if (act) o[lane + 32 * i] = from_f32<QT>(z[i]);
+}
+
+// ------------------------------------------------------------------------------------------------ split kernel
+template <int HD> struct StageLayout {
+  static constexpr int K_OFF = 0;
+  static constexpr int V_OFF = TILE * HD;
+  static constexpr int KS_OFF = 2 * TILE * HD;
+  static constexpr int VS_OFF = 2 * TILE * HD + 2 * TILE;
+  static constexpr int BYTES = 2 * TILE * HD + 4 * TILE;
+};
+
+template <typename QT, int HD, bool GP16, bool BULK>
+__global__ void __launch_bounds__(NTHREAD) attn_split_kernel(const __grid_constant__ AttnParams P) {
+  using L = StageLayout<HD>;
+  constexpr int KSTEPS = HD / 16;  // k16 steps of Q K^T = 32-bit words of a key row per lane
+  constexpr int NT_O = HD / 8;     // n8 tiles of O = bytes of a value row per lane
+  constexpr int ROWS = GP16 ? 16 : 8;
+  constexpr int NST = BULK ? NSTAGE : 1;
+  extern __shared__ __align__(128) unsigned char smem[];
+  __shared__ __align__(8) uint64_t bars[NSTAGE];
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int r = lane >> 2, c = lane & 3;
+  const int bk = blockIdx.x, sid = blockIdx.y;
+  const int b = bk / P.KH, h = bk % P.KH;
+  const int G = P.G;
+
+  // ---- the row's key range and this split's tiles
+  const int64_t p = P.pos[b];
+  int64_t lo = P.starts[b];
+  if (lo < 0) lo = 0;
+  if (P.window > 0 && p - P.window + 1 > lo) lo = p - P.window + 1;
+  int64_t hi = p;
+  if (P.ring) {
+    if (p - P.S + 1 > lo) lo = p - P.S + 1;  // older positions have been overwritten
+  } else if (hi > P.S - 1) {
+    hi = P.S - 1;
+  }
+  int64_t t0 = 0, t1 = 0;
+  if (hi >= lo) {
+    const int64_t t_lo = lo / TILE, t_hi = hi / TILE;
+    const int64_t per = (t_hi - t_lo + P.splits) / P.splits;  // ceil(n_tiles / splits)
+    t0 = t_lo + (int64_t)sid * per;
+    t1 = t0 + per < t_hi + 1 ? t0 + per : t_hi + 1;
+  }
+  const int ntile = t1 > t0 ? (int)(t1 - t0) : 0;
+
+  if (ntile == 0) {  // empty row or inactive split
+    if (P.splits == 1) {
+      for (int i = tid; i < G * HD; i += NTHREAD) {
+        QT* o = static_cast<QT*>(P.out) + (int64_t)b * P.sob + (int64_t)(h * G + i / HD) * P.soh;
+        o[i % HD] = from_f32<QT>(0.f);
+      }
+    } else if (tid < G) {
+      const int64_t row = ((int64_t)bk * P.splits + sid) * G + tid;
+      P.ws_m[row] = -INFINITY;
+      P.ws_l[row] = 0.f;
+    }
+    return;
+  }
+
+  // ---- Q fragments (A operand of Q K^T): lane (r, c) holds head r (and r + 8), dims c*HD/4 + 4j + {0..3}
+  uint32_t qa[KSTEPS][GP16 ? 4 : 2];
+  {
+    const QT* qb = static_cast<const QT*>(P.q) + (int64_t)b * P.sqb + (int64_t)(h * G) * P.sqh + c * (HD / 4);
+#pragma unroll
+    for (int j = 0; j < KSTEPS; ++j) {
+      if (r < G) {
+        const QT* q0 = qb + (int64_t)r * P.sqh + 4 * j;
+        qa[j][0] = q_pair<QT>(q0);
+        qa[j][1] = q_pair<QT>(q0 + 2);
+      } else {
+        qa[j][0] = qa[j][1] = 0u;
+      }
+      if constexpr (GP16) {
+        if (r + 8 < G) {
+          const QT* q1 = qb + (int64_t)(r + 8) * P.sqh + 4 * j;
+          qa[j][2] = q_pair<QT>(q1);
+          qa[j][3] = q_pair<QT>(q1 + 2);
+        } else {
+          qa[j][2] = qa[j][3] = 0u;
+        }
+      }
+    }
+  }
+
+  const int8_t* kbase = P.k + (int64_t)b * P.skb + (int64_t)h * P.skh;
+  const int8_t* vbase = P.v + (int64_t)b * P.svb + (int64_t)h * P.svh;
+  const __half* ksbase = P.ks + (int64_t)b * P.ssb + (int64_t)h * P.ssh;
+  const __half* vsbase = P.vs + (int64_t)b * P.stb + (int64_t)h * P.sth;
+
+  if constexpr (BULK) {
+    if (tid == 0) {
+#pragma unroll
+      for (int s = 0; s < NSTAGE; ++s) mbar_init(smem_u32(&bars[s]), 1);
+      fence_barrier_init();
+    }
+    __syncthreads();
+  }
+
+  // issue the four linear copies of tile ti into stage s (one thread)
+  auto issue = [&](int64_t ti, int s) {
+    const int64_t T0 = ti * TILE;
+    int64_t a = (T0 > lo ? T0 : lo) & ~(int64_t)7;
+    int64_t e = (T0 + TILE < hi + 1 ? T0 + TILE : hi + 1);
+    e = (e + 7) & ~(int64_t)7;
+    const uint32_t cnt = (uint32_t)(e - a);
+    const int64_t slot = P.ring ? a % P.S : a;
+    const uint32_t off = (uint32_t)(a - T0);
+    const uint32_t bar = smem_u32(&bars[s]);
+    const uint32_t st = smem_u32(smem + (size_t)s * L::BYTES);
+    fence_proxy_async();
+    mbar_expect_tx(bar, cnt * (2 * HD + 4));
+    bulk_g2s(st + L::K_OFF + off * HD, kbase + slot * HD, cnt * HD, bar);
+    bulk_g2s(st + L::V_OFF + off * HD, vbase + slot * HD, cnt * HD, bar);
+    bulk_g2s(st + L::KS_OFF + off * 2, ksbase + slot, cnt * 2, bar);
+    bulk_g2s(st + L::VS_OFF + off * 2, vsbase + slot, cnt * 2, bar);
+  };
+
+  // plain-load path: every thread copies 16-byte pieces of the valid keys of tile ti into stage 0
+  auto load_generic = [&](int64_t ti) {
+    const int64_t T0 = ti * TILE;
+    unsigned char* st = smem;
+    constexpr int CH = HD / 16;  // 16-byte chunks per row
+    for (int i = tid; i < TILE * CH * 2; i += NTHREAD) {
+      const int which = i / (TILE * CH);
+      const int j = (i % (TILE * CH)) / CH, ch = i % CH;
+      const int64_t t = T0 + j;
+      if (t < lo || t > hi) continue;
+      const int64_t slot = P.ring ? t % P.S : t;
+      const int8_t* src = which ? vbase + slot * P.svs : kbase + slot * P.sks;
+      *reinterpret_cast<uint4*>(st + (which ? L::V_OFF : L::K_OFF) + j * HD + ch * 16) =
+          *reinterpret_cast<const uint4*>(src + ch * 16);
+    }
+    for (int i = tid; i < TILE * 2; i += NTHREAD) {
+      const int which = i / TILE, j = i % TILE;
+      const int64_t t = T0 + j;
+      if (t < lo || t > hi) continue;
+      const int64_t slot = P.ring ? t % P.S : t;
+      reinterpret_cast<__half*>(st + (which ? L::VS_OFF : L::KS_OFF))[j] = which ? vsbase[slot] : ksbase[slot];
+    }
+  };
+
+  // ---- per-warp online softmax state
+  float o_acc[NT_O][GP16 ? 4 : 2];
+#pragma unroll
+  for (int i = 0; i < NT_O; ++i)
+#pragma unroll
+    for (int j = 0; j < (GP16 ? 4 : 2); ++j) o_acc[i][j] = 0.f;
+  float m_run[GP16 ? 2 : 1], l_run[GP16 ? 2 : 1];
+#pragma unroll
+  for (int j = 0; j < (GP16 ? 2 : 1); ++j) {
+    m_run[j] = -INFINITY;
+    l_run[j] = 0.f;
+  }
+
+  if constexpr (BULK) {
+    if (tid == 0) {
+      const int pre = ntile < NSTAGE - 1 ? ntile : NSTAGE - 1;
+      for (int i = 0; i < pre; ++i) issue(t0 + i, i);
+    }
+  }
+
+  bool dead = false;
+  for (int it = 0; it < ntile; ++it) {
+    const int s = BULK ? it % NSTAGE : 0;
+    __syncthreads();  // every warp is done with the stage that is refilled next
+    if constexpr (BULK) {
+      if (tid == 0 && it + NSTAGE - 1 < ntile) issue(t0 + it + NSTAGE - 1, (it + NSTAGE - 1) % NSTAGE);
+      if (!dead) {  // warp-uniform: a warp whose tile never landed stops consuming and flags the launch
+        const bool got = mbar_wait_bounded(smem_u32(&bars[s]), (uint32_t)((it / NSTAGE) & 1));
+        dead = !__all_sync(0xffffffffu, got);
+      }
+      if (dead) continue;
+    } else {
+      load_generic(t0 + it);
+      __syncthreads();
+    }
+    const unsigned char* st = smem + (size_t)s * L::BYTES;
+    const int64_t kb0 = (t0 + it) * TILE + 16 * warp;  // position of this warp's first key
+    if (kb0 + 15 < lo || kb0 > hi) continue;
+    const bool edge = kb0 < lo || kb0 + 15 > hi;
+
+    // ---- S = Q K^T for 16 keys: two n8 tiles
+    float sc[2][4];
+#pragma unroll
+    for (int t = 0; t < 2; ++t) {
+      sc[t][0] = sc[t][1] = sc[t][2] = sc[t][3] = 0.f;
+      const unsigned char* krow = st + L::K_OFF + (16 * warp + 8 * t + r) * HD + c * (HD / 4);
+      uint32_t kw[KSTEPS];
+      if constexpr (KSTEPS == 1) {
+        kw[0] = *reinterpret_cast<const uint32_t*>(krow);
+      } else if constexpr (KSTEPS == 2) {
+        const uint2 u = *reinterpret_cast<const uint2*>(krow);
+        kw[0] = u.x, kw[1] = u.y;
+      } else {
+#pragma unroll
+        for (int j4 = 0; j4 < KSTEPS / 4; ++j4) {
+          const uint4 u = *reinterpret_cast<const uint4*>(krow + 16 * j4);
+          kw[4 * j4] = u.x, kw[4 * j4 + 1] = u.y, kw[4 * j4 + 2] = u.z, kw[4 * j4 + 3] = u.w;
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < KSTEPS; ++j) {
+        const uint32_t x = kw[j] ^ 0x80808080u;
+        const uint32_t b0 = bias_pair(x, 0x4140), b1 = bias_pair(x, 0x4342);
+        if constexpr (GP16) mma16816(sc[t], qa[j][0], qa[j][2], qa[j][1], qa[j][3], b0, b1);
+        else mma16816(sc[t], qa[j][0], 0u, qa[j][1], 0u, b0, b1);
+      }
+    }
+
+    // ---- scales, masks, online softmax
+    float vsc[2][2];
+    bool ok[2][2];
+#pragma unroll
+    for (int t = 0; t < 2; ++t) {
+      const int kk = 16 * warp + 8 * t + 2 * c;
+      const float2 kf = __half22float2(*reinterpret_cast<const __half2*>(st + L::KS_OFF + kk * 2));
+      const float2 vf = __half22float2(*reinterpret_cast<const __half2*>(st + L::VS_OFF + kk * 2));
+      const int64_t tp = kb0 + 8 * t + 2 * c;
+      ok[t][0] = !edge || (tp >= lo && tp <= hi);
+      ok[t][1] = !edge || (tp + 1 >= lo && tp + 1 <= hi);
+      const float k0 = kf.x * P.scale_log2, k1 = kf.y * P.scale_log2;
+      sc[t][0] = ok[t][0] ? sc[t][0] * k0 : -INFINITY;
+      sc[t][1] = ok[t][1] ? sc[t][1] * k1 : -INFINITY;
+      if constexpr (GP16) {
+        sc[t][2] = ok[t][0] ? sc[t][2] * k0 : -INFINITY;
+        sc[t][3] = ok[t][1] ? sc[t][3] * k1 : -INFINITY;
+      }
+      vsc[t][0] = ok[t][0] ? vf.x : 0.f;
+      vsc[t][1] = ok[t][1] ? vf.y : 0.f;
+    }
+    uint32_t pa[4] = {0u, 0u, 0u, 0u};  // A fragment of P (fp16), V scale folded in
+#pragma unroll
+    for (int hr = 0; hr < (GP16 ? 2 : 1); ++hr) {
+      float mx = fmaxf(fmaxf(sc[0][2 * hr], sc[0][2 * hr + 1]), fmaxf(sc[1][2 * hr], sc[1][2 * hr + 1]));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+      const float m_new = fmaxf(m_run[hr], mx);
+      const float alpha = ex2(m_run[hr] - m_new);
+      m_run[hr] = m_new;
+      float pr[2][2];
+#pragma unroll
+      for (int t = 0; t < 2; ++t) {
+        pr[t][0] = ok[t][0] ? ex2(sc[t][2 * hr] - m_new) : 0.f;
+        pr[t][1] = ok[t][1] ? ex2(sc[t][2 * hr + 1] - m_new) : 0.f;
+      }
+      l_run[hr] = l_run[hr] * alpha + (pr[0][0] + pr[0][1]) + (pr[1][0] + pr[1][1]);
+      pa[hr] = pack_h2(pr[0][0] * vsc[0][0], pr[0][1] * vsc[0][1]);
+      pa[2 + hr] = pack_h2(pr[1][0] * vsc[1][0], pr[1][1] * vsc[1][1]);
+#pragma unroll
+      for (int i = 0; i < NT_O; ++i) {
+        o_acc[i][2 * hr] *= alpha;
+        o_acc[i][2 * hr + 1] *= alpha;
+      }
+    }
+
+    // ---- O += P V: lane (r, c) reads HD/8 bytes at dim offset r*HD/8 of keys 2c, 2c+1, 2c+8, 2c+9 and
+    //      transposes them into B fragments (n8 tile i <-> dim r*HD/8 + i)
+    {
+      const unsigned char* vrow = st + L::V_OFF + (16 * warp + 2 * c) * HD + r * (HD / 8);
+      constexpr int VW = (NT_O + 3) / 4;  // 32-bit words per row piece
+      uint32_t va[VW], vb[VW], vc[VW], vd[VW];
+      auto ld = [&](const unsigned char* ptr, uint32_t(&w)[VW]) {
+        if constexpr (NT_O == 2) {
+          w[0] = *reinterpret_cast<const uint16_t*>(ptr);
+        } else if constexpr (NT_O == 4) {
+          w[0] = *reinterpret_cast<const uint32_t*>(ptr);
+        } else if constexpr (NT_O == 8) {
+          const uint2 u = *reinterpret_cast<const uint2*>(ptr);
+          w[0] = u.x, w[1] = u.y;
+        } else {
+#pragma unroll
+          for (int j4 = 0; j4 < VW / 4; ++j4) {
+            const uint4 u = *reinterpret_cast<const uint4*>(ptr + 16 * j4);
+            w[4 * j4] = u.x, w[4 * j4 + 1] = u.y, w[4 * j4 + 2] = u.z, w[4 * j4 + 3] = u.w;
+          }
+        }
+      };
+      ld(vrow, va);
+      ld(vrow + HD, vb);
+      ld(vrow + 8 * HD, vc);
+      ld(vrow + 9 * HD, vd);
+      float dz[4];  // rows 8..15 when unused: stay zero (0 * finite)
+      dz[2] = dz[3] = 0.f;
+#pragma unroll
+      for (int w = 0; w < VW; ++w) {
+        const uint32_t xa = va[w] ^ 0x80808080u, xb = vb[w] ^ 0x80808080u;
+        const uint32_t xc = vc[w] ^ 0x80808080u, xd = vd[w] ^ 0x80808080u;
+#pragma unroll
+        for (int hw = 0; hw < 2; ++hw) {  // byte pairs (0,1) and (2,3) of the word
+          if (4 * w + 2 * hw >= NT_O) break;
+          const uint32_t tab = __byte_perm(xa, xb, hw ? 0x7362 : 0x5140);  // (A_i, B_i, A_i+1, B_i+1)
+          const uint32_t tcd = __byte_perm(xc, xd, hw ? 0x7362 : 0x5140);
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const int i = 4 * w + 2 * hw + e;
+            const uint32_t b0 = bias_pair(tab, e ? 0x4342 : 0x4140);
+            const uint32_t b1 = bias_pair(tcd, e ? 0x4342 : 0x4140);
+            if constexpr (GP16) {
+              mma16816(o_acc[i], pa[0], pa[1], pa[2], pa[3], b0, b1);
+            } else {
+              dz[0] = o_acc[i][0], dz[1] = o_acc[i][1];
+              mma16816(dz, pa[0], 0u, pa[2], 0u, b0, b1);
+              o_acc[i][0] = dz[0], o_acc[i][1] = dz[1];
+            }
+          }
+        }
+      }
+    }
+  }
+
+  if constexpr (BULK) {
+    if (dead && lane == 0 && P.status) atomicOr(P.status, 1);
+  }
+
+  // ---- merge the warps' states through shared memory (aliases the stage ring: all copies have landed)
+  __syncthreads();
+  float* mg_o = reinterpret_cast<float*>(smem);                    // [NWARP][ROWS][HD]
+  float* mg_m = mg_o + NWARP * ROWS * HD;                          // [NWARP][ROWS]
+  float* mg_l = mg_m + NWARP * ROWS;
+#pragma unroll
+  for (int hr = 0; hr < (GP16 ? 2 : 1); ++hr) {
+    float l = l_run[hr];
+    l += __shfl_xor_sync(0xffffffffu, l, 1);
+    l += __shfl_xor_sync(0xffffffffu, l, 2);
+    const int row = r + 8 * hr;
+    if (c == 0) {
+      mg_m[warp * ROWS + row] = m_run[hr];
+      mg_l[warp * ROWS + row] = l;
+    }
+    float* orow = mg_o + (warp * ROWS + row) * HD;
+#pragma unroll
+    for (int i = 0; i < NT_O; ++i) {
+      orow[(2 * c) * (HD / 8) + i] = o_acc[i][2 * hr];
+      orow[(2 * c + 1) * (HD / 8) + i] = o_acc[i][2 * hr + 1];
+    }
+  }
+  __syncthreads();
+
+  constexpr int EPL = (HD + 31) / 32;
+  for (int row = warp; row < G; row += NWARP) {
+    float mw[NWARP], mx = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < NWARP; ++w) {
+      mw[w] = mg_m[w * ROWS + row];
+      mx = fmaxf(mx, mw[w]);
+    }
+    float lsum = 0.f, z[EPL];
+#pragma unroll
+    for (int i = 0; i < EPL; ++i) z[i] = 0.f;
+#pragma unroll
+    for (int w = 0; w < NWARP; ++w) {
+      const float wt = (mw[w] == -INFINITY) ? 0.f : ex2(mw[w] - mx);
+      lsum += wt * mg_l[w * ROWS + row];
+#pragma unroll
+      for (int i = 0; i < EPL; ++i) {
+        const int d = lane + 32 * i;
+        if (HD >= 32 || d < HD) z[i] += wt * mg_o[(w * ROWS + row) * HD + d];
+      }
+    }
+    if (P.splits == 1) {
+      const float inv = 1.0f / lsum;
+#pragma unroll
+      for (int i = 0; i < EPL; ++i) z[i] *= inv;
+      finalize_row<QT, HD>(z, lane, b, h * G + row, h, P);
+    } else {
+      const int64_t wrow = ((int64_t)bk * P.splits + sid) * G + row;
+      if (lane == 0) {
+        P.ws_m[wrow] = mx;
+        P.ws_l[wrow] = lsum;
+      }
+#pragma unroll
+      for (int i = 0; i < EPL; ++i) {
+        const int d = lane + 32 * i;
+        if (HD >= 32 || d < HD) P.ws_o[wrow * HD + d] = z[i];
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ combine kernel
+// One CTA per (b, kv head); warp per query head; log-sum-exp merge of the split partials, then the same epilogue.
+template <typename QT, int HD>
+__global__ void __launch_bounds__(NTHREAD) attn_combine_kernel(const __grid_constant__ AttnParams P) {
+  constexpr int EPL = (HD + 31) / 32;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int bk = blockIdx.x, b = bk / P.KH, h = bk % P.KH;
+  for (int row = warp; row < P.G; row += NWARP) {
+    const int64_t base = (int64_t)bk * P.splits * P.G + row;
+    float mx = -INFINITY;
+    for (int s = lane; s < P.splits; s += 32) mx = fmaxf(mx, P.ws_m[base + (int64_t)s * P.G]);
+    mx = warp_max(mx);
+    float lsum = 0.f, z[EPL];
+#pragma unroll
+    for (int i = 0; i < EPL; ++i) z[i] = 0.f;
+    if (mx != -INFINITY) {
+      for (int s = 0; s < P.splits; ++s) {
+        const int64_t wrow = base + (int64_t)s * P.G;
+        const float m = P.ws_m[wrow];
+        if (m == -INFINITY) continue;
+        const float wt = ex2(m - mx);
+        lsum += wt * P.ws_l[wrow];
+#pragma unroll
+        for (int i = 0; i < EPL; ++i) {
+          const int d = lane + 32 * i;
+          if (HD >= 32 || d < HD) z[i] += wt * P.ws_o[wrow * HD + d];
+        }
+      }
+      const float inv = 1.0f / lsum;
+#pragma unroll
+      for (int i = 0; i < EPL; ++i) z[i] *= inv;
+    }
+    finalize_row<QT, HD>(z, lane, b, h * P.G + row, h, P);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ host side
+template <typename QT, int HD>
+static int launch_attn(const AttnParams& P, bool bulk, cudaStream_t st) {
+  using L = StageLayout<HD>;
+  const bool gp16 = P.G > 8;
+  const int rows = gp16 ? 16 : 8;
+  const size_t merge = (size_t)NWARP * rows * (HD + 2) * sizeof(float);
+  size_t smem = (size_t)(bulk ? NSTAGE : 1) * L::BYTES;
+  if (merge > smem) smem = merge;
+  dim3 grid((unsigned)(P.B * P.KH), (unsigned)P.splits);
+#define UV_LAUNCH(GP, BK)                                                                                  \
+  do {                                                                                                     \
+    auto kern = attn_split_kernel<QT, HD, GP, BK>;                                                         \
+    if (smem > 48 * 1024) {                                                                                \
+      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);  \
+      if (e != cudaSuccess) {                                                                              \
+        set_last_cuda_error((int)e);                                                                       \
+        return UV_ERR_CUDA;                                                                                \
+      }                                                                                                    \
+    }                                                                                                      \
+    kern<<<grid, NTHREAD, smem, st>>>(P);                                                                  \
+  } while (0)
+  if (gp16) {
+    if (bulk) UV_LAUNCH(true, true);
+    else UV_LAUNCH(true, false);
+  } else {
+    if (bulk) UV_LAUNCH(false, true);
+    else UV_LAUNCH(false, false);
+  }
+#undef UV_LAUNCH
+  int rc = check_launch();
+  if (rc != UV_OK) return rc;
+  if (P.splits > 1) {
+    attn_combine_kernel<QT, HD><<<(unsigned)(P.B * P.KH), NTHREAD, 0, st>>>(P);
+    rc = check_launch();
+  }
+  return rc;
+}
+
+template <typename QT>
+static int dispatch_hd(const AttnParams& P, int hd, bool bulk, cudaStream_t st) {
+  switch (hd) {
+    case 16: return launch_attn<QT, 16>(P, bulk, st);
+    case 32: return launch_attn<QT, 32>(P, bulk, st);
+    case 64: return launch_attn<QT, 64>(P, bulk, st);
+    case 128: return launch_attn<QT, 128>(P, bulk, st);
+    default: return UV_ERR_SHAPE;
+  }
+}
+
+}  // namespace uv
+
+extern "C" size_t uv_decode_attn_workspace_bytes(int B, int KH, int G, int hd, int num_splits) {
+  if (num_splits <= 1 || B <= 0 || KH <= 0 || G <= 0 || hd <= 0) return 0;
+  return (size_t)B * KH * num_splits * G * (size_t)(hd + 2) * sizeof(float);
+}
+
+extern "C" int uv_default_splits(int n_bk, int ctx, int n_sm) {
+  if (n_bk < 1) n_bk = 1;
+  if (n_sm < 1) n_sm = 148;
+  // enough CTAs for ~4 per SM, each split at least 256 keys (4 tiles) so the pipeline fills
+  int want = (4 * n_sm + n_bk - 1) / n_bk;
+  int cap = ctx / 256;
+  if (cap < 1) cap = 1;
+  if (cap > 64) cap = 64;
+  if (want > cap) want = cap;
+  return want < 1 ? 1 : want;
+}
+
+extern "C" int uv_decode_attn(const uv_attn_args* a, void* stream) {
+  using namespace uv;
+  if (!a) return UV_ERR_ARG;
+  if (a->B == 0) return UV_OK;
+  if (!a->q || !a->k_cache || !a->v_cache || !a->pos || !a->starts || !a->out) return UV_ERR_ARG;
+  if (a->B < 0 || a->H < 1 || a->KH < 1 || a->S < 1 || a->H % a->KH || a->num_splits < 1 || a->window < 0)
+    return UV_ERR_ARG;
+  if (a->kv_dtype != UV_I8) return UV_ERR_DTYPE;
+  if (!a->k_scale || !a->v_scale) return UV_ERR_ARG;
+  if (a->q_dtype != UV_F16 && a->q_dtype != UV_BF16) return UV_ERR_DTYPE;
+  const int G = a->H / a->KH, hd = a->hd;
+  if (G > 16) return UV_ERR_SHAPE;
+  if (hd != 16 && hd != 32 && hd != 64 && hd != 128) return UV_ERR_SHAPE;
+  // q / out: pairs are read as 32-bit words
+  if ((reinterpret_cast<uintptr_t>(a->q) & 3) || (a->sqb & 1) || (a->sqh & 1)) return UV_ERR_ALIGN;
+  // cache rows are read in 16-byte pieces on every path
+  if (!aligned16(a->k_cache) || !aligned16(a->v_cache) || (a->skb | a->skh | a->sks | a->svb | a->svh | a->svs) & 15)
+    return UV_ERR_ALIGN;
+  if ((a->xsa_alpha && !a->v_cur) || (a->gate_w && (!a->gate_x || a->gate_ch < 1))) return UV_ERR_ARG;
+
+  AttnParams P{};
+  P.q = a->q, P.k = static_cast<const int8_t*>(a->k_cache), P.v = static_cast<const int8_t*>(a->v_cache);
+  P.ks = reinterpret_cast<const __half*>(a->k_scale), P.vs = reinterpret_cast<const __half*>(a->v_scale);
+  P.pos = a->pos, P.starts = a->starts, P.out = a->out;
+  P.sqb = a->sqb, P.sqh = a->sqh, P.skb = a->skb, P.skh = a->skh, P.sks = a->sks;
+  P.svb = a->svb, P.svh = a->svh, P.svs = a->svs, P.ssb = a->ssb, P.ssh = a->ssh, P.stb = a->stb, P.sth = a->sth;
+  P.sob = a->sob, P.soh = a->soh;
+  P.B = a->B, P.H = a->H, P.KH = a->KH, P.G = G, P.S = a->S, P.window = a->window, P.ring = a->ring ? 1 : 0;
+  P.splits = a->num_splits;
+  P.scale_log2 = a->scale * LOG2E;
+  P.status = nullptr;
+  P.v_cur = a->v_cur, P.v_cur_stride = a->v_cur_stride, P.xsa_alpha = a->xsa_alpha, P.xsa_eps = a->xsa_eps;
+  P.gate_x = a->gate_x, P.gate_x_stride = a->gate_x_stride, P.gate_w = a->gate_w, P.gate_ch = a->gate_ch;
+  if (P.splits > 1) {
+    const size_t need = uv_decode_attn_workspace_bytes(a->B, a->KH, G, hd, P.splits);
+    if (!a->workspace || a->workspace_bytes < need) return UV_ERR_WORKSPACE;
+    if (!aligned16(a->workspace)) return UV_ERR_ALIGN;
+    const size_t rows = (size_t)a->B * a->KH * P.splits * G;
+    P.ws_o = static_cast<float*>(a->workspace);
+    P.ws_m = P.ws_o + rows * hd;
+    P.ws_l = P.ws_m + rows;
+  }
+  // bulk-copy (TMA) path: tiles must be linear and every piece 16-byte aligned
+  bool bulk = a->sks == hd && a->svs == hd;
+  bulk = bulk && (a->ring ? a->S % TILE == 0 : a->S % 8 == 0);
+  bulk = bulk && aligned16(a->k_scale) && aligned16(a->v_scale) &&
+         ((a->ssb | a->ssh | a->stb | a->sth) & 7) == 0;  // scale rows start on 16-byte boundaries (fp16 elements)
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (a->q_dtype == UV_F16) return dispatch_hd<__half>(P, hd, bulk, st);
+  return dispatch_hd<__nv_bfloat16>(P, hd, bulk, st);
+}
