@@ -103,6 +103,11 @@ typedef struct uv_attn_args {
   int num_splits;         /* >= 1; > 1 needs workspace */
   void* workspace;        /* uv_decode_attn_workspace_bytes() bytes, 16-byte aligned */
   size_t workspace_bytes;
+  int* counters;          /* optional, B*KH ints, all zero on entry (left zero on exit): when given and num_splits > 1,
+                             the split CTA that arrives last merges the partials (one launch instead of two); two
+                             launches that overlap on the GPU must not share one counters array */
+  int* status;            /* optional device word: bit 0 is set if a bulk copy did not land within 200 ms (the row's
+                             output is then undefined); never cleared by the library */
   /* fused epilogue, all optional */
   const void* v_cur;      /* (B, KH, hd) q_dtype, row stride v_cur_stride elements between (b, h) vectors */
   int64_t v_cur_stride;

@@ -182,8 +182,10 @@ def test_fused_xsa_gate_epilogue(dtype, splits):
     alpha = T(np.tanh(r.standard_normal(H).astype(np.float32) * 0.3))
     out = torch.empty_like(q)
     ws = workspace_for(B, 1, H, hd, splits, DEV)
+    cnt = torch.zeros(B, dtype=torch.int32, device=DEV)  # last-arriving split merges in the same launch
     attn_launch(q, kq, vq, T(c["pos"]), T(c["starts"]), c["scale"], 0, False, ks, vs, splits, out, ws,
-                v_cur=v_cur, xsa_alpha=alpha, xsa_eps=1e-4, gate_x=xn, gate_w=gate_w)
+                v_cur=v_cur, xsa_alpha=alpha, xsa_eps=1e-4, gate_x=xn, gate_w=gate_w, counters=cnt)
+    assert int(cnt.abs().sum()) == 0  # counters are left zeroed for the next launch
     f = lambda t: t.float().cpu().numpy()
     z = oattn.decode_attention_ref(f(q), f(kq).astype(np.int8), f(vq).astype(np.int8), c["pos"], c["starts"],
                                    c["scale"], k_scale=ks.cpu().numpy(), v_scale=vs.cpu().numpy())

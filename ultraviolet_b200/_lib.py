@@ -35,7 +35,7 @@ class AttnArgs(C.Structure):
         ("out", C.c_void_p), ("sob", C.c_int64), ("soh", C.c_int64),
         ("B", C.c_int), ("H", C.c_int), ("KH", C.c_int), ("hd", C.c_int), ("S", C.c_int),
         ("window", C.c_int), ("ring", C.c_int), ("scale", C.c_float), ("num_splits", C.c_int),
-        ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("counters", C.c_void_p), ("status", C.c_void_p),
         ("v_cur", C.c_void_p), ("v_cur_stride", C.c_int64), ("xsa_alpha", C.c_void_p), ("xsa_eps", C.c_float),
         ("gate_x", C.c_void_p), ("gate_x_stride", C.c_int64), ("gate_w", C.c_void_p), ("gate_ch", C.c_int),
     ]

@@ -1,33 +1,40 @@
 // Split-K single-query (flash-decode) attention over the slot-indexed int8 KV cache, sm_100a.
 //
 // Work decomposition: one CTA per (cache row b, kv head h, split).  The row's valid positions [lo, hi] are cut into
-// 64-key tiles aligned to multiples of 64 in position space; a split owns a contiguous run of tiles.  Tiles stream
-// HBM -> shared memory through the bulk-copy (TMA) engine into a 4-stage ring (cp.async.bulk + mbarrier
+// 128-key tiles aligned to multiples of 128 in position space; a split owns a contiguous run of tiles.  Tiles
+// stream HBM -> shared memory through the bulk-copy (TMA) engine into a 3-stage ring (cp.async.bulk + mbarrier
 // complete_tx), K / V / both scale vectors as four linear copies per tile, trimmed to the row's valid range at
 // 8-key granularity.  Caches whose geometry breaks the 16-byte rules of the bulk engine (row length not a multiple
-// of 8 slots, ring length not a multiple of 64, unaligned views) take a plain-load path with the same shared
+// of 8 slots, ring length not a multiple of 128, unaligned views) take a plain-load path with the same shared
 // memory layout.
 //
-// Math: the G query heads of a kv group form the M rows of warp-level tensor-core tiles (mma.sync.m16n8k16, fp16
-// inputs, fp32 accumulate; G <= 8 leaves rows 8..15 zero, G <= 16 uses them).  S = Q K^T has keys as the N
-// dimension, so its accumulators are already the A fragment of P for O += P V: no transposition of P.  int8 K and
-// V are dequantised in registers (xor 0x80 + byte permute into the mantissa of 1024.0, minus 1152), V through a
-// 4x4 byte transpose that rides on the same permutes.  The per-key K scale multiplies the S columns, the V scale is
-// folded into P.  Head dims are consumed in a permuted order that Q shares (dot products are order free) so every
-// lane reads contiguous 16-byte pieces of a key row.
+// Math: the G query heads of a kv group form the M rows of warp-level tensor-core tiles.
+//   S = Q K^T runs on the int8 pipe (mma.sync.m16n8k32.s8): each query head is split once per CTA into two int8
+//   parts (q ~= s1*q1 + s1/254*q2, error <= max|q|/64516) so the cache bytes are the B operand as they are -- no
+//   dequantisation of K at all.  With G <= 8 the two parts share one MMA (rows 0..7 / 8..15).
+//   O += P V runs on the fp16 pipe (mma.sync.m16n8k16): keys are the N dimension of S, so the score accumulators
+//   are already the A fragment of P; int8 V is dequantised in registers (xor 0x80 + byte permute into the mantissa
+//   of 1024.0, minus 1152) through a 4x4 byte transpose that rides on the same permutes.
+// The per-key K scale multiplies the S columns, the V scale is folded into P.  Head dims are consumed in a permuted
+// order that Q shares (dot products are order free) so every lane reads contiguous 16-byte pieces of a key row.
 //
-// Each of the 4 warps owns 16 keys of every tile with its own online-softmax state; states are merged through
-// shared memory with log-sum-exp weights, and splits > 1 are merged by a second small kernel.
+// Each of the 4 warps owns 32 keys of every tile with its own online-softmax state (the accumulator is rescaled
+// only when a row maximum moves); tiles fully inside [lo, hi] take a mask-free path.  Warp states are merged
+// through shared memory with log-sum-exp weights, and splits > 1 are merged by a second small kernel.
+#include <type_traits>
+
 #include "common.cuh"
 
 namespace uv {
 
-constexpr int TILE = 64;
-constexpr int NSTAGE = 4;
+constexpr int TILE = 128;   // keys per pipeline stage
+constexpr int NSTAGE = 3;
 constexpr int NWARP = 4;
 constexpr int NTHREAD = NWARP * 32;
+constexpr int WKEYS = TILE / NWARP;  // keys one warp consumes per stage
 constexpr unsigned long long WAIT_NS = 200ull * 1000 * 1000;  // a tile that has not landed after 200 ms is abandoned
 constexpr float LOG2E = 1.4426950408889634f;
+constexpr float RESCALE_GAP = 6.0f;  // 2^6 * (largest fp16 scale 65504/127) still fits fp16
 
 struct AttnParams {
   const void* q;
@@ -42,6 +49,7 @@ struct AttnParams {
   float* ws_m;
   float* ws_l;
   int* status;
+  int* counters;  // per (b, kv head) arrival counters for the fused split merge; zero on entry, zero on exit
   int64_t sqb, sqh, skb, skh, sks, svb, svh, svs, ssb, ssh, stb, sth, sob, soh;
   int B, H, KH, G, S, window, ring, splits;
   float scale_log2;
@@ -126,14 +134,6 @@ __device__ __forceinline__ uint32_t bias_pair(uint32_t x, uint32_t sel) {
   return *reinterpret_cast<uint32_t*>(&h);
 }
 
-template <typename QT> __device__ __forceinline__ uint32_t q_pair(const QT* p);
-template <> __device__ __forceinline__ uint32_t q_pair<__half>(const __half* p) {
-  return *reinterpret_cast<const uint32_t*>(p);
-}
-template <> __device__ __forceinline__ uint32_t q_pair<__nv_bfloat16>(const __nv_bfloat16* p) {
-  return pack_h2(__bfloat162float(p[0]), __bfloat162float(p[1]));
-}
-
 // ------------------------------------------------------------------------------------------------ row finalisation
 // One warp holds z (one query head's output, lane owns dims lane + 32*i), applies the optional XSA / head-gate
 // epilogue with the reference's rounding points (Attention.post, ultraviolet/model.py:322-333) and stores it.
@@ -181,6 +181,56 @@ __device__ __forceinline__ void finalize_row(float (&z)[(HD + 31) / 32], int lan
     if (act) o[lane + 32 * i] = from_f32<QT>(z[i]);
 }
 
+// ------------------------------------------------------------------------------------------------ split merge
+// Log-sum-exp merge of the split partials of one (b, kv head): warp per query head, then the shared epilogue.
+// Partials were written by other CTAs: read them through L2 (ld.global.cg).
+template <typename QT, int HD>
+__device__ __forceinline__ void combine_rows(const AttnParams& P, int bk, int warp, int lane) {
+  constexpr int EPL = (HD + 31) / 32;
+  const int b = bk / P.KH, h = bk % P.KH;
+  for (int row = warp; row < P.G; row += NWARP) {
+    const int64_t base = (int64_t)bk * P.splits * P.G + row;
+    float mx = -INFINITY;
+    for (int s = lane; s < P.splits; s += 32) mx = fmaxf(mx, __ldcg(P.ws_m + base + (int64_t)s * P.G));
+    mx = warp_max(mx);
+    float lsum = 0.f, z[EPL];
+#pragma unroll
+    for (int i = 0; i < EPL; ++i) z[i] = 0.f;
+    if (mx != -INFINITY) {
+      for (int s = 0; s < P.splits; ++s) {
+        const int64_t wrow = base + (int64_t)s * P.G;
+        const float m = __ldcg(P.ws_m + wrow);
+        if (m == -INFINITY) continue;
+        const float wt = ex2(m - mx);
+        lsum += wt * __ldcg(P.ws_l + wrow);
+#pragma unroll
+        for (int i = 0; i < EPL; ++i) {
+          const int d = lane + 32 * i;
+          if (HD >= 32 || d < HD) z[i] += wt * __ldcg(P.ws_o + wrow * HD + d);
+        }
+      }
+      const float inv = 1.0f / lsum;
+#pragma unroll
+      for (int i = 0; i < EPL; ++i) z[i] *= inv;
+    }
+    finalize_row<QT, HD>(z, lane, b, h * P.G + row, h, P);
+  }
+}
+
+// Called by every CTA of a split launch after its partials are written: the CTA that arrives last merges.
+template <typename QT, int HD>
+__device__ __forceinline__ void arrive_and_merge(const AttnParams& P, int bk, int tid) {
+  __shared__ int s_last;
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) s_last = atomicAdd(P.counters + bk, 1) == P.splits - 1;
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  combine_rows<QT, HD>(P, bk, tid >> 5, tid & 31);
+  if (tid == 0) P.counters[bk] = 0;
+}
+
 // ------------------------------------------------------------------------------------------------ split kernel
 template <int HD> struct StageLayout {
   static constexpr int K_OFF = 0;
@@ -190,13 +240,53 @@ template <int HD> struct StageLayout {
   static constexpr int BYTES = 2 * TILE * HD + 4 * TILE;
 };
 
+// Two-part symmetric int8 split of one query head slice held by a quad: q ~= s1*q1 + (s1/254)*q2 with
+// |error| <= max|q| / 64516, so Q K^T runs on the int8 tensor-core path against the raw cache bytes.
+template <int N>
+__device__ __forceinline__ void split_q(const float (&qv)[N], uint32_t (&w1)[N / 4], uint32_t (&w2)[N / 4],
+                                        float& f1, float& f2, float scale_log2) {
+  float amax = 0.f;
+#pragma unroll
+  for (int i = 0; i < N; ++i) amax = fmaxf(amax, fabsf(qv[i]));
+  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+  const float s1 = amax > 0.f ? amax / 127.0f : 1.0f;
+  const float inv1 = 1.0f / s1, inv2 = 254.0f / s1;
+#pragma unroll
+  for (int w = 0; w < N / 4; ++w) {
+    uint32_t p1 = 0u, p2 = 0u;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float x = qv[4 * w + i];
+      const float a = fminf(fmaxf(rintf(x * inv1), -127.f), 127.f);
+      const float b = fminf(fmaxf(rintf((x - a * s1) * inv2), -127.f), 127.f);
+      p1 |= ((uint32_t)(__float2int_rn(a) & 0xff)) << (8 * i);
+      p2 |= ((uint32_t)(__float2int_rn(b) & 0xff)) << (8 * i);
+    }
+    w1[w] = p1, w2[w] = p2;
+  }
+  f1 = s1 * scale_log2;
+  f2 = s1 * (1.0f / 254.0f) * scale_log2;
+}
+
+__device__ __forceinline__ void imma16832(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                          uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
 template <typename QT, int HD, bool GP16, bool BULK>
 __global__ void __launch_bounds__(NTHREAD) attn_split_kernel(const __grid_constant__ AttnParams P) {
   using L = StageLayout<HD>;
-  constexpr int KSTEPS = HD / 16;  // k16 steps of Q K^T = 32-bit words of a key row per lane
-  constexpr int NT_O = HD / 8;     // n8 tiles of O = bytes of a value row per lane
+  constexpr int QN = HD / 4;         // query dims per lane = bytes of a key row per lane
+  constexpr int QW = HD / 16;        // 32-bit words of a key row per lane
+  constexpr int ISTEPS = (QW + 1) / 2;  // k32 int8 MMA steps of Q K^T
+  constexpr int NT_S = WKEYS / 8;    // n8 score tiles per warp per stage
+  constexpr int NT_O = HD / 8;       // n8 tiles of O = bytes of a value row per lane
   constexpr int ROWS = GP16 ? 16 : 8;
-  constexpr int NST = BULK ? NSTAGE : 1;
+  constexpr int NH = GP16 ? 2 : 1;   // row halves (heads r and r + 8)
   extern __shared__ __align__(128) unsigned char smem[];
   __shared__ __align__(8) uint64_t bars[NSTAGE];
 
@@ -232,37 +322,35 @@ __global__ void __launch_bounds__(NTHREAD) attn_split_kernel(const __grid_consta
         QT* o = static_cast<QT*>(P.out) + (int64_t)b * P.sob + (int64_t)(h * G + i / HD) * P.soh;
         o[i % HD] = from_f32<QT>(0.f);
       }
-    } else if (tid < G) {
-      const int64_t row = ((int64_t)bk * P.splits + sid) * G + tid;
-      P.ws_m[row] = -INFINITY;
-      P.ws_l[row] = 0.f;
+    } else {
+      if (tid < G) {
+        const int64_t row = ((int64_t)bk * P.splits + sid) * G + tid;
+        P.ws_m[row] = -INFINITY;
+        P.ws_l[row] = 0.f;
+      }
+      if (P.counters) arrive_and_merge<QT, HD>(P, bk, tid);
     }
     return;
   }
 
-  // ---- Q fragments (A operand of Q K^T): lane (r, c) holds head r (and r + 8), dims c*HD/4 + 4j + {0..3}
-  uint32_t qa[KSTEPS][GP16 ? 4 : 2];
-  {
-    const QT* qb = static_cast<const QT*>(P.q) + (int64_t)b * P.sqb + (int64_t)(h * G) * P.sqh + c * (HD / 4);
+  // ---- Q: lane (r, c) owns dims [c*HD/4, (c+1)*HD/4) of head r (and r + 8), split into two int8 parts.
+  //      G <= 8: rows 0..7 of the A operand carry part 1 and rows 8..15 part 2 of the same head.
+  uint32_t q1w[NH][QW], q2w[NH][QW];
+  float f1[NH], f2[NH];
 #pragma unroll
-    for (int j = 0; j < KSTEPS; ++j) {
-      if (r < G) {
-        const QT* q0 = qb + (int64_t)r * P.sqh + 4 * j;
-        qa[j][0] = q_pair<QT>(q0);
-        qa[j][1] = q_pair<QT>(q0 + 2);
+  for (int hr = 0; hr < NH; ++hr) {
+    float qv[QN];
+    const int head = r + 8 * hr;
+    const QT* qb = static_cast<const QT*>(P.q) + (int64_t)b * P.sqb + (int64_t)(h * G + head) * P.sqh + c * QN;
+#pragma unroll
+    for (int i = 0; i < QN; i += 2) {
+      if (head < G) {
+        qv[i] = to_f32<QT>(qb[i]), qv[i + 1] = to_f32<QT>(qb[i + 1]);
       } else {
-        qa[j][0] = qa[j][1] = 0u;
-      }
-      if constexpr (GP16) {
-        if (r + 8 < G) {
-          const QT* q1 = qb + (int64_t)(r + 8) * P.sqh + 4 * j;
-          qa[j][2] = q_pair<QT>(q1);
-          qa[j][3] = q_pair<QT>(q1 + 2);
-        } else {
-          qa[j][2] = qa[j][3] = 0u;
-        }
+        qv[i] = qv[i + 1] = 0.f;
       }
     }
+    split_q<QN>(qv, q1w[hr], q2w[hr], f1[hr], f2[hr], P.scale_log2);
   }
 
   const int8_t* kbase = P.k + (int64_t)b * P.skb + (int64_t)h * P.skh;
@@ -323,17 +411,166 @@ __global__ void __launch_bounds__(NTHREAD) attn_split_kernel(const __grid_consta
   };
 
   // ---- per-warp online softmax state
-  float o_acc[NT_O][GP16 ? 4 : 2];
+  float o_acc[NT_O][4];  // full m16n8 accumulator quads (rows 8..15 stay zero when G <= 8): no register shuffling
 #pragma unroll
-  for (int i = 0; i < NT_O; ++i)
+  for (int i = 0; i < NT_O; ++i) o_acc[i][0] = o_acc[i][1] = o_acc[i][2] = o_acc[i][3] = 0.f;
+  float m_run[NH], l_run[NH];
 #pragma unroll
-    for (int j = 0; j < (GP16 ? 4 : 2); ++j) o_acc[i][j] = 0.f;
-  float m_run[GP16 ? 2 : 1], l_run[GP16 ? 2 : 1];
-#pragma unroll
-  for (int j = 0; j < (GP16 ? 2 : 1); ++j) {
+  for (int j = 0; j < NH; ++j) {
     m_run[j] = -INFINITY;
     l_run[j] = 0.f;
   }
+
+  // one warp's WKEYS keys of one stage.  EDGE: some keys fall outside [lo, hi] (first / last tile of the row).
+  auto block = [&](const unsigned char* st, int lo_rel, int hi_rel, auto edge_tag) {
+    constexpr bool EDGE = decltype(edge_tag)::value;
+    const int k0 = WKEYS * warp;
+    // ---- S = Q K^T on the int8 pipe
+    int acc1[NT_S][4], acc2[GP16 ? NT_S : 1][4];
+#pragma unroll
+    for (int t = 0; t < NT_S; ++t) {
+      acc1[t][0] = acc1[t][1] = acc1[t][2] = acc1[t][3] = 0;
+      if constexpr (GP16) acc2[t][0] = acc2[t][1] = acc2[t][2] = acc2[t][3] = 0;
+      const unsigned char* krow = st + L::K_OFF + (k0 + 8 * t + r) * HD + c * QN;
+      uint32_t kw[QW];
+      if constexpr (QW == 1) {
+        kw[0] = *reinterpret_cast<const uint32_t*>(krow);
+      } else if constexpr (QW == 2) {
+        const uint2 u = *reinterpret_cast<const uint2*>(krow);
+        kw[0] = u.x, kw[1] = u.y;
+      } else {
+#pragma unroll
+        for (int j4 = 0; j4 < QW / 4; ++j4) {
+          const uint4 u = *reinterpret_cast<const uint4*>(krow + 16 * j4);
+          kw[4 * j4] = u.x, kw[4 * j4 + 1] = u.y, kw[4 * j4 + 2] = u.z, kw[4 * j4 + 3] = u.w;
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < ISTEPS; ++j) {
+        const bool two = 2 * j + 1 < QW;
+        const uint32_t b0 = kw[2 * j], b1 = two ? kw[two ? 2 * j + 1 : 0] : 0u;
+        const int j1 = two ? 2 * j + 1 : 0;
+        if constexpr (GP16) {
+          imma16832(acc1[t], q1w[0][2 * j], q1w[1][2 * j], two ? q1w[0][j1] : 0u, two ? q1w[1][j1] : 0u, b0, b1);
+          imma16832(acc2[t], q2w[0][2 * j], q2w[1][2 * j], two ? q2w[0][j1] : 0u, two ? q2w[1][j1] : 0u, b0, b1);
+        } else {
+          imma16832(acc1[t], q1w[0][2 * j], q2w[0][2 * j], two ? q1w[0][j1] : 0u, two ? q2w[0][j1] : 0u, b0, b1);
+        }
+      }
+    }
+    // ---- per-key scales (K: fp32 multipliers of the S columns; V: raw half2, multiplied into P in fp16)
+    float ksf[NT_S][2];
+    uint32_t vsh[NT_S];
+#pragma unroll
+    for (int t = 0; t < NT_S; ++t) {
+      const int kk = 8 * t + 2 * c;
+      const float2 kf = __half22float2(*reinterpret_cast<const __half2*>(st + L::KS_OFF + (k0 + kk) * 2));
+      ksf[t][0] = kf.x, ksf[t][1] = kf.y;
+      vsh[t] = *reinterpret_cast<const uint32_t*>(st + L::VS_OFF + (k0 + kk) * 2);
+      if constexpr (EDGE) {  // keys outside [lo, hi] may sit on bytes no copy has written: zero their V scale
+        const bool ok0 = kk >= lo_rel && kk <= hi_rel, ok1 = kk + 1 >= lo_rel && kk + 1 <= hi_rel;
+        vsh[t] &= (ok0 ? 0x0000ffffu : 0u) | (ok1 ? 0xffff0000u : 0u);
+      }
+    }
+    // ---- online softmax per row half; P (fp16, V scale folded in) becomes the A operand of P V
+    uint32_t pa[WKEYS / 16][4];
+#pragma unroll
+    for (int u = 0; u < WKEYS / 16; ++u) pa[u][0] = pa[u][1] = pa[u][2] = pa[u][3] = 0u;
+#pragma unroll
+    for (int hr = 0; hr < NH; ++hr) {
+      float sc[NT_S][2];
+      float mx = -INFINITY;
+#pragma unroll
+      for (int t = 0; t < NT_S; ++t)
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          float v;
+          if constexpr (GP16)
+            v = (__int2float_rn(acc1[t][2 * hr + e]) * f1[hr] + __int2float_rn(acc2[t][2 * hr + e]) * f2[hr]) *
+                ksf[t][e];
+          else
+            v = (__int2float_rn(acc1[t][e]) * f1[0] + __int2float_rn(acc1[t][2 + e]) * f2[0]) * ksf[t][e];
+          if constexpr (EDGE) {
+            const int kk = 8 * t + 2 * c + e;
+            v = (kk >= lo_rel && kk <= hi_rel) ? v : -INFINITY;
+          }
+          sc[t][e] = v;
+          mx = fmaxf(mx, v);
+        }
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+      // The running maximum is only raised when a row's new maximum beats it by more than RESCALE_GAP (log2
+      // units), so p <= 2^RESCALE_GAP and the accumulator rescale is rare; the final ratio O / l is unaffected.
+      if (__any_sync(0xffffffffu, mx > m_run[hr] + RESCALE_GAP)) {
+        const float m_new = mx > m_run[hr] + RESCALE_GAP ? mx : m_run[hr];
+        const float alpha = ex2(m_run[hr] - m_new);  // 1 for rows that keep their maximum, 0 on the first block
+        l_run[hr] *= alpha;
+#pragma unroll
+        for (int i = 0; i < NT_O; ++i) {
+          o_acc[i][2 * hr] *= alpha;
+          o_acc[i][2 * hr + 1] *= alpha;
+        }
+        m_run[hr] = m_new;
+      }
+      const float m_use = m_run[hr];
+      float ls = 0.f;
+#pragma unroll
+      for (int t = 0; t < NT_S; ++t) {
+        const float p0 = ex2(sc[t][0] - m_use), p1 = ex2(sc[t][1] - m_use);  // masked keys: ex2(-inf) = 0
+        ls += p0 + p1;
+        const __half2 ph = __floats2half2_rn(p0, p1);
+        const __half2 pv = __hmul2(ph, *reinterpret_cast<const __half2*>(&vsh[t]));
+        pa[t / 2][2 * (t & 1) + hr] = *reinterpret_cast<const uint32_t*>(&pv);
+      }
+      l_run[hr] += ls;
+    }
+    // ---- O += P V: lane (r, c) reads HD/8 bytes at dim offset r*HD/8 of keys 2c, 2c+1, 2c+8, 2c+9 of each
+    //      16-key step and transposes them into B fragments (n8 tile i <-> dim r*HD/8 + i)
+#pragma unroll
+    for (int u = 0; u < WKEYS / 16; ++u) {
+      const unsigned char* vrow = st + L::V_OFF + (k0 + 16 * u + 2 * c) * HD + r * (HD / 8);
+      constexpr int VW = (NT_O + 3) / 4;  // 32-bit words per row piece
+      uint32_t va[VW], vb[VW], vc[VW], vd[VW];
+      auto ld = [&](const unsigned char* ptr, uint32_t(&w)[VW]) {
+        if constexpr (NT_O == 2) {
+          w[0] = *reinterpret_cast<const uint16_t*>(ptr);
+        } else if constexpr (NT_O == 4) {
+          w[0] = *reinterpret_cast<const uint32_t*>(ptr);
+        } else if constexpr (NT_O == 8) {
+          const uint2 q2 = *reinterpret_cast<const uint2*>(ptr);
+          w[0] = q2.x, w[1] = q2.y;
+        } else {
+#pragma unroll
+          for (int j4 = 0; j4 < VW / 4; ++j4) {
+            const uint4 q4 = *reinterpret_cast<const uint4*>(ptr + 16 * j4);
+            w[4 * j4] = q4.x, w[4 * j4 + 1] = q4.y, w[4 * j4 + 2] = q4.z, w[4 * j4 + 3] = q4.w;
+          }
+        }
+      };
+      ld(vrow, va);
+      ld(vrow + HD, vb);
+      ld(vrow + 8 * HD, vc);
+      ld(vrow + 9 * HD, vd);
+#pragma unroll
+      for (int w = 0; w < VW; ++w) {
+        const uint32_t xa = va[w] ^ 0x80808080u, xb = vb[w] ^ 0x80808080u;
+        const uint32_t xc = vc[w] ^ 0x80808080u, xd = vd[w] ^ 0x80808080u;
+#pragma unroll
+        for (int hw = 0; hw < 2; ++hw) {  // byte pairs (0,1) and (2,3) of the word
+          if (4 * w + 2 * hw >= NT_O) break;
+          const uint32_t tab = __byte_perm(xa, xb, hw ? 0x7362 : 0x5140);  // (A_i, B_i, A_i+1, B_i+1)
+          const uint32_t tcd = __byte_perm(xc, xd, hw ? 0x7362 : 0x5140);
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const int i = 4 * w + 2 * hw + e;
+            const uint32_t b0 = bias_pair(tab, e ? 0x4342 : 0x4140);
+            const uint32_t b1 = bias_pair(tcd, e ? 0x4342 : 0x4140);
+            mma16816(o_acc[i], pa[u][0], pa[u][1], pa[u][2], pa[u][3], b0, b1);
+          }
+        }
+      }
+    }
+  };
 
   if constexpr (BULK) {
     if (tid == 0) {
@@ -358,136 +595,13 @@ __global__ void __launch_bounds__(NTHREAD) attn_split_kernel(const __grid_consta
       __syncthreads();
     }
     const unsigned char* st = smem + (size_t)s * L::BYTES;
-    const int64_t kb0 = (t0 + it) * TILE + 16 * warp;  // position of this warp's first key
-    if (kb0 + 15 < lo || kb0 > hi) continue;
-    const bool edge = kb0 < lo || kb0 + 15 > hi;
-
-    // ---- S = Q K^T for 16 keys: two n8 tiles
-    float sc[2][4];
-#pragma unroll
-    for (int t = 0; t < 2; ++t) {
-      sc[t][0] = sc[t][1] = sc[t][2] = sc[t][3] = 0.f;
-      const unsigned char* krow = st + L::K_OFF + (16 * warp + 8 * t + r) * HD + c * (HD / 4);
-      uint32_t kw[KSTEPS];
-      if constexpr (KSTEPS == 1) {
-        kw[0] = *reinterpret_cast<const uint32_t*>(krow);
-      } else if constexpr (KSTEPS == 2) {
-        const uint2 u = *reinterpret_cast<const uint2*>(krow);
-        kw[0] = u.x, kw[1] = u.y;
-      } else {
-#pragma unroll
-        for (int j4 = 0; j4 < KSTEPS / 4; ++j4) {
-          const uint4 u = *reinterpret_cast<const uint4*>(krow + 16 * j4);
-          kw[4 * j4] = u.x, kw[4 * j4 + 1] = u.y, kw[4 * j4 + 2] = u.z, kw[4 * j4 + 3] = u.w;
-        }
-      }
-#pragma unroll
-      for (int j = 0; j < KSTEPS; ++j) {
-        const uint32_t x = kw[j] ^ 0x80808080u;
-        const uint32_t b0 = bias_pair(x, 0x4140), b1 = bias_pair(x, 0x4342);
-        if constexpr (GP16) mma16816(sc[t], qa[j][0], qa[j][2], qa[j][1], qa[j][3], b0, b1);
-        else mma16816(sc[t], qa[j][0], 0u, qa[j][1], 0u, b0, b1);
-      }
-    }
-
-    // ---- scales, masks, online softmax
-    float vsc[2][2];
-    bool ok[2][2];
-#pragma unroll
-    for (int t = 0; t < 2; ++t) {
-      const int kk = 16 * warp + 8 * t + 2 * c;
-      const float2 kf = __half22float2(*reinterpret_cast<const __half2*>(st + L::KS_OFF + kk * 2));
-      const float2 vf = __half22float2(*reinterpret_cast<const __half2*>(st + L::VS_OFF + kk * 2));
-      const int64_t tp = kb0 + 8 * t + 2 * c;
-      ok[t][0] = !edge || (tp >= lo && tp <= hi);
-      ok[t][1] = !edge || (tp + 1 >= lo && tp + 1 <= hi);
-      const float k0 = kf.x * P.scale_log2, k1 = kf.y * P.scale_log2;
-      sc[t][0] = ok[t][0] ? sc[t][0] * k0 : -INFINITY;
-      sc[t][1] = ok[t][1] ? sc[t][1] * k1 : -INFINITY;
-      if constexpr (GP16) {
-        sc[t][2] = ok[t][0] ? sc[t][2] * k0 : -INFINITY;
-        sc[t][3] = ok[t][1] ? sc[t][3] * k1 : -INFINITY;
-      }
-      vsc[t][0] = ok[t][0] ? vf.x : 0.f;
-      vsc[t][1] = ok[t][1] ? vf.y : 0.f;
-    }
-    uint32_t pa[4] = {0u, 0u, 0u, 0u};  // A fragment of P (fp16), V scale folded in
-#pragma unroll
-    for (int hr = 0; hr < (GP16 ? 2 : 1); ++hr) {
-      float mx = fmaxf(fmaxf(sc[0][2 * hr], sc[0][2 * hr + 1]), fmaxf(sc[1][2 * hr], sc[1][2 * hr + 1]));
-      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-      const float m_new = fmaxf(m_run[hr], mx);
-      const float alpha = ex2(m_run[hr] - m_new);
-      m_run[hr] = m_new;
-      float pr[2][2];
-#pragma unroll
-      for (int t = 0; t < 2; ++t) {
-        pr[t][0] = ok[t][0] ? ex2(sc[t][2 * hr] - m_new) : 0.f;
-        pr[t][1] = ok[t][1] ? ex2(sc[t][2 * hr + 1] - m_new) : 0.f;
-      }
-      l_run[hr] = l_run[hr] * alpha + (pr[0][0] + pr[0][1]) + (pr[1][0] + pr[1][1]);
-      pa[hr] = pack_h2(pr[0][0] * vsc[0][0], pr[0][1] * vsc[0][1]);
-      pa[2 + hr] = pack_h2(pr[1][0] * vsc[1][0], pr[1][1] * vsc[1][1]);
-#pragma unroll
-      for (int i = 0; i < NT_O; ++i) {
-        o_acc[i][2 * hr] *= alpha;
-        o_acc[i][2 * hr + 1] *= alpha;
-      }
-    }
-
-    // ---- O += P V: lane (r, c) reads HD/8 bytes at dim offset r*HD/8 of keys 2c, 2c+1, 2c+8, 2c+9 and
-    //      transposes them into B fragments (n8 tile i <-> dim r*HD/8 + i)
-    {
-      const unsigned char* vrow = st + L::V_OFF + (16 * warp + 2 * c) * HD + r * (HD / 8);
-      constexpr int VW = (NT_O + 3) / 4;  // 32-bit words per row piece
-      uint32_t va[VW], vb[VW], vc[VW], vd[VW];
-      auto ld = [&](const unsigned char* ptr, uint32_t(&w)[VW]) {
-        if constexpr (NT_O == 2) {
-          w[0] = *reinterpret_cast<const uint16_t*>(ptr);
-        } else if constexpr (NT_O == 4) {
-          w[0] = *reinterpret_cast<const uint32_t*>(ptr);
-        } else if constexpr (NT_O == 8) {
-          const uint2 u = *reinterpret_cast<const uint2*>(ptr);
-          w[0] = u.x, w[1] = u.y;
-        } else {
-#pragma unroll
-          for (int j4 = 0; j4 < VW / 4; ++j4) {
-            const uint4 u = *reinterpret_cast<const uint4*>(ptr + 16 * j4);
-            w[4 * j4] = u.x, w[4 * j4 + 1] = u.y, w[4 * j4 + 2] = u.z, w[4 * j4 + 3] = u.w;
-          }
-        }
-      };
-      ld(vrow, va);
-      ld(vrow + HD, vb);
-      ld(vrow + 8 * HD, vc);
-      ld(vrow + 9 * HD, vd);
-      float dz[4];  // rows 8..15 when unused: stay zero (0 * finite)
-      dz[2] = dz[3] = 0.f;
-#pragma unroll
-      for (int w = 0; w < VW; ++w) {
-        const uint32_t xa = va[w] ^ 0x80808080u, xb = vb[w] ^ 0x80808080u;
-        const uint32_t xc = vc[w] ^ 0x80808080u, xd = vd[w] ^ 0x80808080u;
-#pragma unroll
-        for (int hw = 0; hw < 2; ++hw) {  // byte pairs (0,1) and (2,3) of the word
-          if (4 * w + 2 * hw >= NT_O) break;
-          const uint32_t tab = __byte_perm(xa, xb, hw ? 0x7362 : 0x5140);  // (A_i, B_i, A_i+1, B_i+1)
-          const uint32_t tcd = __byte_perm(xc, xd, hw ? 0x7362 : 0x5140);
-#pragma unroll
-          for (int e = 0; e < 2; ++e) {
-            const int i = 4 * w + 2 * hw + e;
-            const uint32_t b0 = bias_pair(tab, e ? 0x4342 : 0x4140);
-            const uint32_t b1 = bias_pair(tcd, e ? 0x4342 : 0x4140);
-            if constexpr (GP16) {
-              mma16816(o_acc[i], pa[0], pa[1], pa[2], pa[3], b0, b1);
-            } else {
-              dz[0] = o_acc[i][0], dz[1] = o_acc[i][1];
-              mma16816(dz, pa[0], 0u, pa[2], 0u, b0, b1);
-              o_acc[i][0] = dz[0], o_acc[i][1] = dz[1];
-            }
-          }
-        }
-      }
+    const int64_t kb0 = (t0 + it) * TILE + WKEYS * warp;  // position of this warp's first key
+    if (kb0 + WKEYS - 1 < lo || kb0 > hi) continue;
+    if (kb0 < lo || kb0 + WKEYS - 1 > hi) {
+      const int64_t lr = lo - kb0, hr_ = hi - kb0;
+      block(st, lr < 0 ? 0 : (int)lr, hr_ > WKEYS ? WKEYS : (int)hr_, std::true_type{});
+    } else {
+      block(st, 0, WKEYS, std::false_type{});
     }
   }
 
@@ -501,7 +615,7 @@ __global__ void __launch_bounds__(NTHREAD) attn_split_kernel(const __grid_consta
   float* mg_m = mg_o + NWARP * ROWS * HD;                          // [NWARP][ROWS]
   float* mg_l = mg_m + NWARP * ROWS;
 #pragma unroll
-  for (int hr = 0; hr < (GP16 ? 2 : 1); ++hr) {
+  for (int hr = 0; hr < NH; ++hr) {
     float l = l_run[hr];
     l += __shfl_xor_sync(0xffffffffu, l, 1);
     l += __shfl_xor_sync(0xffffffffu, l, 2);
@@ -558,42 +672,12 @@ __global__ void __launch_bounds__(NTHREAD) attn_split_kernel(const __grid_consta
       }
     }
   }
+  if (P.splits > 1 && P.counters) arrive_and_merge<QT, HD>(P, bk, tid);
 }
 
-// ------------------------------------------------------------------------------------------------ combine kernel
-// One CTA per (b, kv head); warp per query head; log-sum-exp merge of the split partials, then the same epilogue.
 template <typename QT, int HD>
 __global__ void __launch_bounds__(NTHREAD) attn_combine_kernel(const __grid_constant__ AttnParams P) {
-  constexpr int EPL = (HD + 31) / 32;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int bk = blockIdx.x, b = bk / P.KH, h = bk % P.KH;
-  for (int row = warp; row < P.G; row += NWARP) {
-    const int64_t base = (int64_t)bk * P.splits * P.G + row;
-    float mx = -INFINITY;
-    for (int s = lane; s < P.splits; s += 32) mx = fmaxf(mx, P.ws_m[base + (int64_t)s * P.G]);
-    mx = warp_max(mx);
-    float lsum = 0.f, z[EPL];
-#pragma unroll
-    for (int i = 0; i < EPL; ++i) z[i] = 0.f;
-    if (mx != -INFINITY) {
-      for (int s = 0; s < P.splits; ++s) {
-        const int64_t wrow = base + (int64_t)s * P.G;
-        const float m = P.ws_m[wrow];
-        if (m == -INFINITY) continue;
-        const float wt = ex2(m - mx);
-        lsum += wt * P.ws_l[wrow];
-#pragma unroll
-        for (int i = 0; i < EPL; ++i) {
-          const int d = lane + 32 * i;
-          if (HD >= 32 || d < HD) z[i] += wt * P.ws_o[wrow * HD + d];
-        }
-      }
-      const float inv = 1.0f / lsum;
-#pragma unroll
-      for (int i = 0; i < EPL; ++i) z[i] *= inv;
-    }
-    finalize_row<QT, HD>(z, lane, b, h * P.G + row, h, P);
-  }
+  combine_rows<QT, HD>(P, blockIdx.x, threadIdx.x >> 5, threadIdx.x & 31);
 }
 
 // ------------------------------------------------------------------------------------------------ host side
@@ -628,7 +712,7 @@ static int launch_attn(const AttnParams& P, bool bulk, cudaStream_t st) {
 #undef UV_LAUNCH
   int rc = check_launch();
   if (rc != UV_OK) return rc;
-  if (P.splits > 1) {
+  if (P.splits > 1 && !P.counters) {
     attn_combine_kernel<QT, HD><<<(unsigned)(P.B * P.KH), NTHREAD, 0, st>>>(P);
     rc = check_launch();
   }
@@ -695,7 +779,8 @@ extern "C" int uv_decode_attn(const uv_attn_args* a, void* stream) {
   P.B = a->B, P.H = a->H, P.KH = a->KH, P.G = G, P.S = a->S, P.window = a->window, P.ring = a->ring ? 1 : 0;
   P.splits = a->num_splits;
   P.scale_log2 = a->scale * LOG2E;
-  P.status = nullptr;
+  P.status = a->status;
+  P.counters = a->num_splits > 1 ? a->counters : nullptr;
   P.v_cur = a->v_cur, P.v_cur_stride = a->v_cur_stride, P.xsa_alpha = a->xsa_alpha, P.xsa_eps = a->xsa_eps;
   P.gate_x = a->gate_x, P.gate_x_stride = a->gate_x_stride, P.gate_w = a->gate_w, P.gate_ch = a->gate_ch;
   if (P.splits > 1) {

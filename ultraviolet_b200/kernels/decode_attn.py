@@ -29,7 +29,8 @@ def default_splits(n_bk: int, ctx: int, device=None, min_chunk: int | None = Non
 def attn_launch(q: Tensor, k_cache: Tensor, v_cache: Tensor, pos: Tensor, starts: Tensor, scale: float, window: int,
                 ring: bool, k_scale: Tensor, v_scale: Tensor, num_splits: int, out: Tensor,
                 workspace: Tensor | None = None, v_cur: Tensor | None = None, xsa_alpha: Tensor | None = None,
-                xsa_eps: float = 1e-4, gate_x: Tensor | None = None, gate_w: Tensor | None = None) -> Tensor:
+                xsa_eps: float = 1e-4, gate_x: Tensor | None = None, gate_w: Tensor | None = None,
+                counters: Tensor | None = None, status: Tensor | None = None) -> Tensor:
     """Raw launch: fills uv_attn_args from tensor metadata.  q / out (B, H, hd) with unit inner stride."""
     B, H, hd = q.shape
     KH, S = k_cache.shape[1], k_cache.shape[2]
@@ -46,6 +47,12 @@ def attn_launch(q: Tensor, k_cache: Tensor, v_cache: Tensor, pos: Tensor, starts
     a.window, a.ring, a.scale, a.num_splits = int(window), int(bool(ring)), float(scale), int(num_splits)
     if num_splits > 1:
         a.workspace, a.workspace_bytes = workspace.data_ptr(), workspace.numel() * workspace.element_size()
+        if counters is not None:
+            if counters.numel() < B * KH or counters.dtype != torch.int32:
+                raise ValueError("counters must hold B*KH int32 zeros")
+            a.counters = counters.data_ptr()
+    if status is not None:
+        a.status = status.data_ptr()
     if xsa_alpha is not None:
         a.v_cur, a.v_cur_stride = v_cur.data_ptr(), v_cur.stride(-2)
         a.xsa_alpha, a.xsa_eps = xsa_alpha.data_ptr(), float(xsa_eps)
