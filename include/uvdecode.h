@@ -95,6 +95,8 @@ typedef struct uv_attn_args {
   int64_t ssb, ssh, stb, sth;
   const int64_t* pos;     /* (B,) position of the newest key (already in the cache) */
   const int64_t* starts;  /* (B,) first valid position */
+  const int64_t* row_map; /* optional (B,): cache row read by batch entry b (default b); lets a sub-batch address
+                             rows of a larger cache, as prefill(rows=...) does (fast_decode.py:70-114) */
   void* out;              /* (B, H, hd) in q_dtype */
   int64_t sob, soh;
   int B, H, KH, hd, S;
@@ -109,8 +111,8 @@ typedef struct uv_attn_args {
   int* status;            /* optional device word: bit 0 is set if a bulk copy did not land within 200 ms (the row's
                              output is then undefined); never cleared by the library */
   /* fused epilogue, all optional */
-  const void* v_cur;      /* (B, KH, hd) q_dtype, row stride v_cur_stride elements between (b, h) vectors */
-  int64_t v_cur_stride;
+  const void* v_cur;      /* (B, KH, hd) q_dtype with batch / head strides v_cur_sb / v_cur_sh (elements) */
+  int64_t v_cur_sb, v_cur_sh;
   const float* xsa_alpha; /* (H,) fp32, already tanh'ed (Attention.fuse, model.py:298-299) */
   float xsa_eps;
   const void* gate_x;     /* (B, >= gate_ch) q_dtype, row stride gate_x_stride */
@@ -124,6 +126,82 @@ size_t uv_decode_attn_workspace_bytes(int B, int KH, int G, int hd, int num_spli
  * decode_attn.py:121-129, retuned for 148-SM parts with 64-key TMA tiles). */
 int uv_default_splits(int n_bk, int ctx, int n_sm);
 int uv_decode_attn(const uv_attn_args* args, void* stream);
+
+/* ---------------------------------------------------------------------------------------------------------------
+ * (d) Row-wise fused kernels of one decode step (the elementwise chain of decode_step_fast, ultraviolet/kernels/
+ * fast_decode.py:272-334, between its GEMMs).  dtype = UV_F16 | UV_BF16 activations; every result is rounded to
+ * dtype where the reference's half-precision torch ops round.
+ *
+ * uv_embed_norm: x = rms_norm(embed[tok]); xn = rms_norm(x)            (fast_decode.py:284, :303)
+ * uv_qkv_post:   in place on the packed QKV GEMM output qkv (B, (H+2K)*hd): value-embedding gate
+ *                v += 2*sigmoid(xn[:, :ve_ch] . ve_gate) * value_embed[tok] (when ve_gate != NULL), per-head RMS norm
+ *                of q and k, partial RoPE with angles pos * inv_freq (when inv_freq != NULL; pairs j <-> j + n_pairs),
+ *                then K and V quantised and appended to the int8 cache at slot pos (ring: pos % S) when k_cache !=
+ *                NULL (Attention.qkv, ultraviolet/model.py:302-320; kv_write, kv_quant.py:26-36); row_map as in
+ *                uv_attn_args (cache row of batch entry b)
+ * uv_resid_norm: h = lambdas[0]*x + lambdas[1]*a; hn = rms_norm(h)     (Block.finish, model.py:567-571)
+ * uv_swiglu:     act = silu(gu[:, :f]) * gu[:, f:]                     (MLP.forward, model.py:388-391)
+ */
+int uv_embed_norm(const int64_t* tok, const void* embed, int dtype, int64_t vocab, int d, void* x, void* xn, int B,
+                  void* stream);
+int uv_qkv_post(void* qkv, const void* xn, const int64_t* tok, const void* value_embed, const void* ve_gate,
+                const float* inv_freq, const int64_t* pos, int8_t* k_cache, int8_t* v_cache, uint16_t* k_scale,
+                uint16_t* v_scale, const int64_t* row_map, int* oob_count, int dtype, int64_t vocab, int B, int H, int K,
+                int hd, int d, int S, int ring, int ve_ch, int n_pairs, void* stream);
+int uv_resid_norm(const void* x, const void* a, const float* lambdas, int dtype, int d, void* h, void* hn, int B,
+                  void* stream);
+int uv_swiglu(const void* gu, int dtype, int f, void* act, int B, void* stream);
+
+/* uv_sample: softcap + token draw + behaviour log-prob per row of the LM-head output x (B, V), V % 256 == 0.
+ * Replaces fused_sample (ultraviolet/kernels/fused_sample.py:68-78) and sample + the log-prob gather
+ * (ultraviolet/model.py:1160-1169, :1194-1211).  precapped = 0: x is the raw head output and z = a*sigmoid((x+b)/c)
+ * is applied here; precapped = 1: x already holds logits z (cap_* ignored).  temperature <= 0: argmax (first index
+ * on ties), logp reported at T = 1.  temperature > 0: inverse-CDF draw of softmax(z / T) restricted to the top_p
+ * nucleus (top_p >= 1: none), with one uniform per row taken from u (B,) or, when u == NULL, from Philox4x32-10 with
+ * key = seed and counter = (steps[row], row_keys[row]).  logp = log softmax(z / T)[token] over the FULL vocabulary. */
+int uv_sample(const void* x, int x_dtype, int64_t x_stride, int B, int V, int precapped, float cap_a, float cap_b,
+              float cap_c, float temperature, float top_p, const float* u, uint64_t seed, const int64_t* row_keys,
+              const int64_t* steps, int64_t* tok_out, float* logp_out, void* stream);
+
+/* ---------------------------------------------------------------------------------------------------------------
+ * (a) GPU-resident continuous-batching scheduler.  Replaces the host loops of StreamGen.chunk / _refill / _park
+ * (scripts/rl_stream.py:76-147) and generate_continuous (ultraviolet/model.py:1266-1354): one single-CTA kernel per
+ * decode step, no host round trip.  All arrays are device memory owned by the caller; rings are addressed by
+ * absolute indices modulo their capacity.
+ *
+ * uv_sched_step, run after the sampler of every step: for each slot with a request, either feed the next prompt
+ * token (prefill as decode; the sample is discarded) or append (samp_tok, samp_lp) to the request's output range and
+ * retire it on EOS (eos >= 0), on reaching limit[r] tokens (force_eos: the last allowed token is replaced by EOS,
+ * the "stop length" of synthetic benchmarks) or when the cache row is full (status bit 1).  Retired requests get
+ * out_len[r] and are pushed to fin_ring; free slots then take the next queued requests in slot order (ranks by
+ * block prefix sum) with cur_tok = first prompt token, pos = starts = 0, row_key = key[r], step_ctr = 0,
+ * start_version[r] = ctl[3]; slots left without work are parked at pos 0 with cur_tok = pad.
+ *
+ * uv_sched_enqueue(n): the host has copied prompt_len / limit / key of n new requests to ring entries
+ * [tail, tail+n) and their tokens back to back at absolute token offset ctl[7]; the kernel assigns prompt_off and
+ * out_off by prefix sum (each request owns limit[r] output slots), clears out_len and publishes tail += n.
+ *
+ * ctl (int64[16]): [0] head  [1] tail  [2] finished count  [3] weight version (host-written)  [4] active slots
+ *                  [5] status bits  [6] steps run  [7] prompt-token tail  [8] output-slot tail
+ */
+typedef struct uv_sched_args {
+  int* req; int* fed; int* gen;                 /* per slot (B,) */
+  int64_t* cur_tok; int64_t* pos; int64_t* starts; int64_t* row_key; int64_t* step_ctr;
+  const int64_t* samp_tok; const float* samp_lp; /* sampler output of the step just run (B,) */
+  int64_t* prompt_off; int* prompt_len; int* limit; int64_t* key; int64_t* out_off; int* out_len;
+  int* start_version;                            /* request rings (q_cap,) */
+  const int* tokens;                             /* prompt-token ring (tok_cap,) */
+  int* out_tok; float* out_lp;                   /* output rings (out_cap,) */
+  int* fin_ring;                                 /* (q_cap,) */
+  int64_t* ctl;                                  /* (16,) */
+  int B, q_cap;
+  int64_t tok_cap, out_cap;
+  int eos, pad, force_eos;
+  int64_t max_len;
+} uv_sched_args;
+
+int uv_sched_step(const uv_sched_args* args, void* stream);
+int uv_sched_enqueue(const uv_sched_args* args, int n, void* stream);
 
 #ifdef __cplusplus
 }

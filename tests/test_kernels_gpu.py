@@ -194,3 +194,99 @@ def test_fused_xsa_gate_epilogue(dtype, splits):
     z = z - f(alpha)[None, :, None] * (z * vd).sum(-1, keepdims=True) * vd
     gate = 2.0 / (1.0 + np.exp(-(f(xn)[:, :128] @ f(gate_w).T)))
     _close(out, z * gate[..., None], 2.5e-2 if dtype == torch.bfloat16 else 6e-3)
+
+
+# ------------------------------------------------------------------------------------------------ sampler
+def _sample(x, **kw):
+    """uv_sample through the engine-independent raw binding."""
+    import ctypes as C
+    from ultraviolet_b200 import _lib
+    from ultraviolet_b200.kernels._util import DTYPE_CODE, stream_ptr
+    B, V = x.shape
+    tok = torch.empty(B, dtype=torch.int64, device=DEV)
+    lp = torch.empty(B, dtype=torch.float32, device=DEV)
+    p = lambda t: None if t is None else t.data_ptr()
+    cap = kw.get("cap", (23.0, 5.0, 7.5))
+    rc = _lib.lib().uv_sample(x.data_ptr(), DTYPE_CODE[x.dtype], x.stride(0), B, V, int(kw.get("precapped", False)),
+                              cap[0], cap[1], cap[2], kw.get("T", 1.0), kw.get("top_p", 1.0), p(kw.get("u")),
+                              C.c_uint64(kw.get("seed", 0)), p(kw.get("row_keys")), p(kw.get("steps")),
+                              tok.data_ptr(), lp.data_ptr(), stream_ptr(torch.device(DEV)))
+    _lib.check(rc, "uv_sample")
+    return tok.cpu().numpy(), lp.cpu().numpy()
+
+
+def _cdf64(x, cap, T):
+    a, b, c = cap
+    z = a / (1.0 + np.exp(-(x.astype(np.float64) + b) / c))
+    e = np.exp((z - a) / T)
+    return z, e, np.cumsum(e, -1)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16, torch.float32])
+def test_fused_sample_matches_reference_golden_and_cdf(dtype):
+    g = golden("sampler")
+    x, u, cap, temps = gi.fused_sample_case()
+    xt = T(x, dtype)
+    xr = xt.float().cpu().numpy()
+    for t in temps:
+        tok, lp = _sample(xt, u=T(u), T=t)
+        z, e, cs = _cdf64(xr, cap, t)
+        S = cs[:, -1]
+        target = (1.0 - u.astype(np.float64)) * S
+        lo = np.where(tok > 0, cs[np.arange(len(tok)), np.maximum(tok - 1, 0)], 0.0)
+        hi = cs[np.arange(len(tok)), tok]
+        # the drawn token's CDF interval contains the target up to fp32 summation error (tests/test_perf_fz.py:95-119)
+        assert (target >= lo - 1e-5 * S).all() and (target <= hi + 1e-5 * S).all()
+        ref_lp = (z[np.arange(len(tok)), tok] - cap[0]) / t - np.log(S)
+        np.testing.assert_allclose(lp, ref_lp, atol=3e-5)
+        if dtype == torch.float16:  # the golden inputs are fp16 values: compare with the reference's own tokens
+            assert (np.abs(tok - g[f"fused.tok.T{t}"]) <= 1).all()
+
+
+def test_greedy_argmax_and_logp():
+    r = np.random.default_rng(3)
+    x = T(r.standard_normal((9, 16384)).astype(np.float32) * 3, torch.bfloat16)
+    x[2, 100] = x[2].max() + 1
+    x[2, 7000] = x[2, 100]          # a tie: the first index wins
+    tok, lp = _sample(x, T=0.0)
+    xr = x.float().cpu().numpy()
+    z, e, cs = _cdf64(xr, (23.0, 5.0, 7.5), 1.0)
+    assert np.array_equal(tok, z.astype(np.float32).argmax(-1)) and tok[2] == 100
+    np.testing.assert_allclose(lp, z[np.arange(9), tok] - 23.0 - np.log(cs[:, -1]), atol=3e-5)
+
+
+def test_sampler_distribution_and_top_p():
+    """Chi-square of 2^16 draws against softmax(z / T) (tests/test_perf_fz.py:122-134) and nucleus support."""
+    from scipy import stats
+    r = np.random.default_rng(4)
+    V, N = 256, 1 << 16
+    row = (r.standard_normal(V) * 2).astype(np.float32)
+    x = T(np.tile(row, (N, 1)))
+    u = torch.rand(N, device=DEV, generator=torch.Generator(DEV).manual_seed(5))
+    tok, _ = _sample(x, u=u, T=0.9, precapped=True)
+    p = np.exp(row.astype(np.float64) / 0.9)
+    p /= p.sum()
+    cnt = np.bincount(tok, minlength=V)
+    keep = p * N >= 5
+    chi = (((cnt - p * N) ** 2 / (p * N))[keep]).sum()
+    assert stats.chi2.sf(chi, keep.sum() - 1) > 1e-3
+    tok, lp = _sample(x, u=u, T=0.9, top_p=0.7, precapped=True)
+    nucleus = om.top_p_keep(row[None], 0.9, 0.7)[0]
+    assert nucleus[np.unique(tok)].all()                       # never outside the reference's nucleus
+    assert set(np.flatnonzero(nucleus & (p > 1e-3))) <= set(np.unique(tok))
+    np.testing.assert_allclose(lp, np.log(p[tok]), atol=3e-5)  # log-prob stays untruncated
+
+
+def test_philox_keyed_draws_match_oracle():
+    from oracle import philox
+    r = np.random.default_rng(6)
+    x = T(r.standard_normal((16, 4096)).astype(np.float32) * 3, torch.bfloat16)
+    keys = torch.arange(100, 116, device=DEV)
+    steps = torch.arange(16, device=DEV) * 3
+    tok, lp = _sample(x, T=1.0, seed=1234567, row_keys=keys, steps=steps)
+    u = np.array([philox.uniform(1234567, 100 + i, 3 * i) for i in range(16)], np.float32)
+    tok_u, lp_u = _sample(x, T=1.0, u=T(u))
+    assert np.array_equal(tok, tok_u) and np.array_equal(lp, lp_u)
+    tok2, _ = _sample(x.flip(0).contiguous(), T=1.0, seed=1234567, row_keys=keys.flip(0).contiguous(),
+                      steps=steps.flip(0).contiguous())
+    assert np.array_equal(tok2[::-1], tok)   # a sequence's draw does not depend on the row it sits in

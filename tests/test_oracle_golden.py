@@ -134,3 +134,15 @@ def test_samplers():
     p = np.exp(z - z.max(-1, keepdims=True))
     p /= p.sum(-1, keepdims=True)
     assert not (keep & ~seen & (p > 5e-3)).any()  # and draws every nucleus token that is not vanishingly rare
+
+
+def test_philox_known_answers():
+    # Random123 known-answer vectors for philox4x32-10
+    from oracle import philox
+    kat = [((0, 0, 0, 0), (0, 0), (0x6627e8d5, 0xe169c58d, 0xbc57ac4c, 0x9b00dbd8)),
+           ((0xffffffff,) * 4, (0xffffffff, 0xffffffff), (0x408f276d, 0x41c83b0e, 0xa20bc7c6, 0x6d5451fd)),
+           ((0x243f6a88, 0x85a308d3, 0x13198a2e, 0x03707344), (0xa4093822, 0x299f31d0),
+            (0xd16cfe09, 0x94fdcceb, 0x5001e420, 0x24126ea1))]
+    for ctr, key, out in kat:
+        assert tuple(int(x) for x in philox.philox4x32_10(ctr, key)) == out
+    assert 0.0 <= float(philox.uniform(7, 3, 11)) < 1.0

@@ -31,14 +31,22 @@ class AttnArgs(C.Structure):
         ("svb", C.c_int64), ("svh", C.c_int64), ("svs", C.c_int64),
         ("k_scale", C.c_void_p), ("v_scale", C.c_void_p),
         ("ssb", C.c_int64), ("ssh", C.c_int64), ("stb", C.c_int64), ("sth", C.c_int64),
-        ("pos", C.c_void_p), ("starts", C.c_void_p),
+        ("pos", C.c_void_p), ("starts", C.c_void_p), ("row_map", C.c_void_p),
         ("out", C.c_void_p), ("sob", C.c_int64), ("soh", C.c_int64),
         ("B", C.c_int), ("H", C.c_int), ("KH", C.c_int), ("hd", C.c_int), ("S", C.c_int),
         ("window", C.c_int), ("ring", C.c_int), ("scale", C.c_float), ("num_splits", C.c_int),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("counters", C.c_void_p), ("status", C.c_void_p),
-        ("v_cur", C.c_void_p), ("v_cur_stride", C.c_int64), ("xsa_alpha", C.c_void_p), ("xsa_eps", C.c_float),
+        ("v_cur", C.c_void_p), ("v_cur_sb", C.c_int64), ("v_cur_sh", C.c_int64), ("xsa_alpha", C.c_void_p), ("xsa_eps", C.c_float),
         ("gate_x", C.c_void_p), ("gate_x_stride", C.c_int64), ("gate_w", C.c_void_p), ("gate_ch", C.c_int),
     ]
+
+
+class SchedArgs(C.Structure):
+    _fields_ = [(n, C.c_void_p) for n in (
+        "req", "fed", "gen", "cur_tok", "pos", "starts", "row_key", "step_ctr", "samp_tok", "samp_lp", "prompt_off",
+        "prompt_len", "limit", "key", "out_off", "out_len", "start_version", "tokens", "out_tok", "out_lp",
+        "fin_ring", "ctl")] + [("B", C.c_int), ("q_cap", C.c_int), ("tok_cap", C.c_int64), ("out_cap", C.c_int64),
+                               ("eos", C.c_int), ("pad", C.c_int), ("force_eos", C.c_int), ("max_len", C.c_int64)]
 
 
 # name -> (restype, argtypes); every symbol include/uvdecode.h declares
@@ -54,6 +62,17 @@ SIGNATURES = {
     "uv_decode_attn_workspace_bytes": (C.c_size_t, [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int]),
     "uv_default_splits": (C.c_int, [C.c_int, C.c_int, C.c_int]),
     "uv_decode_attn": (C.c_int, [C.POINTER(AttnArgs), C.c_void_p]),
+    "uv_embed_norm": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int64, C.c_int, C.c_void_p, C.c_void_p, C.c_int,
+                                C.c_void_p]),
+    "uv_qkv_post": (C.c_int, [C.c_void_p] * 13 + [C.c_int, C.c_int64] + [C.c_int] * 9 + [C.c_void_p]),
+    "uv_resid_norm": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_int,
+                                C.c_void_p]),
+    "uv_swiglu": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_int, C.c_void_p]),
+    "uv_sched_step": (C.c_int, [C.POINTER(SchedArgs), C.c_void_p]),
+    "uv_sched_enqueue": (C.c_int, [C.POINTER(SchedArgs), C.c_int, C.c_void_p]),
+    "uv_sample": (C.c_int, [C.c_void_p, C.c_int, C.c_int64, C.c_int, C.c_int, C.c_int, C.c_float, C.c_float,
+                            C.c_float, C.c_float, C.c_float, C.c_void_p, C.c_uint64, C.c_void_p, C.c_void_p,
+                            C.c_void_p, C.c_void_p, C.c_void_p]),
 }
 
 

@@ -44,6 +44,7 @@ struct AttnParams {
   const __half* vs;
   const int64_t* pos;
   const int64_t* starts;
+  const int64_t* row_map;  // optional: cache row of batch entry b (q / out / pos / starts stay batch-indexed)
   void* out;
   float* ws_o;
   float* ws_m;
@@ -55,7 +56,7 @@ struct AttnParams {
   float scale_log2;
   // fused epilogue
   const void* v_cur;
-  int64_t v_cur_stride;
+  int64_t v_cur_sb, v_cur_sh;
   const float* xsa_alpha;
   float xsa_eps;
   const void* gate_x;
@@ -145,7 +146,7 @@ __device__ __forceinline__ void finalize_row(float (&z)[(HD + 31) / 32], int lan
 #pragma unroll
   for (int i = 0; i < EPL; ++i) z[i] = rnd<QT>(z[i]);  // the attention output itself is in the activation dtype
   if (P.xsa_alpha != nullptr) {
-    const QT* vc = static_cast<const QT*>(P.v_cur) + ((int64_t)b * P.KH + kvh) * P.v_cur_stride;
+    const QT* vc = static_cast<const QT*>(P.v_cur) + (int64_t)b * P.v_cur_sb + (int64_t)kvh * P.v_cur_sh;
     float vv[EPL], n2 = 0.f;
 #pragma unroll
     for (int i = 0; i < EPL; ++i) {
@@ -353,10 +354,11 @@ __global__ void __launch_bounds__(NTHREAD) attn_split_kernel(const __grid_consta
     split_q<QN>(qv, q1w[hr], q2w[hr], f1[hr], f2[hr], P.scale_log2);
   }
 
-  const int8_t* kbase = P.k + (int64_t)b * P.skb + (int64_t)h * P.skh;
-  const int8_t* vbase = P.v + (int64_t)b * P.svb + (int64_t)h * P.svh;
-  const __half* ksbase = P.ks + (int64_t)b * P.ssb + (int64_t)h * P.ssh;
-  const __half* vsbase = P.vs + (int64_t)b * P.stb + (int64_t)h * P.sth;
+  const int64_t cb = P.row_map ? P.row_map[b] : b;  // cache row
+  const int8_t* kbase = P.k + cb * P.skb + (int64_t)h * P.skh;
+  const int8_t* vbase = P.v + cb * P.svb + (int64_t)h * P.svh;
+  const __half* ksbase = P.ks + cb * P.ssb + (int64_t)h * P.ssh;
+  const __half* vsbase = P.vs + cb * P.stb + (int64_t)h * P.sth;
 
   if constexpr (BULK) {
     if (tid == 0) {
@@ -772,7 +774,7 @@ extern "C" int uv_decode_attn(const uv_attn_args* a, void* stream) {
   AttnParams P{};
   P.q = a->q, P.k = static_cast<const int8_t*>(a->k_cache), P.v = static_cast<const int8_t*>(a->v_cache);
   P.ks = reinterpret_cast<const __half*>(a->k_scale), P.vs = reinterpret_cast<const __half*>(a->v_scale);
-  P.pos = a->pos, P.starts = a->starts, P.out = a->out;
+  P.pos = a->pos, P.starts = a->starts, P.row_map = a->row_map, P.out = a->out;
   P.sqb = a->sqb, P.sqh = a->sqh, P.skb = a->skb, P.skh = a->skh, P.sks = a->sks;
   P.svb = a->svb, P.svh = a->svh, P.svs = a->svs, P.ssb = a->ssb, P.ssh = a->ssh, P.stb = a->stb, P.sth = a->sth;
   P.sob = a->sob, P.soh = a->soh;
@@ -781,7 +783,7 @@ extern "C" int uv_decode_attn(const uv_attn_args* a, void* stream) {
   P.scale_log2 = a->scale * LOG2E;
   P.status = a->status;
   P.counters = a->num_splits > 1 ? a->counters : nullptr;
-  P.v_cur = a->v_cur, P.v_cur_stride = a->v_cur_stride, P.xsa_alpha = a->xsa_alpha, P.xsa_eps = a->xsa_eps;
+  P.v_cur = a->v_cur, P.v_cur_sb = a->v_cur_sb, P.v_cur_sh = a->v_cur_sh, P.xsa_alpha = a->xsa_alpha, P.xsa_eps = a->xsa_eps;
   P.gate_x = a->gate_x, P.gate_x_stride = a->gate_x_stride, P.gate_w = a->gate_w, P.gate_ch = a->gate_ch;
   if (P.splits > 1) {
     const size_t need = uv_decode_attn_workspace_bytes(a->B, a->KH, G, hd, P.splits);

@@ -123,6 +123,7 @@ struct QkvPostParams {
   int8_t* v_cache;
   uint16_t* k_scale;
   uint16_t* v_scale;
+  const int64_t* row_map;
   int* oob;
   int64_t vocab;
   int B, H, K, d, S, ring, ve_ch, n_pairs;
@@ -200,7 +201,8 @@ __global__ void __launch_bounds__(128) qkv_post_kernel(const __grid_constant__ Q
       if (lane == 0 && P.oob) atomicAdd(P.oob, 1);
       return;
     }
-    const int64_t dst = ((int64_t)b * P.K + kh) * P.S + p;
+    const int64_t cb = P.row_map ? P.row_map[b] : b;
+    const int64_t dst = (cb * P.K + kh) * P.S + p;
     int8_t* crow = (isv ? P.v_cache : P.k_cache) + dst * HD;
     if (act) {
       if constexpr (E == 4) *reinterpret_cast<char4*>(crow + lane * 4) = make_char4(q8[0], q8[1], q8[2], q8[3]);
@@ -282,9 +284,9 @@ extern "C" int uv_swiglu(const void* gu, int dtype, int f, void* act, int B, voi
 
 extern "C" int uv_qkv_post(void* qkv, const void* xn, const int64_t* tok, const void* value_embed,
                            const void* ve_gate, const float* inv_freq, const int64_t* pos, int8_t* k_cache,
-                           int8_t* v_cache, uint16_t* k_scale, uint16_t* v_scale, int* oob_count, int dtype,
-                           int64_t vocab, int B, int H, int K, int hd, int d, int S, int ring, int ve_ch,
-                           int n_pairs, void* stream) {
+                           int8_t* v_cache, uint16_t* k_scale, uint16_t* v_scale, const int64_t* row_map,
+                           int* oob_count, int dtype, int64_t vocab, int B, int H, int K, int hd, int d, int S,
+                           int ring, int ve_ch, int n_pairs, void* stream) {
   if (B == 0) return UV_OK;
   if (!qkv || !pos || B < 0 || H < 1 || K < 1) return UV_ERR_ARG;
   if (ve_gate && (!xn || !tok || !value_embed || ve_ch < 1)) return UV_ERR_ARG;
@@ -297,7 +299,7 @@ extern "C" int uv_qkv_post(void* qkv, const void* xn, const int64_t* tok, const 
   }
   QkvPostParams P{};
   P.qkv = qkv, P.xn = xn, P.tok = tok, P.value_embed = value_embed, P.ve_gate = ve_gate, P.inv_freq = inv_freq;
-  P.pos = pos, P.k_cache = k_cache, P.v_cache = v_cache, P.k_scale = k_scale, P.v_scale = v_scale, P.oob = oob_count;
+  P.pos = pos, P.k_cache = k_cache, P.v_cache = v_cache, P.k_scale = k_scale, P.v_scale = v_scale, P.row_map = row_map, P.oob = oob_count;
   P.vocab = vocab, P.B = B, P.H = H, P.K = K, P.d = d, P.S = S, P.ring = ring, P.ve_ch = ve_ch, P.n_pairs = n_pairs;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (dtype == UV_F16) return launch_qkv_post<__half>(P, hd, st);

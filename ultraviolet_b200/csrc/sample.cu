@@ -1,0 +1,240 @@
+// Fused softcap + sampling + behaviour log-prob over the raw LM-head output, one CTA per sequence.
+//
+//   z = a * sigmoid((x + b) / c)                      softcap (MathLM.logits, ultraviolet/model.py:824-827)
+//   T <= 0 : token = argmax z (first index on ties)    sample(), ultraviolet/model.py:1197-1198
+//   T  > 0 : e = exp((z - a) / T); token = first index whose running sum of e reaches (1 - u) * sum(e)
+//            (the inverse-CDF draw of fused_sample, ultraviolet/kernels/fused_sample.py:31-58); with top_p < 1 the
+//            draw is restricted to the nucleus of sample() (model.py:1203-1208): tokens whose strictly-larger mass
+//            is below top_p, ties with the cut kept
+//   logp   = (z_tok - a) / T - log(sum e)              untruncated softmax, as the rollout log records it
+//                                                      (model.py:1160-1169); T <= 0 reports it at T = 1
+// u comes from the caller (one uniform per row) or from Philox4x32-10 keyed by (seed; row key, step), so a
+// sequence's random stream depends only on its own key and token index, never on the slot or batch it runs in.
+#include "common.cuh"
+
+namespace uv {
+
+constexpr int SAMPLE_THREADS = 256;
+
+__device__ __forceinline__ void philox_round(uint32_t (&c)[4], uint32_t k0, uint32_t k1) {
+  const uint32_t hi0 = __umulhi(0xD2511F53u, c[0]), lo0 = 0xD2511F53u * c[0];
+  const uint32_t hi1 = __umulhi(0xCD9E8D57u, c[2]), lo1 = 0xCD9E8D57u * c[2];
+  const uint32_t n0 = hi1 ^ c[1] ^ k0, n2 = hi0 ^ c[3] ^ k1;
+  c[0] = n0, c[1] = lo1, c[2] = n2, c[3] = lo0;
+}
+// Philox4x32-10 (Salmon et al., SC'11): counter = (step, row key), key = seed; returns a uniform in [0, 1)
+__device__ __forceinline__ float philox_uniform(uint64_t seed, uint64_t row_key, uint64_t step) {
+  uint32_t c[4] = {(uint32_t)step, (uint32_t)(step >> 32), (uint32_t)row_key, (uint32_t)(row_key >> 32)};
+  uint32_t k0 = (uint32_t)seed, k1 = (uint32_t)(seed >> 32);
+#pragma unroll
+  for (int i = 0; i < 10; ++i) {
+    philox_round(c, k0, k1);
+    k0 += 0x9E3779B9u;
+    k1 += 0xBB67AE85u;
+  }
+  return (float)(c[0] >> 8) * (1.0f / 16777216.0f);
+}
+
+struct SampleParams {
+  const void* x;
+  int64_t x_stride;
+  int B, V;
+  float a, b, c, inv_t, top_p;
+  int greedy;
+  int precapped;  // input rows are already softcapped logits z (sample(), model.py:1194-1211); a = row maximum
+  const float* u;
+  uint64_t seed;
+  const int64_t* row_keys;
+  const int64_t* steps;
+  int64_t* tok;
+  float* logp;
+};
+
+__device__ __forceinline__ float block_sum(float v, float* red, int tid) {
+  v = warp_sum(v);
+  __syncthreads();
+  if ((tid & 31) == 0) red[tid >> 5] = v;
+  __syncthreads();
+  float t = 0.f;
+#pragma unroll
+  for (int w = 0; w < SAMPLE_THREADS / 32; ++w) t += red[w];
+  return t;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(SAMPLE_THREADS) sample_kernel(const __grid_constant__ SampleParams P) {
+  extern __shared__ float e_sm[];  // V + V/CH floats: chunk t of CH values starts at t * (CH + 1) (bank skew)
+  __shared__ float red[SAMPLE_THREADS / 32];
+  __shared__ float red_v[SAMPLE_THREADS / 32];
+  __shared__ int red_i[SAMPLE_THREADS / 32];
+  __shared__ float scan_w[SAMPLE_THREADS / 32];
+  __shared__ int s_tok;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int row = blockIdx.x;
+  const int V = P.V, CH = V / SAMPLE_THREADS;
+  const T* xr = static_cast<const T*>(P.x) + (int64_t)row * P.x_stride;
+  const float inv_c = 1.0f / P.c;
+  float cap_a = P.a;
+  auto zof = [&](int i) {
+    const float x = to_f32<T>(xr[i]);
+    return P.precapped ? x : P.a / (1.0f + expf(-(x + P.b) * inv_c));
+  };
+  if (P.precapped) {  // no analytic bound on z: take the row maximum as the reference point of the exponentials
+    float m = -INFINITY;
+    for (int i = tid; i < V; i += SAMPLE_THREADS) m = fmaxf(m, to_f32<T>(xr[i]));
+    m = warp_max(m);
+    if (lane == 0) red[warp] = m;
+    __syncthreads();
+    m = red[0];
+#pragma unroll
+    for (int w = 1; w < SAMPLE_THREADS / 32; ++w) m = fmaxf(m, red[w]);
+    cap_a = m;
+    __syncthreads();
+  }
+
+  // ---- pass 1: softcap, exp, argmax (coalesced reads; e parked in shared memory)
+  float best = -INFINITY;
+  int best_i = 0x7fffffff;
+  for (int i = tid; i < V; i += SAMPLE_THREADS) {
+    const float z = zof(i);
+    if (z > best) best = z, best_i = i;  // strided ascending per thread: first index wins within a thread
+    e_sm[i + i / CH] = expf((z - cap_a) * P.inv_t);
+  }
+  if (tid == 0) s_tok = V - 1;
+  __syncthreads();
+
+  // ---- per-thread contiguous chunk sums and block scan
+  float* chunk = e_sm + tid * (CH + 1);
+  auto chunk_sum = [&](float cut) {
+    float s = 0.f;
+    for (int j = 0; j < CH; ++j) {
+      const float e = chunk[j];
+      s += e >= cut ? e : 0.f;
+    }
+    return s;
+  };
+  float mine = chunk_sum(0.f);
+  const float S_full = block_sum(mine, red, tid);
+
+  if (P.greedy) {
+    // block argmax with first-index ties
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
+      if (ob > best || (ob == best && oi < best_i)) best = ob, best_i = oi;
+    }
+    if (lane == 0) red_v[warp] = best, red_i[warp] = best_i;
+    __syncthreads();
+    if (tid == 0) {
+      for (int w = 1; w < SAMPLE_THREADS / 32; ++w)
+        if (red_v[w] > best || (red_v[w] == best && red_i[w] < best_i)) best = red_v[w], best_i = red_i[w];
+      P.tok[row] = best_i;
+      P.logp[row] = (best - cap_a) * P.inv_t - logf(S_full);
+    }
+    return;
+  }
+
+  // ---- nucleus: smallest cut (as a float bit pattern) whose strictly-larger mass is below top_p * S
+  float cut = 0.f, S = S_full;
+  if (P.top_p < 1.0f) {
+    const float lim = P.top_p * S_full;
+    uint32_t lo = 0u, hi = 0x3f800001u;  // mass_above(hi) = 0 < lim always (e <= 1)
+    while (hi - lo > 1u) {
+      const uint32_t mid = lo + (hi - lo) / 2u;
+      const float cm = __uint_as_float(mid);
+      float s = 0.f;
+      for (int j = 0; j < CH; ++j) {
+        const float e = chunk[j];
+        s += e > cm ? e : 0.f;
+      }
+      const float above = block_sum(s, red, tid);
+      if (above < lim) hi = mid;
+      else lo = mid;
+    }
+    cut = __uint_as_float(hi);
+    mine = chunk_sum(cut);
+    S = block_sum(mine, red, tid);
+  }
+
+  // ---- inverse CDF: exclusive scan of the chunk sums, then the owning thread walks its chunk
+  float incl = mine;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const float v = __shfl_up_sync(0xffffffffu, incl, o);
+    if (lane >= o) incl += v;
+  }
+  if (lane == 31) scan_w[warp] = incl;
+  __syncthreads();
+  float base = 0.f;
+  for (int w = 0; w < warp; ++w) base += scan_w[w];
+  incl += base;
+  const float excl = incl - mine;
+  float u = P.u ? P.u[row] : philox_uniform(P.seed, (uint64_t)P.row_keys[row], (uint64_t)P.steps[row]);
+  const float target = (1.0f - u) * S;
+  if (excl < target && target <= incl) {
+    float cs = excl;
+    int found = tid * CH + CH - 1;
+    for (int j = 0; j < CH; ++j) {
+      const float e = chunk[j];
+      cs += e >= cut ? e : 0.f;
+      if (cs >= target && e >= cut) {
+        found = tid * CH + j;
+        break;
+      }
+    }
+    atomicMin(&s_tok, found);
+  }
+  __syncthreads();
+  if (tid == 0) {
+    int t = s_tok;
+    if (P.top_p < 1.0f && e_sm[t + t / CH] < cut) {  // rounding left the target past the last kept entry
+      for (t = V - 1; t > 0 && e_sm[t + t / CH] < cut; --t) {}
+    }
+    P.tok[row] = t;
+    P.logp[row] = (zof(t) - cap_a) * P.inv_t - logf(S_full);
+  }
+}
+
+}  // namespace uv
+
+extern "C" int uv_sample(const void* x, int x_dtype, int64_t x_stride, int B, int V, int precapped, float cap_a,
+                         float cap_b, float cap_c, float temperature, float top_p, const float* u, uint64_t seed,
+                         const int64_t* row_keys, const int64_t* steps, int64_t* tok_out, float* logp_out,
+                         void* stream) {
+  using namespace uv;
+  if (B == 0) return UV_OK;
+  if (!x || !tok_out || !logp_out || B < 0) return UV_ERR_ARG;
+  if (V < SAMPLE_THREADS || V % SAMPLE_THREADS || V > 49152) return UV_ERR_SHAPE;
+  const bool greedy = !(temperature > 0.f);
+  if (!greedy && !u && (!row_keys || !steps)) return UV_ERR_ARG;
+  if (!precapped && !(cap_a > 0.f && cap_c > 0.f)) return UV_ERR_ARG;
+  if (!precapped && !greedy && cap_a / temperature > 80.f) return UV_ERR_ARG;  // exp((z - a)/T) leaves fp32 range
+  if (!(top_p > 0.f)) return UV_ERR_ARG;
+  SampleParams P{};
+  P.x = x, P.x_stride = x_stride, P.B = B, P.V = V;
+  P.a = cap_a, P.b = cap_b, P.c = cap_c;
+  P.inv_t = greedy ? 1.0f : 1.0f / temperature;
+  P.top_p = top_p, P.greedy = greedy ? 1 : 0, P.precapped = precapped ? 1 : 0;
+  P.u = u, P.seed = seed, P.row_keys = row_keys, P.steps = steps, P.tok = tok_out, P.logp = logp_out;
+  const size_t smem = (size_t)(V + V / (V / SAMPLE_THREADS) + 1) * sizeof(float);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+#define UV_GO(T)                                                                                              \
+  do {                                                                                                        \
+    if (smem > 48 * 1024) {                                                                                   \
+      cudaError_t e = cudaFuncSetAttribute(sample_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,     \
+                                           (int)smem);                                                        \
+      if (e != cudaSuccess) {                                                                                 \
+        set_last_cuda_error((int)e);                                                                          \
+        return UV_ERR_CUDA;                                                                                   \
+      }                                                                                                       \
+    }                                                                                                         \
+    sample_kernel<T><<<(unsigned)B, SAMPLE_THREADS, smem, st>>>(P);                                           \
+  } while (0)
+  if (x_dtype == UV_F32) UV_GO(float);
+  else if (x_dtype == UV_F16) UV_GO(__half);
+  else if (x_dtype == UV_BF16) UV_GO(__nv_bfloat16);
+  else return UV_ERR_DTYPE;
+#undef UV_GO
+  return check_launch();
+}

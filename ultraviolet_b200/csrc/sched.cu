@@ -1,0 +1,230 @@
+// GPU-resident continuous-batching scheduler: after every decode step one small kernel retires finished
+// sequences (EOS, per-request token limit, cache full), appends the sampled token / log-prob to the request's
+// output range, admits queued requests into the freed slots (free-slot ranks by block prefix sum) and sets each
+// slot's next input token and cache position.  The host never takes part in a step: it appends requests to the
+// device queue and harvests finished ones whenever it likes.
+//
+// It reproduces the per-request output contract of the reference's host schedulers (StreamGen.chunk,
+// scripts/rl_stream.py:103-147; generate_continuous, ultraviolet/model.py:1266-1354): generated tokens up to and
+// including the first EOS, at most `limit` of them (limit = min(max_new, target_len)), one behaviour log-prob per
+// token, the weight version at admission.  A newly admitted request is prefilled by feeding its prompt through the
+// decode step one token per step (sampling output ignored until the last prompt token), starting at position 0.
+//
+// Queue layout (rings addressed by absolute, monotonically increasing indices):
+//   requests  index r -> r % q_cap : prompt_off, prompt_len, limit, key, out_off, out_len, start_version
+//   prompt tokens        absolute offset % tok_cap        (packed back to back; offsets by prefix sum at enqueue)
+//   outputs              absolute offset % out_cap        (each request owns `limit` slots; offsets by prefix sum)
+#include <string.h>
+
+#include "common.cuh"
+
+namespace uv {
+
+constexpr int SCHED_THREADS = 1024;
+
+struct SchedParams {
+  // per slot
+  int* req;            // request index or -1
+  int* fed;            // prompt tokens fed so far (including the one in cur_tok)
+  int* gen;            // tokens generated so far
+  int64_t* cur_tok;    // next input token of the slot (the decode step's tok vector)
+  int64_t* pos;        // cache position cur_tok is written at
+  int64_t* starts;     // first valid position (always 0 in this frame)
+  int64_t* row_key;    // Philox key of the sequence in the slot
+  int64_t* step_ctr;   // Philox counter = index of the token being generated
+  // sampler output of the step just run
+  const int64_t* samp_tok;
+  const float* samp_lp;
+  // request rings
+  int64_t* prompt_off;
+  int* prompt_len;
+  int* limit;
+  int64_t* key;
+  int64_t* out_off;
+  int* out_len;        // -1 until finished
+  int* start_version;
+  const int* tokens;
+  int* out_tok;
+  float* out_lp;
+  int* fin_ring;       // request indices in finishing order (ring of q_cap)
+  // control words: [0] head (next request to admit) [1] tail (requests enqueued) [2] finished count
+  //                [3] weight version [4] active slots after this step [5] status bits [6] steps run
+  //                [7] prompt-token tail [8] output-slot tail
+  int64_t* ctl;
+  int B, q_cap;
+  int64_t tok_cap, out_cap;
+  int eos, pad, force_eos;
+  int64_t max_len;
+};
+
+enum { CTL_HEAD = 0, CTL_TAIL, CTL_FIN, CTL_VERSION, CTL_ACTIVE, CTL_STATUS, CTL_STEPS, CTL_TOK_TAIL, CTL_OUT_TAIL };
+
+__device__ __forceinline__ int block_excl_scan(int v, int* warp_tot, int tid, int& total) {
+  const int lane = tid & 31, warp = tid >> 5;
+  int incl = v;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int t = __shfl_up_sync(0xffffffffu, incl, o);
+    if (lane >= o) incl += t;
+  }
+  __syncthreads();
+  if (lane == 31) warp_tot[warp] = incl;
+  __syncthreads();
+  int base = 0, tot = 0;
+#pragma unroll
+  for (int w = 0; w < SCHED_THREADS / 32; ++w) {
+    const int t = warp_tot[w];
+    if (w < warp) base += t;
+    tot += t;
+  }
+  total = tot;
+  return base + incl - v;
+}
+
+__global__ void __launch_bounds__(SCHED_THREADS) sched_step_kernel(const __grid_constant__ SchedParams P) {
+  __shared__ int warp_tot[SCHED_THREADS / 32];
+  const int tid = threadIdx.x;
+  const int64_t head0 = P.ctl[CTL_HEAD], tail = P.ctl[CTL_TAIL];
+  const int version = (int)P.ctl[CTL_VERSION];
+  int64_t head = head0;
+  int active = 0;
+  for (int base = 0; base < P.B; base += SCHED_THREADS) {  // uniform trip count: every thread joins every scan
+    const int s = base + tid;
+    const bool in = s < P.B;
+    int freed = 0;
+    if (in) {
+      const int r = P.req[s];
+      if (r < 0) {
+        freed = 1;
+      } else {
+        const int ri = r % P.q_cap;
+        const int f = P.fed[s];
+        if (f < P.prompt_len[ri]) {  // still prefilling: next prompt token, the sample is discarded
+          P.cur_tok[s] = P.tokens[(P.prompt_off[ri] + f) % P.tok_cap];
+          P.fed[s] = f + 1;
+          P.pos[s] += 1;
+        } else {
+          int g = P.gen[s];
+          const int lim = P.limit[ri];
+          int64_t t = P.samp_tok[s];
+          if (P.force_eos && g + 1 >= lim) t = P.eos;
+          const int64_t o = (P.out_off[ri] + g) % P.out_cap;
+          P.out_tok[o] = (int)t;
+          P.out_lp[o] = P.samp_lp[s];
+          ++g;
+          const bool full = P.pos[s] + 1 >= P.max_len;
+          if ((P.eos >= 0 && t == P.eos) || g >= lim || full) {
+            P.out_len[ri] = g;
+            const unsigned long long k = atomicAdd(reinterpret_cast<unsigned long long*>(P.ctl + CTL_FIN), 1ull);
+            P.fin_ring[k % P.q_cap] = r;
+            if (full && g < lim)
+              atomicOr(reinterpret_cast<unsigned long long*>(P.ctl + CTL_STATUS), 2ull);  // cut short: cache full
+            P.req[s] = -1;
+            freed = 1;
+          } else {
+            P.gen[s] = g;
+            P.cur_tok[s] = t;
+            P.pos[s] += 1;
+            P.step_ctr[s] = g;
+          }
+        }
+      }
+    }
+    // ---- admit queued requests into the free slots of this chunk, in slot order
+    int total_free;
+    const int rank = block_excl_scan(freed, warp_tot, tid, total_free);
+    const int64_t avail = tail - head;
+    if (in && freed) {
+      if (rank < avail) {
+        const int64_t r = head + rank;
+        const int ri = (int)(r % P.q_cap);
+        P.req[s] = (int)r;
+        P.fed[s] = 1;
+        P.gen[s] = 0;
+        P.cur_tok[s] = P.tokens[P.prompt_off[ri] % P.tok_cap];
+        P.pos[s] = 0;
+        P.starts[s] = 0;
+        P.row_key[s] = P.key[ri];
+        P.step_ctr[s] = 0;
+        P.start_version[ri] = version;
+      } else {  // nothing queued: park the slot at position 0 so it never overruns the cache (model.py:1345-1350)
+        P.cur_tok[s] = P.pad;
+        P.pos[s] = 0;
+        P.starts[s] = 0;
+      }
+    }
+    head += total_free < avail ? total_free : avail;
+    const int is_active = in && P.req[s] >= 0;
+    int tot_active;
+    block_excl_scan(is_active, warp_tot, tid, tot_active);
+    active += tot_active;
+  }
+  if (tid == 0) {
+    P.ctl[CTL_HEAD] = head;
+    P.ctl[CTL_ACTIVE] = active;
+    P.ctl[CTL_STEPS] += 1;
+  }
+}
+
+// Append n requests whose prompt_len / limit / key entries and prompt tokens the host has already copied into the
+// rings at [tail, tail + n) and [tok_tail, tok_tail + sum(len)): computes their prompt and output offsets by prefix
+// sum, clears out_len, then publishes the new tail.
+__global__ void __launch_bounds__(SCHED_THREADS) sched_enqueue_kernel(const __grid_constant__ SchedParams P, int n) {
+  __shared__ int warp_tot[SCHED_THREADS / 32];
+  const int tid = threadIdx.x;
+  const int64_t tail = P.ctl[CTL_TAIL];
+  int64_t tok_base = P.ctl[CTL_TOK_TAIL], out_base = P.ctl[CTL_OUT_TAIL];
+  for (int base = 0; base < n; base += SCHED_THREADS) {
+    const int i = base + tid;
+    const bool in = i < n;
+    const int ri = in ? (int)((tail + i) % P.q_cap) : 0;
+    const int len = in ? P.prompt_len[ri] : 0;
+    const int lim = in ? P.limit[ri] : 0;
+    int tot_len, tot_lim;
+    const int off_len = block_excl_scan(len, warp_tot, tid, tot_len);
+    const int off_lim = block_excl_scan(lim, warp_tot, tid, tot_lim);
+    if (in) {
+      P.prompt_off[ri] = tok_base + off_len;
+      P.out_off[ri] = out_base + off_lim;
+      P.out_len[ri] = -1;
+    }
+    tok_base += tot_len;
+    out_base += tot_lim;
+  }
+  __syncthreads();
+  if (tid == 0) {
+    P.ctl[CTL_TOK_TAIL] = tok_base;
+    P.ctl[CTL_OUT_TAIL] = out_base;
+    __threadfence();
+    P.ctl[CTL_TAIL] = tail + n;
+  }
+}
+
+}  // namespace uv
+
+extern "C" int uv_sched_step(const uv_sched_args* a, void* stream) {
+  using namespace uv;
+  if (!a) return UV_ERR_ARG;
+  if (a->B < 1 || a->q_cap < 1 || a->tok_cap < 1 || a->out_cap < 1 || a->max_len < 1) return UV_ERR_ARG;
+  if (!a->req || !a->fed || !a->gen || !a->cur_tok || !a->pos || !a->starts || !a->row_key || !a->step_ctr ||
+      !a->samp_tok || !a->samp_lp || !a->prompt_off || !a->prompt_len || !a->limit || !a->key || !a->out_off ||
+      !a->out_len || !a->start_version || !a->tokens || !a->out_tok || !a->out_lp || !a->fin_ring || !a->ctl)
+    return UV_ERR_ARG;
+  SchedParams P;
+  static_assert(sizeof(SchedParams) == sizeof(uv_sched_args), "uv_sched_args mirrors SchedParams");
+  memcpy(&P, a, sizeof(P));
+  sched_step_kernel<<<1, SCHED_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(P);
+  return check_launch();
+}
+
+extern "C" int uv_sched_enqueue(const uv_sched_args* a, int n, void* stream) {
+  using namespace uv;
+  if (!a || n < 0) return UV_ERR_ARG;
+  if (n == 0) return UV_OK;
+  if (n > a->q_cap) return UV_ERR_ARG;
+  if (!a->prompt_off || !a->prompt_len || !a->limit || !a->out_off || !a->out_len || !a->ctl) return UV_ERR_ARG;
+  SchedParams P;
+  memcpy(&P, a, sizeof(P));
+  sched_enqueue_kernel<<<1, SCHED_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(P, n);
+  return check_launch();
+}

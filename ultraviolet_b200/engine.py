@@ -1,0 +1,230 @@
+"""Decode engine: fused inference weights in one pointer-stable arena + the per-step kernel sequence.
+
+The arena plays the role of the reference's ``_fused`` dictionaries (Attention.fuse / MLP.fuse, ultraviolet/model.py:
+289-300, :384-386): per layer ``wqkv = cat(wq, wk, wv) * qkv_scale``, ``wo * o_scale``, ``gu = cat(w_gate, w_up)``,
+``down``, the gates, ``tanh(xsa_alpha)`` and the four residual lambdas, plus the (tied) embedding and the value
+embedding.  Everything of activation dtype lives in ONE flat tensor so that a weight refresh is an in-place write (or
+one NCCL broadcast) and every captured CUDA graph keeps reading the same addresses -- the contract of
+``sync_weights_inplace`` (scripts/rl_stream.py:23-36).
+
+One decode step (``step``) is the kernel sequence of ``decode_step_fast`` (ultraviolet/kernels/fast_decode.py:272-334):
+per layer  GEMM(qkv) -> uv_qkv_post (VE gate, QK norm, RoPE, int8 append) -> uv_decode_attn (+XSA, head gate)
+-> GEMM(wo) -> uv_resid_norm -> GEMM(gate|up) -> uv_swiglu -> GEMM(down) -> uv_resid_norm, then the tied LM head and
+uv_sample.  GEMMs are plain library calls (cuBLAS through torch.mm into preallocated outputs); everything else is
+libuvdecode.  Nothing here allocates after warm-up, so the whole step captures into one CUDA graph.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+from torch import Tensor
+
+from . import _lib
+from .config import MathConfig
+from .kernels._util import DTYPE_CODE, stream_ptr
+from .kernels.decode_attn import attn_launch, default_splits, workspace_for
+
+
+def _align(n: int, a: int = 128) -> int:
+    return (n + a - 1) // a * a
+
+
+class DecodeEngine:
+    def __init__(self, cfg: MathConfig, dtype: torch.dtype, device):
+        cfg.check_decode_supported()
+        if dtype not in (torch.float16, torch.bfloat16):
+            raise ValueError("decode engine computes in float16 or bfloat16")
+        self.cfg, self.dtype, self.device = cfg, dtype, torch.device(device)
+        if self.device.type != "cuda":
+            raise RuntimeError("ultraviolet_b200 decodes on CUDA devices only (there is no CPU path)")
+        d, hd, H, K, f = cfg.d_model, cfg.head_dim, cfg.n_heads, cfg.n_kv_heads, cfg.d_ff
+        self.use_ve = any(cfg.has_ve(l) for l in range(cfg.n_layers))
+        # ---- arena layout (element offsets, 128-element aligned so every matrix starts on a 256-byte boundary)
+        shapes = [("embed", (cfg.vocab_size, d))]
+        if self.use_ve:
+            shapes.append(("value_embed", (cfg.vocab_size, K * hd)))
+        for l in range(cfg.n_layers):
+            shapes += [(f"l{l}.wqkv", ((H + 2 * K) * hd, d)), (f"l{l}.wo", (d, H * hd)), (f"l{l}.gu", (2 * f, d)),
+                       (f"l{l}.down", (d, f))]
+            if cfg.has_ve(l):
+                shapes.append((f"l{l}.ve_gate", (K, cfg.ve_gate_channels)))
+            if cfg.gate_channels:
+                shapes.append((f"l{l}.attn_gate", (H, cfg.gate_channels)))
+        off, self.layout = 0, {}
+        for name, shp in shapes:
+            n = 1
+            for s in shp:
+                n *= s
+            self.layout[name] = (off, shp)
+            off = _align(off + n)
+        self.arena = torch.zeros(off, dtype=dtype, device=self.device)
+        # fp32 side arena: per layer 4 lambdas (rounded to dtype) + tanh(xsa_alpha) (H) ; then rope inv_freq
+        self.n32_layer = 4 + H
+        self.arena32 = torch.zeros(cfg.n_layers * self.n32_layer + max(cfg.rope_pairs, 1), dtype=torch.float32,
+                                   device=self.device)
+        self.w = {name: self.arena[o:o + torch.Size(shp).numel()].view(shp) for name, (o, shp) in self.layout.items()}
+        self.lambdas = [self.arena32[l * self.n32_layer:l * self.n32_layer + 4] for l in range(cfg.n_layers)]
+        self.xsa = [self.arena32[l * self.n32_layer + 4:(l + 1) * self.n32_layer] for l in range(cfg.n_layers)]
+        self.inv_freq = self.arena32[cfg.n_layers * self.n32_layer:][:cfg.rope_pairs]
+        # Rotary.inv_freq (model.py:203-204): (1 / base) ** linspace(0, 1, n_pairs), fp32
+        if cfg.rope_pairs:
+            self.inv_freq.copy_((1.0 / cfg.rope_base) ** torch.linspace(0, 1, cfg.rope_pairs, dtype=torch.float32))
+        self._scratch: dict[int, dict] = {}
+        self.version = 0
+        self.n_sm = torch.cuda.get_device_properties(self.device).multi_processor_count
+        _lib.lib()
+
+    # ------------------------------------------------------------------------------------------------ weights
+    @classmethod
+    def from_model(cls, model, dtype=torch.bfloat16) -> "DecodeEngine":
+        from .config import config_from
+        dev = model.embed.weight.device
+        eng = cls(config_from(model.cfg), dtype, dev)
+        eng.load_from(model)
+        return eng
+
+    @torch.no_grad()
+    def load_from(self, model) -> None:
+        """(Re)compute every fused weight from the model's parameters INTO the existing arena (same formulas and
+        rounding as Attention.fuse / MLP.fuse; pointers never change)."""
+        cfg, dt, w = self.cfg, self.dtype, self.w
+        w["embed"].copy_(model.embed.weight)
+        if self.use_ve:
+            w["value_embed"].copy_(model.value_embed.weight)
+        for l, blk in enumerate(model.blocks):
+            at, mlp = blk.attn, blk.mlp
+            w[f"l{l}.wqkv"].copy_((torch.cat([at.wq, at.wk, at.wv]) * at.qkv_scale).to(dt))
+            w[f"l{l}.wo"].copy_((at.wo * at.o_scale).to(dt))
+            w[f"l{l}.gu"].copy_(torch.cat([mlp.w_gate, mlp.w_up]).to(dt))
+            w[f"l{l}.down"].copy_(mlp.w_down.to(dt))
+            if cfg.has_ve(l):
+                w[f"l{l}.ve_gate"].copy_(at.ve_gate.to(dt))
+            if cfg.gate_channels:
+                w[f"l{l}.attn_gate"].copy_(at.attn_gate.to(dt))
+            lam = torch.stack([blk.resid_attn, blk.post_attn, blk.resid_mlp, blk.post_mlp]).detach()
+            self.lambdas[l].copy_(lam.to(dt).float())  # Block.finish casts each scalar to the activation dtype
+            if cfg.xsa:
+                self.xsa[l].copy_(torch.tanh(at.xsa_alpha.detach().float()))
+        self.version += 1
+
+    def nbytes(self) -> int:
+        return self.arena.numel() * self.arena.element_size() + self.arena32.numel() * 4
+
+    # ------------------------------------------------------------------------------------------------ scratch
+    def scratch(self, B: int) -> dict:
+        s = self._scratch.get(B)
+        if s is None:
+            cfg, dt, dev = self.cfg, self.dtype, self.device
+            d, hd, H, K, f = cfg.d_model, cfg.head_dim, cfg.n_heads, cfg.n_kv_heads, cfg.d_ff
+            e = lambda *shape: torch.empty(*shape, dtype=dt, device=dev)
+            s = dict(x=e(B, d), xn=e(B, d), qkv=e(B, (H + 2 * K) * hd), z=e(B, H * hd), a=e(B, d), h=e(B, d),
+                     hn=e(B, d), gu=e(B, 2 * f), act=e(B, f), m=e(B, d), head=e(B, cfg.vocab_size),
+                     tok=torch.zeros(B, dtype=torch.int64, device=dev),
+                     logp=torch.zeros(B, dtype=torch.float32, device=dev),
+                     counters=torch.zeros(B * K, dtype=torch.int32, device=dev),
+                     status=torch.zeros(1, dtype=torch.int32, device=dev),
+                     oob=torch.zeros(1, dtype=torch.int32, device=dev), ws={})
+            self._scratch[B] = s
+        return s
+
+    def _workspace(self, s: dict, B: int, splits: int) -> Tensor | None:
+        if splits <= 1:
+            return None
+        ws = s["ws"].get(splits)
+        if ws is None:
+            cfg = self.cfg
+            ws = s["ws"][splits] = workspace_for(B, cfg.n_kv_heads, cfg.group, cfg.head_dim, splits, self.device)
+        return ws
+
+    # ------------------------------------------------------------------------------------------------ one step
+    def trunk(self, tok: Tensor, st, pos: Tensor, starts: Tensor, g_len: int | None = None,
+              num_splits: dict | None = None, row_map: Tensor | None = None, skip_attn: bool = False) -> Tensor:
+        """One token for every batch entry: writes K/V at `pos` and returns the final normed hidden (B, d) (a view
+        of engine scratch, overwritten by the next call).  pos/starts are batch-indexed (B,) int64; row_map
+        optionally maps batch entries to cache rows."""
+        if skip_attn:
+            raise NotImplementedError("skip_attn (the reference's A/B profiling switch) is not built here")
+        cfg, lib, dt = self.cfg, _lib.lib(), DTYPE_CODE[self.dtype]
+        B = tok.size(0)
+        s = self.scratch(B)
+        d, hd, H, K, f = cfg.d_model, cfg.head_dim, cfg.n_heads, cfg.n_kv_heads, cfg.d_ff
+        sp = stream_ptr(self.device)
+        w = self.w
+        ns = num_splits or {}
+        rm = row_map.data_ptr() if row_map is not None else None
+        with torch.cuda.device(self.device):
+            _lib.check(lib.uv_embed_norm(tok.data_ptr(), w["embed"].data_ptr(), dt, cfg.vocab_size, d,
+                                         s["x"].data_ptr(), s["xn"].data_ptr(), B, sp), "uv_embed_norm")
+            x, xn, h, hn = s["x"], s["xn"], s["h"], s["hn"]
+            qkv3 = s["qkv"].view(B, H + 2 * K, hd)
+            q, v_cur = qkv3[:, :H], qkv3[:, H + K:]
+            z3 = s["z"].view(B, H, hd)
+            for l in range(cfg.n_layers):
+                glob = cfg.is_global(l)
+                torch.mm(xn, w[f"l{l}.wqkv"].t(), out=s["qkv"])
+                kc, vc, ks, vs = st.k[l], st.v[l], st.k_scale[l], st.v_scale[l]
+                S = kc.size(2)
+                ve_gate = w[f"l{l}.ve_gate"].data_ptr() if cfg.has_ve(l) else None
+                rope = (not glob) or cfg.global_rope
+                _lib.check(lib.uv_qkv_post(
+                    s["qkv"].data_ptr(), xn.data_ptr(), tok.data_ptr(),
+                    w["value_embed"].data_ptr() if self.use_ve else None, ve_gate,
+                    self.inv_freq.data_ptr() if rope and cfg.rope_pairs else None, pos.data_ptr(),
+                    kc.data_ptr(), vc.data_ptr(), ks.data_ptr(), vs.data_ptr(), rm,
+                    s["oob"].data_ptr(), dt, cfg.vocab_size, B, H, K, hd, d, S, int(not glob),
+                    cfg.ve_gate_channels, cfg.rope_pairs, sp), "uv_qkv_post")
+                if glob:
+                    ctx = min(g_len or S, S)
+                    splits = ns.get("global") or default_splits(B * K, ctx, self.device)
+                    window, ring = 0, False
+                else:
+                    splits = ns.get("local") or default_splits(B * K, S, self.device)
+                    window, ring = cfg.window, True
+                attn_launch(q, kc, vc, pos, starts, cfg.attn_scale, window, ring, ks, vs, splits, z3,
+                            self._workspace(s, B, splits), v_cur=v_cur,
+                            xsa_alpha=self.xsa[l] if cfg.xsa else None, xsa_eps=cfg.xsa_eps,
+                            gate_x=xn if cfg.gate_channels else None,
+                            gate_w=w[f"l{l}.attn_gate"] if cfg.gate_channels else None,
+                            counters=s["counters"], status=s["status"], row_map=row_map)
+                torch.mm(s["z"], w[f"l{l}.wo"].t(), out=s["a"])
+                lam = self.lambdas[l]
+                _lib.check(lib.uv_resid_norm(x.data_ptr(), s["a"].data_ptr(), lam.data_ptr(), dt, d, h.data_ptr(),
+                                             hn.data_ptr(), B, sp), "uv_resid_norm")
+                torch.mm(hn, w[f"l{l}.gu"].t(), out=s["gu"])
+                _lib.check(lib.uv_swiglu(s["gu"].data_ptr(), dt, f, s["act"].data_ptr(), B, sp), "uv_swiglu")
+                torch.mm(s["act"], w[f"l{l}.down"].t(), out=s["m"])
+                _lib.check(lib.uv_resid_norm(h.data_ptr(), s["m"].data_ptr(), lam[2:].data_ptr(), dt, d,
+                                             x.data_ptr(), xn.data_ptr(), B, sp), "uv_resid_norm")
+        return xn  # rms_norm of the last residual stream == the final norm (fast_decode.py:332-334)
+
+    def head(self, hfin: Tensor) -> Tensor:
+        """Raw tied-head output (B, V) in the activation dtype (the GEMM of MathLM.logits, model.py:826)."""
+        s = self.scratch(hfin.size(0))
+        torch.mm(hfin, self.w["embed"].t(), out=s["head"])
+        return s["head"]
+
+    def logits(self, h: Tensor) -> Tensor:
+        """MathLM.logits (model.py:824-827): fp32 softcapped logits, for API callers that want the full matrix."""
+        a, b, c = self.cfg.softcap
+        z = torch.mm(h.to(self.dtype), self.w["embed"].t()).float()
+        return a * torch.sigmoid((z + b) / c)
+
+    def sample(self, head: Tensor, temperature: float, top_p: float = 1.0, u: Tensor | None = None, seed: int = 0,
+               row_keys: Tensor | None = None, steps: Tensor | None = None, tok_out: Tensor | None = None,
+               logp_out: Tensor | None = None, precapped: bool = False):
+        """uv_sample on (B, V) head output; returns (tok int64 (B,), logp fp32 (B,)) in engine scratch unless
+        output tensors are given."""
+        B, V = head.shape
+        s = self.scratch(B)
+        tok_out = s["tok"] if tok_out is None else tok_out
+        logp_out = s["logp"] if logp_out is None else logp_out
+        a, b, c = self.cfg.softcap
+        p = lambda t: None if t is None else t.data_ptr()
+        with torch.cuda.device(self.device):
+            rc = _lib.lib().uv_sample(head.data_ptr(), DTYPE_CODE[head.dtype], head.stride(0), B, V, int(precapped),
+                                      a, b, c, float(temperature), float(top_p), p(u), C.c_uint64(seed & (2**64 - 1)),
+                                      p(row_keys), p(steps), tok_out.data_ptr(), logp_out.data_ptr(),
+                                      stream_ptr(self.device))
+        _lib.check(rc, "uv_sample")
+        return tok_out, logp_out

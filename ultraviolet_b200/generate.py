@@ -1,0 +1,187 @@
+"""DecodeRunner / sample / generate / generate_continuous with the reference's signatures (ultraviolet/model.py:
+1075-1354) on the B200 decode engine."""
+from __future__ import annotations
+
+import numpy as np
+import torch
+from torch import Tensor
+
+from .fast_decode import _engine
+from .scheduler import GpuScheduler
+
+
+def sample(logits: Tensor, temperature: float, top_k: int = 0, top_p: float = 1.0) -> Tensor:
+    """model.py:1194-1211 on softcapped logits (B, V): temperature <= 0 -> argmax, else a draw from
+    softmax(logits / T) restricted to the top_p nucleus.  One uniform per row from torch's CUDA generator (so
+    torch.manual_seed governs it), inverse-CDF instead of Gumbel-max.  top_k is not built."""
+    if top_k:
+        raise NotImplementedError("top_k sampling is not built in ultraviolet_b200")
+    from . import _lib
+    from .kernels._util import DTYPE_CODE, need_cuda, stream_ptr
+    import ctypes as C
+    need_cuda(logits)
+    if logits.stride(-1) != 1:
+        logits = logits.contiguous()
+    B, V = logits.shape
+    tok = torch.empty(B, dtype=torch.int64, device=logits.device)
+    lp = torch.empty(B, dtype=torch.float32, device=logits.device)
+    u = torch.rand(B, device=logits.device, dtype=torch.float32) if temperature > 0 else None
+    with torch.cuda.device(logits.device):
+        rc = _lib.lib().uv_sample(logits.data_ptr(), DTYPE_CODE[logits.dtype], logits.stride(0), B, V, 1, 0.0, 0.0,
+                                  1.0, float(temperature), float(top_p), None if u is None else u.data_ptr(),
+                                  C.c_uint64(0), None, None, tok.data_ptr(), lp.data_ptr(),
+                                  stream_ptr(logits.device))
+    _lib.check(rc, "uv_sample")
+    return tok
+
+
+class DecodeRunner:
+    """One decode step + sample per call, replayed from a CUDA graph per global-context bucket (model.py:1075-1150).
+    ``out_tok`` / ``out_logp`` are static buffers (callers clone).  ``compile`` is accepted and ignored: the step is
+    already a fixed kernel sequence."""
+
+    def __init__(self, model, st, bucket: int = 1024, use_graph: bool = True, temperature: float = 1.0,
+                 top_k: int = 0, compile: bool = False, skip_attn: bool = False, top_p: float = 1.0, seed: int = 0):
+        if top_k:
+            raise NotImplementedError("top_k sampling is not built in ultraviolet_b200")
+        self.m, self.st, self.bucket = model, st, bucket
+        self.eng = _engine(model)
+        self.use_graph = use_graph
+        self.temperature, self.top_k, self.top_p, self.seed = temperature, top_k, top_p, seed
+        dev = st.pos.device
+        self.tok = torch.zeros(st.B, dtype=torch.long, device=dev)
+        sc = self.eng.scratch(st.B)
+        self.out_tok, self.out_logp = sc["tok"], sc["logp"]
+        self.want_logp = True
+        self.row_keys = torch.arange(st.B, dtype=torch.int64, device=dev)
+        self.steps = torch.zeros(st.B, dtype=torch.int64, device=dev)
+        self.graphs: dict[int, torch.cuda.CUDAGraph] = {}
+        self.skip_attn = skip_attn
+
+    def g_len(self, p: int) -> int:
+        return min(self.st.max_len, ((p + 1 + self.bucket - 1) // self.bucket) * self.bucket)
+
+    @property
+    def out_logits(self) -> Tensor:
+        """fp32 softcapped logits of the last step (computed on demand from the raw head output)."""
+        a, b, c = self.eng.cfg.softcap
+        return a * torch.sigmoid((self.eng.scratch(self.st.B)["head"].float() + b) / c)
+
+    def _body(self, g_len: int) -> None:
+        st, eng = self.st, self.eng
+        h = eng.trunk(self.tok, st, st.pos, st.starts, g_len=g_len, num_splits=self.m.__dict__.get(
+            "decode_num_splits", getattr(type(self.m), "decode_num_splits", None)), skip_attn=self.skip_attn)
+        eng.sample(eng.head(h), self.temperature, self.top_p, seed=self.seed, row_keys=self.row_keys,
+                   steps=self.steps)
+        st.pos.add_(1)
+        self.steps.add_(1)
+
+    def step(self, tok: Tensor) -> Tensor:
+        p = int(self.st.host_pos.max())
+        assert p < self.st.max_len, "cache full"
+        gl = self.g_len(p)
+        self.tok.copy_(tok)
+        if not self.use_graph:
+            self._body(gl)
+        else:
+            g = self.graphs.get(gl)
+            if g is None:
+                dev = self.st.pos.device
+                pos0, steps0 = self.st.pos.clone(), self.steps.clone()
+                s = torch.cuda.Stream(dev)
+                s.wait_stream(torch.cuda.current_stream(dev))
+                with torch.cuda.stream(s):  # warm-up: the slot written now is rewritten by the real replay
+                    self._body(gl)
+                    self.st.pos.copy_(pos0)
+                    self.steps.copy_(steps0)
+                torch.cuda.current_stream(dev).wait_stream(s)
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, capture_error_mode="thread_local"):
+                    self._body(gl)
+                self.graphs[gl] = g
+            g.replay()
+        self.st.host_pos += 1
+        return self.out_tok
+
+
+def _left_pad(prompts, pad_id, dev):
+    Tp = max(len(p) for p in prompts)
+    idx = torch.full((len(prompts), Tp), pad_id, dtype=torch.long)
+    starts = torch.zeros(len(prompts), dtype=torch.long)
+    for b, p in enumerate(prompts):
+        idx[b, Tp - len(p):] = torch.as_tensor(p, dtype=torch.long)
+        starts[b] = Tp - len(p)
+    return idx.to(dev), starts.to(dev)
+
+
+@torch.no_grad()
+def generate(model, prompts, max_new: int, temperature: float = 1.0, top_k: int = 0, eos_id: int | None = None,
+             pad_id: int = 0, max_len: int | None = None, use_graph: bool = True, bucket: int = 1024,
+             dtype=None, compile: bool = True, top_p: float = 1.0):
+    """Static-batch generation (model.py:1228-1263): left-padded prefill, lockstep decode, rows cut after EOS."""
+    eng = _engine(model)
+    dev = eng.device
+    B = len(prompts)
+    idx, starts = _left_pad(prompts, pad_id, dev)
+    max_len = max_len or (idx.size(1) + max_new)
+    st = model.new_state(B, max_len, eng.dtype, dev)
+    runner = DecodeRunner(model, st, bucket=bucket, use_graph=use_graph, temperature=temperature, top_k=top_k,
+                          top_p=top_p)
+    # prefill every position but the last through the decode kernels, then let the runner take the last prompt
+    # token so that token 0 is drawn by the same fused sampler as every later token
+    T = idx.size(1)
+    if T > 1:
+        model.prefill(idx[:, :-1], starts, st)
+    st.starts.copy_(starts)
+    tok = runner.step(idx[:, -1]).clone()
+    out = [tok]
+    done = torch.zeros(B, dtype=torch.bool, device=dev)
+    if eos_id is not None:
+        done |= tok == eos_id
+    for i in range(max_new - 1):
+        if st.host_pos.max() >= max_len:
+            break
+        tok = runner.step(tok).clone()
+        out.append(tok)
+        if eos_id is not None:
+            done |= tok == eos_id
+            if i % 64 == 63 and bool(done.all()):
+                break
+    res = []
+    for row in torch.stack(out, 1).tolist():
+        if eos_id is not None and eos_id in row:
+            row = row[:row.index(eos_id) + 1]
+        res.append(row)
+    return res
+
+
+@torch.no_grad()
+def generate_continuous(model, prompts, max_new: int, batch: int, temperature: float = 1.0, top_k: int = 0,
+                        eos_id: int | None = None, pad_id: int = 0, check_every: int = 16, use_graph: bool = True,
+                        bucket: int = 1024, dtype=None, compile: bool = True, target_lens=None, stats=None,
+                        top_p: float = 1.0, seed: int = 0):
+    """Continuous batching over `batch` cache slots (model.py:1266-1354), scheduled on the device; completions in
+    prompt order.  target_lens[i] caps request i's length (the reference's benchmarking hook, model.py:1312)."""
+    if top_k:
+        raise NotImplementedError("top_k sampling is not built in ultraviolet_b200")
+    eng = _engine(model)
+    n = len(prompts)
+    B = min(batch, n)
+    max_prompt = max(len(p) for p in prompts)
+    st = model.new_state(B, max_prompt + max_new + check_every, eng.dtype, eng.device)
+    sched = GpuScheduler(eng, st, max_new=max_new, temperature=temperature, top_p=top_p, eos_id=eos_id,
+                         pad_id=pad_id, seed=seed, q_cap=max(n, 2), max_prompt=max_prompt, use_graph=use_graph,
+                         tok_cap=sum(len(p) for p in prompts) + 1,
+                         out_cap=(int(np.minimum(np.asarray(target_lens), max_new).sum()) if target_lens is not None
+                                  else n * max_new) + 1)
+    sched.enqueue([list(p) for p in prompts], limits=target_lens, metas=list(range(n)))
+    results = [None] * n
+    got = 0
+    while got < n:
+        sched.run(check_every)
+        for i, toks, _, _ in sched.harvest():
+            results[i] = toks
+            got += 1
+    if stats is not None:
+        stats.update(steps=sched.steps_run, prefilled=n, slots=B)
+    return results

@@ -30,7 +30,8 @@ def attn_launch(q: Tensor, k_cache: Tensor, v_cache: Tensor, pos: Tensor, starts
                 ring: bool, k_scale: Tensor, v_scale: Tensor, num_splits: int, out: Tensor,
                 workspace: Tensor | None = None, v_cur: Tensor | None = None, xsa_alpha: Tensor | None = None,
                 xsa_eps: float = 1e-4, gate_x: Tensor | None = None, gate_w: Tensor | None = None,
-                counters: Tensor | None = None, status: Tensor | None = None) -> Tensor:
+                counters: Tensor | None = None, status: Tensor | None = None,
+                row_map: Tensor | None = None) -> Tensor:
     """Raw launch: fills uv_attn_args from tensor metadata.  q / out (B, H, hd) with unit inner stride."""
     B, H, hd = q.shape
     KH, S = k_cache.shape[1], k_cache.shape[2]
@@ -53,8 +54,10 @@ def attn_launch(q: Tensor, k_cache: Tensor, v_cache: Tensor, pos: Tensor, starts
             a.counters = counters.data_ptr()
     if status is not None:
         a.status = status.data_ptr()
+    if row_map is not None:
+        a.row_map = row_map.data_ptr()
     if xsa_alpha is not None:
-        a.v_cur, a.v_cur_stride = v_cur.data_ptr(), v_cur.stride(-2)
+        a.v_cur, a.v_cur_sb, a.v_cur_sh = v_cur.data_ptr(), v_cur.stride(0), v_cur.stride(1)
         a.xsa_alpha, a.xsa_eps = xsa_alpha.data_ptr(), float(xsa_eps)
     if gate_w is not None:
         a.gate_x, a.gate_x_stride = gate_x.data_ptr(), gate_x.stride(0)

@@ -1,0 +1,96 @@
+"""Streaming rollout generator with the API of scripts/rl_stream.py (StreamGen, sync_weights_inplace), running on
+the GPU-resident scheduler: slots are retired and refilled on the device after every decode step instead of by a host
+loop every ``check_every`` steps.
+
+Differences a caller can observe, all within the reference's contract (rl_stream.py:1-12): a finished row is retired
+at the step it finishes (no tokens are decoded past EOS), a request is prefilled through the decode step starting at
+position 0 (no left padding), and the sampler draws by inverse CDF from Philox keyed by the request (a different
+random stream from Gumbel-max, as the reference's own fused sampler already is, fused_sample.py:13-15).
+"""
+from __future__ import annotations
+
+import collections
+
+import torch
+
+from .fast_decode import _engine, refresh_weights
+from .scheduler import GpuScheduler
+
+
+@torch.no_grad()
+def sync_weights_inplace(gen_m, raw) -> None:
+    """Copy raw's parameters into gen_m and refresh the fused arena in place (rl_stream.py:23-36): every captured
+    graph keeps reading the same addresses; rows in flight continue under the new weights."""
+    for pg, pt in zip(gen_m.parameters(), raw.parameters()):
+        pg.copy_(pt)
+    refresh_weights(gen_m)
+    torch.cuda.synchronize(gen_m.embed.weight.device)
+
+
+class StreamGen:
+    def __init__(self, model, slots, max_prompt, max_new, temperature, eos_id, check_every=16, compile=True,
+                 use_graph=True, pad_id=0, dtype=torch.float16, bucket=1024, top_p: float = 1.0, seed: int = 0,
+                 queue_capacity: int = 8192):
+        assert temperature > 0
+        self.m, self.B, self.max_new, self.T, self.eos = model, slots, max_new, temperature, eos_id
+        self.ce, self.pad, self.dtype, self.max_prompt = check_every, pad_id, dtype, max_prompt
+        eng = _engine(model)
+        self.dev = eng.device
+        self.st = model.new_state(slots, max_prompt + max_new + check_every, eng.dtype, self.dev)
+        self.sched = GpuScheduler(eng, self.st, max_new=max_new, temperature=temperature, top_p=top_p, eos_id=eos_id,
+                                  pad_id=pad_id, seed=seed, q_cap=queue_capacity, max_prompt=max_prompt,
+                                  use_graph=use_graph)
+        self.queue = collections.deque()   # host-side FIFO of (prompt_ids, meta) not yet on the device
+        self._version = 0
+        self.n_decode_steps = 0
+        self.n_tokens = 0
+        self._on_device = 0
+
+    # the caller reads and writes .version (rl_grpo.py:1106, :1172, :1309); the device copy tags admissions
+    @property
+    def version(self):
+        return self._version
+
+    @version.setter
+    def version(self, v):
+        self._version = int(v)
+        self.sched.set_version(self._version)
+
+    def add(self, prompt_ids, meta):
+        assert len(prompt_ids) <= self.max_prompt, "prompt longer than max_prompt"
+        self.queue.append((list(prompt_ids), meta))
+
+    def n_active(self):
+        return self.sched.n_active()
+
+    def n_outstanding(self):
+        return len(self.queue) + (self.sched.n_enqueued - self.sched.n_harvested)
+
+    def _upload(self):
+        """Move host-queued requests to the device queue (bounded so that at most 2 * slots wait on the device, which
+        keeps drop_queued meaningful for everything behind them)."""
+        waiting = self.sched.n_enqueued - self.sched.n_harvested - self.sched.n_active()
+        room = max(0, 2 * self.B - max(waiting, 0))
+        n = min(room, len(self.queue))
+        if n:
+            items = [self.queue.popleft() for _ in range(n)]
+            self.sched.enqueue([p for p, _ in items], metas=[m for _, m in items])
+
+    def chunk(self):
+        """Upload queued requests, run check_every decode steps on the device, return what finished:
+        [(meta, tokens list (EOS-terminated if it stopped), behaviour logp float32 array, start_version)]."""
+        self._upload()
+        if self.sched.n_enqueued == self.sched.n_harvested:
+            return []
+        self.sched.run(self.ce)
+        self.n_decode_steps += self.ce
+        out = self.sched.harvest()
+        self.n_tokens += sum(len(t) for _, t, _, _ in out)
+        return out
+
+    def drop_queued(self, pred):
+        """Remove queued (not yet uploaded) requests whose meta satisfies pred; returns how many."""
+        keep = [x for x in self.queue if not pred(x[1])]
+        n = len(self.queue) - len(keep)
+        self.queue = collections.deque(keep)
+        return n

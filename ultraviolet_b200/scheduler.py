@@ -1,0 +1,197 @@
+"""Host side of the GPU-resident continuous-batching scheduler (csrc/sched.cu).
+
+``GpuScheduler`` owns the device queue (request / prompt-token / output rings), the per-slot state that doubles as the
+decode step's inputs (``cur_tok``, and the cache state's ``pos`` / ``starts``), and one CUDA graph holding a whole
+step:  trunk -> LM head -> uv_sample (Philox keyed per request) -> uv_sched_step.  ``run(n)`` replays the graph n
+times with no host work in between; ``enqueue`` and ``harvest`` are the only host <-> device traffic.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+import torch
+
+from . import _lib
+from .kernels._util import stream_ptr
+
+CTL_HEAD, CTL_TAIL, CTL_FIN, CTL_VERSION, CTL_ACTIVE, CTL_STATUS, CTL_STEPS, CTL_TOK_TAIL, CTL_OUT_TAIL = range(9)
+
+
+def _pow2(n: int) -> int:
+    return 1 << max(1, (n - 1).bit_length())
+
+
+class GpuScheduler:
+    def __init__(self, engine, st, *, max_new: int, temperature: float, top_p: float = 1.0, eos_id: int | None = 0,
+                 pad_id: int = 0, seed: int = 0, q_cap: int = 8192, tok_cap: int | None = None,
+                 out_cap: int | None = None, max_prompt: int = 256, force_eos: bool = False, use_graph: bool = True,
+                 num_splits: dict | None = None):
+        self.eng, self.st, self.B = engine, st, st.B
+        self.dev = engine.device
+        self.max_new, self.T, self.top_p, self.seed = int(max_new), float(temperature), float(top_p), int(seed)
+        self.eos = -1 if eos_id is None else int(eos_id)
+        self.pad, self.force_eos = int(pad_id), bool(force_eos)
+        self.q_cap = _pow2(q_cap)
+        self.tok_cap = int(tok_cap or self.q_cap * max_prompt)
+        self.out_cap = int(out_cap or self.q_cap * self.max_new)
+        self.use_graph, self.num_splits = use_graph, num_splits
+        dev, B, Q = self.dev, self.B, self.q_cap
+        i32 = lambda n, v=0: torch.full((n,), v, dtype=torch.int32, device=dev)
+        i64 = lambda n, v=0: torch.full((n,), v, dtype=torch.int64, device=dev)
+        self.req, self.fed, self.gen = i32(B, -1), i32(B), i32(B)
+        self.cur_tok, self.row_key, self.step_ctr = i64(B, self.pad), i64(B), i64(B)
+        self.prompt_off, self.key, self.out_off = i64(Q), i64(Q), i64(Q)
+        self.prompt_len, self.limit, self.out_len, self.start_version = i32(Q), i32(Q), i32(Q, -1), i32(Q)
+        self.fin_ring = i32(Q, -1)
+        self.tokens = i32(self.tok_cap)
+        self.out_tok = i32(self.out_cap)
+        self.out_lp = torch.zeros(self.out_cap, dtype=torch.float32, device=dev)
+        self.ctl = i64(16)
+        sc = engine.scratch(B)
+        self.samp_tok, self.samp_lp = sc["tok"], sc["logp"]
+        st.pos.zero_()
+        st.starts.zero_()
+        a = self.args = _lib.SchedArgs()
+        for name in ("req", "fed", "gen", "cur_tok", "row_key", "step_ctr", "prompt_off", "prompt_len", "limit",
+                     "key", "out_off", "out_len", "start_version", "tokens", "out_tok", "out_lp", "fin_ring", "ctl",
+                     "samp_tok", "samp_lp"):
+            setattr(a, name, getattr(self, name).data_ptr())
+        a.pos, a.starts = st.pos.data_ptr(), st.starts.data_ptr()
+        a.B, a.q_cap, a.tok_cap, a.out_cap = B, Q, self.tok_cap, self.out_cap
+        a.eos, a.pad, a.force_eos, a.max_len = self.eos, self.pad, int(self.force_eos), st.max_len
+        # host mirrors
+        self.n_enqueued = 0       # == ctl[TAIL]
+        self.n_harvested = 0      # finished requests already returned
+        self.tok_tail = 0
+        self.out_tail = 0
+        # ring accounting: offsets of every unharvested request; the oldest one bounds what may be overwritten
+        self._span: dict[int, tuple[int, int]] = {}   # request -> (prompt offset, output offset)
+        self._oldest = 0
+        self.meta: dict[int, object] = {}
+        self.graph = None
+        self.steps_run = 0
+        self._primed = False
+
+    # ------------------------------------------------------------------------------------------------ queue
+    def set_version(self, v: int) -> None:
+        self.ctl[CTL_VERSION] = int(v)
+
+    def enqueue(self, prompts, limits=None, keys=None, metas=None) -> None:
+        """Append requests: prompts (list of token-id lists), per-request token limits (default max_new), Philox
+        keys (default: the request index) and opaque metadata returned by harvest()."""
+        n = len(prompts)
+        if n == 0:
+            return
+        lens = np.fromiter((len(p) for p in prompts), dtype=np.int64, count=n)
+        if lens.min() < 1:
+            raise ValueError("empty prompt")
+        lim = np.full(n, self.max_new, np.int64) if limits is None else np.minimum(np.asarray(limits, np.int64),
+                                                                                  self.max_new)
+        if lim.min() < 1:
+            raise ValueError("token limits must be >= 1")
+        if int((lens + lim).max()) > self.st.max_len:
+            raise ValueError("prompt + limit exceeds the cache length")
+        in_flight = self.n_enqueued - self.n_harvested
+        if in_flight + n > self.q_cap:
+            raise RuntimeError(f"request ring full ({in_flight} in flight + {n} new > {self.q_cap})")
+        tok_floor, out_floor = self._span.get(self._oldest, (self.tok_tail, self.out_tail))
+        if (self.tok_tail + int(lens.sum()) - tok_floor > self.tok_cap
+                or self.out_tail + int(lim.sum()) - out_floor > self.out_cap):
+            raise RuntimeError("prompt-token or output ring too small for the requests in flight")
+        r0 = self.n_enqueued
+        kk = np.arange(r0, r0 + n, dtype=np.int64) if keys is None else np.asarray(keys, np.int64)
+        ridx = torch.from_numpy((np.arange(r0, r0 + n) % self.q_cap).astype(np.int64)).to(self.dev)
+        self.prompt_len[ridx] = torch.from_numpy(lens.astype(np.int32)).to(self.dev)
+        self.limit[ridx] = torch.from_numpy(lim.astype(np.int32)).to(self.dev)
+        self.key[ridx] = torch.from_numpy(kk).to(self.dev)
+        flat = np.fromiter((t for p in prompts for t in p), dtype=np.int32, count=int(lens.sum()))
+        tidx = torch.from_numpy(((self.tok_tail + np.arange(flat.size)) % self.tok_cap).astype(np.int64)).to(self.dev)
+        self.tokens[tidx] = torch.from_numpy(flat).to(self.dev)
+        with torch.cuda.device(self.dev):
+            _lib.check(_lib.lib().uv_sched_enqueue(C.byref(self.args), n, stream_ptr(self.dev)), "uv_sched_enqueue")
+        t_off = self.tok_tail + np.concatenate([[0], np.cumsum(lens)[:-1]])
+        o_off = self.out_tail + np.concatenate([[0], np.cumsum(lim)[:-1]])
+        for i in range(n):
+            self.meta[r0 + i] = metas[i] if metas is not None else r0 + i
+            self._span[r0 + i] = (int(t_off[i]), int(o_off[i]))
+        self.n_enqueued += n
+        self.tok_tail += int(lens.sum())
+        self.out_tail += int(lim.sum())
+
+    # ------------------------------------------------------------------------------------------------ stepping
+    def _sched_step(self) -> None:
+        with torch.cuda.device(self.dev):
+            _lib.check(_lib.lib().uv_sched_step(C.byref(self.args), stream_ptr(self.dev)), "uv_sched_step")
+
+    def _step_body(self) -> None:
+        eng, st = self.eng, self.st
+        h = eng.trunk(self.cur_tok, st, st.pos, st.starts, g_len=st.max_len, num_splits=self.num_splits)
+        head = eng.head(h)
+        eng.sample(head, self.T, self.top_p, seed=self.seed, row_keys=self.row_key, steps=self.step_ctr)
+        self._sched_step()
+
+    def prime(self) -> None:
+        """First scheduling pass (admits queued requests into the idle slots) and graph capture."""
+        if not self._primed:
+            self._sched_step()
+            self._primed = True
+        if self.use_graph and self.graph is None:
+            # Warm up on a side stream, then capture.  The warm-up steps are real steps (state advances): nothing is
+            # rolled back, they simply count towards the run.
+            s = torch.cuda.Stream(self.dev)
+            s.wait_stream(torch.cuda.current_stream(self.dev))
+            with torch.cuda.stream(s):
+                self._step_body()
+                self.steps_run += 1
+            torch.cuda.current_stream(self.dev).wait_stream(s)
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, capture_error_mode="thread_local"):
+                self._step_body()
+            self.graph = g
+
+    def run(self, n_steps: int) -> None:
+        self.prime()
+        for _ in range(n_steps):
+            if self.graph is not None:
+                self.graph.replay()
+            else:
+                self._step_body()
+        self.steps_run += n_steps
+
+    # ------------------------------------------------------------------------------------------------ harvest
+    def counters(self) -> dict:
+        c = self.ctl.cpu().numpy()
+        return dict(head=int(c[CTL_HEAD]), tail=int(c[CTL_TAIL]), finished=int(c[CTL_FIN]),
+                    active=int(c[CTL_ACTIVE]), status=int(c[CTL_STATUS]), steps=int(c[CTL_STEPS]))
+
+    def harvest(self):
+        """Return the requests that finished since the last call as [(meta, tokens list, logp float32 array,
+        start_version)] in finishing order (one small D2H for the counters, one gather + D2H for the payload)."""
+        fin = int(self.ctl[CTL_FIN].item())
+        if fin == self.n_harvested:
+            return []
+        k = torch.arange(self.n_harvested, fin, device=self.dev) % self.q_cap
+        rid = self.fin_ring[k].long()
+        ri = rid % self.q_cap
+        lens, offs, ver = self.out_len[ri].long(), self.out_off[ri], self.start_version[ri]
+        ends = torch.cumsum(lens, 0)
+        total = int(ends[-1].item())
+        seg = torch.repeat_interleave(torch.arange(rid.numel(), device=self.dev), lens, output_size=total)
+        within = torch.arange(total, device=self.dev) - (ends - lens)[seg]
+        flat = (offs[seg] + within) % self.out_cap
+        toks = self.out_tok[flat].cpu().numpy()
+        lps = self.out_lp[flat].cpu().numpy()
+        rid_h, lens_h, ver_h = rid.cpu().numpy(), lens.cpu().numpy(), ver.cpu().numpy()
+        out, o = [], 0
+        for r, n, v in zip(rid_h.tolist(), lens_h.tolist(), ver_h.tolist()):
+            out.append((self.meta.pop(r), toks[o:o + n].tolist(), lps[o:o + n].copy(), int(v)))
+            self._span.pop(r, None)
+            o += n
+        self.n_harvested = fin
+        while self._oldest < self.n_enqueued and self._oldest not in self._span:
+            self._oldest += 1
+        return out
+
+    def n_active(self) -> int:
+        return int(self.ctl[CTL_ACTIVE].item())
