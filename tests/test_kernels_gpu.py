@@ -240,7 +240,9 @@ def test_fused_sample_matches_reference_golden_and_cdf(dtype):
         ref_lp = (z[np.arange(len(tok)), tok] - cap[0]) / t - np.log(S)
         np.testing.assert_allclose(lp, ref_lp, atol=3e-5)
         if dtype == torch.float16:  # the golden inputs are fp16 values: compare with the reference's own tokens
-            assert (np.abs(tok - g[f"fused.tok.T{t}"]) <= 1).all()
+            # row 0 has u = 0: the target is the total itself and the winner is whichever index first reaches it
+            # in each implementation's own fp32 summation order (the interval test above still holds for it)
+            assert (np.abs(tok - g[f"fused.tok.T{t}"])[1:] <= 1).all()
 
 
 def test_greedy_argmax_and_logp():

@@ -87,11 +87,12 @@ __global__ void __launch_bounds__(SCHED_THREADS) sched_step_kernel(const __grid_
   const int64_t head0 = P.ctl[CTL_HEAD], tail = P.ctl[CTL_TAIL];
   const int version = (int)P.ctl[CTL_VERSION];
   int64_t head = head0;
+  int64_t fin_base = P.ctl[CTL_FIN];
   int active = 0;
   for (int base = 0; base < P.B; base += SCHED_THREADS) {  // uniform trip count: every thread joins every scan
     const int s = base + tid;
     const bool in = s < P.B;
-    int freed = 0;
+    int freed = 0, finished = 0, fin_req = -1;
     if (in) {
       const int r = P.req[s];
       if (r < 0) {
@@ -115,8 +116,7 @@ __global__ void __launch_bounds__(SCHED_THREADS) sched_step_kernel(const __grid_
           const bool full = P.pos[s] + 1 >= P.max_len;
           if ((P.eos >= 0 && t == P.eos) || g >= lim || full) {
             P.out_len[ri] = g;
-            const unsigned long long k = atomicAdd(reinterpret_cast<unsigned long long*>(P.ctl + CTL_FIN), 1ull);
-            P.fin_ring[k % P.q_cap] = r;
+            finished = 1, fin_req = r;
             if (full && g < lim)
               atomicOr(reinterpret_cast<unsigned long long*>(P.ctl + CTL_STATUS), 2ull);  // cut short: cache full
             P.req[s] = -1;
@@ -130,6 +130,11 @@ __global__ void __launch_bounds__(SCHED_THREADS) sched_step_kernel(const __grid_
         }
       }
     }
+    // ---- finished requests enter the ring in slot order (deterministic harvest order)
+    int total_fin;
+    const int frank = block_excl_scan(finished, warp_tot, tid, total_fin);
+    if (finished) P.fin_ring[(fin_base + frank) % P.q_cap] = fin_req;
+    fin_base += total_fin;
     // ---- admit queued requests into the free slots of this chunk, in slot order
     int total_free;
     const int rank = block_excl_scan(freed, warp_tot, tid, total_free);
@@ -161,6 +166,8 @@ __global__ void __launch_bounds__(SCHED_THREADS) sched_step_kernel(const __grid_
   }
   if (tid == 0) {
     P.ctl[CTL_HEAD] = head;
+    __threadfence();  // ring entries and out_len before the count that publishes them
+    P.ctl[CTL_FIN] = fin_base;
     P.ctl[CTL_ACTIVE] = active;
     P.ctl[CTL_STEPS] += 1;
   }
