@@ -1,0 +1,477 @@
+#!/usr/bin/env python
+"""Benchmark of the UV-50M rollout-decode path ("Measurement").
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload fixed|continuous|attn] [--impl reference]
+
+Default workload ("fixed"): UV-50M (uv-50m-alpha preset, vocab 16384, random init seed 0, bf16 weights, int8 KV)
+decoding 256 concurrent sequences per GPU, prompts uniform in [32, 128] tokens, greedy, no retirement.  One STEP is
+one decode step of the whole batch (256 tokens per GPU); K defaults to 512 = the configuration's max_new.
+Under torchrun every rank runs its own replica on its own 256 sequences (weak scaling, no collective inside a step);
+the bf16 weight arena is NCCL-broadcast from rank 0 before the rollout and the generated tokens are gathered to rank 0
+after it (both timed separately and reported in "config").
+
+Prints ONE JSON line (rank 0).  `value` is device-resident throughput (inputs already in HBM); `e2e` is the same
+metric through the public step API with pinned-host token buffers copied in and out every step.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+VOCAB = 16384
+SLOTS = 256
+PROMPT_LO, PROMPT_HI = 32, 128
+
+
+def measured_peaks():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            p = json.load(f)
+        return float(p["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+# ------------------------------------------------------------------------------------------------ clocks
+class ClockSampler:
+    """nvidia-smi clocks / throttle reasons sampled every 200 ms while the timed region runs (read-only)."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc = index, [], None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "200", "-i", str(self.index)], stdout=subprocess.PIPE, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except Exception:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def __exit__(self, *a):
+        if self.proc is not None:
+            time.sleep(0.25)
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=2)
+            except Exception:
+                self.proc.kill()
+
+    def summary(self) -> dict:
+        sm, mx, reasons = [], [], set()
+        for r in self.rows:
+            try:
+                sm.append(float(r[1]))
+                mx.append(float(r[2]))
+            except Exception:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ------------------------------------------------------------------------------------------------ workload pieces
+def make_prompts(n, lo, hi, seed):
+    r = np.random.default_rng(seed)
+    lens = r.integers(lo, hi + 1, n)
+    return [r.integers(1, VOCAB, int(L)).tolist() for L in lens]
+
+
+def build_model(device, dtype):
+    import torch
+    from ultraviolet_b200.model import MathLM, make_config
+    torch.manual_seed(0)
+    m = MathLM(make_config("uv-50m-alpha", vocab_size=VOCAB))
+    return m.to(device).to(dtype).fuse_for_inference(dtype)
+
+
+def attn_bytes(pos, starts, window):
+    p, s = np.asarray(pos, np.int64), np.asarray(starts, np.int64)
+    lo = np.maximum(s, 0)
+    if window:
+        lo = np.maximum(lo, p - window + 1)
+    return int((p + 1 - lo).sum()) * 132 + 2 * len(p) * 8 * 64 * 2
+
+
+def graph_ms(body, reps=5):
+    """Median device time (ms, CUDA events on the launching stream) of one replay of `body` captured as a CUDA
+    graph: launches are enqueued back to back by the device, not paced by the host."""
+    import torch
+    body()
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        body()
+    g.replay()
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(reps):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        g.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        ts.append(e0.elapsed_time(e1))
+    return float(np.median(ts))
+
+
+def time_attention_layers(eng, st, pos, starts, rounds=4):
+    """Average device time of one decode-attention launch over the cache state of the run, per layer kind.  Each
+    round first overwrites a 256 MB buffer (L2 flush, timed alone and subtracted) so the KV bytes come from HBM as
+    they do inside a real step, where 100 MB of weights pass through L2 between two visits of a layer's cache."""
+    import torch
+    from ultraviolet_b200.kernels.decode_attn import attn_launch, default_splits
+    cfg, B = eng.cfg, st.B
+    s = eng.scratch(B)
+    qkv3 = s["qkv"].view(B, cfg.n_heads + 2 * cfg.n_kv_heads, cfg.head_dim)
+    q, out = qkv3[:, :cfg.n_heads], s["z"].view(B, cfg.n_heads, cfg.head_dim)
+    flush = torch.empty(256 << 20, dtype=torch.int8, device=eng.device)
+    t_flush = graph_ms(lambda: [flush.zero_() for _ in range(rounds)])
+    res = {}
+    for kind in ("global", "local"):
+        layers = [l for l in range(cfg.n_layers) if cfg.is_global(l) == (kind == "global")]
+        S = st.k[layers[0]].size(2)
+        splits = default_splits(B * cfg.n_kv_heads, S, eng.device)
+        window, ring = (0, False) if kind == "global" else (cfg.window, True)
+        ws = eng._workspace(s, B, splits)
+
+        def run():
+            for _ in range(rounds):
+                flush.zero_()
+                for l in layers:
+                    attn_launch(q, st.k[l], st.v[l], pos, starts, cfg.attn_scale, window, ring, st.k_scale[l],
+                                st.v_scale[l], splits, out, ws, counters=s["counters"])
+        ms = max(graph_ms(run) - t_flush, 1e-6) / (rounds * len(layers))
+        byt = attn_bytes(pos.cpu().numpy(), starts.cpu().numpy(), window)
+        res[kind] = {"ms": ms, "bytes": byt, "gbs": byt / ms / 1e6, "launches_per_step": len(layers),
+                     "splits": splits}
+    return res
+
+
+def long_context_attention(eng, rounds=4):
+    """The long-context stress shape: 64 sequences with 8192 int8 keys each, one global-layer launch per cache copy
+    (three 69 MB copies visited in turn: more than L2 holds), captured in a CUDA graph."""
+    import torch
+    from ultraviolet_b200.kernels.decode_attn import attn_launch, default_splits, workspace_for
+    dev, B, S, ctx, H, hd = eng.device, 64, 8448, 8192, 8, 64
+    g = torch.Generator(device=dev).manual_seed(1)
+    bufs = []
+    for _ in range(3):
+        bufs.append((torch.randint(-127, 128, (B, 1, S, hd), device=dev, dtype=torch.int8, generator=g),
+                     torch.randint(-127, 128, (B, 1, S, hd), device=dev, dtype=torch.int8, generator=g),
+                     (torch.rand(B, 1, S, device=dev, generator=g) * 0.02 + 0.01).half(),
+                     (torch.rand(B, 1, S, device=dev, generator=g) * 0.02 + 0.01).half()))
+    q = torch.randn(B, H, hd, device=dev, generator=g).to(eng.dtype)
+    pos = torch.full((B,), ctx - 1, device=dev, dtype=torch.long)
+    st0 = torch.zeros(B, device=dev, dtype=torch.long)
+    out = torch.empty_like(q)
+    splits = default_splits(B, ctx, dev)
+    ws = workspace_for(B, 1, H, hd, splits, dev)
+    cnt = torch.zeros(B, dtype=torch.int32, device=dev)
+
+    def run():
+        for _ in range(rounds):
+            for k, v, ks, vs in bufs:
+                attn_launch(q, k, v, pos, st0, 0.14125, 0, False, ks, vs, splits, out, ws, counters=cnt)
+    ms = graph_ms(run) / (rounds * len(bufs))
+    byt = B * ctx * 132 + 2 * B * H * hd * 2
+    return {"ms": ms, "bytes": byt, "gbs": byt / ms / 1e6, "splits": splits}
+
+
+# ------------------------------------------------------------------------------------------------ CPU baseline
+def cpu_decode_tokens_per_s(n_steps: int, slots: int = SLOTS, ctx: int = 160, seed: int = 0):
+    """The oracle's (numpy, fp32) int8-KV decode step on the host cores: `slots` sequences at context ~ctx, n_steps
+    steps.  Returns (tokens/s, seconds, threads)."""
+    import torch
+    from oracle import model as om
+    from ultraviolet_b200.model import MathLM, make_config
+    torch.manual_seed(0)
+    m = MathLM(make_config("uv-50m-alpha", vocab_size=VOCAB))
+    params = {k: om.round_bf16(v.detach().float().numpy()) for k, v in m.state_dict().items()}
+    W = om.fuse_weights(params, m.cfg, "bf16")
+    st = om.State(m.cfg, slots, ctx + n_steps + 2)
+    r = np.random.default_rng(seed)
+    for l in range(m.cfg.n_layers):
+        for c in (st.k[l], st.v[l]):
+            c[...] = r.integers(-127, 128, c.shape, dtype=np.int8)
+        for c in (st.k_scale[l], st.v_scale[l]):
+            c[...] = (r.random(c.shape) * 0.02 + 0.01).astype(np.float16)
+    st.pos[:] = r.integers(ctx - 48, ctx + 1, slots)
+    tok = r.integers(1, VOCAB, slots)
+    om.decode_step(W, m.cfg, tok, st)  # warm the BLAS threads
+    t0 = time.perf_counter()
+    for _ in range(n_steps):
+        tok = om.sample_greedy(om.decode_step(W, m.cfg, tok, st))
+    dt = time.perf_counter() - t0
+    return slots * n_steps / dt, dt, os.cpu_count()
+
+
+def run_reference_arm(args, rank, world):
+    if rank != 0:
+        return
+    steps = max(1, min(args.steps, 6))
+    for _ in range(max(0, min(args.warmup, 1))):
+        cpu_decode_tokens_per_s(1)
+    v, dt, threads = cpu_decode_tokens_per_s(steps)
+    line = {"impl": "reference", "metric": "rollout decode tokens/s", "value": v, "unit": "tokens/s",
+            "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / steps * 1e3,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp32", "data": "synthetic",
+            "config": {"workload": "fixed-batch decode, UV-50M, 256 sequences, int8 KV, greedy", "slots": SLOTS,
+                       "note": "the reference is Python and cannot travel; this arm times the numpy restatement of "
+                               "its CPU path (oracle/) on the host cores"},
+            "cpu_baseline": {"value": v, "unit": "tokens/s", "cores": threads, "kind": "port",
+                             "sample": f"{steps} decode steps of 256 sequences at context ~160 (numpy fp32, all "
+                                       "host threads via BLAS)"},
+            "e2e": {"value": v, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------------------------ continuous batching
+def run_continuous(args, m, rank, world, dev):
+    """4096 synthetic requests sharded i % W == rank, prompts U[16,256], stop length geometric(mean 600) capped at
+    2048 with EOS forced there, 512 slots per GPU, T = 1.0, Philox key per request; slots refilled on the device.
+    A step is one decode step of all 512 slots; `--steps` steps are timed after warm-up (0 = until drained)."""
+    import torch
+    import torch.distributed as dist
+    from ultraviolet_b200 import dist as uvdist
+    from ultraviolet_b200.scheduler import GpuScheduler
+    eng = m.engine
+    n_req, slots, max_new, max_prompt = 4096, 512, 2048, 256
+    r = np.random.default_rng(3)
+    lens = r.integers(16, max_prompt + 1, n_req)
+    stops = np.minimum(r.geometric(1.0 / 600.0, n_req), max_new)
+    prompts_all = [r.integers(1, VOCAB, int(L)).tolist() for L in lens]
+    mine = uvdist.shard_requests(n_req, rank, world)
+    t_bcast = uvdist.broadcast_weights(eng) if world > 1 else 0.0
+    st = m.new_state(slots, max_prompt + max_new + 16)
+    sch = GpuScheduler(eng, st, max_new=max_new, temperature=1.0, eos_id=0, seed=7, q_cap=len(mine),
+                       max_prompt=max_prompt, force_eos=True, tok_cap=int(lens[mine].sum()) + 1,
+                       out_cap=int(stops[mine].sum()) + 1)
+    sch.enqueue([prompts_all[i] for i in mine], limits=stops[mine].tolist(), keys=mine, metas=mine)
+    sch.run(max(args.warmup, 3))
+    torch.cuda.synchronize()
+    c0 = sch.counters()
+    if world > 1:
+        dist.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    done, steps = [], 0
+    with ClockSampler(dev.index or 0) as clk:
+        e0.record()
+        if args.steps > 0:
+            sch.run(args.steps)
+            steps = args.steps
+        else:
+            while len(done) < len(mine):
+                sch.run(64)
+                steps += 64
+                done += sch.harvest()
+        e1.record()
+        torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1)
+    c1 = sch.counters()
+    gen = torch.tensor([c1["generated"] - c0["generated"], c1["slot_steps"] - c0["slot_steps"], steps],
+                       dtype=torch.float64, device=dev)
+    t = torch.tensor([ms], device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dist.all_reduce(gen)
+    if rank == 0:
+        ms = float(t.item())
+        line = {"metric": "rollout decode tokens/s", "value": float(gen[0].item()) / (ms / 1e3), "unit": "tokens/s",
+                "n_gpus": world, "steps": steps, "warmup": max(args.warmup, 3), "ms_per_step": ms / max(steps, 1),
+                "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
+                "data": "synthetic",
+                "config": {"workload": "continuous batching: 4096 requests sharded over ranks, prompts U[16,256], "
+                                       "stop ~ Geometric(mean 600) <= 2048 (EOS forced), 512 slots/GPU, T=1.0, "
+                                       "device-side retire/refill, prefill through the decode step",
+                           "slot_occupancy": float(gen[1].item()) / max(float(gen[2].item()) * slots, 1.0),
+                           "generated_tokens": int(gen[0].item()), "weight_broadcast_ms": t_bcast * 1e3,
+                           "status": c1["status"]},
+                "gpu_launches": (1 + 5 * eng.cfg.n_layers + 2) * steps, "clocks": clk.summary()}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+# ------------------------------------------------------------------------------------------------ main arm
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=512)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--workload", default="fixed", choices=["fixed", "continuous", "attn"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", 0))
+    world = int(os.environ.get("WORLD_SIZE", 1))
+    local = int(os.environ.get("LOCAL_RANK", 0))
+    if args.impl == "reference":
+        return run_reference_arm(args, rank, world)
+
+    import torch
+    import torch.distributed as dist
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the decode path has no CPU fallback")
+    dev = torch.device("cuda", local)
+    torch.cuda.set_device(dev)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    from ultraviolet_b200.generate import DecodeRunner
+    from ultraviolet_b200 import dist as uvdist
+
+    dtype = torch.bfloat16
+    m = build_model(dev, dtype)
+    eng = m.engine
+    hbm_peak, peak_kind = measured_peaks()
+
+    if args.workload == "attn":
+        res = long_context_attention(eng, rounds=max(1, min(args.steps, 8)))
+        if rank == 0:
+            print(json.dumps({"metric": "decode attention HBM GB/s", "value": res["gbs"], "unit": "GB/s",
+                              "config": {"workload": "64 x 8192 int8 keys, one global-layer launch"},
+                              "roofline": {"bound": "hbm", "achieved": res["gbs"], "peak": hbm_peak, "unit": "GB/s",
+                                           "frac": res["gbs"] / hbm_peak, "traffic": None},
+                              "ms_per_launch": res["ms"], "splits": res["splits"]}), flush=True)
+        return
+    if args.workload == "continuous":
+        return run_continuous(args, m, rank, world, dev)
+
+    # ---- weights: rank 0's arena is the policy; everyone else receives it over NCCL
+    t_bcast = uvdist.broadcast_weights(eng) if world > 1 else 0.0
+
+    K, W = args.steps, max(args.warmup, 3)
+    prompts = make_prompts(SLOTS, PROMPT_LO, PROMPT_HI, seed=100 + rank)
+    max_len = PROMPT_HI + K + W + 8
+    st = m.new_state(SLOTS, max_len)
+    from ultraviolet_b200.generate import _left_pad
+    idx, starts = _left_pad(prompts, 0, dev)
+    t0 = time.perf_counter()
+    m.prefill(idx[:, :-1], starts, st)
+    torch.cuda.synchronize()
+    prefill_s = time.perf_counter() - t0
+    runner = DecodeRunner(m, st, bucket=max_len, use_graph=True, temperature=0.0)
+    tok = runner.step(idx[:, -1].contiguous()).clone()
+    for _ in range(W):
+        tok = runner.step(tok).clone()
+    torch.cuda.synchronize()
+    pos_begin = st.pos.clone()
+
+    # ---- timed region: K decode steps, device resident
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    all_tok = torch.empty(K, SLOTS, dtype=torch.long, device=dev)
+    with ClockSampler(local) as clk:
+        e0.record()
+        for i in range(K):
+            tok = runner.step(tok)
+            all_tok[i].copy_(tok)
+        e1.record()
+        torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+        dist.barrier()
+    value = world * SLOTS * K / (ms / 1e3)
+
+    # ---- rollout gather (token ids of every rank to rank 0)
+    t_gather = uvdist.gather_rollouts(all_tok.t().contiguous())[1] if world > 1 else 0.0
+
+    # ---- e2e: the same steps through the public step API with pinned host buffers in and out
+    K2 = min(K, 64)
+    host_in = torch.empty(SLOTS, dtype=torch.long).pin_memory()
+    host_out = torch.empty(SLOTS, dtype=torch.long).pin_memory()
+    host_in.copy_(tok)
+    dev_in = torch.empty(SLOTS, dtype=torch.long, device=dev)
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    t0 = time.perf_counter()
+    for _ in range(K2):
+        dev_in.copy_(host_in, non_blocking=True)
+        out = runner.step(dev_in)
+        host_out.copy_(out, non_blocking=True)
+        torch.cuda.synchronize()
+        host_in, host_out = host_out, host_in
+    e2e_s = time.perf_counter() - t0
+    if world > 1:
+        t = torch.tensor([e2e_s], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_s = float(t.item())
+    e2e = world * SLOTS * K2 / e2e_s
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    # ---- roofline of the dominant kernel of this library (decode attention), at the run's final cache state
+    att = time_attention_layers(eng, st, st.pos - 1, st.starts)
+    att_mid = att["local"] if att["local"]["ms"] * 8 >= att["global"]["ms"] * 2 else att["global"]
+    lc = long_context_attention(eng)
+    # bytes one decode step must move: weights once + KV reads + KV appends (DESIGN.md "Measurement")
+    kv_read = sum(attn_bytes((st.pos - 1).cpu().numpy(), st.starts.cpu().numpy(),
+                             0 if eng.cfg.is_global(l) else eng.cfg.window) for l in range(eng.cfg.n_layers))
+    step_bytes = 99_614_720 + kv_read + SLOTS * 10 * 132
+    line = {
+        "metric": "rollout decode tokens/s", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": K,
+        "warmup": W, "ms_per_step": ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "UV-50M fixed-batch decode: 256 sequences/GPU, prompts U[32,128], greedy, int8 KV, "
+                               f"{K} decode steps after prefill (step = 256 tokens/GPU)",
+                   "slots_per_gpu": SLOTS, "vocab": VOCAB, "weights": "random init seed 0, bf16",
+                   "l2": "per-step working set (99.6 MB weights + KV of 10 layers) exceeds L2; no flush",
+                   "prefill_s": prefill_s, "context_begin": int(pos_begin.float().mean().item()),
+                   "context_end": int(st.pos.float().mean().item()),
+                   "weight_broadcast_ms": t_bcast * 1e3, "rollout_gather_ms": t_gather * 1e3,
+                   "step_bytes_floor": step_bytes,
+                   "step_hbm_frac": step_bytes / (ms / K / 1e3) / 1e9 / hbm_peak},
+        "e2e": {"value": e2e, "unit": "tokens/s", "h2d_bytes_per_step": SLOTS * 8, "d2h_bytes_per_step": SLOTS * 8,
+                "steps": K2},
+        "gpu_launches": (1 + 5 * eng.cfg.n_layers + 1) * K,
+        "clocks": clk.summary(),
+        "roofline": {"bound": "hbm", "kernel": "attn_split_kernel (local-layer launches, 8 per step)"
+                     if att_mid is att["local"] else "attn_split_kernel (global-layer launches, 2 per step)",
+                     "achieved": att_mid["gbs"], "peak": hbm_peak, "peak_kind": peak_kind, "unit": "GB/s",
+                     "frac": att_mid["gbs"] / hbm_peak, "traffic": None,
+                     "bytes_per_launch": att_mid["bytes"], "ms_per_launch": att_mid["ms"]},
+        "attention": {"local": att["local"], "global": att["global"], "long_context_64x8192": lc,
+                      "long_context_frac_of_measured": lc["gbs"] / hbm_peak,
+                      "long_context_frac_of_nominal_8TBs": lc["gbs"] / 8000.0},
+    }
+    if not args.no_cpu_baseline:
+        v, dt, threads = cpu_decode_tokens_per_s(4)
+        line["cpu_baseline"] = {"value": v, "unit": "tokens/s", "cores": threads, "kind": "port",
+                                "sample": "4 decode steps of 256 sequences at context ~160, numpy fp32 oracle, all "
+                                          f"host threads via BLAS ({dt:.1f} s)"}
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

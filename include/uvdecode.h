@@ -183,6 +183,7 @@ int uv_sample(const void* x, int x_dtype, int64_t x_stride, int B, int V, int pr
  *
  * ctl (int64[16]): [0] head  [1] tail  [2] finished count  [3] weight version (host-written)  [4] active slots
  *                  [5] status bits  [6] steps run  [7] prompt-token tail  [8] output-slot tail
+ *                  [9] tokens generated so far  [10] active slots summed over steps (occupancy = [10] / ([6] * B))
  */
 typedef struct uv_sched_args {
   int* req; int* fed; int* gen;                 /* per slot (B,) */

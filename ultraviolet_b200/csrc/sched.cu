@@ -49,7 +49,7 @@ struct SchedParams {
   int* fin_ring;       // request indices in finishing order (ring of q_cap)
   // control words: [0] head (next request to admit) [1] tail (requests enqueued) [2] finished count
   //                [3] weight version [4] active slots after this step [5] status bits [6] steps run
-  //                [7] prompt-token tail [8] output-slot tail
+  //                [7] prompt-token tail [8] output-slot tail [9] tokens generated [10] sum of active slots per step
   int64_t* ctl;
   int B, q_cap;
   int64_t tok_cap, out_cap;
@@ -57,7 +57,8 @@ struct SchedParams {
   int64_t max_len;
 };
 
-enum { CTL_HEAD = 0, CTL_TAIL, CTL_FIN, CTL_VERSION, CTL_ACTIVE, CTL_STATUS, CTL_STEPS, CTL_TOK_TAIL, CTL_OUT_TAIL };
+enum { CTL_HEAD = 0, CTL_TAIL, CTL_FIN, CTL_VERSION, CTL_ACTIVE, CTL_STATUS, CTL_STEPS, CTL_TOK_TAIL, CTL_OUT_TAIL,
+       CTL_GENERATED, CTL_SLOT_STEPS };
 
 __device__ __forceinline__ int block_excl_scan(int v, int* warp_tot, int tid, int& total) {
   const int lane = tid & 31, warp = tid >> 5;
@@ -88,11 +89,11 @@ __global__ void __launch_bounds__(SCHED_THREADS) sched_step_kernel(const __grid_
   const int version = (int)P.ctl[CTL_VERSION];
   int64_t head = head0;
   int64_t fin_base = P.ctl[CTL_FIN];
-  int active = 0;
+  int active = 0, generated = 0;
   for (int base = 0; base < P.B; base += SCHED_THREADS) {  // uniform trip count: every thread joins every scan
     const int s = base + tid;
     const bool in = s < P.B;
-    int freed = 0, finished = 0, fin_req = -1;
+    int freed = 0, finished = 0, fin_req = -1, emitted = 0;
     if (in) {
       const int r = P.req[s];
       if (r < 0) {
@@ -113,6 +114,7 @@ __global__ void __launch_bounds__(SCHED_THREADS) sched_step_kernel(const __grid_
           P.out_tok[o] = (int)t;
           P.out_lp[o] = P.samp_lp[s];
           ++g;
+          emitted = 1;
           const bool full = P.pos[s] + 1 >= P.max_len;
           if ((P.eos >= 0 && t == P.eos) || g >= lim || full) {
             P.out_len[ri] = g;
@@ -135,6 +137,9 @@ __global__ void __launch_bounds__(SCHED_THREADS) sched_step_kernel(const __grid_
     const int frank = block_excl_scan(finished, warp_tot, tid, total_fin);
     if (finished) P.fin_ring[(fin_base + frank) % P.q_cap] = fin_req;
     fin_base += total_fin;
+    int total_emit;
+    block_excl_scan(emitted, warp_tot, tid, total_emit);
+    generated += total_emit;
     // ---- admit queued requests into the free slots of this chunk, in slot order
     int total_free;
     const int rank = block_excl_scan(freed, warp_tot, tid, total_free);
@@ -170,6 +175,8 @@ __global__ void __launch_bounds__(SCHED_THREADS) sched_step_kernel(const __grid_
     P.ctl[CTL_FIN] = fin_base;
     P.ctl[CTL_ACTIVE] = active;
     P.ctl[CTL_STEPS] += 1;
+    P.ctl[CTL_GENERATED] += generated;
+    P.ctl[CTL_SLOT_STEPS] += active;
   }
 }
 

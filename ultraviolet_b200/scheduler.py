@@ -15,7 +15,8 @@ import torch
 from . import _lib
 from .kernels._util import stream_ptr
 
-CTL_HEAD, CTL_TAIL, CTL_FIN, CTL_VERSION, CTL_ACTIVE, CTL_STATUS, CTL_STEPS, CTL_TOK_TAIL, CTL_OUT_TAIL = range(9)
+(CTL_HEAD, CTL_TAIL, CTL_FIN, CTL_VERSION, CTL_ACTIVE, CTL_STATUS, CTL_STEPS, CTL_TOK_TAIL, CTL_OUT_TAIL,
+ CTL_GENERATED, CTL_SLOT_STEPS) = range(11)
 
 
 def _pow2(n: int) -> int:
@@ -163,7 +164,8 @@ class GpuScheduler:
     def counters(self) -> dict:
         c = self.ctl.cpu().numpy()
         return dict(head=int(c[CTL_HEAD]), tail=int(c[CTL_TAIL]), finished=int(c[CTL_FIN]),
-                    active=int(c[CTL_ACTIVE]), status=int(c[CTL_STATUS]), steps=int(c[CTL_STEPS]))
+                    active=int(c[CTL_ACTIVE]), status=int(c[CTL_STATUS]), steps=int(c[CTL_STEPS]),
+                    generated=int(c[CTL_GENERATED]), slot_steps=int(c[CTL_SLOT_STEPS]))
 
     def harvest(self):
         """Return the requests that finished since the last call as [(meta, tokens list, logp float32 array,
