@@ -1,0 +1,66 @@
+"""Host-side logic that needs no GPU: configuration, parameter container, state layout, loud failures."""
+import numpy as np
+import pytest
+import torch
+
+from tests import golden_inputs as gi
+from tests.helpers import build_model, golden
+
+
+def test_preset_geometry():
+    from ultraviolet_b200.config import make_config
+    c = make_config("uv-50m-alpha", vocab_size=16384)
+    assert (c.d_model, c.n_layers, c.n_heads, c.n_kv_heads, c.head_dim, c.d_ff, c.window) == (640, 10, 8, 1, 64,
+                                                                                             1664, 256)
+    assert [l for l in range(10) if c.is_global(l)] == [4, 9]
+    assert [l for l in range(10) if c.has_ve(l)] == [1, 4, 7]
+    assert c.rope_pairs == 16 and abs(c.attn_scale - 0.14125) < 1e-9 and c.gate_channels == 128
+    p = c.param_counts()
+    assert p["non_embedding"] == 39_321_600 and p["embedding_tied"] == 10_485_760 and p["value_embedding"] == 1_048_576
+    c.check_decode_supported()
+    with pytest.raises(NotImplementedError):
+        make_config("uv-50m-alpha", mudd=True).check_decode_supported()
+
+
+@pytest.mark.parametrize("name", sorted(gi.model_specs()))
+def test_parameter_container_matches_reference_init(name):
+    """Same names, shapes, creation order and RNG consumption as the reference's MathLM: the digest stored by
+    make_golden.py is the reference's own state dict."""
+    spec = gi.model_specs()[name]
+    m = build_model(spec)
+    assert gi.state_sha(m.state_dict()) == str(golden("model")[name + ".weights_sha"])
+    if name == "uv50m":
+        assert sum(p.numel() for p in m.parameters()) == 50_866_352
+
+
+def test_state_layout_and_bytes():
+    from ultraviolet_b200.config import make_config
+    from ultraviolet_b200.fast_decode import KernelDecodeState, kv_bytes_per_seq
+    c = make_config("uv-50m-alpha", vocab_size=16384)
+    st = KernelDecodeState(c, 4, 1000, torch.bfloat16, "cpu")
+    assert st.k[0].shape == (4, 1, 256, 64) and st.k[4].shape == (4, 1, 1000, 64) and st.k[0].dtype == torch.int8
+    assert st.k_scale[4].shape == (4, 1, 1000) and st.k_scale[4].dtype == torch.float16
+    assert st.nbytes() == 4 * kv_bytes_per_seq(c, 1000)
+    assert kv_bytes_per_seq(c, 4096) == 132 * (2 * 4096 + 8 * 256)   # 132 B per token per layer
+    with pytest.raises(NotImplementedError):
+        KernelDecodeState(c, 1, 8, torch.bfloat16, "cpu", kv_dtype="fp16")
+
+
+def test_no_cpu_fallback():
+    from ultraviolet_b200.kernels import decode_attention, quantize_kv
+    spec = gi.model_specs()["tiny"]
+    m = build_model(spec)
+    with pytest.raises(RuntimeError):
+        m.fuse_for_inference(torch.bfloat16)          # CPU model: the engine refuses
+    with pytest.raises(RuntimeError):
+        quantize_kv(torch.zeros(2, 64))
+    with pytest.raises(RuntimeError):
+        m.decode_step(torch.zeros(1, dtype=torch.long), None, 8)
+
+
+def test_missing_library_fails_loudly(monkeypatch, tmp_path):
+    from ultraviolet_b200 import _lib
+    monkeypatch.setattr(_lib, "_lib", None)
+    monkeypatch.setattr(_lib, "LIB_PATH", str(tmp_path / "libuvdecode.so"))
+    with pytest.raises(_lib.UvError):
+        _lib.lib()
