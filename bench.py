@@ -362,7 +362,7 @@ def main():
 
     K, W = args.steps, max(args.warmup, 3)
     prompts = make_prompts(SLOTS, PROMPT_LO, PROMPT_HI, seed=100 + rank)
-    max_len = PROMPT_HI + K + W + 8
+    max_len = PROMPT_HI + K + W + min(K, 64) + 16
     st = m.new_state(SLOTS, max_len)
     from ultraviolet_b200.generate import _left_pad
     idx, starts = _left_pad(prompts, 0, dev)

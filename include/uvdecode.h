@@ -100,6 +100,8 @@ typedef struct uv_attn_args {
   void* out;              /* (B, H, hd) in q_dtype */
   int64_t sob, soh;
   int B, H, KH, hd, S;
+  int S_alloc;            /* slots allocated per (b, kv head) row, 0 = S.  A linear (non-ring) cache whose rows are
+                             allocated to a multiple of 8 slots takes the TMA path even when S itself is not */
   int window, ring;
   float scale;
   int num_splits;         /* >= 1; > 1 needs workspace */
@@ -138,7 +140,7 @@ int uv_decode_attn(const uv_attn_args* args, void* stream);
  *                of q and k, partial RoPE with angles pos * inv_freq (when inv_freq != NULL; pairs j <-> j + n_pairs),
  *                then K and V quantised and appended to the int8 cache at slot pos (ring: pos % S) when k_cache !=
  *                NULL (Attention.qkv, ultraviolet/model.py:302-320; kv_write, kv_quant.py:26-36); row_map as in
- *                uv_attn_args (cache row of batch entry b)
+ *                uv_attn_args (cache row of batch entry b); S_alloc (0 = S) = slots allocated per cache row
  * uv_resid_norm: h = lambdas[0]*x + lambdas[1]*a; hn = rms_norm(h)     (Block.finish, model.py:567-571)
  * uv_swiglu:     act = silu(gu[:, :f]) * gu[:, f:]                     (MLP.forward, model.py:388-391)
  */
@@ -147,7 +149,7 @@ int uv_embed_norm(const int64_t* tok, const void* embed, int dtype, int64_t voca
 int uv_qkv_post(void* qkv, const void* xn, const int64_t* tok, const void* value_embed, const void* ve_gate,
                 const float* inv_freq, const int64_t* pos, int8_t* k_cache, int8_t* v_cache, uint16_t* k_scale,
                 uint16_t* v_scale, const int64_t* row_map, int* oob_count, int dtype, int64_t vocab, int B, int H, int K,
-                int hd, int d, int S, int ring, int ve_ch, int n_pairs, void* stream);
+                int hd, int d, int S, int S_alloc, int ring, int ve_ch, int n_pairs, void* stream);
 int uv_resid_norm(const void* x, const void* a, const float* lambdas, int dtype, int d, void* h, void* hn, int B,
                   void* stream);
 int uv_swiglu(const void* gu, int dtype, int f, void* act, int B, void* stream);

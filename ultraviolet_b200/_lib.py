@@ -33,7 +33,7 @@ class AttnArgs(C.Structure):
         ("ssb", C.c_int64), ("ssh", C.c_int64), ("stb", C.c_int64), ("sth", C.c_int64),
         ("pos", C.c_void_p), ("starts", C.c_void_p), ("row_map", C.c_void_p),
         ("out", C.c_void_p), ("sob", C.c_int64), ("soh", C.c_int64),
-        ("B", C.c_int), ("H", C.c_int), ("KH", C.c_int), ("hd", C.c_int), ("S", C.c_int),
+        ("B", C.c_int), ("H", C.c_int), ("KH", C.c_int), ("hd", C.c_int), ("S", C.c_int), ("S_alloc", C.c_int),
         ("window", C.c_int), ("ring", C.c_int), ("scale", C.c_float), ("num_splits", C.c_int),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("counters", C.c_void_p), ("status", C.c_void_p),
         ("v_cur", C.c_void_p), ("v_cur_sb", C.c_int64), ("v_cur_sh", C.c_int64), ("xsa_alpha", C.c_void_p), ("xsa_eps", C.c_float),
@@ -64,7 +64,7 @@ SIGNATURES = {
     "uv_decode_attn": (C.c_int, [C.POINTER(AttnArgs), C.c_void_p]),
     "uv_embed_norm": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int64, C.c_int, C.c_void_p, C.c_void_p, C.c_int,
                                 C.c_void_p]),
-    "uv_qkv_post": (C.c_int, [C.c_void_p] * 13 + [C.c_int, C.c_int64] + [C.c_int] * 9 + [C.c_void_p]),
+    "uv_qkv_post": (C.c_int, [C.c_void_p] * 13 + [C.c_int, C.c_int64] + [C.c_int] * 10 + [C.c_void_p]),
     "uv_resid_norm": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_int,
                                 C.c_void_p]),
     "uv_swiglu": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_int, C.c_void_p]),

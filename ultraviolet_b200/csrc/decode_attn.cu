@@ -796,7 +796,10 @@ extern "C" int uv_decode_attn(const uv_attn_args* a, void* stream) {
   }
   // bulk-copy (TMA) path: tiles must be linear and every piece 16-byte aligned
   bool bulk = a->sks == hd && a->svs == hd;
-  bulk = bulk && (a->ring ? a->S % TILE == 0 : a->S % 8 == 0);
+  // linear caches are read in whole 8-slot groups: the row allocation (S_alloc slots, >= S) must cover the group
+  // that holds slot S - 1
+  const int s_alloc = a->S_alloc > a->S ? a->S_alloc : a->S;
+  bulk = bulk && (a->ring ? a->S % TILE == 0 : s_alloc % 8 == 0);
   bulk = bulk && aligned16(a->k_scale) && aligned16(a->v_scale) &&
          ((a->ssb | a->ssh | a->stb | a->sth) & 7) == 0;  // scale rows start on 16-byte boundaries (fp16 elements)
   cudaStream_t st = static_cast<cudaStream_t>(stream);

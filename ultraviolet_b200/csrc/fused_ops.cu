@@ -28,6 +28,10 @@ template <typename T> __device__ __forceinline__ void st2(T* p, float a, float b
 }
 
 // ------------------------------------------------------------------------------------------------ embed + norms
+// Rows of up to ROW_MAX elements live in registers (lane owns pairs 2*lane + 64*j): one global read, one write.
+constexpr int ROW_MAX = 1024;
+constexpr int ROW_J = ROW_MAX / 64;
+
 // x = rms_norm(embed[tok]); xn = rms_norm(x)   (fast_decode.py:284 and the first layer's pre-norm, :303)
 template <typename T>
 __global__ void __launch_bounds__(128) embed_norm_kernel(const int64_t* __restrict__ tok, const T* __restrict__ embed,
@@ -41,23 +45,29 @@ __global__ void __launch_bounds__(128) embed_norm_kernel(const int64_t* __restri
   const T* e = embed + t * d;
   T* xr = x + (int64_t)row * d;
   T* nr = xn + (int64_t)row * d;
+  float2 v[ROW_J];
   float ss = 0.f;
-  for (int i = 2 * lane; i < d; i += 64) {
-    const float2 v = ld2<T>(e + i);
-    ss += v.x * v.x + v.y * v.y;
+#pragma unroll
+  for (int j = 0; j < ROW_J; ++j) {
+    const int i = 2 * lane + 64 * j;
+    v[j] = i < d ? ld2<T>(e + i) : make_float2(0.f, 0.f);
+    ss += v[j].x * v[j].x + v[j].y * v[j].y;
   }
   float inv = rsqrtf(warp_sum(ss) / (float)d + RMS_EPS);
   ss = 0.f;
-  for (int i = 2 * lane; i < d; i += 64) {
-    const float2 v = ld2<T>(e + i);
-    const float a = rnd<T>(v.x * inv), b = rnd<T>(v.y * inv);
-    st2<T>(xr + i, a, b);
-    ss += a * a + b * b;
+#pragma unroll
+  for (int j = 0; j < ROW_J; ++j) {
+    v[j].x = rnd<T>(v[j].x * inv), v[j].y = rnd<T>(v[j].y * inv);
+    ss += v[j].x * v[j].x + v[j].y * v[j].y;
   }
   inv = rsqrtf(warp_sum(ss) / (float)d + RMS_EPS);
-  for (int i = 2 * lane; i < d; i += 64) {
-    const float2 v = ld2<T>(xr + i);
-    st2<T>(nr + i, v.x * inv, v.y * inv);
+#pragma unroll
+  for (int j = 0; j < ROW_J; ++j) {
+    const int i = 2 * lane + 64 * j;
+    if (i < d) {
+      st2<T>(xr + i, v[j].x, v[j].y);
+      st2<T>(nr + i, v[j].x * inv, v[j].y * inv);
+    }
   }
 }
 
@@ -75,18 +85,28 @@ __global__ void __launch_bounds__(128) resid_norm_kernel(const T* __restrict__ x
   const T* ar = a + (int64_t)row * d;
   T* hr = h + (int64_t)row * d;
   T* nr = hn + (int64_t)row * d;
+  float2 v[ROW_J];
   float ss = 0.f;
-  for (int i = 2 * lane; i < d; i += 64) {
-    const float2 xv = ld2<T>(xr + i), av = ld2<T>(ar + i);
-    const float h0 = rnd<T>(rnd<T>(l0 * xv.x) + rnd<T>(l1 * av.x));
-    const float h1 = rnd<T>(rnd<T>(l0 * xv.y) + rnd<T>(l1 * av.y));
-    st2<T>(hr + i, h0, h1);
-    ss += h0 * h0 + h1 * h1;
+#pragma unroll
+  for (int j = 0; j < ROW_J; ++j) {
+    const int i = 2 * lane + 64 * j;
+    if (i < d) {
+      const float2 xv = ld2<T>(xr + i), av = ld2<T>(ar + i);
+      v[j].x = rnd<T>(rnd<T>(l0 * xv.x) + rnd<T>(l1 * av.x));
+      v[j].y = rnd<T>(rnd<T>(l0 * xv.y) + rnd<T>(l1 * av.y));
+    } else {
+      v[j] = make_float2(0.f, 0.f);
+    }
+    ss += v[j].x * v[j].x + v[j].y * v[j].y;
   }
   const float inv = rsqrtf(warp_sum(ss) / (float)d + RMS_EPS);
-  for (int i = 2 * lane; i < d; i += 64) {
-    const float2 v = ld2<T>(hr + i);
-    st2<T>(nr + i, v.x * inv, v.y * inv);
+#pragma unroll
+  for (int j = 0; j < ROW_J; ++j) {
+    const int i = 2 * lane + 64 * j;
+    if (i < d) {
+      st2<T>(hr + i, v[j].x, v[j].y);
+      st2<T>(nr + i, v[j].x * inv, v[j].y * inv);
+    }
   }
 }
 
@@ -126,7 +146,7 @@ struct QkvPostParams {
   const int64_t* row_map;
   int* oob;
   int64_t vocab;
-  int B, H, K, d, S, ring, ve_ch, n_pairs;
+  int B, H, K, d, S, S_alloc, ring, ve_ch, n_pairs;
 };
 
 template <typename T, int HD>
@@ -202,7 +222,7 @@ __global__ void __launch_bounds__(128) qkv_post_kernel(const __grid_constant__ Q
       return;
     }
     const int64_t cb = P.row_map ? P.row_map[b] : b;
-    const int64_t dst = (cb * P.K + kh) * P.S + p;
+    const int64_t dst = (cb * P.K + kh) * P.S_alloc + p;  // rows may be allocated longer than S
     int8_t* crow = (isv ? P.v_cache : P.k_cache) + dst * HD;
     if (act) {
       if constexpr (E == 4) *reinterpret_cast<char4*>(crow + lane * 4) = make_char4(q8[0], q8[1], q8[2], q8[3]);
@@ -234,7 +254,7 @@ extern "C" int uv_embed_norm(const int64_t* tok, const void* embed, int dtype, i
                              void* xn, int B, void* stream) {
   if (B == 0) return UV_OK;
   if (!tok || !embed || !x || !xn || B < 0 || vocab < 1) return UV_ERR_ARG;
-  if (d < 2 || (d & 1)) return UV_ERR_SHAPE;
+  if (d < 2 || (d & 1) || d > ROW_MAX) return UV_ERR_SHAPE;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const unsigned grid = (unsigned)((B + 3) / 4);
   if (dtype == UV_F16)
@@ -252,7 +272,7 @@ extern "C" int uv_resid_norm(const void* x, const void* a, const float* lambdas,
                              int B, void* stream) {
   if (B == 0) return UV_OK;
   if (!x || !a || !lambdas || !h || !hn || B < 0) return UV_ERR_ARG;
-  if (d < 2 || (d & 1)) return UV_ERR_SHAPE;
+  if (d < 2 || (d & 1) || d > ROW_MAX) return UV_ERR_SHAPE;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const unsigned grid = (unsigned)((B + 3) / 4);
   if (dtype == UV_F16)
@@ -286,7 +306,7 @@ extern "C" int uv_qkv_post(void* qkv, const void* xn, const int64_t* tok, const 
                            const void* ve_gate, const float* inv_freq, const int64_t* pos, int8_t* k_cache,
                            int8_t* v_cache, uint16_t* k_scale, uint16_t* v_scale, const int64_t* row_map,
                            int* oob_count, int dtype, int64_t vocab, int B, int H, int K, int hd, int d, int S,
-                           int ring, int ve_ch, int n_pairs, void* stream) {
+                           int S_alloc, int ring, int ve_ch, int n_pairs, void* stream) {
   if (B == 0) return UV_OK;
   if (!qkv || !pos || B < 0 || H < 1 || K < 1) return UV_ERR_ARG;
   if (ve_gate && (!xn || !tok || !value_embed || ve_ch < 1)) return UV_ERR_ARG;
@@ -300,7 +320,7 @@ extern "C" int uv_qkv_post(void* qkv, const void* xn, const int64_t* tok, const 
   QkvPostParams P{};
   P.qkv = qkv, P.xn = xn, P.tok = tok, P.value_embed = value_embed, P.ve_gate = ve_gate, P.inv_freq = inv_freq;
   P.pos = pos, P.k_cache = k_cache, P.v_cache = v_cache, P.k_scale = k_scale, P.v_scale = v_scale, P.row_map = row_map, P.oob = oob_count;
-  P.vocab = vocab, P.B = B, P.H = H, P.K = K, P.d = d, P.S = S, P.ring = ring, P.ve_ch = ve_ch, P.n_pairs = n_pairs;
+  P.vocab = vocab, P.B = B, P.H = H, P.K = K, P.d = d, P.S = S, P.S_alloc = S_alloc > S ? S_alloc : S, P.ring = ring, P.ve_ch = ve_ch, P.n_pairs = n_pairs;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (dtype == UV_F16) return launch_qkv_post<__half>(P, hd, st);
   if (dtype == UV_BF16) return launch_qkv_post<__nv_bfloat16>(P, hd, st);

@@ -77,7 +77,7 @@ __global__ void __launch_bounds__(SAMPLE_THREADS) sample_kernel(const __grid_con
   float cap_a = P.a;
   auto zof = [&](int i) {
     const float x = to_f32<T>(xr[i]);
-    return P.precapped ? x : P.a / (1.0f + expf(-(x + P.b) * inv_c));
+    return P.precapped ? x : __fdividef(P.a, 1.0f + __expf(-(x + P.b) * inv_c));
   };
   if (P.precapped) {  // no analytic bound on z: take the row maximum as the reference point of the exponentials
     float m = -INFINITY;
@@ -98,7 +98,7 @@ __global__ void __launch_bounds__(SAMPLE_THREADS) sample_kernel(const __grid_con
   for (int i = tid; i < V; i += SAMPLE_THREADS) {
     const float z = zof(i);
     if (z > best) best = z, best_i = i;  // strided ascending per thread: first index wins within a thread
-    e_sm[i + i / CH] = expf((z - cap_a) * P.inv_t);
+    e_sm[i + i / CH] = __expf((z - cap_a) * P.inv_t);
   }
   if (tid == 0) s_tok = V - 1;
   __syncthreads();

@@ -172,7 +172,7 @@ class DecodeEngine:
                     w["value_embed"].data_ptr() if self.use_ve else None, ve_gate,
                     self.inv_freq.data_ptr() if rope and cfg.rope_pairs else None, pos.data_ptr(),
                     kc.data_ptr(), vc.data_ptr(), ks.data_ptr(), vs.data_ptr(), rm,
-                    s["oob"].data_ptr(), dt, cfg.vocab_size, B, H, K, hd, d, S, int(not glob),
+                    s["oob"].data_ptr(), dt, cfg.vocab_size, B, H, K, hd, d, S, kc.stride(1) // hd, int(not glob),
                     cfg.ve_gate_channels, cfg.rope_pairs, sp), "uv_qkv_post")
                 if glob:
                     ctx = min(g_len or S, S)

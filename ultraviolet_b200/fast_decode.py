@@ -34,11 +34,14 @@ class KernelDecodeState:
         self.mix: dict[int, dict] = {}
         for l in range(cfg.n_layers):
             S = max_len if cfg.is_global(l) else self.local_len
-            shp = (B, cfg.n_kv_heads, S, cfg.head_dim)
-            self.k.append(torch.zeros(shp, dtype=torch.int8, device=device))
-            self.v.append(torch.zeros(shp, dtype=torch.int8, device=device))
-            self.k_scale.append(torch.zeros(shp[:3], dtype=torch.float16, device=device))
-            self.v_scale.append(torch.zeros(shp[:3], dtype=torch.float16, device=device))
+            # linear (global) rows are allocated to a multiple of 8 slots so the attention kernel's bulk copies can
+            # fetch whole 16-byte groups of scales; the tensors exposed are the reference's (B, K, S, hd) / (B, K, S)
+            Sa = S if not cfg.is_global(l) else (S + 7) // 8 * 8
+            shp = (B, cfg.n_kv_heads, Sa, cfg.head_dim)
+            self.k.append(torch.zeros(shp, dtype=torch.int8, device=device)[:, :, :S])
+            self.v.append(torch.zeros(shp, dtype=torch.int8, device=device)[:, :, :S])
+            self.k_scale.append(torch.zeros(shp[:3], dtype=torch.float16, device=device)[:, :, :S])
+            self.v_scale.append(torch.zeros(shp[:3], dtype=torch.float16, device=device)[:, :, :S])
         self.pos = torch.zeros(B, dtype=torch.long, device=device)
         self.starts = torch.zeros(B, dtype=torch.long, device=device)
         self.host_pos = np.zeros(B, dtype=np.int64)

@@ -26,6 +26,22 @@ def default_splits(n_bk: int, ctx: int, device=None, min_chunk: int | None = Non
     return int(_lib.lib().uv_default_splits(int(n_bk), int(ctx), _n_sm(dev)))
 
 
+def _row_alloc(k_cache: Tensor, v_cache: Tensor, k_scale: Tensor, v_scale: Tensor, S: int) -> int:
+    """Slots really allocated per cache row when the tensors are [:, :, :S] views of a longer allocation (all four
+    must agree and the padded rows must lie inside their storages); else S."""
+    hd = k_cache.size(-1)
+    if k_cache.stride(2) != hd or k_cache.stride(1) % hd:
+        return S
+    alloc = k_cache.stride(1) // hd
+    if alloc <= S or v_cache.stride(1) != alloc * hd or k_scale.stride(1) != alloc or v_scale.stride(1) != alloc:
+        return S
+    for t, row in ((k_cache, alloc * hd), (v_cache, alloc * hd), (k_scale, alloc), (v_scale, alloc)):
+        last = t.storage_offset() + (t.size(0) - 1) * t.stride(0) + (t.size(1) - 1) * t.stride(1) + row
+        if last * t.element_size() > t.untyped_storage().nbytes():
+            return S
+    return alloc
+
+
 def attn_launch(q: Tensor, k_cache: Tensor, v_cache: Tensor, pos: Tensor, starts: Tensor, scale: float, window: int,
                 ring: bool, k_scale: Tensor, v_scale: Tensor, num_splits: int, out: Tensor,
                 workspace: Tensor | None = None, v_cur: Tensor | None = None, xsa_alpha: Tensor | None = None,
@@ -45,6 +61,7 @@ def attn_launch(q: Tensor, k_cache: Tensor, v_cache: Tensor, pos: Tensor, starts
     a.pos, a.starts = pos.data_ptr(), starts.data_ptr()
     a.out, a.sob, a.soh = out.data_ptr(), out.stride(0), out.stride(1)
     a.B, a.H, a.KH, a.hd, a.S = B, H, KH, hd, S
+    a.S_alloc = _row_alloc(k_cache, v_cache, k_scale, v_scale, S)
     a.window, a.ring, a.scale, a.num_splits = int(window), int(bool(ring)), float(scale), int(num_splits)
     if num_splits > 1:
         a.workspace, a.workspace_bytes = workspace.data_ptr(), workspace.numel() * workspace.element_size()

@@ -60,6 +60,9 @@ def kv_append(k_cache: Tensor, v_cache: Tensor, k_scale: Tensor, v_scale: Tensor
     launch, slot computed on the device from pos (ring: pos % S)."""
     need_cuda(k_cache, v_cache, k_scale, v_scale, pos, k, v)
     B, KH, S, hd = k_cache.shape
+    if not (k_cache.is_contiguous() and v_cache.is_contiguous() and k_scale.is_contiguous()
+            and v_scale.is_contiguous()):
+        raise RuntimeError("kv_append needs contiguous caches and scales")
     k2, v2 = _rows(k, hd), _rows(v, hd)
     if k2.dtype != v2.dtype:
         v2 = v2.to(k2.dtype)
