@@ -37,7 +37,8 @@ enum {
   UV_ERR_SHAPE = -3,      /* head_dim / group size / vocabulary outside the compiled set */
   UV_ERR_ALIGN = -4,      /* pointer or stride alignment requirement not met */
   UV_ERR_WORKSPACE = -5,  /* workspace missing or too small */
-  UV_ERR_CUDA = -6        /* a CUDA runtime call failed; see uv_last_cuda_error() */
+  UV_ERR_CUDA = -6,       /* a CUDA runtime call failed; see uv_last_cuda_error() */
+  UV_ERR_STATIC_LIMIT = -7 /* problem larger than the built-in scratch of uv_decode_attn_static */
 };
 
 int uv_abi_version(void);
@@ -128,6 +129,25 @@ size_t uv_decode_attn_workspace_bytes(int B, int KH, int G, int hd, int num_spli
  * decode_attn.py:121-129, retuned for 148-SM parts with 64-key TMA tiles). */
 int uv_default_splits(int n_bk, int ctx, int n_sm);
 int uv_decode_attn(const uv_attn_args* args, void* stream);
+
+/* uv_decode_attn_static: the same attention, for hosts that cannot allocate device memory.  (No counterpart in the
+ * reference: its Python op allocates split partials with torch.empty on every call.)
+ *
+ * Who needs it: an embedding runtime that owns no CUDA allocator (a service calling this library over FFI whose HBM
+ * is already reserved in full for the KV cache), or a serving loop that is not allowed to call cudaMalloc on its
+ * latency path because device allocation synchronises the whole GPU.  Such callers still pass q, the caches, pos /
+ * starts and out; args->workspace, workspace_bytes and counters are IGNORED.  The split partials and the arrival
+ * counters live in a device array built into the library: 4 MiB of partials and 4096 cache rows (B*KH), held by
+ * every GPU that loads the library until the process exits.  Larger problems -- uv_decode_attn_workspace_bytes(...)
+ * above 4 MiB or B*KH above 4096 -- are rejected with UV_ERR_STATIC_LIMIT and nothing is launched.
+ *
+ * The first call on a device looks the array's device address up (cudaGetSymbolAddress, cached per device); make
+ * that first call outside any stream capture.  All calls share the one array, which keeps the previous call's
+ * contents: the counters are cleared on `stream` before each launch, the partials are fully rewritten before they
+ * are read.  Two calls whose kernels can overlap on the GPU (different streams, no dependency) race on the array
+ * and produce undefined output; serialise them.  The function calls no cudaMalloc / cudaFree and no allocating
+ * library routine. */
+int uv_decode_attn_static(const uv_attn_args* args, void* stream);
 
 /* ---------------------------------------------------------------------------------------------------------------
  * (d) Row-wise fused kernels of one decode step (the elementwise chain of decode_step_fast, ultraviolet/kernels/

@@ -62,6 +62,7 @@ SIGNATURES = {
     "uv_decode_attn_workspace_bytes": (C.c_size_t, [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int]),
     "uv_default_splits": (C.c_int, [C.c_int, C.c_int, C.c_int]),
     "uv_decode_attn": (C.c_int, [C.POINTER(AttnArgs), C.c_void_p]),
+    "uv_decode_attn_static": (C.c_int, [C.POINTER(AttnArgs), C.c_void_p]),
     "uv_embed_norm": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int64, C.c_int, C.c_void_p, C.c_void_p, C.c_int,
                                 C.c_void_p]),
     "uv_qkv_post": (C.c_int, [C.c_void_p] * 13 + [C.c_int, C.c_int64] + [C.c_int] * 10 + [C.c_void_p]),

@@ -19,6 +19,8 @@ extern "C" const char* uv_error_string(int code) {
     case UV_ERR_ALIGN: return "pointer or stride alignment requirement not met";
     case UV_ERR_WORKSPACE: return "workspace missing or too small";
     case UV_ERR_CUDA: return "CUDA runtime error (see uv_last_cuda_error)";
+    case UV_ERR_STATIC_LIMIT:
+      return "problem exceeds the built-in scratch of uv_decode_attn_static (4 MiB of split partials, 4096 cache rows)";
     default: return "unknown error code";
   }
 }

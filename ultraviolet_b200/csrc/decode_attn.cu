@@ -21,6 +21,7 @@
 // Each of the 4 warps owns 32 keys of every tile with its own online-softmax state (the accumulator is rescaled
 // only when a row maximum moves); tiles fully inside [lo, hi] take a mask-free path.  Warp states are merged
 // through shared memory with log-sum-exp weights, and splits > 1 are merged by a second small kernel.
+#include <mutex>
 #include <type_traits>
 
 #include "common.cuh"
@@ -805,4 +806,69 @@ extern "C" int uv_decode_attn(const uv_attn_args* a, void* stream) {
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (a->q_dtype == UV_F16) return dispatch_hd<__half>(P, hd, bulk, st);
   return dispatch_hd<__nv_bfloat16>(P, hd, bulk, st);
+}
+
+
+// ------------------------------------------------------------------------------------------------ built-in scratch
+// uv_decode_attn_static: split-K decode attention for callers that may not allocate device memory at all.
+// The split partials and the arrival counters live in this file-scope device array instead of a caller workspace.
+// Every GPU that loads the library holds the array (4 MiB + 16 KiB) until the process exits.
+#define UV_STATIC_PARTIAL_BYTES (4u << 20)
+#define UV_STATIC_MAX_ROWS 4096
+static __device__ __align__(256) unsigned char uv_static_scratch[UV_STATIC_PARTIAL_BYTES +
+                                                                 UV_STATIC_MAX_ROWS * sizeof(int)];
+
+namespace uv {
+constexpr int MAX_DEVICES = 64;
+static void* g_static_ptr[MAX_DEVICES] = {nullptr};
+static std::mutex g_static_mu;
+
+// Device address of uv_static_scratch on the CURRENT device.  The array's name is only a host-side handle; the
+// address a kernel can use comes from cudaGetSymbolAddress, looked up once per device and cached.
+static int static_scratch_ptr(void** out) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= MAX_DEVICES) {
+    set_last_cuda_error((int)(e != cudaSuccess ? e : cudaErrorInvalidDevice));
+    return UV_ERR_CUDA;
+  }
+  std::lock_guard<std::mutex> lock(g_static_mu);
+  if (g_static_ptr[dev] == nullptr) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, uv_static_scratch);
+    if (e != cudaSuccess || p == nullptr) {
+      set_last_cuda_error((int)e);
+      return UV_ERR_CUDA;
+    }
+    g_static_ptr[dev] = p;
+  }
+  *out = g_static_ptr[dev];
+  return UV_OK;
+}
+}  // namespace uv
+
+extern "C" int uv_decode_attn_static(const uv_attn_args* a, void* stream) {
+  using namespace uv;
+  if (!a) return UV_ERR_ARG;
+  if (a->B <= 0 || a->KH <= 0 || a->H <= 0 || a->num_splits < 1) return a->B == 0 ? UV_OK : UV_ERR_ARG;
+  const size_t need = uv_decode_attn_workspace_bytes(a->B, a->KH, a->H / a->KH, a->hd, a->num_splits);
+  if (need > UV_STATIC_PARTIAL_BYTES || (int64_t)a->B * a->KH > UV_STATIC_MAX_ROWS) return UV_ERR_STATIC_LIMIT;
+  void* base = nullptr;
+  const int rc = static_scratch_ptr(&base);
+  if (rc != UV_OK) return rc;
+  uv_attn_args b = *a;
+  b.workspace = base;
+  b.workspace_bytes = UV_STATIC_PARTIAL_BYTES;
+  b.counters = nullptr;
+  if (a->num_splits > 1) {
+    // the array keeps whatever the previous call left: the arrival counters must start at zero
+    b.counters = reinterpret_cast<int*>(static_cast<unsigned char*>(base) + UV_STATIC_PARTIAL_BYTES);
+    cudaError_t e = cudaMemsetAsync(b.counters, 0, (size_t)a->B * a->KH * sizeof(int),
+                                    static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) {
+      set_last_cuda_error((int)e);
+      return UV_ERR_CUDA;
+    }
+  }
+  return uv_decode_attn(&b, stream);
 }
