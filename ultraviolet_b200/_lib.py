@@ -10,7 +10,7 @@ import os
 import threading
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(HERE, "libuvdecode.so")
+LIB_PATH = os.environ.get("UVDECODE_LIB") or os.path.join(HERE, "libuvdecode.so")
 
 UV_F32, UV_F16, UV_BF16, UV_I8 = 0, 1, 2, 3
 UV_ABI_VERSION = 1

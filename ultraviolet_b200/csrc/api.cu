@@ -1,9 +1,18 @@
 // Library-level entry points: ABI version, error strings, per-thread CUDA error slot.
+#include <stdlib.h>
+
 #include "common.cuh"
 
 namespace uv {
 static thread_local int g_last_cuda_error = 0;
 void set_last_cuda_error(int e) { g_last_cuda_error = e; }
+bool pdl_enabled() {
+  static const bool on = [] {
+    const char* v = getenv("UVDECODE_PDL");
+    return v && v[0] == '1';  // opt-in: measured neutral-to-slightly-slower inside CUDA graphs on B200
+  }();
+  return on;
+}
 }  // namespace uv
 
 extern "C" int uv_abi_version(void) { return UV_ABI_VERSION; }

@@ -28,9 +28,18 @@
 
 namespace uv {
 
-constexpr int TILE = 128;   // keys per pipeline stage
-constexpr int NSTAGE = 3;
-constexpr int NWARP = 4;
+#ifndef UV_ATTN_TILE
+#define UV_ATTN_TILE 128
+#endif
+#ifndef UV_ATTN_NSTAGE
+#define UV_ATTN_NSTAGE 3
+#endif
+#ifndef UV_ATTN_NWARP
+#define UV_ATTN_NWARP 4
+#endif
+constexpr int TILE = UV_ATTN_TILE;   // keys per pipeline stage
+constexpr int NSTAGE = UV_ATTN_NSTAGE;
+constexpr int NWARP = UV_ATTN_NWARP;
 constexpr int NTHREAD = NWARP * 32;
 constexpr int WKEYS = TILE / NWARP;  // keys one warp consumes per stage
 constexpr unsigned long long WAIT_NS = 200ull * 1000 * 1000;  // a tile that has not landed after 200 ms is abandoned
@@ -297,6 +306,8 @@ __global__ void __launch_bounds__(NTHREAD) attn_split_kernel(const __grid_consta
   const int bk = blockIdx.x, sid = blockIdx.y;
   const int b = bk / P.KH, h = bk % P.KH;
   const int G = P.G;
+  pdl_wait();     // positions, q and the newest cache entries come from the kernels before this one
+  pdl_trigger();
 
   // ---- the row's key range and this split's tiles
   const int64_t p = P.pos[b];
@@ -339,22 +350,6 @@ __global__ void __launch_bounds__(NTHREAD) attn_split_kernel(const __grid_consta
   //      G <= 8: rows 0..7 of the A operand carry part 1 and rows 8..15 part 2 of the same head.
   uint32_t q1w[NH][QW], q2w[NH][QW];
   float f1[NH], f2[NH];
-#pragma unroll
-  for (int hr = 0; hr < NH; ++hr) {
-    float qv[QN];
-    const int head = r + 8 * hr;
-    const QT* qb = static_cast<const QT*>(P.q) + (int64_t)b * P.sqb + (int64_t)(h * G + head) * P.sqh + c * QN;
-#pragma unroll
-    for (int i = 0; i < QN; i += 2) {
-      if (head < G) {
-        qv[i] = to_f32<QT>(qb[i]), qv[i + 1] = to_f32<QT>(qb[i + 1]);
-      } else {
-        qv[i] = qv[i + 1] = 0.f;
-      }
-    }
-    split_q<QN>(qv, q1w[hr], q2w[hr], f1[hr], f2[hr], P.scale_log2);
-  }
-
   const int64_t cb = P.row_map ? P.row_map[b] : b;  // cache row
   const int8_t* kbase = P.k + cb * P.skb + (int64_t)h * P.skh;
   const int8_t* vbase = P.v + cb * P.svb + (int64_t)h * P.svh;
@@ -581,6 +576,23 @@ __global__ void __launch_bounds__(NTHREAD) attn_split_kernel(const __grid_consta
       for (int i = 0; i < pre; ++i) issue(t0 + i, i);
     }
   }
+  // the first tiles are in flight: load and split Q under their latency
+#pragma unroll
+  for (int hr = 0; hr < NH; ++hr) {
+    float qv[QN];
+    const int head = r + 8 * hr;
+    const QT* qb = static_cast<const QT*>(P.q) + (int64_t)b * P.sqb + (int64_t)(h * G + head) * P.sqh + c * QN;
+#pragma unroll
+    for (int i = 0; i < QN; i += 2) {
+      if (head < G) {
+        qv[i] = to_f32<QT>(qb[i]), qv[i + 1] = to_f32<QT>(qb[i + 1]);
+      } else {
+        qv[i] = qv[i + 1] = 0.f;
+      }
+    }
+    split_q<QN>(qv, q1w[hr], q2w[hr], f1[hr], f2[hr], P.scale_log2);
+  }
+
 
   bool dead = false;
   for (int it = 0; it < ntile; ++it) {
@@ -703,7 +715,7 @@ static int launch_attn(const AttnParams& P, bool bulk, cudaStream_t st) {
         return UV_ERR_CUDA;                                                                                \
       }                                                                                                    \
     }                                                                                                      \
-    kern<<<grid, NTHREAD, smem, st>>>(P);                                                                  \
+    launch_pdl(kern, grid, dim3(NTHREAD), smem, st, P);                                                    \
   } while (0)
   if (gp16) {
     if (bulk) UV_LAUNCH(true, true);

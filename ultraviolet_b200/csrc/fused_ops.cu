@@ -28,9 +28,24 @@ template <typename T> __device__ __forceinline__ void st2(T* p, float a, float b
 }
 
 // ------------------------------------------------------------------------------------------------ embed + norms
-// Rows of up to ROW_MAX elements live in registers (lane owns pairs 2*lane + 64*j): one global read, one write.
+// A warp owns a row; rows of up to ROW_MAX elements live in registers as 16-byte vectors (lane owns elements
+// 8*lane + 256*j .. +7): one global read and one write per element, three or four memory instructions per lane.
 constexpr int ROW_MAX = 1024;
-constexpr int ROW_J = ROW_MAX / 64;
+constexpr int ROW_J = ROW_MAX / 256;
+
+template <typename T> __device__ __forceinline__ void ld8(const T* p, float (&v)[8]) {
+  const uint4 u = *reinterpret_cast<const uint4*>(p);
+  const typename Vec2<T>::type* h = reinterpret_cast<const typename Vec2<T>::type*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) v[2 * i] = to_f32<T>(h[i].x), v[2 * i + 1] = to_f32<T>(h[i].y);
+}
+template <typename T> __device__ __forceinline__ void st8(T* p, const float (&v)[8]) {
+  uint4 u;
+  typename Vec2<T>::type* h = reinterpret_cast<typename Vec2<T>::type*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) h[i].x = from_f32<T>(v[2 * i]), h[i].y = from_f32<T>(v[2 * i + 1]);
+  *reinterpret_cast<uint4*>(p) = u;
+}
 
 // x = rms_norm(embed[tok]); xn = rms_norm(x)   (fast_decode.py:284 and the first layer's pre-norm, :303)
 template <typename T>
@@ -39,34 +54,44 @@ __global__ void __launch_bounds__(128) embed_norm_kernel(const int64_t* __restri
                                                          int B) {
   const int lane = threadIdx.x & 31;
   const int row = blockIdx.x * 4 + (threadIdx.x >> 5);
+  pdl_wait();
+  pdl_trigger();
   if (row >= B) return;
   int64_t t = tok[row];
   if (t < 0 || t >= vocab) t = 0;  // out-of-range ids read row 0 instead of faulting
   const T* e = embed + t * d;
-  T* xr = x + (int64_t)row * d;
-  T* nr = xn + (int64_t)row * d;
-  float2 v[ROW_J];
+  float v[ROW_J][8];
   float ss = 0.f;
 #pragma unroll
   for (int j = 0; j < ROW_J; ++j) {
-    const int i = 2 * lane + 64 * j;
-    v[j] = i < d ? ld2<T>(e + i) : make_float2(0.f, 0.f);
-    ss += v[j].x * v[j].x + v[j].y * v[j].y;
+    const int i = 8 * lane + 256 * j;
+    if (i < d) {
+      ld8<T>(e + i, v[j]);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) ss += v[j][k] * v[j][k];
+    }
   }
   float inv = rsqrtf(warp_sum(ss) / (float)d + RMS_EPS);
   ss = 0.f;
 #pragma unroll
   for (int j = 0; j < ROW_J; ++j) {
-    v[j].x = rnd<T>(v[j].x * inv), v[j].y = rnd<T>(v[j].y * inv);
-    ss += v[j].x * v[j].x + v[j].y * v[j].y;
+    if (8 * lane + 256 * j < d) {
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        v[j][k] = rnd<T>(v[j][k] * inv);
+        ss += v[j][k] * v[j][k];
+      }
+    }
   }
   inv = rsqrtf(warp_sum(ss) / (float)d + RMS_EPS);
 #pragma unroll
   for (int j = 0; j < ROW_J; ++j) {
-    const int i = 2 * lane + 64 * j;
+    const int i = 8 * lane + 256 * j;
     if (i < d) {
-      st2<T>(xr + i, v[j].x, v[j].y);
-      st2<T>(nr + i, v[j].x * inv, v[j].y * inv);
+      st8<T>(x + (int64_t)row * d + i, v[j]);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) v[j][k] *= inv;
+      st8<T>(xn + (int64_t)row * d + i, v[j]);
     }
   }
 }
@@ -79,33 +104,36 @@ __global__ void __launch_bounds__(128) resid_norm_kernel(const T* __restrict__ x
                                                          T* __restrict__ h, T* __restrict__ hn, int B) {
   const int lane = threadIdx.x & 31;
   const int row = blockIdx.x * 4 + (threadIdx.x >> 5);
+  pdl_wait();
+  pdl_trigger();
   if (row >= B) return;
   const float l0 = lambdas[0], l1 = lambdas[1];
-  const T* xr = x + (int64_t)row * d;
-  const T* ar = a + (int64_t)row * d;
-  T* hr = h + (int64_t)row * d;
-  T* nr = hn + (int64_t)row * d;
-  float2 v[ROW_J];
+  const int64_t ro = (int64_t)row * d;
+  float v[ROW_J][8];
   float ss = 0.f;
 #pragma unroll
   for (int j = 0; j < ROW_J; ++j) {
-    const int i = 2 * lane + 64 * j;
+    const int i = 8 * lane + 256 * j;
     if (i < d) {
-      const float2 xv = ld2<T>(xr + i), av = ld2<T>(ar + i);
-      v[j].x = rnd<T>(rnd<T>(l0 * xv.x) + rnd<T>(l1 * av.x));
-      v[j].y = rnd<T>(rnd<T>(l0 * xv.y) + rnd<T>(l1 * av.y));
-    } else {
-      v[j] = make_float2(0.f, 0.f);
+      float xv[8], av[8];
+      ld8<T>(x + ro + i, xv);
+      ld8<T>(a + ro + i, av);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        v[j][k] = rnd<T>(rnd<T>(l0 * xv[k]) + rnd<T>(l1 * av[k]));
+        ss += v[j][k] * v[j][k];
+      }
     }
-    ss += v[j].x * v[j].x + v[j].y * v[j].y;
   }
   const float inv = rsqrtf(warp_sum(ss) / (float)d + RMS_EPS);
 #pragma unroll
   for (int j = 0; j < ROW_J; ++j) {
-    const int i = 2 * lane + 64 * j;
+    const int i = 8 * lane + 256 * j;
     if (i < d) {
-      st2<T>(hr + i, v[j].x, v[j].y);
-      st2<T>(nr + i, v[j].x * inv, v[j].y * inv);
+      st8<T>(h + ro + i, v[j]);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) v[j][k] *= inv;
+      st8<T>(hn + ro + i, v[j]);
     }
   }
 }
@@ -116,6 +144,8 @@ template <typename T>
 __global__ void __launch_bounds__(256) swiglu_kernel(const T* __restrict__ gu, int f, T* __restrict__ act,
                                                      int64_t n_pairs) {
   const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;  // pair index over (B, f/2)
+  pdl_wait();
+  pdl_trigger();
   if (i >= n_pairs) return;
   const int half_f = f / 2;
   const int64_t row = i / half_f;
@@ -155,6 +185,8 @@ __global__ void __launch_bounds__(128) qkv_post_kernel(const __grid_constant__ Q
   const int lane = threadIdx.x & 31;
   const int slots = P.H + 2 * P.K;
   const int item = blockIdx.x * 4 + (threadIdx.x >> 5);
+  pdl_wait();
+  pdl_trigger();
   if (item >= P.B * slots) return;
   const int b = item / slots, hs = item % slots;
   const bool act = lane * E < HD;
@@ -237,10 +269,10 @@ template <typename T>
 static int launch_qkv_post(const QkvPostParams& P, int hd, cudaStream_t st) {
   const unsigned grid = (unsigned)(((int64_t)P.B * (P.H + 2 * P.K) + 3) / 4);
   switch (hd) {
-    case 16: qkv_post_kernel<T, 16><<<grid, 128, 0, st>>>(P); break;
-    case 32: qkv_post_kernel<T, 32><<<grid, 128, 0, st>>>(P); break;
-    case 64: qkv_post_kernel<T, 64><<<grid, 128, 0, st>>>(P); break;
-    case 128: qkv_post_kernel<T, 128><<<grid, 128, 0, st>>>(P); break;
+    case 16: launch_pdl(qkv_post_kernel<T, 16>, dim3(grid), dim3(128), 0, st, P); break;
+    case 32: launch_pdl(qkv_post_kernel<T, 32>, dim3(grid), dim3(128), 0, st, P); break;
+    case 64: launch_pdl(qkv_post_kernel<T, 64>, dim3(grid), dim3(128), 0, st, P); break;
+    case 128: launch_pdl(qkv_post_kernel<T, 128>, dim3(grid), dim3(128), 0, st, P); break;
     default: return UV_ERR_SHAPE;
   }
   return check_launch();
@@ -254,16 +286,16 @@ extern "C" int uv_embed_norm(const int64_t* tok, const void* embed, int dtype, i
                              void* xn, int B, void* stream) {
   if (B == 0) return UV_OK;
   if (!tok || !embed || !x || !xn || B < 0 || vocab < 1) return UV_ERR_ARG;
-  if (d < 2 || (d & 1) || d > ROW_MAX) return UV_ERR_SHAPE;
+  if (d < 8 || (d & 7) || d > ROW_MAX) return UV_ERR_SHAPE;  // rows are moved as 16-byte vectors
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const unsigned grid = (unsigned)((B + 3) / 4);
   if (dtype == UV_F16)
-    embed_norm_kernel<__half><<<grid, 128, 0, st>>>(tok, static_cast<const __half*>(embed), vocab, d,
-                                                    static_cast<__half*>(x), static_cast<__half*>(xn), B);
+    launch_pdl(embed_norm_kernel<__half>, dim3(grid), dim3(128), 0, st, tok, static_cast<const __half*>(embed), vocab,
+               d, static_cast<__half*>(x), static_cast<__half*>(xn), B);
   else if (dtype == UV_BF16)
-    embed_norm_kernel<__nv_bfloat16><<<grid, 128, 0, st>>>(tok, static_cast<const __nv_bfloat16*>(embed), vocab, d,
-                                                           static_cast<__nv_bfloat16*>(x),
-                                                           static_cast<__nv_bfloat16*>(xn), B);
+    launch_pdl(embed_norm_kernel<__nv_bfloat16>, dim3(grid), dim3(128), 0, st, tok,
+               static_cast<const __nv_bfloat16*>(embed), vocab, d, static_cast<__nv_bfloat16*>(x),
+               static_cast<__nv_bfloat16*>(xn), B);
   else return UV_ERR_DTYPE;
   return check_launch();
 }
@@ -272,16 +304,16 @@ extern "C" int uv_resid_norm(const void* x, const void* a, const float* lambdas,
                              int B, void* stream) {
   if (B == 0) return UV_OK;
   if (!x || !a || !lambdas || !h || !hn || B < 0) return UV_ERR_ARG;
-  if (d < 2 || (d & 1) || d > ROW_MAX) return UV_ERR_SHAPE;
+  if (d < 8 || (d & 7) || d > ROW_MAX) return UV_ERR_SHAPE;  // rows are moved as 16-byte vectors
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const unsigned grid = (unsigned)((B + 3) / 4);
   if (dtype == UV_F16)
-    resid_norm_kernel<__half><<<grid, 128, 0, st>>>(static_cast<const __half*>(x), static_cast<const __half*>(a),
-                                                    lambdas, d, static_cast<__half*>(h), static_cast<__half*>(hn), B);
+    launch_pdl(resid_norm_kernel<__half>, dim3(grid), dim3(128), 0, st, static_cast<const __half*>(x),
+               static_cast<const __half*>(a), lambdas, d, static_cast<__half*>(h), static_cast<__half*>(hn), B);
   else if (dtype == UV_BF16)
-    resid_norm_kernel<__nv_bfloat16><<<grid, 128, 0, st>>>(
-        static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(a), lambdas, d,
-        static_cast<__nv_bfloat16*>(h), static_cast<__nv_bfloat16*>(hn), B);
+    launch_pdl(resid_norm_kernel<__nv_bfloat16>, dim3(grid), dim3(128), 0, st, static_cast<const __nv_bfloat16*>(x),
+               static_cast<const __nv_bfloat16*>(a), lambdas, d, static_cast<__nv_bfloat16*>(h),
+               static_cast<__nv_bfloat16*>(hn), B);
   else return UV_ERR_DTYPE;
   return check_launch();
 }
@@ -294,10 +326,11 @@ extern "C" int uv_swiglu(const void* gu, int dtype, int f, void* act, int B, voi
   const int64_t n = (int64_t)B * (f / 2);
   const unsigned grid = (unsigned)((n + 255) / 256);
   if (dtype == UV_F16)
-    swiglu_kernel<__half><<<grid, 256, 0, st>>>(static_cast<const __half*>(gu), f, static_cast<__half*>(act), n);
+    launch_pdl(swiglu_kernel<__half>, dim3(grid), dim3(256), 0, st, static_cast<const __half*>(gu), f,
+               static_cast<__half*>(act), n);
   else if (dtype == UV_BF16)
-    swiglu_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(gu), f,
-                                                       static_cast<__nv_bfloat16*>(act), n);
+    launch_pdl(swiglu_kernel<__nv_bfloat16>, dim3(grid), dim3(256), 0, st, static_cast<const __nv_bfloat16*>(gu), f,
+               static_cast<__nv_bfloat16*>(act), n);
   else return UV_ERR_DTYPE;
   return check_launch();
 }

@@ -72,6 +72,8 @@ __global__ void __launch_bounds__(SAMPLE_THREADS) sample_kernel(const __grid_con
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int row = blockIdx.x;
   const int V = P.V, CH = V / SAMPLE_THREADS;
+  pdl_wait();
+  pdl_trigger();
   const T* xr = static_cast<const T*>(P.x) + (int64_t)row * P.x_stride;
   const float inv_c = 1.0f / P.c;
   float cap_a = P.a;
@@ -229,7 +231,7 @@ extern "C" int uv_sample(const void* x, int x_dtype, int64_t x_stride, int B, in
         return UV_ERR_CUDA;                                                                                   \
       }                                                                                                       \
     }                                                                                                         \
-    sample_kernel<T><<<(unsigned)B, SAMPLE_THREADS, smem, st>>>(P);                                           \
+    launch_pdl(sample_kernel<T>, dim3((unsigned)B), dim3(SAMPLE_THREADS), smem, st, P);                       \
   } while (0)
   if (x_dtype == UV_F32) UV_GO(float);
   else if (x_dtype == UV_F16) UV_GO(__half);

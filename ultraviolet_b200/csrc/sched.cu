@@ -85,6 +85,8 @@ __device__ __forceinline__ int block_excl_scan(int v, int* warp_tot, int tid, in
 __global__ void __launch_bounds__(SCHED_THREADS) sched_step_kernel(const __grid_constant__ SchedParams P) {
   __shared__ int warp_tot[SCHED_THREADS / 32];
   const int tid = threadIdx.x;
+  pdl_wait();
+  pdl_trigger();
   const int64_t head0 = P.ctl[CTL_HEAD], tail = P.ctl[CTL_TAIL];
   const int version = (int)P.ctl[CTL_VERSION];
   int64_t head = head0;
@@ -227,7 +229,7 @@ extern "C" int uv_sched_step(const uv_sched_args* a, void* stream) {
   SchedParams P;
   static_assert(sizeof(SchedParams) == sizeof(uv_sched_args), "uv_sched_args mirrors SchedParams");
   memcpy(&P, a, sizeof(P));
-  sched_step_kernel<<<1, SCHED_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(P);
+  launch_pdl(sched_step_kernel, dim3(1), dim3(SCHED_THREADS), 0, static_cast<cudaStream_t>(stream), P);
   return check_launch();
 }
 
