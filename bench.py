@@ -335,10 +335,11 @@ def main():
         raise SystemExit("bench.py needs a CUDA device: the decode path has no CPU fallback")
     dev = torch.device("cuda", local)
     torch.cuda.set_device(dev)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
     from ultraviolet_b200.generate import DecodeRunner
     from ultraviolet_b200 import dist as uvdist
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+        uvdist.warmup(dev)
 
     dtype = torch.bfloat16
     m = build_model(dev, dtype)

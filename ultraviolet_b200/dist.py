@@ -27,6 +27,22 @@ def shard_requests(n: int, rank: int, world_size: int) -> list[int]:
     return list(range(rank, n, world_size))
 
 
+def warmup(device) -> None:
+    """Create the communicator and its channels before anything is timed (the first collective of a process pays
+    for NCCL initialisation)."""
+    rank, W = world()
+    if W == 1:
+        return
+    t = torch.ones(1024, device=device)
+    dist.all_reduce(t)
+    dist.broadcast(t, 0)
+    out = [torch.empty_like(t) for _ in range(W)] if rank == 0 else None
+    dist.gather(t, out, dst=0)
+    lst = [torch.empty_like(t) for _ in range(W)]
+    dist.all_gather(lst, t)
+    _sync(t)
+
+
 def _sync(t: torch.Tensor) -> None:
     if t.is_cuda:
         torch.cuda.synchronize(t.device)
