@@ -6,3 +6,4 @@ on CPU tensors (there is no eager fallback).
 """
 from .decode_attn import decode_attention, default_splits  # noqa: F401
 from .kv_quant import dequantize_kv, kv_append, kv_write, kv_write_rows, quantize_kv  # noqa: F401
+from .sampling import fused_sample, fused_sample_ok  # noqa: E402,F401
