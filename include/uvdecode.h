@@ -174,6 +174,23 @@ int uv_resid_norm(const void* x, const void* a, const float* lambdas, int dtype,
                   void* stream);
 int uv_swiglu(const void* gu, int dtype, int f, void* act, int B, void* stream);
 
+/* GEMMs of the decode step with the row-wise kernels above fused into their epilogues (hand-written mma.sync
+ * mainloop; same results as library GEMM + the separate kernel up to the summation order of the fp32 accumulation).
+ * Activations (B, K) row-major with row stride ld*, weights (N, K) row-major contiguous, K % 64 == 0.
+ *   uv_gemm_qkv:        qkv = xn . wqkv^T followed by everything uv_qkv_post does (head_dim 64 only)
+ *   uv_gemm_swiglu:     act = silu(hn . Wg^T) * (hn . Wu^T), w_gu = [Wg ; Wu] (2f, d), f % 32 == 0
+ *   uv_gemm_resid_norm: h = lambdas[0]*x + lambdas[1]*(a . w^T), hn = rms_norm(h); d % 80 == 0 and d <= 640 (the d
+ *                       columns are split over a thread-block cluster of d/80 CTAs whose row sums meet in
+ *                       distributed shared memory) */
+int uv_gemm_qkv(const void* xn, int64_t ldx, const void* wqkv, void* qkv, const int64_t* tok, const void* value_embed,
+                const void* ve_gate, const float* inv_freq, const int64_t* pos, int8_t* k_cache, int8_t* v_cache,
+                uint16_t* k_scale, uint16_t* v_scale, const int64_t* row_map, int* oob_count, int dtype, int64_t vocab,
+                int B, int H, int KH, int hd, int d, int S, int S_alloc, int ring, int ve_ch, int n_pairs, void* stream);
+int uv_gemm_swiglu(const void* hn, int64_t ldh, const void* w_gu, void* act, int dtype, int B, int d, int f,
+                   void* stream);
+int uv_gemm_resid_norm(const void* a, int64_t lda, const void* w, int K, const void* x, const float* lambdas, void* h,
+                       void* hn, int dtype, int B, int d, void* stream);
+
 /* uv_sample: softcap + token draw + behaviour log-prob per row of the LM-head output x (B, V), V % 256 == 0.
  * Replaces fused_sample (ultraviolet/kernels/fused_sample.py:68-78) and sample + the log-prob gather
  * (ultraviolet/model.py:1160-1169, :1194-1211).  precapped = 0: x is the raw head output and z = a*sigmoid((x+b)/c)

@@ -69,6 +69,12 @@ SIGNATURES = {
     "uv_resid_norm": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_int,
                                 C.c_void_p]),
     "uv_swiglu": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_int, C.c_void_p]),
+    "uv_gemm_qkv": (C.c_int, [C.c_void_p, C.c_int64] + [C.c_void_p] * 13 + [C.c_int, C.c_int64] + [C.c_int] * 10
+                    + [C.c_void_p]),
+    "uv_gemm_swiglu": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int,
+                                 C.c_void_p]),
+    "uv_gemm_resid_norm": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p,
+                                     C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p]),
     "uv_sched_step": (C.c_int, [C.POINTER(SchedArgs), C.c_void_p]),
     "uv_sched_enqueue": (C.c_int, [C.POINTER(SchedArgs), C.c_int, C.c_void_p]),
     "uv_sample": (C.c_int, [C.c_void_p, C.c_int, C.c_int64, C.c_int, C.c_int, C.c_int, C.c_float, C.c_float,

@@ -40,7 +40,7 @@ namespace uv {
 constexpr int TILE = UV_ATTN_TILE;   // keys per pipeline stage
 constexpr int NSTAGE = UV_ATTN_NSTAGE;
 constexpr int NWARP = UV_ATTN_NWARP;
-constexpr int NTHREAD = NWARP * 32;
+constexpr int NTHREAD = (NWARP + 1) * 32;  // NWARP consumer warps + one warp that issues the bulk copies
 constexpr int WKEYS = TILE / NWARP;  // keys one warp consumes per stage
 constexpr unsigned long long WAIT_NS = 200ull * 1000 * 1000;  // a tile that has not landed after 200 ms is abandoned
 constexpr float LOG2E = 1.4426950408889634f;
@@ -92,6 +92,9 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
                "l"(src), "r"(bytes), "r"(bar)
                : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
@@ -199,7 +202,7 @@ template <typename QT, int HD>
 __device__ __forceinline__ void combine_rows(const AttnParams& P, int bk, int warp, int lane) {
   constexpr int EPL = (HD + 31) / 32;
   const int b = bk / P.KH, h = bk % P.KH;
-  for (int row = warp; row < P.G; row += NWARP) {
+  for (int row = warp; row < P.G && warp < NWARP; row += NWARP) {
     const int64_t base = (int64_t)bk * P.splits * P.G + row;
     float mx = -INFINITY;
     for (int s = lane; s < P.splits; s += 32) mx = fmaxf(mx, __ldcg(P.ws_m + base + (int64_t)s * P.G));
@@ -288,6 +291,15 @@ __device__ __forceinline__ void imma16832(int (&d)[4], uint32_t a0, uint32_t a1,
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+// first k-step of a tile: C = 0, so the accumulators need no clearing
+__device__ __forceinline__ void imma16832_z(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                            uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+      : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
+}
+
 template <typename QT, int HD, bool GP16, bool BULK>
 __global__ void __launch_bounds__(NTHREAD) attn_split_kernel(const __grid_constant__ AttnParams P) {
   using L = StageLayout<HD>;
@@ -299,9 +311,11 @@ __global__ void __launch_bounds__(NTHREAD) attn_split_kernel(const __grid_consta
   constexpr int ROWS = GP16 ? 16 : 8;
   constexpr int NH = GP16 ? 2 : 1;   // row halves (heads r and r + 8)
   extern __shared__ __align__(128) unsigned char smem[];
-  __shared__ __align__(8) uint64_t bars[NSTAGE];
+  __shared__ __align__(8) uint64_t bars[NSTAGE];   // "full": a tile has landed (transaction bytes)
+  __shared__ __align__(8) uint64_t empty[NSTAGE];  // "empty": every consumer warp is done with the stage
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const bool producer = warp == NWARP;  // the copy-issuing warp never computes
   const int r = lane >> 2, c = lane & 3;
   const int bk = blockIdx.x, sid = blockIdx.y;
   const int b = bk / P.KH, h = bk % P.KH;
@@ -359,7 +373,10 @@ __global__ void __launch_bounds__(NTHREAD) attn_split_kernel(const __grid_consta
   if constexpr (BULK) {
     if (tid == 0) {
 #pragma unroll
-      for (int s = 0; s < NSTAGE; ++s) mbar_init(smem_u32(&bars[s]), 1);
+      for (int s = 0; s < NSTAGE; ++s) {
+        mbar_init(smem_u32(&bars[s]), 1);
+        mbar_init(smem_u32(&empty[s]), NWARP);
+      }
       fence_barrier_init();
     }
     __syncthreads();
@@ -427,8 +444,6 @@ __global__ void __launch_bounds__(NTHREAD) attn_split_kernel(const __grid_consta
     int acc1[NT_S][4], acc2[GP16 ? NT_S : 1][4];
 #pragma unroll
     for (int t = 0; t < NT_S; ++t) {
-      acc1[t][0] = acc1[t][1] = acc1[t][2] = acc1[t][3] = 0;
-      if constexpr (GP16) acc2[t][0] = acc2[t][1] = acc2[t][2] = acc2[t][3] = 0;
       const unsigned char* krow = st + L::K_OFF + (k0 + 8 * t + r) * HD + c * QN;
       uint32_t kw[QW];
       if constexpr (QW == 1) {
@@ -449,10 +464,18 @@ __global__ void __launch_bounds__(NTHREAD) attn_split_kernel(const __grid_consta
         const uint32_t b0 = kw[2 * j], b1 = two ? kw[two ? 2 * j + 1 : 0] : 0u;
         const int j1 = two ? 2 * j + 1 : 0;
         if constexpr (GP16) {
-          imma16832(acc1[t], q1w[0][2 * j], q1w[1][2 * j], two ? q1w[0][j1] : 0u, two ? q1w[1][j1] : 0u, b0, b1);
-          imma16832(acc2[t], q2w[0][2 * j], q2w[1][2 * j], two ? q2w[0][j1] : 0u, two ? q2w[1][j1] : 0u, b0, b1);
+          if (j == 0) {
+            imma16832_z(acc1[t], q1w[0][0], q1w[1][0], two ? q1w[0][j1] : 0u, two ? q1w[1][j1] : 0u, b0, b1);
+            imma16832_z(acc2[t], q2w[0][0], q2w[1][0], two ? q2w[0][j1] : 0u, two ? q2w[1][j1] : 0u, b0, b1);
+          } else {
+            imma16832(acc1[t], q1w[0][2 * j], q1w[1][2 * j], two ? q1w[0][j1] : 0u, two ? q1w[1][j1] : 0u, b0, b1);
+            imma16832(acc2[t], q2w[0][2 * j], q2w[1][2 * j], two ? q2w[0][j1] : 0u, two ? q2w[1][j1] : 0u, b0, b1);
+          }
         } else {
-          imma16832(acc1[t], q1w[0][2 * j], q2w[0][2 * j], two ? q1w[0][j1] : 0u, two ? q2w[0][j1] : 0u, b0, b1);
+          if (j == 0)
+            imma16832_z(acc1[t], q1w[0][0], q2w[0][0], two ? q1w[0][j1] : 0u, two ? q2w[0][j1] : 0u, b0, b1);
+          else
+            imma16832(acc1[t], q1w[0][2 * j], q2w[0][2 * j], two ? q1w[0][j1] : 0u, two ? q2w[0][j1] : 0u, b0, b1);
         }
       }
     }
@@ -570,13 +593,25 @@ __global__ void __launch_bounds__(NTHREAD) attn_split_kernel(const __grid_consta
     }
   };
 
+  bool dead = false;
   if constexpr (BULK) {
-    if (tid == 0) {
-      const int pre = ntile < NSTAGE - 1 ? ntile : NSTAGE - 1;
-      for (int i = 0; i < pre; ++i) issue(t0 + i, i);
+    // The producer warp runs ahead of the consumers by up to NSTAGE tiles: it refills a stage as soon as all
+    // consumer warps have released it, so consumer warps drift freely instead of meeting at a CTA barrier per tile.
+    if (producer) {
+      if (lane == 0) {
+        for (int j = 0; j < ntile; ++j) {
+          const int s = j % NSTAGE, k = j / NSTAGE;
+          if (k > 0 && !mbar_wait_bounded(smem_u32(&empty[s]), (uint32_t)((k - 1) & 1))) {
+            dead = true;  // consumers will time out on the full barrier and flag the launch as well
+            break;
+          }
+          issue(t0 + j, s);
+        }
+      }
     }
   }
-  // the first tiles are in flight: load and split Q under their latency
+  // the first tiles are in flight: consumers load and split Q under their latency
+  if (!producer)
 #pragma unroll
   for (int hr = 0; hr < NH; ++hr) {
     float qv[QN];
@@ -594,29 +629,44 @@ __global__ void __launch_bounds__(NTHREAD) attn_split_kernel(const __grid_consta
   }
 
 
-  bool dead = false;
-  for (int it = 0; it < ntile; ++it) {
-    const int s = BULK ? it % NSTAGE : 0;
-    __syncthreads();  // every warp is done with the stage that is refilled next
-    if constexpr (BULK) {
-      if (tid == 0 && it + NSTAGE - 1 < ntile) issue(t0 + it + NSTAGE - 1, (it + NSTAGE - 1) % NSTAGE);
-      if (!dead) {  // warp-uniform: a warp whose tile never landed stops consuming and flags the launch
-        const bool got = mbar_wait_bounded(smem_u32(&bars[s]), (uint32_t)((it / NSTAGE) & 1));
-        dead = !__all_sync(0xffffffffu, got);
+  if constexpr (BULK) {
+    if (!producer) {
+      for (int it = 0; it < ntile; ++it) {
+        const int s = it % NSTAGE;
+        if (!dead) {  // warp-uniform: a warp whose tile never landed stops consuming and flags the launch
+          const bool got = mbar_wait_bounded(smem_u32(&bars[s]), (uint32_t)((it / NSTAGE) & 1));
+          dead = !__all_sync(0xffffffffu, got);
+        }
+        if (!dead) {
+          const unsigned char* st = smem + (size_t)s * L::BYTES;
+          const int64_t kb0 = (t0 + it) * TILE + WKEYS * warp;  // position of this warp's first key
+          if (kb0 + WKEYS - 1 >= lo && kb0 <= hi) {
+            if (kb0 < lo || kb0 + WKEYS - 1 > hi) {
+              const int64_t lr = lo - kb0, hr_ = hi - kb0;
+              block(st, lr < 0 ? 0 : (int)lr, hr_ > WKEYS ? WKEYS : (int)hr_, std::true_type{});
+            } else {
+              block(st, 0, WKEYS, std::false_type{});
+            }
+          }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&empty[s]));  // release the stage (also when skipped or dead)
       }
-      if (dead) continue;
-    } else {
+    }
+  } else {
+    for (int it = 0; it < ntile; ++it) {
+      __syncthreads();  // every warp is done with the single stage
       load_generic(t0 + it);
       __syncthreads();
-    }
-    const unsigned char* st = smem + (size_t)s * L::BYTES;
-    const int64_t kb0 = (t0 + it) * TILE + WKEYS * warp;  // position of this warp's first key
-    if (kb0 + WKEYS - 1 < lo || kb0 > hi) continue;
-    if (kb0 < lo || kb0 + WKEYS - 1 > hi) {
-      const int64_t lr = lo - kb0, hr_ = hi - kb0;
-      block(st, lr < 0 ? 0 : (int)lr, hr_ > WKEYS ? WKEYS : (int)hr_, std::true_type{});
-    } else {
-      block(st, 0, WKEYS, std::false_type{});
+      if (producer) continue;
+      const int64_t kb0 = (t0 + it) * TILE + WKEYS * warp;
+      if (kb0 + WKEYS - 1 < lo || kb0 > hi) continue;
+      if (kb0 < lo || kb0 + WKEYS - 1 > hi) {
+        const int64_t lr = lo - kb0, hr_ = hi - kb0;
+        block(smem, lr < 0 ? 0 : (int)lr, hr_ > WKEYS ? WKEYS : (int)hr_, std::true_type{});
+      } else {
+        block(smem, 0, WKEYS, std::false_type{});
+      }
     }
   }
 
@@ -629,6 +679,7 @@ __global__ void __launch_bounds__(NTHREAD) attn_split_kernel(const __grid_consta
   float* mg_o = reinterpret_cast<float*>(smem);                    // [NWARP][ROWS][HD]
   float* mg_m = mg_o + NWARP * ROWS * HD;                          // [NWARP][ROWS]
   float* mg_l = mg_m + NWARP * ROWS;
+  if (!producer)
 #pragma unroll
   for (int hr = 0; hr < NH; ++hr) {
     float l = l_run[hr];
@@ -649,7 +700,7 @@ __global__ void __launch_bounds__(NTHREAD) attn_split_kernel(const __grid_consta
   __syncthreads();
 
   constexpr int EPL = (HD + 31) / 32;
-  for (int row = warp; row < G; row += NWARP) {
+  for (int row = warp; row < G && !producer; row += NWARP) {
     float mw[NWARP], mx = -INFINITY;
 #pragma unroll
     for (int w = 0; w < NWARP; ++w) {

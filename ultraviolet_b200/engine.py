@@ -16,6 +16,7 @@ libuvdecode.  Nothing here allocates after warm-up, so the whole step captures i
 from __future__ import annotations
 
 import ctypes as C
+import os
 
 import torch
 from torch import Tensor
@@ -72,6 +73,9 @@ class DecodeEngine:
             self.inv_freq.copy_((1.0 / cfg.rope_base) ** torch.linspace(0, 1, cfg.rope_pairs, dtype=torch.float32))
         self._scratch: dict[int, dict] = {}
         self.version = 0
+        # GEMMs with fused epilogues (csrc/gemm_fused.cu) where the geometry allows; else cuBLAS + row kernels
+        self.fused_gemm = (os.environ.get("UVDECODE_FUSED_GEMM", "1") != "0" and hd == 64 and d % 80 == 0
+                           and d // 80 <= 8 and f % 64 == 0 and d % 64 == 0 and (H * hd) % 64 == 0)
         self.n_sm = torch.cuda.get_device_properties(self.device).multi_processor_count
         _lib.lib()
 
@@ -153,6 +157,7 @@ class DecodeEngine:
         w = self.w
         ns = num_splits or {}
         rm = row_map.data_ptr() if row_map is not None else None
+        fused = self.fused_gemm
         with torch.cuda.device(self.device):
             _lib.check(lib.uv_embed_norm(tok.data_ptr(), w["embed"].data_ptr(), dt, cfg.vocab_size, d,
                                          s["x"].data_ptr(), s["xn"].data_ptr(), B, sp), "uv_embed_norm")
@@ -162,18 +167,21 @@ class DecodeEngine:
             z3 = s["z"].view(B, H, hd)
             for l in range(cfg.n_layers):
                 glob = cfg.is_global(l)
-                torch.mm(xn, w[f"l{l}.wqkv"].t(), out=s["qkv"])
                 kc, vc, ks, vs = st.k[l], st.v[l], st.k_scale[l], st.v_scale[l]
                 S = kc.size(2)
                 ve_gate = w[f"l{l}.ve_gate"].data_ptr() if cfg.has_ve(l) else None
                 rope = (not glob) or cfg.global_rope
-                _lib.check(lib.uv_qkv_post(
-                    s["qkv"].data_ptr(), xn.data_ptr(), tok.data_ptr(),
-                    w["value_embed"].data_ptr() if self.use_ve else None, ve_gate,
-                    self.inv_freq.data_ptr() if rope and cfg.rope_pairs else None, pos.data_ptr(),
-                    kc.data_ptr(), vc.data_ptr(), ks.data_ptr(), vs.data_ptr(), rm,
-                    s["oob"].data_ptr(), dt, cfg.vocab_size, B, H, K, hd, d, S, kc.stride(1) // hd, int(not glob),
-                    cfg.ve_gate_channels, cfg.rope_pairs, sp), "uv_qkv_post")
+                post_args = (tok.data_ptr(), w["value_embed"].data_ptr() if self.use_ve else None, ve_gate,
+                             self.inv_freq.data_ptr() if rope and cfg.rope_pairs else None, pos.data_ptr(),
+                             kc.data_ptr(), vc.data_ptr(), ks.data_ptr(), vs.data_ptr(), rm, s["oob"].data_ptr(), dt,
+                             cfg.vocab_size, B, H, K, hd, d, S, kc.stride(1) // hd, int(not glob),
+                             cfg.ve_gate_channels, cfg.rope_pairs, sp)
+                if fused:
+                    _lib.check(lib.uv_gemm_qkv(xn.data_ptr(), d, w[f"l{l}.wqkv"].data_ptr(), s["qkv"].data_ptr(),
+                                               *post_args), "uv_gemm_qkv")
+                else:
+                    torch.mm(xn, w[f"l{l}.wqkv"].t(), out=s["qkv"])
+                    _lib.check(lib.uv_qkv_post(s["qkv"].data_ptr(), xn.data_ptr(), *post_args), "uv_qkv_post")
                 if glob:
                     ctx = min(g_len or S, S)
                     splits = ns.get("global") or default_splits(B * K, ctx, self.device)
@@ -187,8 +195,18 @@ class DecodeEngine:
                             gate_x=xn if cfg.gate_channels else None,
                             gate_w=w[f"l{l}.attn_gate"] if cfg.gate_channels else None,
                             counters=s["counters"], status=s["status"], row_map=row_map)
-                torch.mm(s["z"], w[f"l{l}.wo"].t(), out=s["a"])
                 lam = self.lambdas[l]
+                if fused:
+                    _lib.check(lib.uv_gemm_resid_norm(s["z"].data_ptr(), H * hd, w[f"l{l}.wo"].data_ptr(), H * hd,
+                                                      x.data_ptr(), lam.data_ptr(), h.data_ptr(), hn.data_ptr(), dt,
+                                                      B, d, sp), "uv_gemm_resid_norm")
+                    _lib.check(lib.uv_gemm_swiglu(hn.data_ptr(), d, w[f"l{l}.gu"].data_ptr(), s["act"].data_ptr(),
+                                                  dt, B, d, f, sp), "uv_gemm_swiglu")
+                    _lib.check(lib.uv_gemm_resid_norm(s["act"].data_ptr(), f, w[f"l{l}.down"].data_ptr(), f,
+                                                      h.data_ptr(), lam[2:].data_ptr(), x.data_ptr(), xn.data_ptr(),
+                                                      dt, B, d, sp), "uv_gemm_resid_norm")
+                    continue
+                torch.mm(s["z"], w[f"l{l}.wo"].t(), out=s["a"])
                 _lib.check(lib.uv_resid_norm(x.data_ptr(), s["a"].data_ptr(), lam.data_ptr(), dt, d, h.data_ptr(),
                                              hn.data_ptr(), B, sp), "uv_resid_norm")
                 torch.mm(hn, w[f"l{l}.gu"].t(), out=s["gu"])
