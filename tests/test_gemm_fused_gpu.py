@@ -28,7 +28,7 @@ def test_fused_gemm_step_matches_unfused_step(B):
     spec = gi.model_specs()["uv50m"]
     m = build_model(spec).to(DEV).to(torch.bfloat16).fuse_for_inference(torch.bfloat16)
     eng = m.engine
-    assert eng.fused_gemm
+    assert eng.fused_gemm_ok
     a, sa = _run(eng, m, True, B, 6, 1)
     b, sb = _run(eng, m, False, B, 6, 1)
     eng.fused_gemm = True
@@ -49,7 +49,8 @@ def test_fused_gemm_step_matches_oracle():
     mc = build_model(spec)
     W = oracle_weights(mc, "bf16")
     m = build_model(spec).to(DEV).to(torch.bfloat16).fuse_for_inference(torch.bfloat16)
-    assert m.engine.fused_gemm
+    assert m.engine.fused_gemm_ok
+    m.engine.fused_gemm = True
     B, steps = 5, 4
     r = np.random.default_rng(2)
     toks = r.integers(1, mc.cfg.vocab_size, (steps, B))

@@ -73,9 +73,12 @@ class DecodeEngine:
             self.inv_freq.copy_((1.0 / cfg.rope_base) ** torch.linspace(0, 1, cfg.rope_pairs, dtype=torch.float32))
         self._scratch: dict[int, dict] = {}
         self.version = 0
-        # GEMMs with fused epilogues (csrc/gemm_fused.cu) where the geometry allows; else cuBLAS + row kernels
-        self.fused_gemm = (os.environ.get("UVDECODE_FUSED_GEMM", "1") != "0" and hd == 64 and d % 80 == 0
-                           and d // 80 <= 8 and f % 64 == 0 and d % 64 == 0 and (H * hd) % 64 == 0)
+        # GEMMs with fused epilogues (csrc/gemm_fused.cu).  Correct, but measured SLOWER than cuBLAS + the separate row
+        # kernels on B200 at decode batch sizes (per pair 8-20 us against 6-8 us: four warps of straight-line code per
+        # SM stall on instruction fetch and on the serial MMA chain), so the path is opt-in: UVDECODE_FUSED_GEMM=1.
+        self.fused_gemm_ok = (hd == 64 and d % 80 == 0 and d // 80 <= 8 and f % 64 == 0 and d % 64 == 0
+                              and (H * hd) % 64 == 0)
+        self.fused_gemm = os.environ.get("UVDECODE_FUSED_GEMM", "0") == "1" and self.fused_gemm_ok
         self.n_sm = torch.cuda.get_device_properties(self.device).multi_processor_count
         _lib.lib()
 
