@@ -197,10 +197,12 @@ int uv_gemm_resid_norm(const void* a, int64_t lda, const void* w, int K, const v
  * is applied here; precapped = 1: x already holds logits z (cap_* ignored).  temperature <= 0: argmax (first index
  * on ties), logp reported at T = 1.  temperature > 0: inverse-CDF draw of softmax(z / T) restricted to the top_p
  * nucleus (top_p >= 1: none), with one uniform per row taken from u (B,) or, when u == NULL, from Philox4x32-10 with
- * key = seed and counter = (steps[row], row_keys[row]).  logp = log softmax(z / T)[token] over the FULL vocabulary. */
+ * key = seed and counter = (steps[row], row_keys[row]).  logp = log softmax(z / T)[token] over the FULL vocabulary.
+ * inc_a / inc_b (optional, (B,) int64): counters advanced by one per row after the draw -- the decode step passes
+ * the cache positions and the Philox step counters here instead of launching two more kernels. */
 int uv_sample(const void* x, int x_dtype, int64_t x_stride, int B, int V, int precapped, float cap_a, float cap_b,
               float cap_c, float temperature, float top_p, const float* u, uint64_t seed, const int64_t* row_keys,
-              const int64_t* steps, int64_t* tok_out, float* logp_out, void* stream);
+              const int64_t* steps, int64_t* tok_out, float* logp_out, int64_t* inc_a, int64_t* inc_b, void* stream);
 
 /* ---------------------------------------------------------------------------------------------------------------
  * (a) GPU-resident continuous-batching scheduler.  Replaces the host loops of StreamGen.chunk / _refill / _park

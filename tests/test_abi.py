@@ -51,7 +51,7 @@ def test_argument_errors_return_codes_without_launching(lib):
     assert lib.uv_kv_quant_scatter(None, 0, 64, 4, 64, None, None, None, 4, None, None) == -1
     assert lib.uv_kv_quant_scatter(None, 0, 64, 0, 64, None, None, None, 0, None, None) == 0
     assert lib.uv_sample(None, 2, 0, 4, 16384, 0, 23.0, 5.0, 7.5, 1.0, 1.0, None, 0, None, None, None, None,
-                         None) == -1
+                         None, None, None) == -1
     assert lib.uv_sched_step(None, None) == -1
     assert lib.uv_embed_norm(None, None, 2, 10, 640, None, None, 0, None) == 0
 

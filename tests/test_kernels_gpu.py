@@ -210,7 +210,7 @@ def _sample(x, **kw):
     rc = _lib.lib().uv_sample(x.data_ptr(), DTYPE_CODE[x.dtype], x.stride(0), B, V, int(kw.get("precapped", False)),
                               cap[0], cap[1], cap[2], kw.get("T", 1.0), kw.get("top_p", 1.0), p(kw.get("u")),
                               C.c_uint64(kw.get("seed", 0)), p(kw.get("row_keys")), p(kw.get("steps")),
-                              tok.data_ptr(), lp.data_ptr(), stream_ptr(torch.device(DEV)))
+                              tok.data_ptr(), lp.data_ptr(), None, None, stream_ptr(torch.device(DEV)))
     _lib.check(rc, "uv_sample")
     return tok.cpu().numpy(), lp.cpu().numpy()
 

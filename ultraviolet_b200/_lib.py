@@ -79,7 +79,7 @@ SIGNATURES = {
     "uv_sched_enqueue": (C.c_int, [C.POINTER(SchedArgs), C.c_int, C.c_void_p]),
     "uv_sample": (C.c_int, [C.c_void_p, C.c_int, C.c_int64, C.c_int, C.c_int, C.c_int, C.c_float, C.c_float,
                             C.c_float, C.c_float, C.c_float, C.c_void_p, C.c_uint64, C.c_void_p, C.c_void_p,
-                            C.c_void_p, C.c_void_p, C.c_void_p]),
+                            C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
 }
 
 

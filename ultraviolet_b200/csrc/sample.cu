@@ -48,6 +48,8 @@ struct SampleParams {
   const int64_t* steps;
   int64_t* tok;
   float* logp;
+  int64_t* inc_a;  // optional per-row counters advanced by one after the draw (cache position, Philox step)
+  int64_t* inc_b;
 };
 
 __device__ __forceinline__ float block_sum(float v, float* red, int tid) {
@@ -94,6 +96,42 @@ __global__ void __launch_bounds__(SAMPLE_THREADS) sample_kernel(const __grid_con
     __syncthreads();
   }
 
+  if constexpr (sizeof(T) == 2)
+  if (P.greedy && !P.precapped && (reinterpret_cast<uintptr_t>(xr) & 15) == 0 && V % 8 == 0) {
+    // greedy over the softcap: no cumulative sums needed, so nothing is parked in shared memory -- one vectorised
+    // pass (8 values per 16-byte load) for the arg-max and the normaliser of the log-prob
+    float best = -INFINITY, sum = 0.f;
+    int best_i = 0x7fffffff;
+    for (int i = tid * 8; i < V; i += SAMPLE_THREADS * 8) {
+      const uint4 u4 = *reinterpret_cast<const uint4*>(xr + i);
+      const T* v = reinterpret_cast<const T*>(&u4);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        const float z = __fdividef(P.a, 1.0f + __expf(-(to_f32<T>(v[k]) + P.b) * inv_c));
+        if (z > best) best = z, best_i = i + k;
+        sum += __expf((z - P.a) * P.inv_t);
+      }
+    }
+    const float S_all = block_sum(sum, red, tid);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
+      if (ob > best || (ob == best && oi < best_i)) best = ob, best_i = oi;
+    }
+    if (lane == 0) red_v[warp] = best, red_i[warp] = best_i;
+    __syncthreads();
+    if (tid == 0) {
+      for (int w = 1; w < SAMPLE_THREADS / 32; ++w)
+        if (red_v[w] > best || (red_v[w] == best && red_i[w] < best_i)) best = red_v[w], best_i = red_i[w];
+      P.tok[row] = best_i;
+      P.logp[row] = (best - P.a) * P.inv_t - logf(S_all);
+      if (P.inc_a) P.inc_a[row] += 1;
+      if (P.inc_b) P.inc_b[row] += 1;
+    }
+    return;
+  }
+
   // ---- pass 1: softcap, exp, argmax (coalesced reads; e parked in shared memory)
   float best = -INFINITY;
   int best_i = 0x7fffffff;
@@ -133,6 +171,8 @@ __global__ void __launch_bounds__(SAMPLE_THREADS) sample_kernel(const __grid_con
         if (red_v[w] > best || (red_v[w] == best && red_i[w] < best_i)) best = red_v[w], best_i = red_i[w];
       P.tok[row] = best_i;
       P.logp[row] = (best - cap_a) * P.inv_t - logf(S_full);
+      if (P.inc_a) P.inc_a[row] += 1;
+      if (P.inc_b) P.inc_b[row] += 1;
     }
     return;
   }
@@ -195,6 +235,8 @@ __global__ void __launch_bounds__(SAMPLE_THREADS) sample_kernel(const __grid_con
     }
     P.tok[row] = t;
     P.logp[row] = (zof(t) - cap_a) * P.inv_t - logf(S_full);
+    if (P.inc_a) P.inc_a[row] += 1;  // every thread read steps[row] before the barrier above
+    if (P.inc_b) P.inc_b[row] += 1;
   }
 }
 
@@ -203,7 +245,7 @@ __global__ void __launch_bounds__(SAMPLE_THREADS) sample_kernel(const __grid_con
 extern "C" int uv_sample(const void* x, int x_dtype, int64_t x_stride, int B, int V, int precapped, float cap_a,
                          float cap_b, float cap_c, float temperature, float top_p, const float* u, uint64_t seed,
                          const int64_t* row_keys, const int64_t* steps, int64_t* tok_out, float* logp_out,
-                         void* stream) {
+                         int64_t* inc_a, int64_t* inc_b, void* stream) {
   using namespace uv;
   if (B == 0) return UV_OK;
   if (!x || !tok_out || !logp_out || B < 0) return UV_ERR_ARG;
@@ -219,6 +261,7 @@ extern "C" int uv_sample(const void* x, int x_dtype, int64_t x_stride, int B, in
   P.inv_t = greedy ? 1.0f : 1.0f / temperature;
   P.top_p = top_p, P.greedy = greedy ? 1 : 0, P.precapped = precapped ? 1 : 0;
   P.u = u, P.seed = seed, P.row_keys = row_keys, P.steps = steps, P.tok = tok_out, P.logp = logp_out;
+  P.inc_a = inc_a, P.inc_b = inc_b;
   const size_t smem = (size_t)(V + V / (V / SAMPLE_THREADS) + 1) * sizeof(float);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
 #define UV_GO(T)                                                                                              \

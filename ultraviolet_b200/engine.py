@@ -233,7 +233,8 @@ class DecodeEngine:
 
     def sample(self, head: Tensor, temperature: float, top_p: float = 1.0, u: Tensor | None = None, seed: int = 0,
                row_keys: Tensor | None = None, steps: Tensor | None = None, tok_out: Tensor | None = None,
-               logp_out: Tensor | None = None, precapped: bool = False):
+               logp_out: Tensor | None = None, precapped: bool = False, inc_a: Tensor | None = None,
+               inc_b: Tensor | None = None):
         """uv_sample on (B, V) head output; returns (tok int64 (B,), logp fp32 (B,)) in engine scratch unless
         output tensors are given."""
         B, V = head.shape
@@ -245,7 +246,7 @@ class DecodeEngine:
         with torch.cuda.device(self.device):
             rc = _lib.lib().uv_sample(head.data_ptr(), DTYPE_CODE[head.dtype], head.stride(0), B, V, int(precapped),
                                       a, b, c, float(temperature), float(top_p), p(u), C.c_uint64(seed & (2**64 - 1)),
-                                      p(row_keys), p(steps), tok_out.data_ptr(), logp_out.data_ptr(),
-                                      stream_ptr(self.device))
+                                      p(row_keys), p(steps), tok_out.data_ptr(), logp_out.data_ptr(), p(inc_a),
+                                      p(inc_b), stream_ptr(self.device))
         _lib.check(rc, "uv_sample")
         return tok_out, logp_out

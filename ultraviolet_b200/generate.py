@@ -29,7 +29,7 @@ def sample(logits: Tensor, temperature: float, top_k: int = 0, top_p: float = 1.
     with torch.cuda.device(logits.device):
         rc = _lib.lib().uv_sample(logits.data_ptr(), DTYPE_CODE[logits.dtype], logits.stride(0), B, V, 1, 0.0, 0.0,
                                   1.0, float(temperature), float(top_p), None if u is None else u.data_ptr(),
-                                  C.c_uint64(0), None, None, tok.data_ptr(), lp.data_ptr(),
+                                  C.c_uint64(0), None, None, tok.data_ptr(), lp.data_ptr(), None, None,
                                   stream_ptr(logits.device))
     _lib.check(rc, "uv_sample")
     return tok
@@ -72,9 +72,7 @@ class DecodeRunner:
         h = eng.trunk(self.tok, st, st.pos, st.starts, g_len=g_len, num_splits=self.m.__dict__.get(
             "decode_num_splits", getattr(type(self.m), "decode_num_splits", None)), skip_attn=self.skip_attn)
         eng.sample(eng.head(h), self.temperature, self.top_p, seed=self.seed, row_keys=self.row_keys,
-                   steps=self.steps)
-        st.pos.add_(1)
-        self.steps.add_(1)
+                   steps=self.steps, inc_a=st.pos, inc_b=self.steps)  # the sampler advances both counters
 
     def step(self, tok: Tensor) -> Tensor:
         p = int(self.st.host_pos.max())

@@ -33,6 +33,6 @@ def fused_sample(x: Tensor, u: Tensor, softcap, temperature: float = 1.0, block:
     with torch.cuda.device(x.device):
         rc = _lib.lib().uv_sample(x.data_ptr(), DTYPE_CODE[x.dtype], x.stride(0), B, V, 0, a, b, c,
                                   float(temperature), float(top_p), u.data_ptr(), C.c_uint64(0), None, None,
-                                  out.data_ptr(), lp.data_ptr(), stream_ptr(x.device))
+                                  out.data_ptr(), lp.data_ptr(), None, None, stream_ptr(x.device))
     _lib.check(rc, "uv_sample")
     return out, lp
