@@ -96,15 +96,47 @@ def prefill_fast(self, idx: Tensor, starts: Tensor, st: KernelDecodeState, rows:
     rows = rows.to(torch.int64)
     starts = starts.to(torch.int64).contiguous()
     idx_t = idx.t().contiguous()  # (T, n): one contiguous token vector per position
-    pos = torch.zeros(n, dtype=torch.int64, device=idx.device)
-    h = None
-    for t in range(T):
-        pos.fill_(t)
-        h = eng.trunk(idx_t[t], st, pos, starts, g_len=T, row_map=None if full else rows)
+    h = _prefill_positions(eng, st, idx_t, starts, None if full else rows, T)
     st.starts[rows] = starts
     st.pos[rows] = T
     st.host_pos[rows.cpu().numpy()] = T
     return eng.logits(h)
+
+
+def _prefill_positions(eng, st, idx_t: Tensor, starts: Tensor, rows, T: int) -> Tensor:
+    """Feed positions 0..T-1 of a left-padded sub-batch through the decode kernels.  The step for one position is
+    captured once as a CUDA graph reading a static token / position pair and replayed T times (positions differ
+    only through those two device tensors); short prompts run eagerly."""
+    n = idx_t.size(1)
+    dev = idx_t.device
+    pos = torch.zeros(n, dtype=torch.int64, device=dev)
+    if T < 8:
+        h = None
+        for t in range(T):
+            pos.fill_(t)
+            h = eng.trunk(idx_t[t], st, pos, starts, g_len=T, row_map=rows)
+        return h
+    tok = torch.zeros(n, dtype=torch.int64, device=dev)
+    out = {}
+
+    def body():
+        out["h"] = eng.trunk(tok, st, pos, starts, g_len=T, row_map=rows)
+        pos.add_(1)
+
+    tok.copy_(idx_t[0])
+    side = torch.cuda.Stream(dev)
+    side.wait_stream(torch.cuda.current_stream(dev))
+    with torch.cuda.stream(side):   # warm-up run of position 0 (allocates scratch); it is simply redone below
+        body()
+        pos.zero_()
+    torch.cuda.current_stream(dev).wait_stream(side)
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g, capture_error_mode="thread_local"):
+        body()
+    for t in range(T):
+        tok.copy_(idx_t[t])
+        g.replay()
+    return out["h"].clone()  # the graph's private pool goes away with the graph
 
 
 def patch_model(model, kv_dtype: str = "int8", num_splits: dict | None = None, backend: str = "auto",
