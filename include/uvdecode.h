@@ -105,7 +105,8 @@ typedef struct uv_attn_args {
                              allocated to a multiple of 8 slots takes the TMA path even when S itself is not */
   int window, ring;
   float scale;
-  int num_splits;         /* >= 1; > 1 needs workspace */
+  int num_splits;         /* >= 1.  2..8 splits of a row run as one thread-block cluster and merge through distributed
+                             shared memory; more than 8 merge through workspace */
   void* workspace;        /* uv_decode_attn_workspace_bytes() bytes, 16-byte aligned */
   size_t workspace_bytes;
   int* counters;          /* optional, B*KH ints, all zero on entry (left zero on exit): when given and num_splits > 1,
@@ -126,7 +127,8 @@ typedef struct uv_attn_args {
 
 size_t uv_decode_attn_workspace_bytes(int B, int KH, int G, int hd, int num_splits);
 /* Split count for (B*KH) cache rows of at most ctx keys on a device with n_sm SMs (role of default_splits,
- * decode_attn.py:121-129, retuned for 148-SM parts with 64-key TMA tiles). */
+ * decode_attn.py:121-129): every CTA resident in one wave (4 per SM), at least two 128-key tiles per split, and at
+ * most 8 splits (the cluster merge) unless the batch is so small that 8 per row leave most SMs idle. */
 int uv_default_splits(int n_bk, int ctx, int n_sm);
 int uv_decode_attn(const uv_attn_args* args, void* stream);
 

@@ -57,8 +57,14 @@ def test_argument_errors_return_codes_without_launching(lib):
 
 
 def test_split_heuristic_and_workspace(lib):
-    assert lib.uv_default_splits(512, 2320, 148) == 2
-    assert lib.uv_default_splits(64, 8448, 148) == 10
+    # one resident wave (4 CTAs per SM): 512 rows leave room for one split each, 64 rows for 9 -> 8 (cluster merge)
+    assert lib.uv_default_splits(512, 2320, 148) == 1
+    assert lib.uv_default_splits(64, 8192, 148) == 8
+    assert lib.uv_default_splits(128, 4096, 148) == 4
+    assert lib.uv_default_splits(8, 32768, 148) == 16  # a batch too small to fill the SMs with 8 splits per row
+    for n_bk, ctx in ((16, 8192), (64, 2048), (256, 2048), (3, 70000)):
+        s = lib.uv_default_splits(n_bk, ctx, 148)
+        assert 1 <= s <= 64 and n_bk * s <= 4 * 148 + n_bk
     assert lib.uv_default_splits(4096, 256, 148) == 1
     assert lib.uv_default_splits(1, 100, 148) == 1
     assert lib.uv_decode_attn_workspace_bytes(64, 1, 8, 64, 1) == 0

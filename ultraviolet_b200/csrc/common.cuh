@@ -42,6 +42,25 @@ inline void launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t sme
   cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);  // errors surface through check_launch()
 }
 
+// launch_pdl plus a thread-block cluster shape (cluster.x * y * z == 1: no cluster attribute)
+template <typename... KArgs, typename... Args>
+inline void launch_cluster(void (*kern)(KArgs...), dim3 grid, dim3 block, dim3 cluster, size_t smem, cudaStream_t st,
+                           Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid, cfg.blockDim = block, cfg.dynamicSmemBytes = smem, cfg.stream = st;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
+  int n = 1;
+  if (cluster.x * cluster.y * cluster.z > 1) {
+    attr[1].id = cudaLaunchAttributeClusterDimension;
+    attr[1].val.clusterDim.x = cluster.x, attr[1].val.clusterDim.y = cluster.y, attr[1].val.clusterDim.z = cluster.z;
+    n = 2;
+  }
+  cfg.attrs = attr, cfg.numAttrs = n;
+  cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
+
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 // ---- element conversion

@@ -24,6 +24,8 @@
 #include <mutex>
 #include <type_traits>
 
+#include <stdlib.h>
+
 #include "common.cuh"
 
 namespace uv {
@@ -73,6 +75,7 @@ struct AttnParams {
   int64_t gate_x_stride;
   const void* gate_w;
   int gate_ch;
+  int cluster;  // the splits of one cache row form a thread-block cluster and merge through distributed shared memory
 };
 
 // ------------------------------------------------------------------------------------------------ PTX wrappers
@@ -123,6 +126,18 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity)
       else if (now - t_begin > WAIT_NS) return false;
     }
   }
+}
+
+// Thread-block cluster: hardware barrier (no spinning) and loads from a peer CTA's shared memory.
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float ld_peer_f32(uint32_t local_addr, uint32_t rank) {
+  uint32_t remote;
+  float v;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+  return v;
 }
 
 __device__ __forceinline__ float ex2(float x) {
@@ -245,6 +260,50 @@ __device__ __forceinline__ void arrive_and_merge(const AttnParams& P, int bk, in
   if (tid == 0) P.counters[bk] = 0;
 }
 
+// Cluster merge: every split CTA of a cache row has left its partial (o[G][HD], m[G], l[G], fp32) at `part` in its
+// own shared memory.  After a cluster barrier the CTA of rank j merges query heads j, j + splits, ... reading its
+// peers' partials through distributed shared memory, and runs the epilogue; a second barrier keeps every CTA (and
+// its shared memory) alive until all peers have read it.  Called by ALL threads of ALL CTAs of the cluster.
+template <typename QT, int HD>
+__device__ __forceinline__ void cluster_merge(const AttnParams& P, const float* part, int bk, int sid, int warp,
+                                              int lane) {
+  constexpr int EPL = (HD + 31) / 32;
+  const int G = P.G, b = bk / P.KH, h = bk % P.KH;
+  cluster_sync_all();
+  const uint32_t po = smem_u32(part), pm = po + (uint32_t)(G * HD) * 4u, pl = pm + (uint32_t)G * 4u;
+  for (int row = sid + warp * P.splits; row < G; row += (NWARP + 1) * P.splits) {
+    // lane s holds split s's running maximum and sum (splits <= 8 <= 32)
+    float m_s = -INFINITY, l_s = 0.f;
+    if (lane < P.splits) {
+      m_s = ld_peer_f32(pm + (uint32_t)row * 4u, (uint32_t)lane);
+      l_s = ld_peer_f32(pl + (uint32_t)row * 4u, (uint32_t)lane);
+    }
+    const float mx = warp_max(m_s);
+    const float wt_s = (m_s == -INFINITY) ? 0.f : ex2(m_s - mx);
+    const float lsum = warp_sum(wt_s * l_s);
+    float z[EPL];
+#pragma unroll
+    for (int i = 0; i < EPL; ++i) z[i] = 0.f;
+    if (mx != -INFINITY) {
+#pragma unroll 8
+      for (int s = 0; s < P.splits; ++s) {
+        const float wt = __shfl_sync(0xffffffffu, wt_s, s);
+        if (wt == 0.f) continue;  // an empty split never wrote its o
+#pragma unroll
+        for (int i = 0; i < EPL; ++i) {
+          const int d = lane + 32 * i;
+          if (HD >= 32 || d < HD) z[i] += wt * ld_peer_f32(po + (uint32_t)(row * HD + d) * 4u, (uint32_t)s);
+        }
+      }
+      const float inv = 1.0f / lsum;
+#pragma unroll
+      for (int i = 0; i < EPL; ++i) z[i] *= inv;
+    }
+    finalize_row<QT, HD>(z, lane, b, h * G + row, h, P);
+  }
+  cluster_sync_all();
+}
+
 // ------------------------------------------------------------------------------------------------ split kernel
 template <int HD> struct StageLayout {
   static constexpr int K_OFF = 0;
@@ -349,6 +408,13 @@ __global__ void __launch_bounds__(NTHREAD) attn_split_kernel(const __grid_consta
         QT* o = static_cast<QT*>(P.out) + (int64_t)b * P.sob + (int64_t)(h * G + i / HD) * P.soh;
         o[i % HD] = from_f32<QT>(0.f);
       }
+    } else if (P.cluster) {
+      float* part = reinterpret_cast<float*>(smem) + NWARP * ROWS * (HD + 2);
+      if (tid < G) {
+        part[G * HD + tid] = -INFINITY;
+        part[G * HD + G + tid] = 0.f;
+      }
+      cluster_merge<QT, HD>(P, part, bk, sid, warp, lane);
     } else {
       if (tid < G) {
         const int64_t row = ((int64_t)bk * P.splits + sid) * G + tid;
@@ -725,6 +791,17 @@ __global__ void __launch_bounds__(NTHREAD) attn_split_kernel(const __grid_consta
 #pragma unroll
       for (int i = 0; i < EPL; ++i) z[i] *= inv;
       finalize_row<QT, HD>(z, lane, b, h * G + row, h, P);
+    } else if (P.cluster) {
+      float* part = reinterpret_cast<float*>(smem) + NWARP * ROWS * (HD + 2);
+      if (lane == 0) {
+        part[G * HD + row] = mx;
+        part[G * HD + G + row] = lsum;
+      }
+#pragma unroll
+      for (int i = 0; i < EPL; ++i) {
+        const int d = lane + 32 * i;
+        if (HD >= 32 || d < HD) part[row * HD + d] = z[i];
+      }
     } else {
       const int64_t wrow = ((int64_t)bk * P.splits + sid) * G + row;
       if (lane == 0) {
@@ -738,7 +815,12 @@ __global__ void __launch_bounds__(NTHREAD) attn_split_kernel(const __grid_consta
       }
     }
   }
-  if (P.splits > 1 && P.counters) arrive_and_merge<QT, HD>(P, bk, tid);
+  if (P.splits > 1) {
+    if (P.cluster)
+      cluster_merge<QT, HD>(P, reinterpret_cast<float*>(smem) + NWARP * ROWS * (HD + 2), bk, sid, warp, lane);
+    else if (P.counters)
+      arrive_and_merge<QT, HD>(P, bk, tid);
+  }
 }
 
 template <typename QT, int HD>
@@ -752,10 +834,12 @@ static int launch_attn(const AttnParams& P, bool bulk, cudaStream_t st) {
   using L = StageLayout<HD>;
   const bool gp16 = P.G > 8;
   const int rows = gp16 ? 16 : 8;
-  const size_t merge = (size_t)NWARP * rows * (HD + 2) * sizeof(float);
+  // warp-merge arrays, then (cluster launches) this CTA's split partial
+  const size_t merge = (size_t)(NWARP + 1) * rows * (HD + 2) * sizeof(float);
   size_t smem = (size_t)(bulk ? NSTAGE : 1) * L::BYTES;
   if (merge > smem) smem = merge;
   dim3 grid((unsigned)(P.B * P.KH), (unsigned)P.splits);
+  const dim3 cluster(1, P.cluster ? (unsigned)P.splits : 1u, 1);
 #define UV_LAUNCH(GP, BK)                                                                                  \
   do {                                                                                                     \
     auto kern = attn_split_kernel<QT, HD, GP, BK>;                                                         \
@@ -766,7 +850,7 @@ static int launch_attn(const AttnParams& P, bool bulk, cudaStream_t st) {
         return UV_ERR_CUDA;                                                                                \
       }                                                                                                    \
     }                                                                                                      \
-    launch_pdl(kern, grid, dim3(NTHREAD), smem, st, P);                                                    \
+    launch_cluster(kern, grid, dim3(NTHREAD), cluster, smem, st, P);                                                    \
   } while (0)
   if (gp16) {
     if (bulk) UV_LAUNCH(true, true);
@@ -778,7 +862,7 @@ static int launch_attn(const AttnParams& P, bool bulk, cudaStream_t st) {
 #undef UV_LAUNCH
   int rc = check_launch();
   if (rc != UV_OK) return rc;
-  if (P.splits > 1 && !P.counters) {
+  if (P.splits > 1 && !P.counters && !P.cluster) {
     attn_combine_kernel<QT, HD><<<(unsigned)(P.B * P.KH), NTHREAD, 0, st>>>(P);
     rc = check_launch();
   }
@@ -803,19 +887,34 @@ extern "C" size_t uv_decode_attn_workspace_bytes(int B, int KH, int G, int hd, i
   return (size_t)B * KH * num_splits * G * (size_t)(hd + 2) * sizeof(float);
 }
 
+namespace uv {
+static bool cluster_merge_enabled() {
+  static const bool on = [] {
+    const char* v = getenv("UVDECODE_CLUSTER_MERGE");  // "0" falls back to the workspace + arrival-counter merge
+    return !(v && v[0] == '0');
+  }();
+  return on;
+}
+}  // namespace uv
+
 extern "C" int uv_default_splits(int n_bk, int ctx, int n_sm) {
   if (n_bk < 1) n_bk = 1;
   if (n_sm < 1) n_sm = 148;
-  // enough CTAs for ~4 per SM, each split at least 256 keys (4 tiles) so the pipeline fills
-  int want = (4 * n_sm + n_bk - 1) / n_bk;
-  int cap = ctx / 256;
-  if (cap < 1) cap = 1;
-  if (cap > 64) cap = 64;
-  if (want > cap) want = cap;
-  return want < 1 ? 1 : want;
+  const int tiles = (ctx + uv::TILE - 1) / uv::TILE;
+  // All CTAs resident at once (4 per SM): a launch that spills into a second wave pays that wave's whole latency.
+  int s = 4 * n_sm / n_bk;
+  if (s > tiles / 2) s = tiles / 2;  // at least two tiles per split
+  if (s > 64) s = 64;
+  if (s < 1) s = 1;
+  // Up to 8 splits merge inside a thread-block cluster, ~3.5 us cheaper than the workspace merge: more than 8 only
+  // pays when 8 per row would leave most of the SMs without a CTA.
+  if (s > 8) s = (16 * n_bk <= n_sm) ? (s < 16 ? s : 16) : 8;
+  const int per = (tiles + s - 1) / s;  // tiles per split; the fewest splits with that much work each
+  s = (tiles + per - 1) / per;
+  return s < 1 ? 1 : s;
 }
 
-extern "C" int uv_decode_attn(const uv_attn_args* a, void* stream) {
+static int decode_attn_impl(const uv_attn_args* a, void* stream, bool allow_cluster) {
   using namespace uv;
   if (!a) return UV_ERR_ARG;
   if (a->B == 0) return UV_OK;
@@ -849,7 +948,9 @@ extern "C" int uv_decode_attn(const uv_attn_args* a, void* stream) {
   P.counters = a->num_splits > 1 ? a->counters : nullptr;
   P.v_cur = a->v_cur, P.v_cur_sb = a->v_cur_sb, P.v_cur_sh = a->v_cur_sh, P.xsa_alpha = a->xsa_alpha, P.xsa_eps = a->xsa_eps;
   P.gate_x = a->gate_x, P.gate_x_stride = a->gate_x_stride, P.gate_w = a->gate_w, P.gate_ch = a->gate_ch;
-  if (P.splits > 1) {
+  // up to 8 splits (the portable cluster size) merge inside a thread-block cluster and need no workspace
+  P.cluster = (allow_cluster && P.splits > 1 && P.splits <= 8 && cluster_merge_enabled()) ? 1 : 0;
+  if (P.splits > 1 && !P.cluster) {
     const size_t need = uv_decode_attn_workspace_bytes(a->B, a->KH, G, hd, P.splits);
     if (!a->workspace || a->workspace_bytes < need) return UV_ERR_WORKSPACE;
     if (!aligned16(a->workspace)) return UV_ERR_ALIGN;
@@ -873,6 +974,8 @@ extern "C" int uv_decode_attn(const uv_attn_args* a, void* stream) {
 
 
 // ------------------------------------------------------------------------------------------------ built-in scratch
+extern "C" int uv_decode_attn(const uv_attn_args* a, void* stream) { return decode_attn_impl(a, stream, true); }
+
 // uv_decode_attn_static: split-K decode attention for callers that may not allocate device memory at all.
 // The split partials and the arrival counters live in this file-scope device array instead of a caller workspace.
 // Every GPU that loads the library holds the array (4 MiB + 16 KiB) until the process exits.
@@ -933,5 +1036,5 @@ extern "C" int uv_decode_attn_static(const uv_attn_args* a, void* stream) {
       return UV_ERR_CUDA;
     }
   }
-  return uv_decode_attn(&b, stream);
+  return decode_attn_impl(&b, stream, false);  // the split partials go through the built-in array
 }
