@@ -168,6 +168,10 @@ int uv_decode_attn_static(const uv_attn_args* args, void* stream);
  */
 int uv_embed_norm(const int64_t* tok, const void* embed, int dtype, int64_t vocab, int d, void* x, void* xn, int B,
                   void* stream);
+/* uv_embed_norm that also writes the step's RoPE table rope_cs (B, 2*n_pairs) fp32: cos(pos*inv_freq[j]) for j <
+ * n_pairs, then the sines, each rounded to dtype (the cos / sin operands of apply_rope, fast_decode.py:286-290). */
+int uv_embed_norm_rope(const int64_t* tok, const void* embed, int dtype, int64_t vocab, int d, void* x, void* xn,
+                       int B, const int64_t* pos, const float* inv_freq, int n_pairs, float* rope_cs, void* stream);
 int uv_qkv_post(void* qkv, const void* xn, const int64_t* tok, const void* value_embed, const void* ve_gate,
                 const float* inv_freq, const int64_t* pos, int8_t* k_cache, int8_t* v_cache, uint16_t* k_scale,
                 uint16_t* v_scale, const int64_t* row_map, int* oob_count, int dtype, int64_t vocab, int B, int H, int K,
@@ -175,6 +179,36 @@ int uv_qkv_post(void* qkv, const void* xn, const int64_t* tok, const void* value
 int uv_resid_norm(const void* x, const void* a, const float* lambdas, int dtype, int d, void* h, void* hn, int B,
                   void* stream);
 int uv_swiglu(const void* gu, int dtype, int f, void* act, int B, void* stream);
+
+/* uv_qkv_attn: uv_qkv_post followed by uv_decode_attn on the same rows, as ONE launch.  The attention CTAs do the
+ * per-head post-processing of their row in their prologue, while the bulk copies of the older cache tiles are already
+ * in flight; the split that owns position pos appends the new key / value and only then copies that tile.  Both
+ * argument blocks must describe the same step: same B / H / K / hd / S / ring, the same pos, row_map, cache and scale
+ * pointers; attn->q = qkv, attn->v_cur = the value slots of qkv; cache rows contiguous with S_alloc slots.  The
+ * one-launch form needs the bulk-copy path, arrival counters for more than 8 splits and, on layers with RoPE, the
+ * rope_cs table; otherwise the function runs the two launches itself.  qkv is left unmodified by the one-launch form and post-processed in place by the
+ * two-launch form: callers must not read it afterwards. */
+typedef struct uv_qkv_args { /* the parameters of uv_qkv_post, by name */
+  void* qkv;
+  const void* xn;
+  const int64_t* tok;
+  const void* value_embed;
+  const void* ve_gate;
+  const float* inv_freq;
+  const int64_t* pos;
+  int8_t* k_cache;
+  int8_t* v_cache;
+  uint16_t* k_scale;
+  uint16_t* v_scale;
+  const int64_t* row_map;
+  int* oob_count;
+  int dtype;
+  int64_t vocab;
+  int B, H, K, hd, d, S, S_alloc, ring, ve_ch, n_pairs;
+  const float* rope_cs;   /* optional (B, 2*n_pairs) table from uv_embed_norm_rope for these pos: read instead of
+                             evaluating cos / sin in every layer (same values bit for bit) */
+} uv_qkv_args;
+int uv_qkv_attn(const uv_qkv_args* qkv, const uv_attn_args* attn, void* stream);
 
 /* GEMMs of the decode step with the row-wise kernels above fused into their epilogues (hand-written mma.sync
  * mainloop; same results as library GEMM + the separate kernel up to the summation order of the fp32 accumulation).

@@ -294,3 +294,93 @@ def test_philox_keyed_draws_match_oracle():
     tok2, _ = _sample(x.flip(0).contiguous(), T=1.0, seed=1234567, row_keys=keys.flip(0).contiguous(),
                       steps=steps.flip(0).contiguous())
     assert np.array_equal(tok2[::-1], tok)   # a sequence's draw does not depend on the row it sits in
+
+
+# ------------------------------------------------------------------------------------------------ fused QKV + attention
+def _qkv_attn_case(dtype, ring, splits, rope, ve, fused, G=8, hd=64, seed=0):
+    """One layer's uv_qkv_post + uv_decode_attn (fused=False) or uv_qkv_attn (fused=True) on identical inputs.
+    Returns (attention output, k cache, v cache, k scales, v scales)."""
+    import ctypes as C
+    from ultraviolet_b200 import _lib
+    from ultraviolet_b200.kernels._util import DTYPE_CODE
+    from ultraviolet_b200.kernels.decode_attn import attn_launch, workspace_for
+    r = np.random.default_rng(seed)
+    B, H, K, d, vocab = 12, G, 1, 640, 512
+    S = 256 if ring else 1024
+    window = 256 if ring else 0
+    slots = H + 2 * K
+    # positions that sit on, just before and just after 128-key tile edges; row 0 is a fresh sequence
+    pos_np = np.array([0, 5, 127, 128, 129, 255, 256, 383, 384, 600, 777, 1000], np.int64)
+    starts_np = np.array([0, 2, 0, 100, 0, 130, 0, 0, 300, 0, 512, 0], np.int64)
+    rows_np = r.permutation(16)[:B].astype(np.int64)  # batch entries live in arbitrary rows of a 16-row cache
+    kc = T(r.integers(-127, 128, (16, K, S, hd)).astype(np.int8))
+    vc = T(r.integers(-127, 128, (16, K, S, hd)).astype(np.int8))
+    ks = T((r.random((16, K, S)) * 0.02 + 0.005).astype(np.float16))
+    vs = T((r.random((16, K, S)) * 0.02 + 0.005).astype(np.float16))
+    qkv = T(r.standard_normal((B, slots * hd)).astype(np.float32), dtype)
+    xn = T(r.standard_normal((B, d)).astype(np.float32), dtype)
+    tok = T(r.integers(0, vocab, B).astype(np.int64))
+    vemb = T(r.standard_normal((vocab, K * hd)).astype(np.float32), dtype)
+    vgate = T(r.standard_normal((K, 12)).astype(np.float32) * 0.3, dtype)
+    inv_freq = T((1024.0 ** (-np.arange(16) / 16.0)).astype(np.float32))
+    gate_w = T(r.standard_normal((H, 128)).astype(np.float32) * 0.3, dtype)
+    alpha = T(np.tanh(r.standard_normal(H).astype(np.float32) * 0.3))
+    pos, starts, rows = T(pos_np), T(starts_np), T(rows_np)
+    oob = torch.zeros(1, dtype=torch.int32, device=DEV)
+    post = (tok.data_ptr(), vemb.data_ptr() if ve else None, vgate.data_ptr() if ve else None,
+            inv_freq.data_ptr() if rope else None, pos.data_ptr(), kc.data_ptr(), vc.data_ptr(), ks.data_ptr(),
+            vs.data_ptr(), rows.data_ptr(), oob.data_ptr(), DTYPE_CODE[dtype], vocab, B, H, K, hd, d, S, S,
+            int(ring), 12, 16)
+    q3 = qkv.view(B, slots, hd)
+    out = torch.empty(B, H, hd, dtype=dtype, device=DEV)
+    ws = workspace_for(B, K, G, hd, splits, DEV)
+    cnt = torch.zeros(B * K, dtype=torch.int32, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    pre = None
+    raw = qkv.clone()
+    if fused:
+        pre = _lib.QkvArgs()
+        (pre.qkv, pre.xn, pre.tok, pre.value_embed, pre.ve_gate, pre.inv_freq, pre.pos, pre.k_cache, pre.v_cache,
+         pre.k_scale, pre.v_scale, pre.row_map, pre.oob_count, pre.dtype, pre.vocab, pre.B, pre.H, pre.K, pre.hd,
+         pre.d, pre.S, pre.S_alloc, pre.ring, pre.ve_ch, pre.n_pairs) = (qkv.data_ptr(), xn.data_ptr(), *post)
+        if rope:  # the step's cos / sin table, as the engine gets it from the kernel that opens the step
+            emb = torch.zeros(vocab, d, dtype=dtype, device=DEV)
+            x0, x1 = torch.empty(B, d, dtype=dtype, device=DEV), torch.empty(B, d, dtype=dtype, device=DEV)
+            cs = torch.zeros(B, 32, dtype=torch.float32, device=DEV)
+            _lib.check(_lib.lib().uv_embed_norm_rope(tok.data_ptr(), emb.data_ptr(), DTYPE_CODE[dtype], vocab, d,
+                                                     x0.data_ptr(), x1.data_ptr(), B, pos.data_ptr(),
+                                                     inv_freq.data_ptr(), 16, cs.data_ptr(),
+                                                     torch.cuda.current_stream().cuda_stream), "uv_embed_norm_rope")
+            pre.rope_cs = cs.data_ptr()
+    else:
+        _lib.check(_lib.lib().uv_qkv_post(qkv.data_ptr(), xn.data_ptr(), *post,
+                                          torch.cuda.current_stream().cuda_stream), "uv_qkv_post")
+    attn_launch(q3[:, :H], kc, vc, pos, starts, 0.14125, window, ring, ks, vs, splits, out, ws,
+                v_cur=q3[:, H + K:], xsa_alpha=alpha, xsa_eps=1e-4, gate_x=xn, gate_w=gate_w, counters=cnt,
+                status=status, row_map=rows, pre=pre)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0 and int(cnt.abs().sum()) == 0
+    # the one-launch form reads the projection and leaves it alone; the two-launch form rewrites it in place
+    assert torch.equal(raw, qkv) == fused
+    return out, kc, vc, ks, vs, int(oob.item())
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("ring,rope,ve", [(True, True, True), (True, True, False), (False, False, True),
+                                          (False, False, False)])
+@pytest.mark.parametrize("splits", [1, 3, 8, 11])
+def test_qkv_attn_one_launch_equals_two(dtype, ring, rope, ve, splits):
+    """uv_qkv_attn == uv_qkv_post then uv_decode_attn: cache bytes and scales bit-identical, outputs identical."""
+    a = _qkv_attn_case(dtype, ring, splits, rope, ve, fused=False)
+    b = _qkv_attn_case(dtype, ring, splits, rope, ve, fused=True)
+    for x, y, name in zip(a[1:5], b[1:5], ("k", "v", "k_scale", "v_scale")):
+        assert torch.equal(x, y), name
+    assert a[5] == b[5]  # rows past the end of a linear cache are counted, not written, either way
+    assert torch.equal(a[0], b[0])
+
+
+def test_qkv_attn_group16_and_small_heads():
+    for G, hd in ((16, 64), (8, 32), (4, 128)):
+        a = _qkv_attn_case(torch.bfloat16, True, 2, True, True, fused=False, G=G, hd=hd, seed=G + hd)
+        b = _qkv_attn_case(torch.bfloat16, True, 2, True, True, fused=True, G=G, hd=hd, seed=G + hd)
+        assert torch.equal(a[0], b[0]) and torch.equal(a[1], b[1]) and torch.equal(a[2], b[2])

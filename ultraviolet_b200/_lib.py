@@ -41,6 +41,19 @@ class AttnArgs(C.Structure):
     ]
 
 
+class QkvArgs(C.Structure):
+    """uv_qkv_args (include/uvdecode.h): the parameters of uv_qkv_post, by name."""
+    _fields_ = [
+        ("qkv", C.c_void_p), ("xn", C.c_void_p), ("tok", C.c_void_p), ("value_embed", C.c_void_p),
+        ("ve_gate", C.c_void_p), ("inv_freq", C.c_void_p), ("pos", C.c_void_p),
+        ("k_cache", C.c_void_p), ("v_cache", C.c_void_p), ("k_scale", C.c_void_p), ("v_scale", C.c_void_p),
+        ("row_map", C.c_void_p), ("oob_count", C.c_void_p), ("dtype", C.c_int), ("vocab", C.c_int64),
+        ("B", C.c_int), ("H", C.c_int), ("K", C.c_int), ("hd", C.c_int), ("d", C.c_int), ("S", C.c_int),
+        ("S_alloc", C.c_int), ("ring", C.c_int), ("ve_ch", C.c_int), ("n_pairs", C.c_int),
+        ("rope_cs", C.c_void_p),
+    ]
+
+
 class SchedArgs(C.Structure):
     _fields_ = [(n, C.c_void_p) for n in (
         "req", "fed", "gen", "cur_tok", "pos", "starts", "row_key", "step_ctr", "samp_tok", "samp_lp", "prompt_off",
@@ -65,7 +78,10 @@ SIGNATURES = {
     "uv_decode_attn_static": (C.c_int, [C.POINTER(AttnArgs), C.c_void_p]),
     "uv_embed_norm": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int64, C.c_int, C.c_void_p, C.c_void_p, C.c_int,
                                 C.c_void_p]),
+    "uv_embed_norm_rope": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int64, C.c_int, C.c_void_p, C.c_void_p,
+                                     C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]),
     "uv_qkv_post": (C.c_int, [C.c_void_p] * 13 + [C.c_int, C.c_int64] + [C.c_int] * 10 + [C.c_void_p]),
+    "uv_qkv_attn": (C.c_int, [C.POINTER(QkvArgs), C.POINTER(AttnArgs), C.c_void_p]),
     "uv_resid_norm": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_int,
                                 C.c_void_p]),
     "uv_swiglu": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_int, C.c_void_p]),

@@ -27,6 +27,7 @@
 #include <stdlib.h>
 
 #include "common.cuh"
+#include "qkv_post.cuh"
 
 namespace uv {
 
@@ -76,6 +77,10 @@ struct AttnParams {
   const void* gate_w;
   int gate_ch;
   int cluster;  // the splits of one cache row form a thread-block cluster and merge through distributed shared memory
+  // uv_qkv_attn: the kernel first post-processes the row's raw QKV projection (q / k / v of this step) and appends
+  // the new key and value to the cache; q and the current v are then taken from shared memory
+  int has_pre;
+  QkvPostParams pre;
 };
 
 // ------------------------------------------------------------------------------------------------ PTX wrappers
@@ -128,6 +133,11 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity)
   }
 }
 
+// Named CTA barrier for a subset of the warps (id 1: the consumer warps).
+__device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
+
 // Thread-block cluster: hardware barrier (no spinning) and loads from a peer CTA's shared memory.
 __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
@@ -168,13 +178,16 @@ __device__ __forceinline__ uint32_t bias_pair(uint32_t x, uint32_t sel) {
 // epilogue with the reference's rounding points (Attention.post, ultraviolet/model.py:322-333) and stores it.
 template <typename QT, int HD>
 __device__ __forceinline__ void finalize_row(float (&z)[(HD + 31) / 32], int lane, int b, int head, int kvh,
-                                             const AttnParams& P) {
+                                             const AttnParams& P, const QT* v_stage = nullptr) {
   constexpr int EPL = (HD + 31) / 32;
   const bool act = (HD >= 32) || lane < HD;
 #pragma unroll
   for (int i = 0; i < EPL; ++i) z[i] = rnd<QT>(z[i]);  // the attention output itself is in the activation dtype
   if (P.xsa_alpha != nullptr) {
-    const QT* vc = static_cast<const QT*>(P.v_cur) + (int64_t)b * P.v_cur_sb + (int64_t)kvh * P.v_cur_sh;
+    // the current token's unquantised v: from the caller's tensor, or from the shared-memory copy the fused
+    // prologue left
+    const QT* vc = v_stage ? v_stage
+                           : static_cast<const QT*>(P.v_cur) + (int64_t)b * P.v_cur_sb + (int64_t)kvh * P.v_cur_sh;
     float vv[EPL], n2 = 0.f;
 #pragma unroll
     for (int i = 0; i < EPL; ++i) {
@@ -214,7 +227,8 @@ __device__ __forceinline__ void finalize_row(float (&z)[(HD + 31) / 32], int lan
 // Log-sum-exp merge of the split partials of one (b, kv head): warp per query head, then the shared epilogue.
 // Partials were written by other CTAs: read them through L2 (ld.global.cg).
 template <typename QT, int HD>
-__device__ __forceinline__ void combine_rows(const AttnParams& P, int bk, int warp, int lane) {
+__device__ __forceinline__ void combine_rows(const AttnParams& P, int bk, int warp, int lane,
+                                             const QT* v_stage = nullptr) {
   constexpr int EPL = (HD + 31) / 32;
   const int b = bk / P.KH, h = bk % P.KH;
   for (int row = warp; row < P.G && warp < NWARP; row += NWARP) {
@@ -242,13 +256,13 @@ __device__ __forceinline__ void combine_rows(const AttnParams& P, int bk, int wa
 #pragma unroll
       for (int i = 0; i < EPL; ++i) z[i] *= inv;
     }
-    finalize_row<QT, HD>(z, lane, b, h * P.G + row, h, P);
+    finalize_row<QT, HD>(z, lane, b, h * P.G + row, h, P, v_stage);
   }
 }
 
 // Called by every CTA of a split launch after its partials are written: the CTA that arrives last merges.
 template <typename QT, int HD>
-__device__ __forceinline__ void arrive_and_merge(const AttnParams& P, int bk, int tid) {
+__device__ __forceinline__ void arrive_and_merge(const AttnParams& P, int bk, int tid, const QT* v_stage = nullptr) {
   __shared__ int s_last;
   __threadfence();
   __syncthreads();
@@ -256,7 +270,7 @@ __device__ __forceinline__ void arrive_and_merge(const AttnParams& P, int bk, in
   __syncthreads();
   if (!s_last) return;
   __threadfence();
-  combine_rows<QT, HD>(P, bk, tid >> 5, tid & 31);
+  combine_rows<QT, HD>(P, bk, tid >> 5, tid & 31, v_stage);
   if (tid == 0) P.counters[bk] = 0;
 }
 
@@ -266,7 +280,7 @@ __device__ __forceinline__ void arrive_and_merge(const AttnParams& P, int bk, in
 // its shared memory) alive until all peers have read it.  Called by ALL threads of ALL CTAs of the cluster.
 template <typename QT, int HD>
 __device__ __forceinline__ void cluster_merge(const AttnParams& P, const float* part, int bk, int sid, int warp,
-                                              int lane) {
+                                              int lane, const QT* v_stage = nullptr) {
   constexpr int EPL = (HD + 31) / 32;
   const int G = P.G, b = bk / P.KH, h = bk % P.KH;
   cluster_sync_all();
@@ -299,7 +313,7 @@ __device__ __forceinline__ void cluster_merge(const AttnParams& P, const float* 
 #pragma unroll
       for (int i = 0; i < EPL; ++i) z[i] *= inv;
     }
-    finalize_row<QT, HD>(z, lane, b, h * G + row, h, P);
+    finalize_row<QT, HD>(z, lane, b, h * G + row, h, P, v_stage);
   }
   cluster_sync_all();
 }
@@ -359,7 +373,7 @@ __device__ __forceinline__ void imma16832_z(int (&d)[4], uint32_t a0, uint32_t a
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
 }
 
-template <typename QT, int HD, bool GP16, bool BULK>
+template <typename QT, int HD, bool GP16, bool BULK, bool PRE>
 __global__ void __launch_bounds__(NTHREAD) attn_split_kernel(const __grid_constant__ AttnParams P) {
   using L = StageLayout<HD>;
   constexpr int QN = HD / 4;         // query dims per lane = bytes of a key row per lane
@@ -394,13 +408,69 @@ __global__ void __launch_bounds__(NTHREAD) attn_split_kernel(const __grid_consta
     hi = P.S - 1;
   }
   int64_t t0 = 0, t1 = 0;
+  int owner_sid = 0;  // the split whose tiles hold position p (it appends the new key / value in the fused form)
   if (hi >= lo) {
     const int64_t t_lo = lo / TILE, t_hi = hi / TILE;
     const int64_t per = (t_hi - t_lo + P.splits) / P.splits;  // ceil(n_tiles / splits)
     t0 = t_lo + (int64_t)sid * per;
     t1 = t0 + per < t_hi + 1 ? t0 + per : t_hi + 1;
+    if (p == hi) owner_sid = (int)((t_hi - t_lo) / per);
   }
   const int ntile = t1 > t0 ? (int)(t1 - t0) : 0;
+
+  // ---- fused form (uv_qkv_attn): the consumer warps post-process the row's raw q / k / v head slots, leave them in
+  //      shared memory behind the stage ring ([G] query heads, key, value) and, in the owning split, append the
+  //      quantised key and value to the cache.  Splits of one row repeat the arithmetic; only the owner writes.
+//      No copy waits for that write: every tile is requested up front, and the entry at p is patched into the
+//      landed tile from shared memory.
+  QT* const pre_stage = reinterpret_cast<QT*>(smem + (size_t)NSTAGE * L::BYTES);  // [G + 2][HD] activations,
+  int8_t* const pre_q8 = reinterpret_cast<int8_t*>(pre_stage + (ROWS + 2) * HD);     // then [2][HD] int8 (k, v)
+  uint16_t* const pre_sc = reinterpret_cast<uint16_t*>(pre_q8 + 2 * HD);             // and their two fp16 scales
+  const QT* v_stage = nullptr;
+  auto pre_items = [&]() {
+    constexpr int E = HD >= 32 ? HD / 32 : 1;
+    constexpr int MAXI = (ROWS + 2 + NWARP - 1) / NWARP;
+    const int slots = P.pre.H + 2 * P.pre.K;
+    const QT* raw = static_cast<const QT*>(P.pre.qkv) + (int64_t)b * slots * HD;
+    const bool act = lane * E < HD;
+    float x[MAXI][E];
+    int hs[MAXI];
+#pragma unroll
+    for (int n = 0; n < MAXI; ++n) {  // all loads first: one round trip for the warp's items
+      const int it = warp + n * NWARP;
+      hs[n] = it < G ? h * G + it : (it == G ? P.pre.H + h : P.pre.H + P.pre.K + h);
+#pragma unroll
+      for (int i = 0; i < E; ++i)
+        x[n][i] = (it < G + 2 && act) ? to_f32<QT>(raw[(int64_t)hs[n] * HD + lane * E + i]) : 0.f;
+    }
+#pragma unroll
+    for (int n = 0; n < MAXI; ++n) {
+      const int it = warp + n * NWARP;
+      if (it >= G + 2) continue;  // warp-uniform
+      qkv_post_compute<QT, HD, true>(P.pre, b, hs[n], lane, x[n]);
+#pragma unroll
+      for (int i = 0; i < E; ++i)
+        if (act) pre_stage[it * HD + lane * E + i] = from_f32<QT>(x[n][i]);
+      if (it >= G) {
+        // the quantised entry stays in shared memory too: the warp that consumes position p patches it into the
+        // landed tile, so no copy has to wait for the global write below
+        int8_t q8[E];
+        const uint16_t s = quantize_lane<E>(x[n], q8);
+#pragma unroll
+        for (int i = 0; i < E; ++i)
+          if (act) pre_q8[(it - G) * HD + lane * E + i] = q8[i];
+        if (lane == 0) pre_sc[it - G] = s;
+        if (sid == owner_sid) qkv_post_store<HD>(P.pre, b, hs[n], lane, q8, s);
+      }
+    }
+  };
+  if constexpr (PRE) {
+    v_stage = pre_stage + (G + 1) * HD;
+    if (ntile == 0) {
+      if (!producer) pre_items();
+      __syncthreads();
+    }
+  }
 
   if (ntile == 0) {  // empty row or inactive split
     if (P.splits == 1) {
@@ -414,14 +484,14 @@ __global__ void __launch_bounds__(NTHREAD) attn_split_kernel(const __grid_consta
         part[G * HD + tid] = -INFINITY;
         part[G * HD + G + tid] = 0.f;
       }
-      cluster_merge<QT, HD>(P, part, bk, sid, warp, lane);
+      cluster_merge<QT, HD>(P, part, bk, sid, warp, lane, v_stage);
     } else {
       if (tid < G) {
         const int64_t row = ((int64_t)bk * P.splits + sid) * G + tid;
         P.ws_m[row] = -INFINITY;
         P.ws_l[row] = 0.f;
       }
-      if (P.counters) arrive_and_merge<QT, HD>(P, bk, tid);
+      if (P.counters) arrive_and_merge<QT, HD>(P, bk, tid, v_stage);
     }
     return;
   }
@@ -674,6 +744,9 @@ __global__ void __launch_bounds__(NTHREAD) attn_split_kernel(const __grid_consta
           issue(t0 + j, s);
         }
       }
+    } else if constexpr (PRE) {
+      pre_items();
+      named_bar_sync(1, NWARP * 32);  // every consumer warp reads the q heads (and the new entry) the others staged
     }
   }
   // the first tiles are in flight: consumers load and split Q under their latency
@@ -682,7 +755,9 @@ __global__ void __launch_bounds__(NTHREAD) attn_split_kernel(const __grid_consta
   for (int hr = 0; hr < NH; ++hr) {
     float qv[QN];
     const int head = r + 8 * hr;
-    const QT* qb = static_cast<const QT*>(P.q) + (int64_t)b * P.sqb + (int64_t)(h * G + head) * P.sqh + c * QN;
+    const QT* qb = PRE
+                       ? pre_stage + head * HD + c * QN
+                       : static_cast<const QT*>(P.q) + (int64_t)b * P.sqb + (int64_t)(h * G + head) * P.sqh + c * QN;
 #pragma unroll
     for (int i = 0; i < QN; i += 2) {
       if (head < G) {
@@ -706,6 +781,22 @@ __global__ void __launch_bounds__(NTHREAD) attn_split_kernel(const __grid_consta
         if (!dead) {
           const unsigned char* st = smem + (size_t)s * L::BYTES;
           const int64_t kb0 = (t0 + it) * TILE + WKEYS * warp;  // position of this warp's first key
+          if constexpr (PRE) {
+            // The tile was copied while the cache entry at p was being rewritten: the warp that consumes
+            // position p (no other warp reads it) overwrites that entry in the landed tile with the staged bytes.
+            if (p == hi && p >= kb0 && p < kb0 + WKEYS) {
+              unsigned char* sw = smem + (size_t)s * L::BYTES;
+              const int kk = (int)(p - (t0 + it) * TILE);
+              for (int w = lane; w < HD / 2; w += 32) {
+                const uint32_t v = reinterpret_cast<const uint32_t*>(pre_q8)[w];
+                if (w < HD / 4) *reinterpret_cast<uint32_t*>(sw + L::K_OFF + kk * HD + 4 * w) = v;
+                else *reinterpret_cast<uint32_t*>(sw + L::V_OFF + kk * HD + 4 * (w - HD / 4)) = v;
+              }
+              if (lane == 0) *reinterpret_cast<uint16_t*>(sw + L::KS_OFF + kk * 2) = pre_sc[0];
+              if (lane == 1) *reinterpret_cast<uint16_t*>(sw + L::VS_OFF + kk * 2) = pre_sc[1];
+              __syncwarp();
+            }
+          }
           if (kb0 + WKEYS - 1 >= lo && kb0 <= hi) {
             if (kb0 < lo || kb0 + WKEYS - 1 > hi) {
               const int64_t lr = lo - kb0, hr_ = hi - kb0;
@@ -790,7 +881,7 @@ __global__ void __launch_bounds__(NTHREAD) attn_split_kernel(const __grid_consta
       const float inv = 1.0f / lsum;
 #pragma unroll
       for (int i = 0; i < EPL; ++i) z[i] *= inv;
-      finalize_row<QT, HD>(z, lane, b, h * G + row, h, P);
+      finalize_row<QT, HD>(z, lane, b, h * G + row, h, P, v_stage);
     } else if (P.cluster) {
       float* part = reinterpret_cast<float*>(smem) + NWARP * ROWS * (HD + 2);
       if (lane == 0) {
@@ -817,9 +908,10 @@ __global__ void __launch_bounds__(NTHREAD) attn_split_kernel(const __grid_consta
   }
   if (P.splits > 1) {
     if (P.cluster)
-      cluster_merge<QT, HD>(P, reinterpret_cast<float*>(smem) + NWARP * ROWS * (HD + 2), bk, sid, warp, lane);
+      cluster_merge<QT, HD>(P, reinterpret_cast<float*>(smem) + NWARP * ROWS * (HD + 2), bk, sid, warp, lane,
+                            v_stage);
     else if (P.counters)
-      arrive_and_merge<QT, HD>(P, bk, tid);
+      arrive_and_merge<QT, HD>(P, bk, tid, v_stage);
   }
 }
 
@@ -838,11 +930,13 @@ static int launch_attn(const AttnParams& P, bool bulk, cudaStream_t st) {
   const size_t merge = (size_t)(NWARP + 1) * rows * (HD + 2) * sizeof(float);
   size_t smem = (size_t)(bulk ? NSTAGE : 1) * L::BYTES;
   if (merge > smem) smem = merge;
+  // staged q heads, key and value (activations), then the quantised key / value and their scales, behind the ring
+  if (P.has_pre) smem += (size_t)(rows + 2) * HD * sizeof(QT) + 2 * HD + 16;
   dim3 grid((unsigned)(P.B * P.KH), (unsigned)P.splits);
   const dim3 cluster(1, P.cluster ? (unsigned)P.splits : 1u, 1);
-#define UV_LAUNCH(GP, BK)                                                                                  \
+#define UV_LAUNCH(GP, BK, PR)                                                                              \
   do {                                                                                                     \
-    auto kern = attn_split_kernel<QT, HD, GP, BK>;                                                         \
+    auto kern = attn_split_kernel<QT, HD, GP, BK, PR>;                                                     \
     if (smem > 48 * 1024) {                                                                                \
       cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);  \
       if (e != cudaSuccess) {                                                                              \
@@ -853,11 +947,13 @@ static int launch_attn(const AttnParams& P, bool bulk, cudaStream_t st) {
     launch_cluster(kern, grid, dim3(NTHREAD), cluster, smem, st, P);                                                    \
   } while (0)
   if (gp16) {
-    if (bulk) UV_LAUNCH(true, true);
-    else UV_LAUNCH(true, false);
+    if (bulk && P.has_pre) UV_LAUNCH(true, true, true);
+    else if (bulk) UV_LAUNCH(true, true, false);
+    else UV_LAUNCH(true, false, false);
   } else {
-    if (bulk) UV_LAUNCH(false, true);
-    else UV_LAUNCH(false, false);
+    if (bulk && P.has_pre) UV_LAUNCH(false, true, true);
+    else if (bulk) UV_LAUNCH(false, true, false);
+    else UV_LAUNCH(false, false, false);
   }
 #undef UV_LAUNCH
   int rc = check_launch();
@@ -914,7 +1010,11 @@ extern "C" int uv_default_splits(int n_bk, int ctx, int n_sm) {
   return s < 1 ? 1 : s;
 }
 
-static int decode_attn_impl(const uv_attn_args* a, void* stream, bool allow_cluster) {
+// pre != nullptr: the caller wants uv_qkv_post's work done in the kernel's prologue.  *fused tells it whether that
+// happened; when the launch cannot take the fused form (plain-load path, or more than 8 splits without arrival
+// counters) nothing is launched, *fused = false and the caller runs the two-launch form.
+static int decode_attn_impl(const uv_attn_args* a, void* stream, bool allow_cluster,
+                            const uv::QkvPostParams* pre = nullptr, bool* fused = nullptr) {
   using namespace uv;
   if (!a) return UV_ERR_ARG;
   if (a->B == 0) return UV_OK;
@@ -967,6 +1067,14 @@ static int decode_attn_impl(const uv_attn_args* a, void* stream, bool allow_clus
   bulk = bulk && (a->ring ? a->S % TILE == 0 : s_alloc % 8 == 0);
   bulk = bulk && aligned16(a->k_scale) && aligned16(a->v_scale) &&
          ((a->ssb | a->ssh | a->stb | a->sth) & 7) == 0;  // scale rows start on 16-byte boundaries (fp16 elements)
+  if (pre != nullptr) {
+    // one launch needs: the bulk-copy path, a merge that runs inside the launch, and the step's RoPE table
+    const bool ok = bulk && (P.splits == 1 || P.cluster || P.counters) && (!pre->inv_freq || pre->rope_cs);
+    *fused = ok;
+    if (!ok) return UV_OK;
+    P.has_pre = 1;
+    P.pre = *pre;
+  }
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (a->q_dtype == UV_F16) return dispatch_hd<__half>(P, hd, bulk, st);
   return dispatch_hd<__nv_bfloat16>(P, hd, bulk, st);
@@ -975,6 +1083,47 @@ static int decode_attn_impl(const uv_attn_args* a, void* stream, bool allow_clus
 
 // ------------------------------------------------------------------------------------------------ built-in scratch
 extern "C" int uv_decode_attn(const uv_attn_args* a, void* stream) { return decode_attn_impl(a, stream, true); }
+
+extern "C" int uv_qkv_attn(const uv_qkv_args* qa, const uv_attn_args* a, void* stream) {
+  using namespace uv;
+  if (!qa || !a) return UV_ERR_ARG;
+  if (a->B == 0) return UV_OK;
+  // the two argument blocks must describe the same step of the same cache
+  const int slots = qa->H + 2 * qa->K;
+  if (qa->B != a->B || qa->H != a->H || qa->K != a->KH || qa->hd != a->hd || qa->dtype != a->q_dtype ||
+      qa->S != a->S || (qa->ring != 0) != (a->ring != 0) || qa->pos != a->pos || qa->row_map != a->row_map ||
+      static_cast<const void*>(qa->k_cache) != a->k_cache || static_cast<const void*>(qa->v_cache) != a->v_cache ||
+      qa->k_scale != a->k_scale || qa->v_scale != a->v_scale)
+    return UV_ERR_ARG;
+  // q and the current v are slots of the packed projection
+  const size_t esz = 2;
+  if (a->q != qa->qkv || a->sqb != (int64_t)slots * qa->hd || a->sqh != qa->hd) return UV_ERR_ARG;
+  if (a->xsa_alpha &&
+      (a->v_cur != static_cast<const char*>(qa->qkv) + (size_t)(qa->H + qa->K) * qa->hd * esz ||
+       a->v_cur_sb != (int64_t)slots * qa->hd || a->v_cur_sh != qa->hd))
+    return UV_ERR_ARG;
+  // contiguous cache rows of S_alloc slots (what uv_qkv_post addresses) must be what the attention strides say
+  const int s_alloc = qa->S_alloc > qa->S ? qa->S_alloc : qa->S;
+  if (a->sks != a->hd || a->svs != a->hd || a->skh != (int64_t)s_alloc * a->hd || a->svh != a->skh ||
+      a->skb != a->skh * a->KH || a->svb != a->skb || a->ssh != s_alloc || a->sth != s_alloc ||
+      a->ssb != (int64_t)s_alloc * a->KH || a->stb != a->ssb)
+    return UV_ERR_ARG;
+  QkvPostParams qp{};
+  int rc = qkv_post_params(&qp, qa->qkv, qa->xn, qa->tok, qa->value_embed, qa->ve_gate, qa->inv_freq, qa->pos,
+                           qa->k_cache, qa->v_cache, qa->k_scale, qa->v_scale, qa->row_map, qa->oob_count, qa->vocab,
+                           qa->B, qa->H, qa->K, qa->hd, qa->d, qa->S, qa->S_alloc, qa->ring, qa->ve_ch, qa->n_pairs);
+  if (rc != UV_OK) return rc;
+  if (!qa->k_cache) return UV_ERR_ARG;
+  qp.rope_cs = qa->inv_freq ? qa->rope_cs : nullptr;  // without the table the two-launch form runs
+  bool fused = false;
+  rc = decode_attn_impl(a, stream, true, &qp, &fused);
+  if (rc != UV_OK || fused) return rc;
+  rc = uv_qkv_post(qa->qkv, qa->xn, qa->tok, qa->value_embed, qa->ve_gate, qa->inv_freq, qa->pos, qa->k_cache,
+                   qa->v_cache, qa->k_scale, qa->v_scale, qa->row_map, qa->oob_count, qa->dtype, qa->vocab, qa->B,
+                   qa->H, qa->K, qa->hd, qa->d, qa->S, qa->S_alloc, qa->ring, qa->ve_ch, qa->n_pairs, stream);
+  if (rc != UV_OK) return rc;
+  return decode_attn_impl(a, stream, true);
+}
 
 // uv_decode_attn_static: split-K decode attention for callers that may not allocate device memory at all.
 // The split partials and the arrival counters live in this file-scope device array instead of a caller workspace.

@@ -7,10 +7,9 @@
 // where the reference's half-precision torch ops round (ultraviolet/kernels/fast_decode.py:272-334,
 // ultraviolet/model.py:302-320, :567-571, :388-391), norms accumulate in fp32 with eps = 2^-23.
 #include "common.cuh"
+#include "qkv_post.cuh"
 
 namespace uv {
-
-constexpr float RMS_EPS = 1.1920929e-07f;  // torch.finfo(float32).eps: F.rms_norm's default in fp32 opmath
 
 template <typename T> struct Vec2;
 template <> struct Vec2<__half> { using type = __half2; };
@@ -51,12 +50,24 @@ template <typename T> __device__ __forceinline__ void st8(T* p, const float (&v)
 template <typename T>
 __global__ void __launch_bounds__(128) embed_norm_kernel(const int64_t* __restrict__ tok, const T* __restrict__ embed,
                                                          int64_t vocab, int d, T* __restrict__ x, T* __restrict__ xn,
-                                                         int B) {
+                                                         int B, const int64_t* __restrict__ pos,
+                                                         const float* __restrict__ inv_freq, int n_pairs,
+                                                         float* __restrict__ rope_cs) {
   const int lane = threadIdx.x & 31;
   const int row = blockIdx.x * 4 + (threadIdx.x >> 5);
   pdl_wait();
   pdl_trigger();
   if (row >= B) return;
+  if (rope_cs != nullptr) {
+    // the step's RoPE table: cos / sin of pos * inv_freq rounded to T, as apply_rope's operands are
+    // (fast_decode.py:286-290); every layer's q / k rotation reads it instead of evaluating cosf / sinf
+    const float pf = (float)pos[row];
+    for (int j = lane; j < n_pairs; j += 32) {
+      const float th = pf * inv_freq[j];
+      rope_cs[(int64_t)row * 2 * n_pairs + j] = rnd<T>(cosf(th));
+      rope_cs[(int64_t)row * 2 * n_pairs + n_pairs + j] = rnd<T>(sinf(th));
+    }
+  }
   int64_t t = tok[row];
   if (t < 0 || t >= vocab) t = 0;  // out-of-range ids read row 0 instead of faulting
   const T* e = embed + t * d;
@@ -157,28 +168,7 @@ __global__ void __launch_bounds__(256) swiglu_kernel(const T* __restrict__ gu, i
 }
 
 // ------------------------------------------------------------------------------------------------ QKV post
-// One warp per (row b, head slot): slots [0, H) are query heads, [H, H+K) key heads, [H+K, H+2K) value heads of the
-// packed GEMM output qkv (B, (H+2K)*hd).  In place: q <- rope(rms_norm(q)); k <- rope(rms_norm(k)); v <- v + ve gate.
-// K and V are also quantised and appended to the int8 cache at the row's slot (Attention.qkv, model.py:302-320;
-// kv_write, kv_quant.py:26-36; slot rule fast_decode.py:292-294).
-struct QkvPostParams {
-  void* qkv;
-  const void* xn;            // (B, d) pre-norm activations (value-embedding gate input)
-  const int64_t* tok;        // (B,)
-  const void* value_embed;   // (vocab, K*hd) or null
-  const void* ve_gate;       // (K, ve_ch) or null when the layer has no value embedding
-  const float* inv_freq;     // (n_pairs,) or null when the layer is NoPE
-  const int64_t* pos;        // (B,)
-  int8_t* k_cache;
-  int8_t* v_cache;
-  uint16_t* k_scale;
-  uint16_t* v_scale;
-  const int64_t* row_map;
-  int* oob;
-  int64_t vocab;
-  int B, H, K, d, S, S_alloc, ring, ve_ch, n_pairs;
-};
-
+// One warp per (row b, head slot), in place on the packed GEMM output; the arithmetic lives in qkv_post.cuh.
 template <typename T, int HD>
 __global__ void __launch_bounds__(128) qkv_post_kernel(const __grid_constant__ QkvPostParams P) {
   constexpr int E = HD >= 32 ? HD / 32 : 1;
@@ -194,75 +184,11 @@ __global__ void __launch_bounds__(128) qkv_post_kernel(const __grid_constant__ Q
   float x[E];
 #pragma unroll
   for (int i = 0; i < E; ++i) x[i] = act ? to_f32<T>(vec[lane * E + i]) : 0.f;
-
-  const bool is_v = hs >= P.H + P.K;
-  if (is_v) {
-    if (P.ve_gate != nullptr) {
-      const int kh = hs - P.H - P.K;
-      const T* xr = static_cast<const T*>(P.xn) + (int64_t)b * P.d;
-      const T* gw = static_cast<const T*>(P.ve_gate) + (int64_t)kh * P.ve_ch;
-      float acc = 0.f;
-      for (int ch = lane; ch < P.ve_ch; ch += 32) acc += to_f32<T>(xr[ch]) * to_f32<T>(gw[ch]);
-      acc = rnd<T>(warp_sum(acc));
-      const float g = rnd<T>(2.0f * rnd<T>(1.0f / (1.0f + __expf(-acc))));
-      int64_t t = P.tok[b];
-      if (t < 0 || t >= P.vocab) t = 0;
-      const T* ve = static_cast<const T*>(P.value_embed) + (t * P.K + kh) * HD;
-#pragma unroll
-      for (int i = 0; i < E; ++i)
-        if (act) x[i] = rnd<T>(x[i] + rnd<T>(g * to_f32<T>(ve[lane * E + i])));
-    }
-  } else {
-    float ss = 0.f;
-#pragma unroll
-    for (int i = 0; i < E; ++i) ss += x[i] * x[i];
-    const float inv = rsqrtf(warp_sum(ss) / (float)HD + RMS_EPS);
-#pragma unroll
-    for (int i = 0; i < E; ++i) x[i] = rnd<T>(x[i] * inv);
-    if (P.inv_freq != nullptr) {
-      // half-split pairing: dim j < n_pairs rotates with dim j + n_pairs (apply_rope, model.py:219-226)
-      const int pl = P.n_pairs / E;  // lanes holding x1
-      const float pf = (float)P.pos[b];
-#pragma unroll
-      for (int i = 0; i < E; ++i) {
-        const float other = __shfl_xor_sync(0xffffffffu, x[i], pl);
-        const int dim = lane * E + i;
-        if (dim < 2 * P.n_pairs) {
-          const int j = dim < P.n_pairs ? dim : dim - P.n_pairs;
-          const float th = pf * P.inv_freq[j];
-          const float cs = rnd<T>(cosf(th)), sn = rnd<T>(sinf(th));
-          // x1' = x1*c - x2*s ; x2' = x1*s + x2*c, each product and the sum rounded
-          x[i] = dim < P.n_pairs ? rnd<T>(rnd<T>(x[i] * cs) - rnd<T>(other * sn))
-                                 : rnd<T>(rnd<T>(other * sn) + rnd<T>(x[i] * cs));
-        }
-      }
-    }
-  }
+  qkv_post_compute<T, HD>(P, b, hs, lane, x);
 #pragma unroll
   for (int i = 0; i < E; ++i)
     if (act) vec[lane * E + i] = from_f32<T>(x[i]);
-
-  if (hs >= P.H && P.k_cache != nullptr) {  // key or value head: quantise + append
-    const bool isv = is_v;
-    const int kh = isv ? hs - P.H - P.K : hs - P.H;
-    int8_t q8[E];
-    const uint16_t s = quantize_lane<E>(x, q8);
-    int64_t p = P.pos[b];
-    if (P.ring) p = ((p % P.S) + P.S) % P.S;
-    if (p < 0 || p >= P.S) {
-      if (lane == 0 && P.oob) atomicAdd(P.oob, 1);
-      return;
-    }
-    const int64_t cb = P.row_map ? P.row_map[b] : b;
-    const int64_t dst = (cb * P.K + kh) * P.S_alloc + p;  // rows may be allocated longer than S
-    int8_t* crow = (isv ? P.v_cache : P.k_cache) + dst * HD;
-    if (act) {
-      if constexpr (E == 4) *reinterpret_cast<char4*>(crow + lane * 4) = make_char4(q8[0], q8[1], q8[2], q8[3]);
-      else if constexpr (E == 2) *reinterpret_cast<char2*>(crow + lane * 2) = make_char2(q8[0], q8[1]);
-      else crow[lane] = q8[0];
-    }
-    if (lane == 0) (isv ? P.v_scale : P.k_scale)[dst] = s;
-  }
+  if (hs >= P.H && P.k_cache != nullptr) qkv_post_append<T, HD>(P, b, hs, lane, x);
 }
 
 template <typename T>
@@ -282,22 +208,29 @@ static int launch_qkv_post(const QkvPostParams& P, int hd, cudaStream_t st) {
 
 using namespace uv;
 
-extern "C" int uv_embed_norm(const int64_t* tok, const void* embed, int dtype, int64_t vocab, int d, void* x,
-                             void* xn, int B, void* stream) {
+extern "C" int uv_embed_norm_rope(const int64_t* tok, const void* embed, int dtype, int64_t vocab, int d, void* x,
+                                  void* xn, int B, const int64_t* pos, const float* inv_freq, int n_pairs,
+                                  float* rope_cs, void* stream) {
   if (B == 0) return UV_OK;
   if (!tok || !embed || !x || !xn || B < 0 || vocab < 1) return UV_ERR_ARG;
+  if (rope_cs && (!pos || !inv_freq || n_pairs < 1)) return UV_ERR_ARG;
   if (d < 8 || (d & 7) || d > ROW_MAX) return UV_ERR_SHAPE;  // rows are moved as 16-byte vectors
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const unsigned grid = (unsigned)((B + 3) / 4);
   if (dtype == UV_F16)
     launch_pdl(embed_norm_kernel<__half>, dim3(grid), dim3(128), 0, st, tok, static_cast<const __half*>(embed), vocab,
-               d, static_cast<__half*>(x), static_cast<__half*>(xn), B);
+               d, static_cast<__half*>(x), static_cast<__half*>(xn), B, pos, inv_freq, n_pairs, rope_cs);
   else if (dtype == UV_BF16)
     launch_pdl(embed_norm_kernel<__nv_bfloat16>, dim3(grid), dim3(128), 0, st, tok,
                static_cast<const __nv_bfloat16*>(embed), vocab, d, static_cast<__nv_bfloat16*>(x),
-               static_cast<__nv_bfloat16*>(xn), B);
+               static_cast<__nv_bfloat16*>(xn), B, pos, inv_freq, n_pairs, rope_cs);
   else return UV_ERR_DTYPE;
   return check_launch();
+}
+
+extern "C" int uv_embed_norm(const int64_t* tok, const void* embed, int dtype, int64_t vocab, int d, void* x,
+                             void* xn, int B, void* stream) {
+  return uv_embed_norm_rope(tok, embed, dtype, vocab, d, x, xn, B, nullptr, nullptr, 0, nullptr, stream);
 }
 
 extern "C" int uv_resid_norm(const void* x, const void* a, const float* lambdas, int dtype, int d, void* h, void* hn,
@@ -341,19 +274,10 @@ extern "C" int uv_qkv_post(void* qkv, const void* xn, const int64_t* tok, const 
                            int* oob_count, int dtype, int64_t vocab, int B, int H, int K, int hd, int d, int S,
                            int S_alloc, int ring, int ve_ch, int n_pairs, void* stream) {
   if (B == 0) return UV_OK;
-  if (!qkv || !pos || B < 0 || H < 1 || K < 1) return UV_ERR_ARG;
-  if (ve_gate && (!xn || !tok || !value_embed || ve_ch < 1)) return UV_ERR_ARG;
-  if (k_cache && (!v_cache || !k_scale || !v_scale || S < 1)) return UV_ERR_ARG;
-  if (hd != 16 && hd != 32 && hd != 64 && hd != 128) return UV_ERR_SHAPE;
-  if (inv_freq) {
-    const int E = hd >= 32 ? hd / 32 : 1;
-    const int pl = n_pairs / E;
-    if (n_pairs < 1 || 2 * n_pairs > hd || n_pairs % E || (pl & (pl - 1))) return UV_ERR_SHAPE;
-  }
   QkvPostParams P{};
-  P.qkv = qkv, P.xn = xn, P.tok = tok, P.value_embed = value_embed, P.ve_gate = ve_gate, P.inv_freq = inv_freq;
-  P.pos = pos, P.k_cache = k_cache, P.v_cache = v_cache, P.k_scale = k_scale, P.v_scale = v_scale, P.row_map = row_map, P.oob = oob_count;
-  P.vocab = vocab, P.B = B, P.H = H, P.K = K, P.d = d, P.S = S, P.S_alloc = S_alloc > S ? S_alloc : S, P.ring = ring, P.ve_ch = ve_ch, P.n_pairs = n_pairs;
+  const int rc = qkv_post_params(&P, qkv, xn, tok, value_embed, ve_gate, inv_freq, pos, k_cache, v_cache, k_scale,
+                                 v_scale, row_map, oob_count, vocab, B, H, K, hd, d, S, S_alloc, ring, ve_ch, n_pairs);
+  if (rc != UV_OK) return rc;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (dtype == UV_F16) return launch_qkv_post<__half>(P, hd, st);
   if (dtype == UV_BF16) return launch_qkv_post<__nv_bfloat16>(P, hd, st);

@@ -1,0 +1,156 @@
+// Per-head post-processing of the packed QKV projection, shared by uv_qkv_post (its own launch) and uv_qkv_attn
+// (the same work done in the prologue of the attention kernel).  One warp per (row b, head slot): slots [0, H) are
+// query heads, [H, H+K) key heads, [H+K, H+2K) value heads of qkv (B, (H+2K)*hd).
+//   q <- rope(rms_norm(q)); k <- rope(rms_norm(k)); v <- v + 2*sigmoid(xn[:ve_ch] . ve_gate) * value_embed[tok]
+// (Attention.qkv, ultraviolet/model.py:302-320), then K and V quantised and appended to the int8 cache at the row's
+// slot (kv_write, ultraviolet/kernels/kv_quant.py:26-36; slot rule ultraviolet/kernels/fast_decode.py:292-294).
+// Every elementwise result is rounded to the activation dtype where the reference's half-precision ops round.
+#pragma once
+
+#include "common.cuh"
+
+namespace uv {
+
+constexpr float RMS_EPS = 1.1920929e-07f;  // torch.finfo(float32).eps: F.rms_norm's default in fp32 opmath
+
+struct QkvPostParams {
+  void* qkv;
+  const void* xn;            // (B, d) pre-norm activations (value-embedding gate input)
+  const int64_t* tok;        // (B,)
+  const void* value_embed;   // (vocab, K*hd) or null
+  const void* ve_gate;       // (K, ve_ch) or null when the layer has no value embedding
+  const float* inv_freq;     // (n_pairs,) or null when the layer is NoPE
+  const float* rope_cs;      // optional (B, 2*n_pairs): cos then sin of pos*inv_freq, already rounded to the
+                             // activation dtype (uv_embed_norm_rope writes it once per step)
+  const int64_t* pos;        // (B,)
+  int8_t* k_cache;
+  int8_t* v_cache;
+  uint16_t* k_scale;
+  uint16_t* v_scale;
+  const int64_t* row_map;
+  int* oob;
+  int64_t vocab;
+  int B, H, K, d, S, S_alloc, ring, ve_ch, n_pairs;
+};
+
+// Host-side argument check + parameter block (shared by the two entry points).
+inline int qkv_post_params(QkvPostParams* out, void* qkv, const void* xn, const int64_t* tok, const void* value_embed,
+                           const void* ve_gate, const float* inv_freq, const int64_t* pos, int8_t* k_cache,
+                           int8_t* v_cache, uint16_t* k_scale, uint16_t* v_scale, const int64_t* row_map,
+                           int* oob_count, int64_t vocab, int B, int H, int K, int hd, int d, int S, int S_alloc,
+                           int ring, int ve_ch, int n_pairs) {
+  if (!qkv || !pos || B < 0 || H < 1 || K < 1) return UV_ERR_ARG;
+  if (ve_gate && (!xn || !tok || !value_embed || ve_ch < 1)) return UV_ERR_ARG;
+  if (k_cache && (!v_cache || !k_scale || !v_scale || S < 1)) return UV_ERR_ARG;
+  if (hd != 16 && hd != 32 && hd != 64 && hd != 128) return UV_ERR_SHAPE;
+  if (inv_freq) {
+    const int E = hd >= 32 ? hd / 32 : 1;
+    const int pl = n_pairs / E;
+    if (n_pairs < 1 || 2 * n_pairs > hd || n_pairs % E || (pl & (pl - 1))) return UV_ERR_SHAPE;
+  }
+  QkvPostParams P{};
+  P.qkv = qkv, P.xn = xn, P.tok = tok, P.value_embed = value_embed, P.ve_gate = ve_gate, P.inv_freq = inv_freq;
+  P.pos = pos, P.k_cache = k_cache, P.v_cache = v_cache, P.k_scale = k_scale, P.v_scale = v_scale;
+  P.row_map = row_map, P.oob = oob_count;
+  P.vocab = vocab, P.B = B, P.H = H, P.K = K, P.d = d, P.S = S, P.S_alloc = S_alloc > S ? S_alloc : S;
+  P.ring = ring, P.ve_ch = ve_ch, P.n_pairs = n_pairs;
+  *out = P;
+  return UV_OK;
+}
+
+// x: the slot's raw projection values held by a warp (lane owns elements [lane*E, lane*E + E)), replaced by the
+// post-processed values.  Called by a full warp.
+// TABLE: the rotation always reads P.rope_cs (the caller checked that it is there), so that no cosf / sinf code
+// is compiled into the kernel.
+template <typename T, int HD, bool TABLE = false>
+__device__ __forceinline__ void qkv_post_compute(const QkvPostParams& P, int b, int hs, int lane,
+                                                 float (&x)[HD >= 32 ? HD / 32 : 1]) {
+  constexpr int E = HD >= 32 ? HD / 32 : 1;
+  const bool act = lane * E < HD;
+  if (hs >= P.H + P.K) {
+    if (P.ve_gate != nullptr) {
+      const int kh = hs - P.H - P.K;
+      const T* xr = static_cast<const T*>(P.xn) + (int64_t)b * P.d;
+      const T* gw = static_cast<const T*>(P.ve_gate) + (int64_t)kh * P.ve_ch;
+      float acc = 0.f;
+      for (int ch = lane; ch < P.ve_ch; ch += 32) acc += to_f32<T>(xr[ch]) * to_f32<T>(gw[ch]);
+      acc = rnd<T>(warp_sum(acc));
+      const float g = rnd<T>(2.0f * rnd<T>(1.0f / (1.0f + __expf(-acc))));
+      int64_t t = P.tok[b];
+      if (t < 0 || t >= P.vocab) t = 0;
+      const T* ve = static_cast<const T*>(P.value_embed) + (t * P.K + kh) * HD;
+#pragma unroll
+      for (int i = 0; i < E; ++i)
+        if (act) x[i] = rnd<T>(x[i] + rnd<T>(g * to_f32<T>(ve[lane * E + i])));
+    }
+    return;
+  }
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < E; ++i) ss += x[i] * x[i];
+  const float inv = rsqrtf(warp_sum(ss) / (float)HD + RMS_EPS);
+#pragma unroll
+  for (int i = 0; i < E; ++i) x[i] = rnd<T>(x[i] * inv);
+  if (P.inv_freq != nullptr) {
+    // half-split pairing: dim j < n_pairs rotates with dim j + n_pairs (apply_rope, model.py:219-226)
+    const int pl = P.n_pairs / E;  // lanes holding x1
+    const float pf = (float)P.pos[b];
+#pragma unroll
+    for (int i = 0; i < E; ++i) {
+      const float other = __shfl_xor_sync(0xffffffffu, x[i], pl);
+      const int dim = lane * E + i;
+      if (dim < 2 * P.n_pairs) {
+        const int j = dim < P.n_pairs ? dim : dim - P.n_pairs;
+        float cs, sn;
+        if (TABLE || P.rope_cs != nullptr) {
+          cs = P.rope_cs[(int64_t)b * 2 * P.n_pairs + j];
+          sn = P.rope_cs[(int64_t)b * 2 * P.n_pairs + P.n_pairs + j];
+        } else {
+          const float th = pf * P.inv_freq[j];
+          cs = rnd<T>(cosf(th)), sn = rnd<T>(sinf(th));
+        }
+        // x1' = x1*c - x2*s ; x2' = x1*s + x2*c, each product and the sum rounded
+        x[i] = dim < P.n_pairs ? rnd<T>(rnd<T>(x[i] * cs) - rnd<T>(other * sn))
+                               : rnd<T>(rnd<T>(other * sn) + rnd<T>(x[i] * cs));
+      }
+    }
+  }
+}
+
+// Store a quantised key / value slot (lane owns bytes [lane*E, lane*E + E)) and its scale at the cache row of batch
+// entry b.  Full warp.
+template <int HD>
+__device__ __forceinline__ void qkv_post_store(const QkvPostParams& P, int b, int hs, int lane,
+                                               const int8_t (&q8)[HD >= 32 ? HD / 32 : 1], uint16_t s) {
+  constexpr int E = HD >= 32 ? HD / 32 : 1;
+  const bool act = lane * E < HD;
+  const bool isv = hs >= P.H + P.K;
+  const int kh = isv ? hs - P.H - P.K : hs - P.H;
+  int64_t p = P.pos[b];
+  if (P.ring) p = ((p % P.S) + P.S) % P.S;
+  if (p < 0 || p >= P.S) {
+    if (lane == 0 && P.oob) atomicAdd(P.oob, 1);
+    return;
+  }
+  const int64_t cb = P.row_map ? P.row_map[b] : b;
+  const int64_t dst = (cb * P.K + kh) * P.S_alloc + p;  // rows may be allocated longer than S
+  int8_t* crow = (isv ? P.v_cache : P.k_cache) + dst * HD;
+  if (act) {
+    if constexpr (E == 4) *reinterpret_cast<char4*>(crow + lane * 4) = make_char4(q8[0], q8[1], q8[2], q8[3]);
+    else if constexpr (E == 2) *reinterpret_cast<char2*>(crow + lane * 2) = make_char2(q8[0], q8[1]);
+    else crow[lane] = q8[0];
+  }
+  if (lane == 0) (isv ? P.v_scale : P.k_scale)[dst] = s;
+}
+
+// Quantise a post-processed key / value slot and append it to the cache row of batch entry b.  Full warp.
+template <typename T, int HD>
+__device__ __forceinline__ void qkv_post_append(const QkvPostParams& P, int b, int hs, int lane,
+                                                const float (&x)[HD >= 32 ? HD / 32 : 1]) {
+  constexpr int E = HD >= 32 ? HD / 32 : 1;
+  int8_t q8[E];
+  const uint16_t s = quantize_lane<E>(x, q8);
+  qkv_post_store<HD>(P, b, hs, lane, q8, s);
+}
+
+}  // namespace uv

@@ -79,6 +79,11 @@ class DecodeEngine:
         self.fused_gemm_ok = (hd == 64 and d % 80 == 0 and d // 80 <= 8 and f % 64 == 0 and d % 64 == 0
                               and (H * hd) % 64 == 0)
         self.fused_gemm = os.environ.get("UVDECODE_FUSED_GEMM", "0") == "1" and self.fused_gemm_ok
+        # uv_qkv_attn: one launch for the QKV post-processing + cache append + attention of a layer.  Opt-in: results
+        # are bit-identical, but inside the decode step the one launch measured ~1 us per layer SLOWER than the two
+        # (four warps per row do serially what uv_qkv_post spreads over ten, and the longer kernel pays more cold
+        # instruction fetch), although it is ~0.5 us faster when timed back to back in isolation.
+        self.qkv_in_attn = os.environ.get("UVDECODE_QKV_IN_ATTN", "0") == "1"
         self.n_sm = torch.cuda.get_device_properties(self.device).multi_processor_count
         _lib.lib()
 
@@ -131,7 +136,8 @@ class DecodeEngine:
                      logp=torch.zeros(B, dtype=torch.float32, device=dev),
                      counters=torch.zeros(B * K, dtype=torch.int32, device=dev),
                      status=torch.zeros(1, dtype=torch.int32, device=dev),
-                     oob=torch.zeros(1, dtype=torch.int32, device=dev), ws={})
+                     oob=torch.zeros(1, dtype=torch.int32, device=dev),
+                     rope_cs=torch.zeros(B, 2 * max(cfg.rope_pairs, 1), dtype=torch.float32, device=dev), ws={})
             self._scratch[B] = s
         return s
 
@@ -162,8 +168,15 @@ class DecodeEngine:
         rm = row_map.data_ptr() if row_map is not None else None
         fused = self.fused_gemm
         with torch.cuda.device(self.device):
-            _lib.check(lib.uv_embed_norm(tok.data_ptr(), w["embed"].data_ptr(), dt, cfg.vocab_size, d,
-                                         s["x"].data_ptr(), s["xn"].data_ptr(), B, sp), "uv_embed_norm")
+            use_table = self.qkv_in_attn and not fused and cfg.rope_pairs > 0
+            if use_table:  # one cos / sin table per step instead of cosf / sinf in every layer's prologue
+                _lib.check(lib.uv_embed_norm_rope(tok.data_ptr(), w["embed"].data_ptr(), dt, cfg.vocab_size, d,
+                                                  s["x"].data_ptr(), s["xn"].data_ptr(), B, pos.data_ptr(),
+                                                  self.inv_freq.data_ptr(), cfg.rope_pairs, s["rope_cs"].data_ptr(),
+                                                  sp), "uv_embed_norm_rope")
+            else:
+                _lib.check(lib.uv_embed_norm(tok.data_ptr(), w["embed"].data_ptr(), dt, cfg.vocab_size, d,
+                                             s["x"].data_ptr(), s["xn"].data_ptr(), B, sp), "uv_embed_norm")
             x, xn, h, hn = s["x"], s["xn"], s["h"], s["hn"]
             qkv3 = s["qkv"].view(B, H + 2 * K, hd)
             q, v_cur = qkv3[:, :H], qkv3[:, H + K:]
@@ -173,6 +186,7 @@ class DecodeEngine:
                 kc, vc, ks, vs = st.k[l], st.v[l], st.k_scale[l], st.v_scale[l]
                 S = kc.size(2)
                 ve_gate = w[f"l{l}.ve_gate"].data_ptr() if cfg.has_ve(l) else None
+                pre = None
                 rope = (not glob) or cfg.global_rope
                 post_args = (tok.data_ptr(), w["value_embed"].data_ptr() if self.use_ve else None, ve_gate,
                              self.inv_freq.data_ptr() if rope and cfg.rope_pairs else None, pos.data_ptr(),
@@ -184,7 +198,15 @@ class DecodeEngine:
                                                *post_args), "uv_gemm_qkv")
                 else:
                     torch.mm(xn, w[f"l{l}.wqkv"].t(), out=s["qkv"])
-                    _lib.check(lib.uv_qkv_post(s["qkv"].data_ptr(), xn.data_ptr(), *post_args), "uv_qkv_post")
+                    if self.qkv_in_attn:  # the attention launch below does uv_qkv_post's work in its prologue
+                        pre = _lib.QkvArgs()
+                        (pre.qkv, pre.xn, pre.tok, pre.value_embed, pre.ve_gate, pre.inv_freq, pre.pos, pre.k_cache,
+                         pre.v_cache, pre.k_scale, pre.v_scale, pre.row_map, pre.oob_count, pre.dtype, pre.vocab,
+                         pre.B, pre.H, pre.K, pre.hd, pre.d, pre.S, pre.S_alloc, pre.ring, pre.ve_ch,
+                         pre.n_pairs) = (s["qkv"].data_ptr(), xn.data_ptr(), *post_args[:-1])
+                        pre.rope_cs = s["rope_cs"].data_ptr() if use_table else None
+                    else:
+                        _lib.check(lib.uv_qkv_post(s["qkv"].data_ptr(), xn.data_ptr(), *post_args), "uv_qkv_post")
                 if glob:
                     ctx = min(g_len or S, S)
                     splits = ns.get("global") or default_splits(B * K, ctx, self.device)
@@ -197,7 +219,7 @@ class DecodeEngine:
                             xsa_alpha=self.xsa[l] if cfg.xsa else None, xsa_eps=cfg.xsa_eps,
                             gate_x=xn if cfg.gate_channels else None,
                             gate_w=w[f"l{l}.attn_gate"] if cfg.gate_channels else None,
-                            counters=s["counters"], status=s["status"], row_map=row_map)
+                            counters=s["counters"], status=s["status"], row_map=row_map, pre=pre)
                 lam = self.lambdas[l]
                 if fused:
                     _lib.check(lib.uv_gemm_resid_norm(s["z"].data_ptr(), H * hd, w[f"l{l}.wo"].data_ptr(), H * hd,

@@ -47,8 +47,9 @@ def attn_launch(q: Tensor, k_cache: Tensor, v_cache: Tensor, pos: Tensor, starts
                 workspace: Tensor | None = None, v_cur: Tensor | None = None, xsa_alpha: Tensor | None = None,
                 xsa_eps: float = 1e-4, gate_x: Tensor | None = None, gate_w: Tensor | None = None,
                 counters: Tensor | None = None, status: Tensor | None = None,
-                row_map: Tensor | None = None) -> Tensor:
-    """Raw launch: fills uv_attn_args from tensor metadata.  q / out (B, H, hd) with unit inner stride."""
+                row_map: Tensor | None = None, pre=None) -> Tensor:
+    """Raw launch: fills uv_attn_args from tensor metadata.  q / out (B, H, hd) with unit inner stride.
+    pre: a filled _lib.QkvArgs -> uv_qkv_attn (uv_qkv_post's work done inside the attention launch)."""
     B, H, hd = q.shape
     KH, S = k_cache.shape[1], k_cache.shape[2]
     a = _lib.AttnArgs()
@@ -80,8 +81,11 @@ def attn_launch(q: Tensor, k_cache: Tensor, v_cache: Tensor, pos: Tensor, starts
         a.gate_x, a.gate_x_stride = gate_x.data_ptr(), gate_x.stride(0)
         a.gate_w, a.gate_ch = gate_w.data_ptr(), gate_w.size(-1)
     with torch.cuda.device(q.device):
-        rc = _lib.lib().uv_decode_attn(C.byref(a), stream_ptr(q.device))
-    _lib.check(rc, "uv_decode_attn")
+        if pre is not None:
+            rc = _lib.lib().uv_qkv_attn(C.byref(pre), C.byref(a), stream_ptr(q.device))
+        else:
+            rc = _lib.lib().uv_decode_attn(C.byref(a), stream_ptr(q.device))
+    _lib.check(rc, "uv_qkv_attn" if pre is not None else "uv_decode_attn")
     return out
 
 
