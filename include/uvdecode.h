@@ -209,6 +209,8 @@ typedef struct uv_qkv_args { /* the parameters of uv_qkv_post, by name */
                              evaluating cos / sin in every layer (same values bit for bit) */
 } uv_qkv_args;
 int uv_qkv_attn(const uv_qkv_args* qkv, const uv_attn_args* attn, void* stream);
+/* uv_qkv_post with its parameters by name; with rope_cs set the rotation reads the step's table. */
+int uv_qkv_post_args(const uv_qkv_args* qkv, void* stream);
 
 /* GEMMs of the decode step with the row-wise kernels above fused into their epilogues (hand-written mma.sync
  * mainloop; same results as library GEMM + the separate kernel up to the summation order of the fp32 accumulation).

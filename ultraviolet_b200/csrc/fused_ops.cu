@@ -169,7 +169,7 @@ __global__ void __launch_bounds__(256) swiglu_kernel(const T* __restrict__ gu, i
 
 // ------------------------------------------------------------------------------------------------ QKV post
 // One warp per (row b, head slot), in place on the packed GEMM output; the arithmetic lives in qkv_post.cuh.
-template <typename T, int HD>
+template <typename T, int HD, bool TABLE>
 __global__ void __launch_bounds__(128) qkv_post_kernel(const __grid_constant__ QkvPostParams P) {
   constexpr int E = HD >= 32 ? HD / 32 : 1;
   const int lane = threadIdx.x & 31;
@@ -184,7 +184,7 @@ __global__ void __launch_bounds__(128) qkv_post_kernel(const __grid_constant__ Q
   float x[E];
 #pragma unroll
   for (int i = 0; i < E; ++i) x[i] = act ? to_f32<T>(vec[lane * E + i]) : 0.f;
-  qkv_post_compute<T, HD>(P, b, hs, lane, x);
+  qkv_post_compute<T, HD, TABLE>(P, b, hs, lane, x);
 #pragma unroll
   for (int i = 0; i < E; ++i)
     if (act) vec[lane * E + i] = from_f32<T>(x[i]);
@@ -194,13 +194,20 @@ __global__ void __launch_bounds__(128) qkv_post_kernel(const __grid_constant__ Q
 template <typename T>
 static int launch_qkv_post(const QkvPostParams& P, int hd, cudaStream_t st) {
   const unsigned grid = (unsigned)(((int64_t)P.B * (P.H + 2 * P.K) + 3) / 4);
+  // with the step's RoPE table the kernel carries no cosf / sinf code at all
+#define UV_QKV_POST(HD_)                                                                        \
+  case HD_:                                                                                     \
+    if (P.rope_cs) launch_pdl(qkv_post_kernel<T, HD_, true>, dim3(grid), dim3(128), 0, st, P);  \
+    else launch_pdl(qkv_post_kernel<T, HD_, false>, dim3(grid), dim3(128), 0, st, P);           \
+    break;
   switch (hd) {
-    case 16: launch_pdl(qkv_post_kernel<T, 16>, dim3(grid), dim3(128), 0, st, P); break;
-    case 32: launch_pdl(qkv_post_kernel<T, 32>, dim3(grid), dim3(128), 0, st, P); break;
-    case 64: launch_pdl(qkv_post_kernel<T, 64>, dim3(grid), dim3(128), 0, st, P); break;
-    case 128: launch_pdl(qkv_post_kernel<T, 128>, dim3(grid), dim3(128), 0, st, P); break;
+    UV_QKV_POST(16)
+    UV_QKV_POST(32)
+    UV_QKV_POST(64)
+    UV_QKV_POST(128)
     default: return UV_ERR_SHAPE;
   }
+#undef UV_QKV_POST
   return check_launch();
 }
 
@@ -231,6 +238,21 @@ extern "C" int uv_embed_norm_rope(const int64_t* tok, const void* embed, int dty
 extern "C" int uv_embed_norm(const int64_t* tok, const void* embed, int dtype, int64_t vocab, int d, void* x,
                              void* xn, int B, void* stream) {
   return uv_embed_norm_rope(tok, embed, dtype, vocab, d, x, xn, B, nullptr, nullptr, 0, nullptr, stream);
+}
+
+extern "C" int uv_qkv_post_args(const uv_qkv_args* a, void* stream) {
+  if (!a) return UV_ERR_ARG;
+  if (a->B == 0) return UV_OK;
+  QkvPostParams P{};
+  const int rc = qkv_post_params(&P, a->qkv, a->xn, a->tok, a->value_embed, a->ve_gate, a->inv_freq, a->pos, a->k_cache,
+                                 a->v_cache, a->k_scale, a->v_scale, a->row_map, a->oob_count, a->vocab, a->B, a->H,
+                                 a->K, a->hd, a->d, a->S, a->S_alloc, a->ring, a->ve_ch, a->n_pairs);
+  if (rc != UV_OK) return rc;
+  P.rope_cs = a->inv_freq ? a->rope_cs : nullptr;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (a->dtype == UV_F16) return launch_qkv_post<__half>(P, a->hd, st);
+  if (a->dtype == UV_BF16) return launch_qkv_post<__nv_bfloat16>(P, a->hd, st);
+  return UV_ERR_DTYPE;
 }
 
 extern "C" int uv_resid_norm(const void* x, const void* a, const float* lambdas, int dtype, int d, void* h, void* hn,

@@ -84,6 +84,8 @@ class DecodeEngine:
         # (four warps per row do serially what uv_qkv_post spreads over ten, and the longer kernel pays more cold
         # instruction fetch), although it is ~0.5 us faster when timed back to back in isolation.
         self.qkv_in_attn = os.environ.get("UVDECODE_QKV_IN_ATTN", "0") == "1"
+        # cos / sin of pos * inv_freq once per step (uv_embed_norm_rope) instead of in every layer's q / k rotation
+        self.rope_table = os.environ.get("UVDECODE_ROPE_TABLE", "1") != "0"
         self.n_sm = torch.cuda.get_device_properties(self.device).multi_processor_count
         _lib.lib()
 
@@ -168,7 +170,7 @@ class DecodeEngine:
         rm = row_map.data_ptr() if row_map is not None else None
         fused = self.fused_gemm
         with torch.cuda.device(self.device):
-            use_table = self.qkv_in_attn and not fused and cfg.rope_pairs > 0
+            use_table = self.rope_table and not fused and cfg.rope_pairs > 0
             if use_table:  # one cos / sin table per step instead of cosf / sinf in every layer's prologue
                 _lib.check(lib.uv_embed_norm_rope(tok.data_ptr(), w["embed"].data_ptr(), dt, cfg.vocab_size, d,
                                                   s["x"].data_ptr(), s["xn"].data_ptr(), B, pos.data_ptr(),
@@ -198,15 +200,16 @@ class DecodeEngine:
                                                *post_args), "uv_gemm_qkv")
                 else:
                     torch.mm(xn, w[f"l{l}.wqkv"].t(), out=s["qkv"])
+                    qa = _lib.QkvArgs()
+                    (qa.qkv, qa.xn, qa.tok, qa.value_embed, qa.ve_gate, qa.inv_freq, qa.pos, qa.k_cache,
+                     qa.v_cache, qa.k_scale, qa.v_scale, qa.row_map, qa.oob_count, qa.dtype, qa.vocab,
+                     qa.B, qa.H, qa.K, qa.hd, qa.d, qa.S, qa.S_alloc, qa.ring, qa.ve_ch,
+                     qa.n_pairs) = (s["qkv"].data_ptr(), xn.data_ptr(), *post_args[:-1])
+                    qa.rope_cs = s["rope_cs"].data_ptr() if use_table else None
                     if self.qkv_in_attn:  # the attention launch below does uv_qkv_post's work in its prologue
-                        pre = _lib.QkvArgs()
-                        (pre.qkv, pre.xn, pre.tok, pre.value_embed, pre.ve_gate, pre.inv_freq, pre.pos, pre.k_cache,
-                         pre.v_cache, pre.k_scale, pre.v_scale, pre.row_map, pre.oob_count, pre.dtype, pre.vocab,
-                         pre.B, pre.H, pre.K, pre.hd, pre.d, pre.S, pre.S_alloc, pre.ring, pre.ve_ch,
-                         pre.n_pairs) = (s["qkv"].data_ptr(), xn.data_ptr(), *post_args[:-1])
-                        pre.rope_cs = s["rope_cs"].data_ptr() if use_table else None
+                        pre = qa
                     else:
-                        _lib.check(lib.uv_qkv_post(s["qkv"].data_ptr(), xn.data_ptr(), *post_args), "uv_qkv_post")
+                        _lib.check(lib.uv_qkv_post_args(C.byref(qa), sp), "uv_qkv_post")
                 if glob:
                     ctx = min(g_len or S, S)
                     splits = ns.get("global") or default_splits(B * K, ctx, self.device)
