@@ -123,6 +123,8 @@ typedef struct uv_attn_args {
   int64_t gate_x_stride;
   const void* gate_w;     /* (H, gate_ch) q_dtype contiguous */
   int gate_ch;
+  const float* gate_vals; /* optional (B, H) fp32: the gates themselves, as uv_qkv_post_args writes them (gate_out);
+                             when set, gate_x / gate_w are not read */
 } uv_attn_args;
 
 size_t uv_decode_attn_workspace_bytes(int B, int KH, int G, int hd, int num_splits);
@@ -207,6 +209,9 @@ typedef struct uv_qkv_args { /* the parameters of uv_qkv_post, by name */
   int B, H, K, hd, d, S, S_alloc, ring, ve_ch, n_pairs;
   const float* rope_cs;   /* optional (B, 2*n_pairs) table from uv_embed_norm_rope for these pos: read instead of
                              evaluating cos / sin in every layer (same values bit for bit) */
+  const void* gate_w;     /* optional, uv_qkv_post_args only: (H, gate_ch) attention output gate weights; the kernel */
+  float* gate_out;        /* also writes gate_out (B, H) = 2*sigmoid(xn[b, :gate_ch] . gate_w[head]) for the */
+  int gate_ch;            /* attention launch that follows (uv_attn_args.gate_vals) */
 } uv_qkv_args;
 int uv_qkv_attn(const uv_qkv_args* qkv, const uv_attn_args* attn, void* stream);
 /* uv_qkv_post with its parameters by name; with rope_cs set the rotation reads the step's table. */

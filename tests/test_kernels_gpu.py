@@ -297,7 +297,7 @@ def test_philox_keyed_draws_match_oracle():
 
 
 # ------------------------------------------------------------------------------------------------ fused QKV + attention
-def _qkv_attn_case(dtype, ring, splits, rope, ve, fused, G=8, hd=64, seed=0):
+def _qkv_attn_case(dtype, ring, splits, rope, ve, fused, G=8, hd=64, seed=0, gate_pre=False):
     """One layer's uv_qkv_post + uv_decode_attn (fused=False) or uv_qkv_attn (fused=True) on identical inputs.
     Returns (attention output, k cache, v cache, k scales, v scales)."""
     import ctypes as C
@@ -352,12 +352,21 @@ def _qkv_attn_case(dtype, ring, splits, rope, ve, fused, G=8, hd=64, seed=0):
                                                      inv_freq.data_ptr(), 16, cs.data_ptr(),
                                                      torch.cuda.current_stream().cuda_stream), "uv_embed_norm_rope")
             pre.rope_cs = cs.data_ptr()
+    elif gate_pre:  # parameters by name; the kernel also leaves the head gates for the attention launch
+        qa = _lib.QkvArgs()
+        (qa.qkv, qa.xn, qa.tok, qa.value_embed, qa.ve_gate, qa.inv_freq, qa.pos, qa.k_cache, qa.v_cache, qa.k_scale,
+         qa.v_scale, qa.row_map, qa.oob_count, qa.dtype, qa.vocab, qa.B, qa.H, qa.K, qa.hd, qa.d, qa.S, qa.S_alloc,
+         qa.ring, qa.ve_ch, qa.n_pairs) = (qkv.data_ptr(), xn.data_ptr(), *post)
+        gates = torch.zeros(B, H, dtype=torch.float32, device=DEV)
+        qa.gate_w, qa.gate_out, qa.gate_ch = gate_w.data_ptr(), gates.data_ptr(), 128
+        _lib.check(_lib.lib().uv_qkv_post_args(C.byref(qa), torch.cuda.current_stream().cuda_stream),
+                   "uv_qkv_post_args")
     else:
         _lib.check(_lib.lib().uv_qkv_post(qkv.data_ptr(), xn.data_ptr(), *post,
                                           torch.cuda.current_stream().cuda_stream), "uv_qkv_post")
     attn_launch(q3[:, :H], kc, vc, pos, starts, 0.14125, window, ring, ks, vs, splits, out, ws,
                 v_cur=q3[:, H + K:], xsa_alpha=alpha, xsa_eps=1e-4, gate_x=xn, gate_w=gate_w, counters=cnt,
-                status=status, row_map=rows, pre=pre)
+                status=status, row_map=rows, pre=pre, gate_vals=gates if gate_pre and not fused else None)
     torch.cuda.synchronize()
     assert int(status.item()) == 0 and int(cnt.abs().sum()) == 0
     # the one-launch form reads the projection and leaves it alone; the two-launch form rewrites it in place
@@ -377,6 +386,13 @@ def test_qkv_attn_one_launch_equals_two(dtype, ring, rope, ve, splits):
         assert torch.equal(x, y), name
     assert a[5] == b[5]  # rows past the end of a linear cache are counted, not written, either way
     assert torch.equal(a[0], b[0])
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_head_gates_from_qkv_post_equal_epilogue_gates(dtype):
+    a = _qkv_attn_case(dtype, True, 1, True, True, fused=False)
+    b = _qkv_attn_case(dtype, True, 1, True, True, fused=False, gate_pre=True)
+    assert torch.equal(a[0], b[0]) and torch.equal(a[1], b[1]) and torch.equal(a[2], b[2])
 
 
 def test_qkv_attn_group16_and_small_heads():

@@ -38,6 +38,7 @@ class AttnArgs(C.Structure):
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("counters", C.c_void_p), ("status", C.c_void_p),
         ("v_cur", C.c_void_p), ("v_cur_sb", C.c_int64), ("v_cur_sh", C.c_int64), ("xsa_alpha", C.c_void_p), ("xsa_eps", C.c_float),
         ("gate_x", C.c_void_p), ("gate_x_stride", C.c_int64), ("gate_w", C.c_void_p), ("gate_ch", C.c_int),
+        ("gate_vals", C.c_void_p),
     ]
 
 
@@ -50,7 +51,7 @@ class QkvArgs(C.Structure):
         ("row_map", C.c_void_p), ("oob_count", C.c_void_p), ("dtype", C.c_int), ("vocab", C.c_int64),
         ("B", C.c_int), ("H", C.c_int), ("K", C.c_int), ("hd", C.c_int), ("d", C.c_int), ("S", C.c_int),
         ("S_alloc", C.c_int), ("ring", C.c_int), ("ve_ch", C.c_int), ("n_pairs", C.c_int),
-        ("rope_cs", C.c_void_p),
+        ("rope_cs", C.c_void_p), ("gate_w", C.c_void_p), ("gate_out", C.c_void_p), ("gate_ch", C.c_int),
     ]
 
 

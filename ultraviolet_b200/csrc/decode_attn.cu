@@ -76,6 +76,7 @@ struct AttnParams {
   int64_t gate_x_stride;
   const void* gate_w;
   int gate_ch;
+  const float* gate_vals;  // (B, H) gates already computed (uv_qkv_post_args): replaces gate_x / gate_w
   int cluster;  // the splits of one cache row form a thread-block cluster and merge through distributed shared memory
   // uv_qkv_attn: the kernel first post-processes the row's raw QKV projection (q / k / v of this step) and appends
   // the new key and value to the cache; q and the current v are then taken from shared memory
@@ -207,13 +208,13 @@ __device__ __forceinline__ void finalize_row(float (&z)[(HD + 31) / 32], int lan
 #pragma unroll
     for (int i = 0; i < EPL; ++i) z[i] = rnd<QT>(z[i] - a * dot * vv[i]);
   }
-  if (P.gate_w != nullptr) {
-    const QT* gx = static_cast<const QT*>(P.gate_x) + (int64_t)b * P.gate_x_stride;
-    const QT* gw = static_cast<const QT*>(P.gate_w) + (int64_t)head * P.gate_ch;
-    float acc = 0.f;
-    for (int ch = lane; ch < P.gate_ch; ch += 32) acc += to_f32<QT>(gx[ch]) * to_f32<QT>(gw[ch]);
-    acc = rnd<QT>(warp_sum(acc));
-    const float g = rnd<QT>(2.0f * rnd<QT>(1.0f / (1.0f + __expf(-acc))));
+  if (P.gate_vals != nullptr) {
+    const float g = P.gate_vals[(int64_t)b * P.H + head];
+#pragma unroll
+    for (int i = 0; i < EPL; ++i) z[i] = rnd<QT>(z[i] * g);
+  } else if (P.gate_w != nullptr) {
+    const float g = head_gate<QT>(static_cast<const QT*>(P.gate_x) + (int64_t)b * P.gate_x_stride,
+                                  static_cast<const QT*>(P.gate_w) + (int64_t)head * P.gate_ch, P.gate_ch, lane);
 #pragma unroll
     for (int i = 0; i < EPL; ++i) z[i] = rnd<QT>(z[i] * g);
   }
@@ -1032,7 +1033,8 @@ static int decode_attn_impl(const uv_attn_args* a, void* stream, bool allow_clus
   // cache rows are read in 16-byte pieces on every path
   if (!aligned16(a->k_cache) || !aligned16(a->v_cache) || (a->skb | a->skh | a->sks | a->svb | a->svh | a->svs) & 15)
     return UV_ERR_ALIGN;
-  if ((a->xsa_alpha && !a->v_cur) || (a->gate_w && (!a->gate_x || a->gate_ch < 1))) return UV_ERR_ARG;
+  if ((a->xsa_alpha && !a->v_cur) || (a->gate_w && !a->gate_vals && (!a->gate_x || a->gate_ch < 1)))
+    return UV_ERR_ARG;
 
   AttnParams P{};
   P.q = a->q, P.k = static_cast<const int8_t*>(a->k_cache), P.v = static_cast<const int8_t*>(a->v_cache);
@@ -1048,6 +1050,7 @@ static int decode_attn_impl(const uv_attn_args* a, void* stream, bool allow_clus
   P.counters = a->num_splits > 1 ? a->counters : nullptr;
   P.v_cur = a->v_cur, P.v_cur_sb = a->v_cur_sb, P.v_cur_sh = a->v_cur_sh, P.xsa_alpha = a->xsa_alpha, P.xsa_eps = a->xsa_eps;
   P.gate_x = a->gate_x, P.gate_x_stride = a->gate_x_stride, P.gate_w = a->gate_w, P.gate_ch = a->gate_ch;
+  P.gate_vals = a->gate_vals;
   // up to 8 splits (the portable cluster size) merge inside a thread-block cluster and need no workspace
   P.cluster = (allow_cluster && P.splits > 1 && P.splits <= 8 && cluster_merge_enabled()) ? 1 : 0;
   if (P.splits > 1 && !P.cluster) {

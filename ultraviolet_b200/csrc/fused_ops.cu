@@ -174,11 +174,19 @@ __global__ void __launch_bounds__(128) qkv_post_kernel(const __grid_constant__ Q
   constexpr int E = HD >= 32 ? HD / 32 : 1;
   const int lane = threadIdx.x & 31;
   const int slots = P.H + 2 * P.K;
+  const int per_row = slots + (P.gate_out ? P.H : 0);  // head slots, then one gate item per query head
   const int item = blockIdx.x * 4 + (threadIdx.x >> 5);
   pdl_wait();
   pdl_trigger();
-  if (item >= P.B * slots) return;
-  const int b = item / slots, hs = item % slots;
+  if (item >= P.B * per_row) return;
+  const int b = item / per_row, hs = item % per_row;
+  if (hs >= slots) {
+    const int head = hs - slots;
+    const float g = head_gate<T>(static_cast<const T*>(P.xn) + (int64_t)b * P.d,
+                                 static_cast<const T*>(P.gate_w) + (int64_t)head * P.gate_ch, P.gate_ch, lane);
+    if (lane == 0) P.gate_out[(int64_t)b * P.H + head] = g;
+    return;
+  }
   const bool act = lane * E < HD;
   T* vec = static_cast<T*>(P.qkv) + ((int64_t)b * slots + hs) * HD;
   float x[E];
@@ -193,7 +201,7 @@ __global__ void __launch_bounds__(128) qkv_post_kernel(const __grid_constant__ Q
 
 template <typename T>
 static int launch_qkv_post(const QkvPostParams& P, int hd, cudaStream_t st) {
-  const unsigned grid = (unsigned)(((int64_t)P.B * (P.H + 2 * P.K) + 3) / 4);
+  const unsigned grid = (unsigned)(((int64_t)P.B * (P.H + 2 * P.K + (P.gate_out ? P.H : 0)) + 3) / 4);
   // with the step's RoPE table the kernel carries no cosf / sinf code at all
 #define UV_QKV_POST(HD_)                                                                        \
   case HD_:                                                                                     \
@@ -249,6 +257,10 @@ extern "C" int uv_qkv_post_args(const uv_qkv_args* a, void* stream) {
                                  a->K, a->hd, a->d, a->S, a->S_alloc, a->ring, a->ve_ch, a->n_pairs);
   if (rc != UV_OK) return rc;
   P.rope_cs = a->inv_freq ? a->rope_cs : nullptr;
+  if (a->gate_out) {
+    if (!a->gate_w || !a->xn || a->gate_ch < 1 || a->gate_ch > a->d) return UV_ERR_ARG;
+    P.gate_w = a->gate_w, P.gate_out = a->gate_out, P.gate_ch = a->gate_ch;
+  }
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (a->dtype == UV_F16) return launch_qkv_post<__half>(P, a->hd, st);
   if (a->dtype == UV_BF16) return launch_qkv_post<__nv_bfloat16>(P, a->hd, st);

@@ -31,7 +31,22 @@ struct QkvPostParams {
   int* oob;
   int64_t vocab;
   int B, H, K, d, S, S_alloc, ring, ve_ch, n_pairs;
+  // optional: the attention output gate of every query head, 2*sigmoid(xn[b, :gate_ch] . gate_w[head]), computed
+  // here (it depends on xn only) so that the attention epilogue loads one float instead of two 128-channel rows
+  const void* gate_w;        // (H, gate_ch)
+  float* gate_out;           // (B, H)
+  int gate_ch;
 };
+
+// The head gate of Attention.post (ultraviolet/model.py:330-333) with its rounding points; lane-strided products,
+// then a warp sum.  Full warp; every lane returns the gate.
+template <typename T>
+__device__ __forceinline__ float head_gate(const T* gx, const T* gw, int gate_ch, int lane) {
+  float acc = 0.f;
+  for (int ch = lane; ch < gate_ch; ch += 32) acc += to_f32<T>(gx[ch]) * to_f32<T>(gw[ch]);
+  acc = rnd<T>(warp_sum(acc));
+  return rnd<T>(2.0f * rnd<T>(1.0f / (1.0f + __expf(-acc))));
+}
 
 // Host-side argument check + parameter block (shared by the two entry points).
 inline int qkv_post_params(QkvPostParams* out, void* qkv, const void* xn, const int64_t* tok, const void* value_embed,

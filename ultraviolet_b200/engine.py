@@ -86,6 +86,8 @@ class DecodeEngine:
         self.qkv_in_attn = os.environ.get("UVDECODE_QKV_IN_ATTN", "0") == "1"
         # cos / sin of pos * inv_freq once per step (uv_embed_norm_rope) instead of in every layer's q / k rotation
         self.rope_table = os.environ.get("UVDECODE_ROPE_TABLE", "1") != "0"
+        # attention output gates computed by uv_qkv_post (they depend on xn only) instead of in the attention epilogue
+        self.gate_pre = os.environ.get("UVDECODE_GATE_PRE", "1") != "0"
         self.n_sm = torch.cuda.get_device_properties(self.device).multi_processor_count
         _lib.lib()
 
@@ -139,7 +141,8 @@ class DecodeEngine:
                      counters=torch.zeros(B * K, dtype=torch.int32, device=dev),
                      status=torch.zeros(1, dtype=torch.int32, device=dev),
                      oob=torch.zeros(1, dtype=torch.int32, device=dev),
-                     rope_cs=torch.zeros(B, 2 * max(cfg.rope_pairs, 1), dtype=torch.float32, device=dev), ws={})
+                     rope_cs=torch.zeros(B, 2 * max(cfg.rope_pairs, 1), dtype=torch.float32, device=dev),
+                     gate=torch.zeros(B, H, dtype=torch.float32, device=dev), ws={})
             self._scratch[B] = s
         return s
 
@@ -188,7 +191,7 @@ class DecodeEngine:
                 kc, vc, ks, vs = st.k[l], st.v[l], st.k_scale[l], st.v_scale[l]
                 S = kc.size(2)
                 ve_gate = w[f"l{l}.ve_gate"].data_ptr() if cfg.has_ve(l) else None
-                pre = None
+                pre = gate_vals = None
                 rope = (not glob) or cfg.global_rope
                 post_args = (tok.data_ptr(), w["value_embed"].data_ptr() if self.use_ve else None, ve_gate,
                              self.inv_freq.data_ptr() if rope and cfg.rope_pairs else None, pos.data_ptr(),
@@ -209,6 +212,10 @@ class DecodeEngine:
                     if self.qkv_in_attn:  # the attention launch below does uv_qkv_post's work in its prologue
                         pre = qa
                     else:
+                        if cfg.gate_channels and self.gate_pre:  # the gates depend on xn only: computed here, off the
+                            qa.gate_w = w[f"l{l}.attn_gate"].data_ptr()  # attention kernel's critical tail
+                            qa.gate_out, qa.gate_ch = s["gate"].data_ptr(), cfg.gate_channels
+                            gate_vals = s["gate"]
                         _lib.check(lib.uv_qkv_post_args(C.byref(qa), sp), "uv_qkv_post")
                 if glob:
                     ctx = min(g_len or S, S)
@@ -222,7 +229,8 @@ class DecodeEngine:
                             xsa_alpha=self.xsa[l] if cfg.xsa else None, xsa_eps=cfg.xsa_eps,
                             gate_x=xn if cfg.gate_channels else None,
                             gate_w=w[f"l{l}.attn_gate"] if cfg.gate_channels else None,
-                            counters=s["counters"], status=s["status"], row_map=row_map, pre=pre)
+                            counters=s["counters"], status=s["status"], row_map=row_map, pre=pre,
+                            gate_vals=gate_vals)
                 lam = self.lambdas[l]
                 if fused:
                     _lib.check(lib.uv_gemm_resid_norm(s["z"].data_ptr(), H * hd, w[f"l{l}.wo"].data_ptr(), H * hd,

@@ -47,7 +47,7 @@ def attn_launch(q: Tensor, k_cache: Tensor, v_cache: Tensor, pos: Tensor, starts
                 workspace: Tensor | None = None, v_cur: Tensor | None = None, xsa_alpha: Tensor | None = None,
                 xsa_eps: float = 1e-4, gate_x: Tensor | None = None, gate_w: Tensor | None = None,
                 counters: Tensor | None = None, status: Tensor | None = None,
-                row_map: Tensor | None = None, pre=None) -> Tensor:
+                row_map: Tensor | None = None, pre=None, gate_vals: Tensor | None = None) -> Tensor:
     """Raw launch: fills uv_attn_args from tensor metadata.  q / out (B, H, hd) with unit inner stride.
     pre: a filled _lib.QkvArgs -> uv_qkv_attn (uv_qkv_post's work done inside the attention launch)."""
     B, H, hd = q.shape
@@ -77,7 +77,9 @@ def attn_launch(q: Tensor, k_cache: Tensor, v_cache: Tensor, pos: Tensor, starts
     if xsa_alpha is not None:
         a.v_cur, a.v_cur_sb, a.v_cur_sh = v_cur.data_ptr(), v_cur.stride(0), v_cur.stride(1)
         a.xsa_alpha, a.xsa_eps = xsa_alpha.data_ptr(), float(xsa_eps)
-    if gate_w is not None:
+    if gate_vals is not None:  # (B, H) fp32 gates computed by uv_qkv_post_args
+        a.gate_vals = gate_vals.data_ptr()
+    elif gate_w is not None:
         a.gate_x, a.gate_x_stride = gate_x.data_ptr(), gate_x.stride(0)
         a.gate_w, a.gate_ch = gate_w.data_ptr(), gate_w.size(-1)
     with torch.cuda.device(q.device):
