@@ -50,8 +50,9 @@ class DecodeRunner:
         self.temperature, self.top_k, self.top_p, self.seed = temperature, top_k, top_p, seed
         dev = st.pos.device
         self.tok = torch.zeros(st.B, dtype=torch.long, device=dev)
-        sc = self.eng.scratch(st.B)
-        self.out_tok, self.out_logp = sc["tok"], sc["logp"]
+        # The sampler writes the new tokens straight into the step's input buffer: feeding step() its own output
+        # costs no copy.
+        self.out_tok, self.out_logp = self.tok, self.eng.scratch(st.B)["logp"]
         self.want_logp = True
         self.row_keys = torch.arange(st.B, dtype=torch.int64, device=dev)
         self.steps = torch.zeros(st.B, dtype=torch.int64, device=dev)
@@ -72,26 +73,28 @@ class DecodeRunner:
         h = eng.trunk(self.tok, st, st.pos, st.starts, g_len=g_len, num_splits=self.m.__dict__.get(
             "decode_num_splits", getattr(type(self.m), "decode_num_splits", None)), skip_attn=self.skip_attn)
         eng.sample(eng.head(h), self.temperature, self.top_p, seed=self.seed, row_keys=self.row_keys,
-                   steps=self.steps, inc_a=st.pos, inc_b=self.steps)  # the sampler advances both counters
+                   steps=self.steps, tok_out=self.tok, inc_a=st.pos, inc_b=self.steps)  # advances both counters
 
     def step(self, tok: Tensor) -> Tensor:
         p = int(self.st.host_pos.max())
         assert p < self.st.max_len, "cache full"
         gl = self.g_len(p)
-        self.tok.copy_(tok)
+        if tok.data_ptr() != self.tok.data_ptr():
+            self.tok.copy_(tok)
         if not self.use_graph:
             self._body(gl)
         else:
             g = self.graphs.get(gl)
             if g is None:
                 dev = self.st.pos.device
-                pos0, steps0 = self.st.pos.clone(), self.steps.clone()
+                pos0, steps0, tok0 = self.st.pos.clone(), self.steps.clone(), self.tok.clone()
                 s = torch.cuda.Stream(dev)
                 s.wait_stream(torch.cuda.current_stream(dev))
                 with torch.cuda.stream(s):  # warm-up: the slot written now is rewritten by the real replay
                     self._body(gl)
                     self.st.pos.copy_(pos0)
                     self.steps.copy_(steps0)
+                    self.tok.copy_(tok0)
                 torch.cuda.current_stream(dev).wait_stream(s)
                 g = torch.cuda.CUDAGraph()
                 with torch.cuda.graph(g, capture_error_mode="thread_local"):
