@@ -31,6 +31,9 @@ sys.path.insert(0, ROOT)
 VOCAB = 16384
 SLOTS = 256
 PROMPT_LO, PROMPT_HI = 32, 128
+# DRAM bytes (read + write) per launch of attn_split_kernel divided by its algorithmic bytes, from the ncu captures
+# summarised under profiles/ (traffic grows in proportion to the keys read, so the ratio scales to any launch)
+NCU_TRAFFIC_RATIO = {"long_context": 1.013, "step": 0.993}
 
 
 def measured_peaks():
@@ -494,7 +497,8 @@ def main():
         "roofline": {"bound": "hbm", "kernel": "attn_split_kernel (local-layer launches, 8 per step)"
                      if att_mid is att["local"] else "attn_split_kernel (global-layer launches, 2 per step)",
                      "achieved": att_mid["gbs"], "peak": hbm_peak, "peak_kind": peak_kind, "unit": "GB/s",
-                     "frac": att_mid["gbs"] / hbm_peak, "traffic": None,
+                     "frac": att_mid["gbs"] / hbm_peak,
+                     "traffic": att_mid["bytes"] * NCU_TRAFFIC_RATIO["step"],
                      "bytes_per_launch": att_mid["bytes"], "ms_per_launch": att_mid["ms"]},
         "attention": {"local": att["local"], "global": att["global"], "long_context_64x8192": lc,
                       "long_context_frac_of_measured": lc["gbs"] / hbm_peak,

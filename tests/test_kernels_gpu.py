@@ -400,3 +400,54 @@ def test_qkv_attn_group16_and_small_heads():
         a = _qkv_attn_case(torch.bfloat16, True, 2, True, True, fused=False, G=G, hd=hd, seed=G + hd)
         b = _qkv_attn_case(torch.bfloat16, True, 2, True, True, fused=True, G=G, hd=hd, seed=G + hd)
         assert torch.equal(a[0], b[0]) and torch.equal(a[1], b[1]) and torch.equal(a[2], b[2])
+
+
+# ------------------------------------------------------------------------------------------------ prefill-time writes
+def test_kv_write_rows_all_index_forms():
+    """kv_write_rows (kv_quant.py:39-54): whole batch, a row subset with a slice of slots, a row subset with a
+    tensor of slots (the local-ring write of the last 256 positions) -- against the oracle's restatement."""
+    from ultraviolet_b200.kernels import kv_write_rows
+    r = np.random.default_rng(11)
+    B, K, S, hd = 6, 2, 40, 64
+    base_c = r.integers(-127, 128, (B, K, S, hd)).astype(np.int8)
+    base_s = (r.random((B, K, S)) * 0.02).astype(np.float16)
+    cases = [
+        (None, slice(3, 19), r.standard_normal((B, K, 16, hd)).astype(np.float32)),
+        (np.array([4, 1, 5]), slice(0, 7), r.standard_normal((3, K, 7, hd)).astype(np.float32) * 3),
+        (np.array([2, 0]), np.array([39, 0, 1, 17, 5]), r.standard_normal((2, K, 5, hd)).astype(np.float32)),
+    ]
+    for rows, slots, new in cases:
+        c_ref, s_ref = base_c.copy(), base_s.copy()
+        okv.kv_write_rows(c_ref, s_ref, new, slots, rows)
+        c, s = T(base_c), T(base_s)
+        kv_write_rows(c, s, T(new), slots if isinstance(slots, slice) else T(slots),
+                      None if rows is None else T(rows))
+        assert np.array_equal(c.cpu().numpy(), c_ref)
+        assert np.array_equal(u16(s), s_ref.view(np.uint16))
+
+
+def test_decode_attention_is_a_registered_custom_op():
+    """The reference registers its launch as a custom op with a fake implementation so that graph capture and
+    tracing keep working (decode_attn.py:174-190); the same holds here."""
+    from ultraviolet_b200.kernels import decode_attention
+    assert hasattr(torch.ops.uvb200, "decode_attn")
+    c = gi.attn_cases()["uv.global"]
+    kq, ks, vq, vs = _quant(c)
+    q = T(c["q"], torch.float16)
+    args = (q, kq, vq, T(c["pos"]), T(c["starts"]), c["scale"], 0, False, ks, vs, 2)
+    torch.library.opcheck(torch.ops.uvb200.decode_attn.default, args,
+                          test_utils=("test_schema", "test_faketensor"))
+    # and the launch is capturable: a replay reproduces the eager result
+    eager = decode_attention(q, kq, vq, T(c["pos"]), T(c["starts"]), c["scale"], k_scale=ks, v_scale=vs, num_splits=2)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        decode_attention(q, kq, vq, T(c["pos"]), T(c["starts"]), c["scale"], k_scale=ks, v_scale=vs, num_splits=2)
+    torch.cuda.current_stream().wait_stream(side)
+    g = torch.cuda.CUDAGraph()
+    pos, starts = T(c["pos"]), T(c["starts"])
+    with torch.cuda.graph(g):
+        out = decode_attention(q, kq, vq, pos, starts, c["scale"], k_scale=ks, v_scale=vs, num_splits=2)
+    g.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(out, eager)

@@ -87,6 +87,45 @@ def test_streamgen_is_deterministic_per_request():
     assert c != b                 # another seed, another stream
 
 
+def test_streamgen_top_p_stays_in_the_nucleus():
+    """With top_p < 1 every drawn token lies in the smallest prefix of the sorted teacher-forced distribution whose
+    mass reaches top_p (first token always kept, model.py:1200-1208), and the behaviour log-prob stays the
+    UNTRUNCATED one (rl_stream.py:119)."""
+    from ultraviolet_b200.rl_stream import StreamGen
+    m = _model()
+    T, top_p, max_new = 1.0, 0.6, 8
+    gen = StreamGen(m, slots=3, max_prompt=6, max_new=max_new, temperature=T, eos_id=0, check_every=4, seed=11,
+                    top_p=top_p)
+    r = np.random.default_rng(4)
+    prompts = {i: r.integers(1, 500, r.integers(2, 6)).tolist() for i in range(6)}
+    for i, p in prompts.items():
+        gen.add(p, meta=i)
+    got = {}
+    for _ in range(100):
+        for meta, toks, lp, _ in gen.chunk():
+            got[meta] = (toks, lp)
+        if not gen.n_outstanding():
+            break
+    assert sorted(got) == list(range(6))
+    outside, total, lp_err = 0, 0, []
+    for i, (toks, lp) in got.items():
+        st = m.new_state(1, len(prompts[i]) + len(toks) + 1)
+        seq = list(prompts[i]) + list(toks)
+        for j, t in enumerate(seq[:-1]):
+            lg = m.decode_step(torch.tensor([t], device=DEV), st, st.max_len)
+            if j < len(prompts[i]) - 1:
+                continue
+            logp = torch.log_softmax(lg.float() / T, -1)[0]
+            prob, order = torch.sort(logp.exp(), descending=True)
+            keep = int((torch.cumsum(prob, 0) - prob < top_p).sum())   # tokens whose preceding mass is < top_p
+            nxt = seq[j + 1]
+            total += 1
+            outside += int(nxt not in order[:keep + 1].tolist())       # one slack entry for bf16 ties at the edge
+            lp_err.append(abs(float(logp[nxt]) - float(lp[j - len(prompts[i]) + 1])))
+    assert total >= 12 and outside == 0, (outside, total)
+    assert np.mean(lp_err) < 0.05
+
+
 def test_fused_sample_api():
     from ultraviolet_b200.kernels import fused_sample, fused_sample_ok
     x = torch.randn(5, 16384, device=DEV).half()
