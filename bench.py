@@ -1,5 +1,5 @@
 #!/usr/bin/env python
-"""Benchmark of the UV-50M rollout-decode path ("Measurement").
+"""Benchmark of the UV-50M rollout-decode path.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--workload fixed|continuous|attn] [--impl reference]
 
@@ -473,7 +473,7 @@ def main():
     att = time_attention_layers(eng, st, st.pos - 1, st.starts)
     att_mid = att["local"] if att["local"]["ms"] * 8 >= att["global"]["ms"] * 2 else att["global"]
     lc = long_context_attention(eng)
-    # bytes one decode step must move: weights once + KV reads + KV appends (DESIGN.md "Measurement")
+    # bytes one decode step must move: weights once (99.6 MB bf16) + KV reads + KV appends (132 B per row per layer)
     kv_read = sum(attn_bytes((st.pos - 1).cpu().numpy(), st.starts.cpu().numpy(),
                              0 if eng.cfg.is_global(l) else eng.cfg.window) for l in range(eng.cfg.n_layers))
     step_bytes = 99_614_720 + kv_read + SLOTS * 10 * 132

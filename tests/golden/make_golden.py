@@ -1,8 +1,8 @@
 """Generate the golden fixtures in this directory from the reference implementation itself.
 
-Run where the reference checkout is importable (``REFERENCE_ROOT``, default ``/root/reference``):
+Run where the reference checkout is available, with ``REFERENCE_ROOT`` pointing at it:
 
-    python tests/golden/make_golden.py
+    REFERENCE_ROOT=/path/to/ultraviolet python tests/golden/make_golden.py
 
 It imports the reference's own CPU-runnable code for the rollout-decode path (ultraviolet.kernels.quantize_kv,
 kv_write, decode_attention_ref, fused_sample_ref; fast_decode.decode_step_fast / prefill_fast with the attention
@@ -22,7 +22,9 @@ import torch
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
-sys.path.insert(0, os.environ.get("REFERENCE_ROOT", "/root/reference"))
+if "REFERENCE_ROOT" not in os.environ:
+    sys.exit("set REFERENCE_ROOT to the reference checkout (hliuson/ultraviolet)")
+sys.path.insert(0, os.environ["REFERENCE_ROOT"])
 
 from tests import golden_inputs as gi  # noqa: E402
 import ultraviolet.kernels.fast_decode as ref_fd  # noqa: E402

@@ -451,3 +451,70 @@ def test_decode_attention_is_a_registered_custom_op():
     g.replay()
     torch.cuda.synchronize()
     assert torch.equal(out, eager)
+
+
+# ------------------------------------------------------------------------------------------------ full-size properties
+def _long_context_inputs(B=64, ctx=8192, seed=1):
+    """The long-context stress shape: B sequences with int8 KV filled to ctx tokens from N(0, 1)."""
+    from ultraviolet_b200.kernels import quantize_kv
+    g = torch.Generator(device=DEV).manual_seed(seed)
+    S = ctx + 256
+    k = torch.randn(B, 1, S, 64, device=DEV, generator=g)
+    v = torch.randn(B, 1, S, 64, device=DEV, generator=g)
+    kq, ks = quantize_kv(k)
+    vq, vs = quantize_kv(v)
+    q = torch.randn(B, 8, 64, device=DEV, generator=g).half()
+    pos = torch.full((B,), ctx - 1, device=DEV, dtype=torch.long)
+    pos[::7] -= torch.arange(0, B, 7, device=DEV) * 37          # ragged: some rows are shorter
+    starts = torch.zeros(B, dtype=torch.long, device=DEV)
+    starts[::5] = 1000
+    return q, kq, ks, vq, vs, pos, starts
+
+
+def test_long_context_full_size_properties():
+    """64 sequences x 8192 keys, where the oracle is too slow for every row: (1) the result does not depend on the
+    split count (1, the 8-split cluster merge, the 12-split workspace merge); (2) three rows against the oracle;
+    (3) linearity in V: doubling every V scale doubles the output; (4) a window equal to the whole context changes
+    nothing."""
+    from ultraviolet_b200.kernels import decode_attention
+    q, kq, ks, vq, vs, pos, starts = _long_context_inputs()
+    outs = {s: decode_attention(q, kq, vq, pos, starts, 0.14125, k_scale=ks, v_scale=vs, num_splits=s)
+            for s in (1, 8, 12)}
+    for s in (8, 12):
+        torch.testing.assert_close(outs[s].float(), outs[1].float(), atol=2e-3, rtol=2e-3)
+    rows = [0, 7, 35]  # a full row, two ragged ones (row 35 also starts at 1000)
+    ref = oattn.decode_attention_ref(q[rows].float().cpu().numpy(), kq[rows].cpu().numpy(), vq[rows].cpu().numpy(),
+                                     pos[rows].cpu().numpy(), starts[rows].cpu().numpy(), 0.14125,
+                                     k_scale=ks[rows].cpu().numpy(), v_scale=vs[rows].cpu().numpy())
+    np.testing.assert_allclose(outs[8][rows].float().cpu().numpy(), ref, atol=2e-3, rtol=2e-3)
+    dbl = decode_attention(q, kq, vq, pos, starts, 0.14125, k_scale=ks, v_scale=vs * 2, num_splits=8)
+    torch.testing.assert_close(dbl.float(), 2 * outs[8].float(), atol=4e-3, rtol=2e-3)
+    win = decode_attention(q, kq, vq, pos, starts, 0.14125, window=8192, k_scale=ks, v_scale=vs, num_splits=8)
+    assert torch.equal(win, outs[8])
+
+
+def test_appended_key_changes_only_its_row():
+    """kv_append of one new key per row followed by attention at pos + 1 equals attention over a cache that was
+    quantised with that key in place from the start (the append is the quantiser, bit for bit)."""
+    from ultraviolet_b200.kernels import decode_attention, kv_append, quantize_kv
+    g = torch.Generator(device=DEV).manual_seed(5)
+    B, S = 32, 2048
+    k = torch.randn(B, 1, S, 64, device=DEV, generator=g)
+    v = torch.randn(B, 1, S, 64, device=DEV, generator=g)
+    q = torch.randn(B, 8, 64, device=DEV, generator=g).half()
+    pos = torch.randint(100, S - 1, (B,), device=DEV, generator=g)
+    starts = torch.zeros(B, dtype=torch.long, device=DEV)
+    kq, ks = quantize_kv(k)
+    vq, vs = quantize_kv(v)
+    full = decode_attention(q, kq, vq, pos, starts, 0.14125, k_scale=ks, v_scale=vs)
+    # wipe the entry at pos, then append it again from the unquantised vectors
+    idx = pos.view(B, 1, 1, 1).expand(B, 1, 1, 64)
+    kq2, vq2, ks2, vs2 = kq.clone(), vq.clone(), ks.clone(), vs.clone()
+    kq2.scatter_(2, idx, 0), vq2.scatter_(2, idx, 0)
+    ks2.scatter_(2, pos.view(B, 1, 1), 0), vs2.scatter_(2, pos.view(B, 1, 1), 0)
+    knew = k.gather(2, idx).squeeze(2)
+    vnew = v.gather(2, idx).squeeze(2)
+    kv_append(kq2, vq2, ks2, vs2, pos, knew, vnew, ring=False)
+    assert torch.equal(kq2, kq) and torch.equal(vq2, vq) and torch.equal(ks2, ks) and torch.equal(vs2, vs)
+    again = decode_attention(q, kq2, vq2, pos, starts, 0.14125, k_scale=ks2, v_scale=vs2)
+    assert torch.equal(again, full)
