@@ -299,10 +299,10 @@ def run_continuous(args, m, rank, world, dev):
     prompts_all = [r.integers(1, VOCAB, int(L)).tolist() for L in lens]
     mine = uvdist.shard_requests(n_req, rank, world)
     t_bcast = uvdist.broadcast_weights(eng) if world > 1 else 0.0
-    st = m.new_state(slots, max_prompt + max_new + 16)
+    st = m.new_state(GpuScheduler.state_rows(slots, args.lanes), max_prompt + max_new + 16)
     sch = GpuScheduler(eng, st, max_new=max_new, temperature=1.0, eos_id=0, seed=7, q_cap=len(mine),
                        max_prompt=max_prompt, force_eos=True, tok_cap=int(lens[mine].sum()) + 1,
-                       out_cap=int(stops[mine].sum()) + 1)
+                       out_cap=int(stops[mine].sum()) + 1, prefill_lanes=args.lanes, lane_chunk=args.lane_chunk)
     sch.enqueue([prompts_all[i] for i in mine], limits=stops[mine].tolist(), keys=mine, metas=mine)
     sch.run(max(args.warmup, 3))
     torch.cuda.synchronize()
@@ -340,7 +340,7 @@ def run_continuous(args, m, rank, world, dev):
                 "config": {"workload": "continuous batching: 4096 requests sharded over ranks, prompts U[16,256], "
                                        "stop ~ Geometric(mean 600) <= 2048 (EOS forced), 512 slots/GPU, T=1.0, "
                                        "device-side retire/refill, prefill through the decode step",
-                           "slot_occupancy": float(gen[1].item()) / max(float(gen[2].item()) * slots, 1.0),
+                           "prefill_lanes": args.lanes, "lane_chunk": args.lane_chunk, "slot_occupancy": float(gen[1].item()) / max(float(gen[2].item()) * slots, 1.0),
                            "generated_tokens": int(gen[0].item()), "weight_broadcast_ms": t_bcast * 1e3,
                            "status": c1["status"]},
                 "gpu_launches": (1 + 5 * eng.cfg.n_layers + 2) * steps, "clocks": clk.summary()}
@@ -358,6 +358,10 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="fixed", choices=["fixed", "continuous", "attn"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--lanes", type=int, default=128,
+                    help="continuous workload: extra batch rows that carry prompt tokens of refilling slots (0 = "
+                         "one prompt token per slot per step)")
+    ap.add_argument("--lane-chunk", type=int, default=8, help="prompt tokens one slot may feed per step with lanes")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", 0))
     world = int(os.environ.get("WORLD_SIZE", 1))

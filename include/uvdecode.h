@@ -283,6 +283,15 @@ typedef struct uv_sched_args {
   int64_t tok_cap, out_cap;
   int eos, pad, force_eos;
   int64_t max_len;
+  /* Prefill lanes (0 = off).  cur_tok / pos / starts then have B + lanes entries and row_map (B + lanes,) names the
+   * cache row of every batch row of the decode step ([0, B): the identity).  A slot still feeding its prompt gets up
+   * to lane_chunk - 1 lane rows per step, which carry its next prompt tokens at consecutive positions of its cache
+   * row while its own row moves to the last token of the chunk: a prompt of P tokens takes about P / lane_chunk
+   * steps.  Idle lanes are parked on cache row B (one spare row).  A chunk never crosses position ring_len - 1 (the
+   * length of the shortest ring cache), where a wrapped write would overwrite keys the chunk still reads. */
+  int64_t* row_map;
+  int lanes, lane_chunk;
+  int64_t ring_len;
 } uv_sched_args;
 
 int uv_sched_step(const uv_sched_args* args, void* stream);

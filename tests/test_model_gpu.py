@@ -109,6 +109,25 @@ def test_generate_and_continuous_tiny():
         assert same > 0.8, (i, solo, cont[i])
 
 
+def test_continuous_with_prefill_lanes_matches_without():
+    """Prefill lanes only change how fast prompts enter the cache: per-request greedy outputs stay the same (up to
+    the batch-size dependent bf16 GEMM rounding that the other comparisons of this file also allow), with the
+    graph and without."""
+    from ultraviolet_b200.generate import generate_continuous
+    spec = gi.model_specs()["tiny"]
+    m = _gpu_model(spec)
+    c = spec["continuous"]
+    r = np.random.default_rng(8)
+    prompts = [r.integers(1, 500, r.integers(3, 40)).tolist() for _ in range(14)]
+    kw = dict(batch=4, temperature=0.0, eos_id=c["eos_id"], check_every=4)
+    base = generate_continuous(m, prompts, 10, **kw)
+    for graph in (False, True):
+        lanes = generate_continuous(m, prompts, 10, prefill_lanes=6, use_graph=graph, **kw)
+        assert [len(x) for x in lanes] == [len(x) for x in base]
+        agree = np.mean([a == b for x, y in zip(lanes, base) for a, b in zip(x, y)])
+        assert agree > 0.9, (graph, agree)
+
+
 def test_patch_reference_style_object_and_weight_refresh():
     """patch_model binds onto any object with MathLM's parameter layout; refresh keeps the arena pointers."""
     from ultraviolet_b200.fast_decode import patch_model, refresh_weights, unpatch_model

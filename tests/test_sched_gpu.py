@@ -119,3 +119,75 @@ def test_scheduler_matches_host_simulation(B, n, eos_every, force_eos):
     c = sch.counters()
     assert c["finished"] == len(fin) and c["tail"] == n and c["status"] == 0
     assert c["active"] == sum(x >= 0 for x in sch.req.cpu().numpy())
+
+
+@pytest.mark.parametrize("B,L,chunk,ring", [(4, 6, 4, 64), (8, 5, 8, 16), (33, 40, 3, 10)])
+def test_prefill_lanes_feed_every_prompt_once_and_change_no_output(B, L, chunk, ring):
+    """Prefill lanes: extra batch rows carry further prompt tokens of slots that are still prefilling.  Checked on
+    the scheduler alone with the fake sampler: (1) per request, the (position, token) pairs fed over all rows and
+    steps are exactly its prompt followed by its generated tokens, every position once, each step's rows of one
+    request at consecutive positions ending at the slot's own row; (2) no chunk crosses position ring - 1;
+    (3) idle lanes sit on the spare cache row; (4) outputs equal the run without lanes; (5) prompts take fewer steps."""
+    from ultraviolet_b200.scheduler import GpuScheduler
+    r = np.random.default_rng(B + L)
+    n = 5 * B
+    prompts = [r.integers(1, 1000, r.integers(1, 30)).tolist() for _ in range(n)]
+    limits = r.integers(1, 12, n).tolist()
+    max_len, max_new = 48, 12
+
+    def run(lanes):
+        st = _FakeState(GpuScheduler.state_rows(B, lanes), max_len)
+        st.k = [torch.empty(1, 1, ring, 1), torch.empty(1, 1, max_len, 1)]
+        eng = _FakeEngine(B)
+        sch = GpuScheduler(eng, st, max_new=max_new, temperature=1.0, eos_id=0, q_cap=4096, max_prompt=32,
+                           use_graph=False, prefill_lanes=lanes, lane_chunk=chunk)
+        sch.enqueue(prompts, limits=limits)
+        sch._sched_step()
+        sch._primed = True
+        fed = {}       # request -> list of (pos, tok) in feeding order
+        steps = 0
+        while int(sch.ctl[2].item()) < n:
+            req = sch.req.cpu().numpy()
+            tok = sch.cur_tok.cpu().numpy()
+            pos = (sch.pos_all if lanes else st.pos).cpu().numpy()
+            rows = [(int(s), int(s)) for s in range(B) if req[s] >= 0]
+            if lanes:
+                rm = sch.row_map.cpu().numpy()
+                assert (rm[:B] == np.arange(B)).all()
+                for l in range(B, B + lanes):
+                    if rm[l] == B:                                   # (3) parked on the spare row
+                        assert pos[l] == 0 and tok[l] == 0
+                    else:
+                        assert req[rm[l]] >= 0
+                        rows.append((l, int(rm[l])))
+            by_slot = {}
+            for row, s in rows:
+                by_slot.setdefault(s, []).append((int(pos[row]), int(tok[row]), row))
+            for s, lst in by_slot.items():
+                lst.sort()
+                ps = [p for p, _, _ in lst]
+                assert ps == list(range(ps[0], ps[0] + len(ps)))      # consecutive positions
+                assert lst[-1][2] == s and len(lst) <= chunk          # the slot's own row is the last one
+                if len(lst) > 1:
+                    assert ps[-1] <= ring - 1                         # (2)
+                fed.setdefault(int(req[s]), []).extend((p, t) for p, t, _ in lst)
+            gen = sch.gen.cpu().numpy()
+            eng._s["tok"].copy_(torch.from_numpy(_fake_token(req.astype(np.int64), gen.astype(np.int64), 7)
+                                                 .astype(np.int64)))
+            eng._s["logp"].copy_(torch.from_numpy((-(req + 1) - gen / 100).astype(np.float32)))
+            sch._sched_step()
+            steps += 1
+            assert steps < 5000
+        res = {m: toks for m, toks, _, _ in sch.harvest()}
+        assert sch.counters()["status"] == 0
+        return res, fed, steps
+
+    base, fed0, steps0 = run(0)
+    got, fed1, steps1 = run(L)
+    assert got == base and sorted(got) == list(range(n))              # (4)
+    for i in range(n):                                                # (1)
+        want = prompts[i] + got[i][:-1]   # the last generated token is never fed back
+        for fed in (fed0, fed1):
+            assert [p for p, _ in fed[i]] == list(range(len(want))), i
+            assert [t for _, t in fed[i]] == want, i
+    assert steps1 < steps0                                            # (5)

@@ -60,7 +60,9 @@ class SchedArgs(C.Structure):
         "req", "fed", "gen", "cur_tok", "pos", "starts", "row_key", "step_ctr", "samp_tok", "samp_lp", "prompt_off",
         "prompt_len", "limit", "key", "out_off", "out_len", "start_version", "tokens", "out_tok", "out_lp",
         "fin_ring", "ctl")] + [("B", C.c_int), ("q_cap", C.c_int), ("tok_cap", C.c_int64), ("out_cap", C.c_int64),
-                               ("eos", C.c_int), ("pad", C.c_int), ("force_eos", C.c_int), ("max_len", C.c_int64)]
+                               ("eos", C.c_int), ("pad", C.c_int), ("force_eos", C.c_int), ("max_len", C.c_int64),
+                               ("row_map", C.c_void_p), ("lanes", C.c_int), ("lane_chunk", C.c_int),
+                               ("ring_len", C.c_int64)]
 
 
 # name -> (restype, argtypes); every symbol include/uvdecode.h declares

@@ -55,6 +55,15 @@ struct SchedParams {
   int64_t tok_cap, out_cap;
   int eos, pad, force_eos;
   int64_t max_len;
+  // prefill lanes: rows [B, B + lanes) of cur_tok / pos / starts / row_map are extra batch rows of the decode step.
+  // A slot that is still feeding its prompt gets up to lane_chunk - 1 of them per step: the lanes carry the next
+  // prompt tokens at consecutive positions of the slot's cache row (row_map = slot) and the slot's own row moves to
+  // the last token of the chunk, so a prompt of P tokens takes P / lane_chunk steps instead of P.  Idle lanes are
+  // parked on cache row B (one spare row the caller allocates).
+  int64_t* row_map;    // (B + lanes,) cache row of every batch row; [0, B) is the identity
+  int lanes, lane_chunk;
+  int64_t ring_len;    // length of the shortest ring cache: a chunk never wraps it (a wrapped write would destroy
+                       // keys that the chunk's earlier positions still attend to)
 };
 
 enum { CTL_HEAD = 0, CTL_TAIL, CTL_FIN, CTL_VERSION, CTL_ACTIVE, CTL_STATUS, CTL_STEPS, CTL_TOK_TAIL, CTL_OUT_TAIL,
@@ -171,6 +180,50 @@ __global__ void __launch_bounds__(SCHED_THREADS) sched_step_kernel(const __grid_
     block_excl_scan(is_active, warp_tot, tid, tot_active);
     active += tot_active;
   }
+  // ---- prefill lanes (see SchedParams): hand out the lane rows in slot order by prefix sum
+  if (P.lanes > 0) {
+    int used = 0;
+    for (int base = 0; base < P.B; base += SCHED_THREADS) {
+      const int s = base + tid;
+      int want = 0, f = 0, ri = 0;
+      int64_t p = 0;
+      if (s < P.B && P.req[s] >= 0) {
+        ri = P.req[s] % P.q_cap;
+        f = P.fed[s];                                  // prompt tokens handed out so far (cur_tok is token f - 1)
+        p = P.pos[s];
+        const int64_t rem = (int64_t)P.prompt_len[ri] - f;  // prompt tokens after cur_tok
+        const int64_t room = P.ring_len - 1 - p;       // the chunk's last position must not wrap the ring
+        int64_t w = rem < P.lane_chunk - 1 ? rem : P.lane_chunk - 1;
+        if (w > room) w = room;
+        want = w > 0 ? (int)w : 0;
+      }
+      int total;
+      const int off = block_excl_scan(want, warp_tot, tid, total);
+      int grant = want;
+      if (used + off >= P.lanes) grant = 0;
+      else if (used + off + want > P.lanes) grant = P.lanes - used - off;
+      if (grant > 0) {
+        const int64_t toff = P.prompt_off[ri];
+        for (int j = 0; j < grant; ++j) {              // lanes: tokens f-1 .. f+grant-2 at positions p .. p+grant-1
+          const int lane = P.B + used + off + j;
+          P.cur_tok[lane] = j == 0 ? P.cur_tok[s] : (int64_t)P.tokens[(toff + f + j - 1) % P.tok_cap];
+          P.pos[lane] = p + j;
+          P.starts[lane] = 0;
+          P.row_map[lane] = s;
+        }
+        P.cur_tok[s] = P.tokens[(toff + f + grant - 1) % P.tok_cap];  // the slot's row: last token of the chunk
+        P.pos[s] = p + grant;
+        P.fed[s] = f + grant;
+      }
+      used = used + total < P.lanes ? used + total : P.lanes;
+    }
+    for (int l = used + tid; l < P.lanes; l += SCHED_THREADS) {  // idle lanes: the spare cache row, position 0
+      P.cur_tok[P.B + l] = P.pad;
+      P.pos[P.B + l] = 0;
+      P.starts[P.B + l] = 0;
+      P.row_map[P.B + l] = P.B;
+    }
+  }
   if (tid == 0) {
     P.ctl[CTL_HEAD] = head;
     __threadfence();  // ring entries and out_len before the count that publishes them
@@ -226,6 +279,7 @@ extern "C" int uv_sched_step(const uv_sched_args* a, void* stream) {
       !a->samp_tok || !a->samp_lp || !a->prompt_off || !a->prompt_len || !a->limit || !a->key || !a->out_off ||
       !a->out_len || !a->start_version || !a->tokens || !a->out_tok || !a->out_lp || !a->fin_ring || !a->ctl)
     return UV_ERR_ARG;
+  if (a->lanes < 0 || (a->lanes > 0 && (!a->row_map || a->lane_chunk < 2 || a->ring_len < 1))) return UV_ERR_ARG;
   SchedParams P;
   static_assert(sizeof(SchedParams) == sizeof(uv_sched_args), "uv_sched_args mirrors SchedParams");
   memcpy(&P, a, sizeof(P));

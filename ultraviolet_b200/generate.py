@@ -160,7 +160,7 @@ def generate(model, prompts, max_new: int, temperature: float = 1.0, top_k: int 
 def generate_continuous(model, prompts, max_new: int, batch: int, temperature: float = 1.0, top_k: int = 0,
                         eos_id: int | None = None, pad_id: int = 0, check_every: int = 16, use_graph: bool = True,
                         bucket: int = 1024, dtype=None, compile: bool = True, target_lens=None, stats=None,
-                        top_p: float = 1.0, seed: int = 0):
+                        top_p: float = 1.0, seed: int = 0, prefill_lanes: int = 0):
     """Continuous batching over `batch` cache slots (model.py:1266-1354), scheduled on the device; completions in
     prompt order.  target_lens[i] caps request i's length (the reference's benchmarking hook, model.py:1312)."""
     if top_k:
@@ -169,9 +169,11 @@ def generate_continuous(model, prompts, max_new: int, batch: int, temperature: f
     n = len(prompts)
     B = min(batch, n)
     max_prompt = max(len(p) for p in prompts)
-    st = model.new_state(B, max_prompt + max_new + check_every, eng.dtype, eng.device)
+    st = model.new_state(GpuScheduler.state_rows(B, prefill_lanes), max_prompt + max_new + check_every, eng.dtype,
+                         eng.device)
     sched = GpuScheduler(eng, st, max_new=max_new, temperature=temperature, top_p=top_p, eos_id=eos_id,
                          pad_id=pad_id, seed=seed, q_cap=max(n, 2), max_prompt=max_prompt, use_graph=use_graph,
+                         prefill_lanes=prefill_lanes,
                          tok_cap=sum(len(p) for p in prompts) + 1,
                          out_cap=(int(np.minimum(np.asarray(target_lens), max_new).sum()) if target_lens is not None
                                   else n * max_new) + 1)

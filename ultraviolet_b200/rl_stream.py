@@ -30,16 +30,19 @@ def sync_weights_inplace(gen_m, raw) -> None:
 class StreamGen:
     def __init__(self, model, slots, max_prompt, max_new, temperature, eos_id, check_every=16, compile=True,
                  use_graph=True, pad_id=0, dtype=torch.float16, bucket=1024, top_p: float = 1.0, seed: int = 0,
-                 queue_capacity: int = 8192):
+                 queue_capacity: int = 8192, prefill_lanes: int | None = None):
         assert temperature > 0
         self.m, self.B, self.max_new, self.T, self.eos = model, slots, max_new, temperature, eos_id
         self.ce, self.pad, self.dtype, self.max_prompt = check_every, pad_id, dtype, max_prompt
         eng = _engine(model)
         self.dev = eng.device
-        self.st = model.new_state(slots, max_prompt + max_new + check_every, eng.dtype, self.dev)
+        if prefill_lanes is None:  # a quarter more batch rows for prompt tokens once the batch is large enough
+            prefill_lanes = slots // 4 if slots >= 32 else 0
+        self.st = model.new_state(GpuScheduler.state_rows(slots, prefill_lanes), max_prompt + max_new + check_every,
+                                  eng.dtype, self.dev)
         self.sched = GpuScheduler(eng, self.st, max_new=max_new, temperature=temperature, top_p=top_p, eos_id=eos_id,
                                   pad_id=pad_id, seed=seed, q_cap=queue_capacity, max_prompt=max_prompt,
-                                  use_graph=use_graph)
+                                  use_graph=use_graph, prefill_lanes=prefill_lanes)
         self.queue = collections.deque()   # host-side FIFO of (prompt_ids, meta) not yet on the device
         self._version = 0
         self.n_decode_steps = 0

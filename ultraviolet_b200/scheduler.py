@@ -27,8 +27,13 @@ class GpuScheduler:
     def __init__(self, engine, st, *, max_new: int, temperature: float, top_p: float = 1.0, eos_id: int | None = 0,
                  pad_id: int = 0, seed: int = 0, q_cap: int = 8192, tok_cap: int | None = None,
                  out_cap: int | None = None, max_prompt: int = 256, force_eos: bool = False, use_graph: bool = True,
-                 num_splits: dict | None = None):
-        self.eng, self.st, self.B = engine, st, st.B
+                 num_splits: dict | None = None, prefill_lanes: int = 0, lane_chunk: int = 8):
+        """prefill_lanes > 0: the decode step runs on slots + prefill_lanes batch rows; the extra rows carry further
+        prompt tokens of slots that are still prefilling (up to lane_chunk tokens per slot per step).  The state must
+        then hold one spare cache row: st.B == slots + 1 (see ``state_rows``)."""
+        self.eng, self.st = engine, st
+        self.L = int(prefill_lanes)
+        self.B = st.B - 1 if self.L > 0 else st.B
         self.dev = engine.device
         self.max_new, self.T, self.top_p, self.seed = int(max_new), float(temperature), float(top_p), int(seed)
         self.eos = -1 if eos_id is None else int(eos_id)
@@ -41,7 +46,13 @@ class GpuScheduler:
         i32 = lambda n, v=0: torch.full((n,), v, dtype=torch.int32, device=dev)
         i64 = lambda n, v=0: torch.full((n,), v, dtype=torch.int64, device=dev)
         self.req, self.fed, self.gen = i32(B, -1), i32(B), i32(B)
-        self.cur_tok, self.row_key, self.step_ctr = i64(B, self.pad), i64(B), i64(B)
+        self.cur_tok, self.row_key, self.step_ctr = i64(B + self.L, self.pad), i64(B), i64(B)
+        if self.L > 0:
+            # batch rows = slots then lanes; the slots' pos / starts stay visible as the state's own (first B rows
+            # of the cache; row B is the spare row idle lanes are parked on)
+            self.pos_all, self.starts_all = i64(B + self.L), i64(B + self.L)
+            self.row_map = torch.cat([torch.arange(B, dtype=torch.int64, device=dev), i64(self.L, B)])
+            st.pos, st.starts = self.pos_all[:B], self.starts_all[:B]
         self.prompt_off, self.key, self.out_off = i64(Q), i64(Q), i64(Q)
         self.prompt_len, self.limit, self.out_len, self.start_version = i32(Q), i32(Q), i32(Q, -1), i32(Q)
         self.fin_ring = i32(Q, -1)
@@ -54,11 +65,14 @@ class GpuScheduler:
         st.pos.zero_()
         st.starts.zero_()
         a = self.args = _lib.SchedArgs()
+        if self.L > 0:
+            a.row_map, a.lanes, a.lane_chunk = self.row_map.data_ptr(), self.L, int(lane_chunk)
+            a.ring_len = min(int(k.size(2)) for k in st.k)
         for name in ("req", "fed", "gen", "cur_tok", "row_key", "step_ctr", "prompt_off", "prompt_len", "limit",
                      "key", "out_off", "out_len", "start_version", "tokens", "out_tok", "out_lp", "fin_ring", "ctl",
                      "samp_tok", "samp_lp"):
             setattr(a, name, getattr(self, name).data_ptr())
-        a.pos, a.starts = st.pos.data_ptr(), st.starts.data_ptr()
+        a.pos, a.starts = st.pos.data_ptr(), st.starts.data_ptr()  # (with lanes: the first rows of pos_all / starts_all)
         a.B, a.q_cap, a.tok_cap, a.out_cap = B, Q, self.tok_cap, self.out_cap
         a.eos, a.pad, a.force_eos, a.max_len = self.eos, self.pad, int(self.force_eos), st.max_len
         # host mirrors
@@ -73,6 +87,11 @@ class GpuScheduler:
         self.graph = None
         self.steps_run = 0
         self._primed = False
+
+    @staticmethod
+    def state_rows(slots: int, prefill_lanes: int = 0) -> int:
+        """Cache rows the decode state needs for `slots` sequences: one spare row when prefill lanes are on."""
+        return slots + (1 if prefill_lanes > 0 else 0)
 
     # ------------------------------------------------------------------------------------------------ queue
     def set_version(self, v: int) -> None:
@@ -127,7 +146,11 @@ class GpuScheduler:
 
     def _step_body(self) -> None:
         eng, st = self.eng, self.st
-        h = eng.trunk(self.cur_tok, st, st.pos, st.starts, g_len=st.max_len, num_splits=self.num_splits)
+        if self.L > 0:
+            h = eng.trunk(self.cur_tok, st, self.pos_all, self.starts_all, g_len=st.max_len,
+                          num_splits=self.num_splits, row_map=self.row_map)[:self.B]  # only slots are sampled
+        else:
+            h = eng.trunk(self.cur_tok, st, st.pos, st.starts, g_len=st.max_len, num_splits=self.num_splits)
         head = eng.head(h)
         eng.sample(head, self.T, self.top_p, seed=self.seed, row_keys=self.row_key, steps=self.step_ctr)
         self._sched_step()
