@@ -87,6 +87,34 @@ def test_streamgen_is_deterministic_per_request():
     assert c != b                 # another seed, another stream
 
 
+def test_streamgen_with_prefill_lanes_contract():
+    """32 slots -> 8 prefill lanes by default: the output contract and the behaviour log-probs hold as without."""
+    from ultraviolet_b200.rl_stream import StreamGen
+    m = _model()
+    T, max_new = 1.0, 8
+    gen = StreamGen(m, slots=32, max_prompt=30, max_new=max_new, temperature=T, eos_id=0, check_every=4, seed=9)
+    assert gen.sched.L == 8
+    r = np.random.default_rng(12)
+    prompts = {i: r.integers(1, 500, r.integers(2, 31)).tolist() for i in range(48)}
+    for i, p in prompts.items():
+        gen.add(p, meta=i)
+    got = {}
+    for _ in range(200):
+        for meta, toks, lp, _ in gen.chunk():
+            assert meta not in got
+            got[meta] = (toks, lp)
+        if not gen.n_outstanding():
+            break
+    assert sorted(got) == list(range(48))
+    errs = []
+    for i, (toks, lp) in got.items():
+        assert 1 <= len(toks) <= max_new and len(lp) == len(toks)
+        assert 0 not in toks[:-1] and (len(toks) == max_new or toks[-1] == 0)
+        if i % 6 == 0:
+            errs.append(np.abs(_teacher_logp(m, prompts[i], toks, T) - lp).mean())
+    assert max(errs) < 0.05, errs
+
+
 def test_streamgen_top_p_stays_in_the_nucleus():
     """With top_p < 1 every drawn token lies in the smallest prefix of the sorted teacher-forced distribution whose
     mass reaches top_p (first token always kept, model.py:1200-1208), and the behaviour log-prob stays the
