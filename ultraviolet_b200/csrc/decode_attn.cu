@@ -1008,6 +1008,9 @@ extern "C" int uv_default_splits(int n_bk, int ctx, int n_sm) {
   if (s > 8) s = (16 * n_bk <= n_sm) ? (s < 16 ? s : 16) : 8;
   const int per = (tiles + s - 1) / s;  // tiles per split; the fewest splits with that much work each
   s = (tiles + per - 1) / per;
+  // a split launch costs ~3 us more than an unsplit one (cluster scheduling + merge) and a tile ~0.9 us: splitting
+  // pays only when it takes at least four tiles off every CTA's serial chain
+  if (tiles - per < 4) s = 1;
   return s < 1 ? 1 : s;
 }
 
