@@ -41,6 +41,7 @@ struct SampleParams {
   int B, V;
   float a, b, c, inv_t, top_p;
   int greedy;
+  int greedy_fast;  // host-decided: the vectorised arg-max path (needs no shared memory: launched with none)
   int precapped;  // input rows are already softcapped logits z (sample(), model.py:1194-1211); a = row maximum
   const float* u;
   uint64_t seed;
@@ -74,6 +75,9 @@ __global__ void __launch_bounds__(SAMPLE_THREADS) sample_kernel(const __grid_con
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int row = blockIdx.x;
   const int V = P.V, CH = V / SAMPLE_THREADS;
+  // chunk index of element i: a shift when CH is a power of two (every vocabulary in use), else a division
+  const int ch_shift = (CH & (CH - 1)) == 0 ? 31 - __clz(CH) : -1;
+  auto chunk_of = [&](int i) { return ch_shift >= 0 ? i >> ch_shift : i / CH; };
   pdl_wait();
   pdl_trigger();
   const T* xr = static_cast<const T*>(P.x) + (int64_t)row * P.x_stride;
@@ -97,19 +101,30 @@ __global__ void __launch_bounds__(SAMPLE_THREADS) sample_kernel(const __grid_con
   }
 
   if constexpr (sizeof(T) == 2)
-  if (P.greedy && !P.precapped && (reinterpret_cast<uintptr_t>(xr) & 15) == 0 && V % 8 == 0) {
+  if (P.greedy_fast) {
     // greedy over the softcap: no cumulative sums needed, so nothing is parked in shared memory -- one vectorised
     // pass (8 values per 16-byte load) for the arg-max and the normaliser of the log-prob
     float best = -INFINITY, sum = 0.f;
     int best_i = 0x7fffffff;
-    for (int i = tid * 8; i < V; i += SAMPLE_THREADS * 8) {
-      const uint4 u4 = *reinterpret_cast<const uint4*>(xr + i);
-      const T* v = reinterpret_cast<const T*>(&u4);
+    constexpr int UN = 4;  // 16-byte loads in flight per thread: the row is read in two round trips, not eight
+    for (int i0 = tid * 8; i0 < V; i0 += SAMPLE_THREADS * 8 * UN) {
+      uint4 u4[UN];
 #pragma unroll
-      for (int k = 0; k < 8; ++k) {
-        const float z = __fdividef(P.a, 1.0f + __expf(-(to_f32<T>(v[k]) + P.b) * inv_c));
-        if (z > best) best = z, best_i = i + k;
-        sum += __expf((z - P.a) * P.inv_t);
+      for (int j = 0; j < UN; ++j) {
+        const int i = i0 + j * SAMPLE_THREADS * 8;
+        if (i < V) u4[j] = *reinterpret_cast<const uint4*>(xr + i);
+      }
+#pragma unroll
+      for (int j = 0; j < UN; ++j) {
+        const int i = i0 + j * SAMPLE_THREADS * 8;
+        if (i >= V) break;
+        const T* v = reinterpret_cast<const T*>(&u4[j]);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const float z = __fdividef(P.a, 1.0f + __expf(-(to_f32<T>(v[k]) + P.b) * inv_c));
+          if (z > best) best = z, best_i = i + k;
+          sum += __expf((z - P.a) * P.inv_t);
+        }
       }
     }
     const float S_all = block_sum(sum, red, tid);
@@ -135,10 +150,43 @@ __global__ void __launch_bounds__(SAMPLE_THREADS) sample_kernel(const __grid_con
   // ---- pass 1: softcap, exp, argmax (coalesced reads; e parked in shared memory)
   float best = -INFINITY;
   int best_i = 0x7fffffff;
-  for (int i = tid; i < V; i += SAMPLE_THREADS) {
-    const float z = zof(i);
-    if (z > best) best = z, best_i = i;  // strided ascending per thread: first index wins within a thread
-    e_sm[i + i / CH] = __expf((z - cap_a) * P.inv_t);
+  bool vec = false;
+  if constexpr (sizeof(T) == 2) vec = (reinterpret_cast<uintptr_t>(xr) & 3) == 0 && V % 2 == 0 && CH % 2 == 0;
+  if (vec) {
+    // 4-byte loads (two values), eight in flight per thread before any of them is used: the stores to shared
+    // memory below would otherwise keep the compiler from hoisting the next load over them.  Two values per lane
+    // keep the shared-memory stores at a 2-way bank conflict.
+    if constexpr (sizeof(T) == 2) {
+      constexpr int UN = 8;
+      for (int i0 = tid * 2; i0 < V; i0 += SAMPLE_THREADS * 2 * UN) {
+        uint32_t w[UN];
+#pragma unroll
+        for (int j = 0; j < UN; ++j) {
+          const int i = i0 + j * SAMPLE_THREADS * 2;
+          if (i < V) w[j] = *reinterpret_cast<const uint32_t*>(xr + i);
+        }
+#pragma unroll
+        for (int j = 0; j < UN; ++j) {
+          const int i = i0 + j * SAMPLE_THREADS * 2;
+          if (i >= V) break;
+          const T* v = reinterpret_cast<const T*>(&w[j]);
+          float* dst = e_sm + i + chunk_of(i);  // two consecutive entries of one chunk
+#pragma unroll
+          for (int k = 0; k < 2; ++k) {
+            const float x = to_f32<T>(v[k]);
+            const float z = P.precapped ? x : __fdividef(P.a, 1.0f + __expf(-(x + P.b) * inv_c));
+            if (z > best) best = z, best_i = i + k;  // ascending per thread: first index wins within a thread
+            dst[k] = __expf((z - cap_a) * P.inv_t);
+          }
+        }
+      }
+    }
+  } else {
+    for (int i = tid; i < V; i += SAMPLE_THREADS) {
+      const float z = zof(i);
+      if (z > best) best = z, best_i = i;  // strided ascending per thread: first index wins within a thread
+      e_sm[i + chunk_of(i)] = __expf((z - cap_a) * P.inv_t);
+    }
   }
   if (tid == 0) s_tok = V - 1;
   __syncthreads();
@@ -262,7 +310,11 @@ extern "C" int uv_sample(const void* x, int x_dtype, int64_t x_stride, int B, in
   P.top_p = top_p, P.greedy = greedy ? 1 : 0, P.precapped = precapped ? 1 : 0;
   P.u = u, P.seed = seed, P.row_keys = row_keys, P.steps = steps, P.tok = tok_out, P.logp = logp_out;
   P.inc_a = inc_a, P.inc_b = inc_b;
-  const size_t smem = (size_t)(V + V / (V / SAMPLE_THREADS) + 1) * sizeof(float);
+  // greedy over 16-bit logits whose rows start on 16-byte boundaries: one vectorised pass, no shared memory, so
+  // more rows are resident per SM
+  P.greedy_fast = greedy && !precapped && x_dtype != UV_F32 && (reinterpret_cast<uintptr_t>(x) & 15) == 0 &&
+                  (x_stride * 2) % 16 == 0 && V % 8 == 0;
+  const size_t smem = P.greedy_fast ? 0 : (size_t)(V + V / (V / SAMPLE_THREADS) + 1) * sizeof(float);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
 #define UV_GO(T)                                                                                              \
   do {                                                                                                        \
