@@ -91,8 +91,40 @@ __device__ __forceinline__ int block_excl_scan(int v, int* warp_tot, int tid, in
   return base + incl - v;
 }
 
+// The same scan over three counters at once, packed 20 bits each into one 64-bit word (a chunk holds at most
+// SCHED_THREADS = 2^10 ones per counter): one pass through the barriers instead of three.
+__device__ __forceinline__ unsigned long long pack3(int a, int b, int c) {
+  return (unsigned long long)a | ((unsigned long long)b << 20) | ((unsigned long long)c << 40);
+}
+__device__ __forceinline__ int field(unsigned long long v, int i) { return (int)((v >> (20 * i)) & 0xfffffull); }
+__device__ __forceinline__ unsigned long long block_excl_scan3(unsigned long long v, unsigned long long* warp_tot,
+                                                               int tid, unsigned long long& total) {
+  const int lane = tid & 31, warp = tid >> 5;
+  unsigned long long incl = v;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const unsigned long long t = __shfl_up_sync(0xffffffffu, incl, o);
+    if (lane >= o) incl += t;
+  }
+  __syncthreads();
+  if (lane == 31) warp_tot[warp] = incl;
+  __syncthreads();
+  // every warp scans the 32 warp totals itself: lane w holds the total of warp w
+  unsigned long long wt = warp_tot[lane], wincl = wt;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const unsigned long long t = __shfl_up_sync(0xffffffffu, wincl, o);
+    if (lane >= o) wincl += t;
+  }
+  total = __shfl_sync(0xffffffffu, wincl, 31);
+  const unsigned long long base = __shfl_sync(0xffffffffu, wincl - wt, warp);
+  return base + incl - v;
+}
+
 __global__ void __launch_bounds__(SCHED_THREADS) sched_step_kernel(const __grid_constant__ SchedParams P) {
   __shared__ int warp_tot[SCHED_THREADS / 32];
+  __shared__ unsigned long long warp_tot3[SCHED_THREADS / 32];
+  static_assert(SCHED_THREADS == 1024, "block_excl_scan3 scans the warp totals with one warp: 32 warps");
   const int tid = threadIdx.x;
   pdl_wait();
   pdl_trigger();
@@ -143,17 +175,16 @@ __global__ void __launch_bounds__(SCHED_THREADS) sched_step_kernel(const __grid_
         }
       }
     }
-    // ---- finished requests enter the ring in slot order (deterministic harvest order)
-    int total_fin;
-    const int frank = block_excl_scan(finished, warp_tot, tid, total_fin);
+    // ---- one packed scan: finished requests enter the ring in slot order (deterministic harvest order), emitted
+    //      tokens are only counted, freed slots get their rank among the chunk's free slots
+    unsigned long long tot3;
+    const unsigned long long pre3 = block_excl_scan3(pack3(finished, emitted, freed), warp_tot3, tid, tot3);
+    const int frank = field(pre3, 0), total_fin = field(tot3, 0);
     if (finished) P.fin_ring[(fin_base + frank) % P.q_cap] = fin_req;
     fin_base += total_fin;
-    int total_emit;
-    block_excl_scan(emitted, warp_tot, tid, total_emit);
-    generated += total_emit;
+    generated += field(tot3, 1);
     // ---- admit queued requests into the free slots of this chunk, in slot order
-    int total_free;
-    const int rank = block_excl_scan(freed, warp_tot, tid, total_free);
+    const int rank = field(pre3, 2), total_free = field(tot3, 2);
     const int64_t avail = tail - head;
     if (in && freed) {
       if (rank < avail) {
@@ -174,11 +205,11 @@ __global__ void __launch_bounds__(SCHED_THREADS) sched_step_kernel(const __grid_
         P.starts[s] = 0;
       }
     }
-    head += total_free < avail ? total_free : avail;
-    const int is_active = in && P.req[s] >= 0;
-    int tot_active;
-    block_excl_scan(is_active, warp_tot, tid, tot_active);
-    active += tot_active;
+    const int admitted = total_free < avail ? total_free : (int)avail;
+    head += admitted;
+    // slots of this chunk that hold a request after the step: the ones that kept theirs plus the admissions
+    const int n_in = P.B - base < SCHED_THREADS ? P.B - base : SCHED_THREADS;
+    active += n_in - total_free + admitted;
   }
   // ---- prefill lanes (see SchedParams): hand out the lane rows in slot order by prefix sum
   if (P.lanes > 0) {
