@@ -247,6 +247,18 @@ int uv_sample(const void* x, int x_dtype, int64_t x_stride, int B, int V, int pr
               float cap_c, float temperature, float top_p, const float* u, uint64_t seed, const int64_t* row_keys,
               const int64_t* steps, int64_t* tok_out, float* logp_out, int64_t* inc_a, int64_t* inc_b, void* stream);
 
+/* GEMM on the tcgen05 tensor cores with TMEM accumulators and TMA operand tiles (bf16 only; K % 64 == 0; A (M, K)
+ * row stride lda, W (N, K) row stride ldw, 16-byte aligned rows).  The tensor maps are encoded on the host at every
+ * call (driver entry point cuTensorMapEncodeTiled): nothing is cached, nothing is allocated.
+ *   uv_gemm_tc:        C (M, N) = A . W^T, N % 64 == 0
+ *   uv_gemm_tc_swiglu: act (M, f) = silu(A . Wg^T) * (A . Wu^T) with w_gu = [Wg ; Wu] (2f, K) contiguous, f % 32 == 0;
+ *                      same rounding points as library GEMM + uv_swiglu
+ * status: optional device word, bit 2 is set if a bounded wait inside the kernel ran out (output then undefined). */
+int uv_gemm_tc(const void* a, int64_t lda, const void* w, int64_t ldw, void* c, int64_t ldc, int dtype, int M, int N,
+               int K, int* status, void* stream);
+int uv_gemm_tc_swiglu(const void* a, int64_t lda, const void* w_gu, void* act, int dtype, int M, int K, int f,
+                      int* status, void* stream);
+
 /* ---------------------------------------------------------------------------------------------------------------
  * (a) GPU-resident continuous-batching scheduler.  Replaces the host loops of StreamGen.chunk / _refill / _park
  * (scripts/rl_stream.py:76-147) and generate_continuous (ultraviolet/model.py:1266-1354): one single-CTA kernel per

@@ -91,6 +91,10 @@ SIGNATURES = {
     "uv_swiglu": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_int, C.c_void_p]),
     "uv_gemm_qkv": (C.c_int, [C.c_void_p, C.c_int64] + [C.c_void_p] * 13 + [C.c_int, C.c_int64] + [C.c_int] * 10
                     + [C.c_void_p]),
+    "uv_gemm_tc": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_int, C.c_int,
+                             C.c_int, C.c_int, C.c_void_p, C.c_void_p]),
+    "uv_gemm_tc_swiglu": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int,
+                                    C.c_void_p, C.c_void_p]),
     "uv_gemm_swiglu": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int,
                                  C.c_void_p]),
     "uv_gemm_resid_norm": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p,
