@@ -191,3 +191,43 @@ def test_prefill_lanes_feed_every_prompt_once_and_change_no_output(B, L, chunk, 
             assert [p for p, _ in fed[i]] == list(range(len(want))), i
             assert [t for _, t in fed[i]] == want, i
     assert steps1 < steps0                                            # (5)
+
+
+def test_harvest_packed_is_the_same_payload_on_the_device():
+    """harvest_packed() hands the finished rollouts over as device tensors (flat tokens / log-probs + offsets);
+    harvest() is its host view."""
+    from ultraviolet_b200.scheduler import GpuScheduler
+    r = np.random.default_rng(5)
+    n, B = 30, 6
+    prompts = [r.integers(1, 1000, r.integers(1, 6)).tolist() for _ in range(n)]
+    limits = r.integers(1, 9, n).tolist()
+
+    def drive(packed):
+        st, eng = _FakeState(B, 24), _FakeEngine(B)
+        sch = GpuScheduler(eng, st, max_new=9, temperature=1.0, eos_id=0, q_cap=64, max_prompt=8, use_graph=False)
+        sch.enqueue(prompts, limits=limits)
+        sch._sched_step()
+        sch._primed = True
+        out = []
+        for _ in range(120):
+            req, gen = sch.req.cpu().numpy(), sch.gen.cpu().numpy()
+            eng._s["tok"].copy_(torch.from_numpy(_fake_token(req.astype(np.int64), gen.astype(np.int64), 6)
+                                                 .astype(np.int64)))
+            eng._s["logp"].copy_(torch.from_numpy((-(req + 1) - gen / 100).astype(np.float32)))
+            sch._sched_step()
+            if packed:
+                p = sch.harvest_packed()
+                if p is not None:
+                    assert p["tokens"].is_cuda and p["logp"].is_cuda and p["offsets"].is_cuda
+                    assert p["tokens"].dtype == torch.int32 and p["offsets"][0] == 0
+                    assert int(p["offsets"][-1]) == p["tokens"].numel() == p["logp"].numel()
+                    off = p["offsets"].cpu().numpy()
+                    t, l = p["tokens"].cpu().numpy(), p["logp"].cpu().numpy()
+                    out += [(m, t[off[i]:off[i + 1]].tolist(), l[off[i]:off[i + 1]].tolist(), int(p["versions"][i]))
+                            for i, m in enumerate(p["metas"])]
+            else:
+                out += [(m, t, l.tolist(), v) for m, t, l, v in sch.harvest()]
+        return out
+
+    a, b = drive(False), drive(True)
+    assert len(a) == n and a == b

@@ -190,12 +190,15 @@ class GpuScheduler:
                     active=int(c[CTL_ACTIVE]), status=int(c[CTL_STATUS]), steps=int(c[CTL_STEPS]),
                     generated=int(c[CTL_GENERATED]), slot_steps=int(c[CTL_SLOT_STEPS]))
 
-    def harvest(self):
-        """Return the requests that finished since the last call as [(meta, tokens list, logp float32 array,
-        start_version)] in finishing order (one small D2H for the counters, one gather + D2H for the payload)."""
+    def harvest_packed(self):
+        """Finished requests since the last call as DEVICE tensors (the packed hand-off a trainer consumes without a
+        host round trip of the payload; role of perf.py:55-95's packed micro-batches): dict with ``tokens`` int32 and
+        ``logp`` fp32 (total,), ``offsets`` int64 (n + 1,) delimiting each request's span, ``versions`` int32 (n,),
+        ``requests`` int64 (n,) request indices in finishing order, and ``metas`` (host list).  One small D2H (the
+        finished count and the span lengths' total); None when nothing finished."""
         fin = int(self.ctl[CTL_FIN].item())
         if fin == self.n_harvested:
-            return []
+            return None
         k = torch.arange(self.n_harvested, fin, device=self.dev) % self.q_cap
         rid = self.fin_ring[k].long()
         ri = rid % self.q_cap
@@ -205,18 +208,26 @@ class GpuScheduler:
         seg = torch.repeat_interleave(torch.arange(rid.numel(), device=self.dev), lens, output_size=total)
         within = torch.arange(total, device=self.dev) - (ends - lens)[seg]
         flat = (offs[seg] + within) % self.out_cap
-        toks = self.out_tok[flat].cpu().numpy()
-        lps = self.out_lp[flat].cpu().numpy()
-        rid_h, lens_h, ver_h = rid.cpu().numpy(), lens.cpu().numpy(), ver.cpu().numpy()
-        out, o = [], 0
-        for r, n, v in zip(rid_h.tolist(), lens_h.tolist(), ver_h.tolist()):
-            out.append((self.meta.pop(r), toks[o:o + n].tolist(), lps[o:o + n].copy(), int(v)))
+        rid_h = rid.cpu().tolist()
+        metas = [self.meta.pop(r) for r in rid_h]
+        for r in rid_h:
             self._span.pop(r, None)
-            o += n
         self.n_harvested = fin
         while self._oldest < self.n_enqueued and self._oldest not in self._span:
             self._oldest += 1
-        return out
+        return dict(tokens=self.out_tok[flat], logp=self.out_lp[flat],
+                    offsets=torch.cat([ends.new_zeros(1), ends]), versions=ver, requests=rid, metas=metas)
+
+    def harvest(self):
+        """Return the requests that finished since the last call as [(meta, tokens list, logp float32 array,
+        start_version)] in finishing order (one small D2H for the counters, one gather + D2H for the payload)."""
+        p = self.harvest_packed()
+        if p is None:
+            return []
+        toks, lps = p["tokens"].cpu().numpy(), p["logp"].cpu().numpy()
+        off, ver_h = p["offsets"].cpu().numpy(), p["versions"].cpu().numpy()
+        return [(m, toks[off[i]:off[i + 1]].tolist(), lps[off[i]:off[i + 1]].copy(), int(ver_h[i]))
+                for i, m in enumerate(p["metas"])]
 
     def n_active(self) -> int:
         return int(self.ctl[CTL_ACTIVE].item())
