@@ -108,12 +108,15 @@ def build_model(device, dtype):
     return m.to(device).to(dtype).fuse_for_inference(dtype)
 
 
-def attn_bytes(pos, starts, window):
+def attn_bytes(pos, starts, window, S=None, ring=False):
+    """Algorithmic bytes of one attention launch: 132 per attended key + q in and out."""
     p, s = np.asarray(pos, np.int64), np.asarray(starts, np.int64)
     lo = np.maximum(s, 0)
     if window:
         lo = np.maximum(lo, p - window + 1)
-    return int((p + 1 - lo).sum()) * 132 + 2 * len(p) * 8 * 64 * 2
+    if ring and S:
+        lo = np.maximum(lo, p - S + 1)
+    return int(np.maximum(p + 1 - lo, 0).sum()) * 132 + 2 * len(p) * 8 * 64 * 2
 
 
 def graph_ms(body, reps=5):
@@ -139,44 +142,67 @@ def graph_ms(body, reps=5):
 
 
 def time_attention_layers(eng, st, pos, starts, rounds=4):
-    """Average device time of one decode-attention launch over the cache state of the run, per layer kind.  Each
-    round first overwrites a 256 MB buffer (L2 flush, timed alone and subtracted) so the KV bytes come from HBM as
-    they do inside a real step, where 100 MB of weights pass through L2 between two visits of a layer's cache."""
+    """Average device time of one decode-attention launch at the cache state of the run, per layer kind, exactly as
+    the step issues it (XSA + precomputed head gates in the epilogue).  The run's own layer caches plus clones of
+    them -- together more than L2 holds -- are visited in turn inside one CUDA graph, so every launch reads its KV
+    bytes from HBM as it does inside a real step (where 100 MB of weights pass through L2 between two visits of a
+    layer's cache).  No flush, no subtraction: graph time / launches."""
     import torch
-    from ultraviolet_b200.kernels.decode_attn import attn_launch, default_splits
+    from ultraviolet_b200 import _lib
+    from ultraviolet_b200.kernels.decode_attn import attn_args, attn_launch, default_splits
     cfg, B = eng.cfg, st.B
     s = eng.scratch(B)
     qkv3 = s["qkv"].view(B, cfg.n_heads + 2 * cfg.n_kv_heads, cfg.head_dim)
     q, out = qkv3[:, :cfg.n_heads], s["z"].view(B, cfg.n_heads, cfg.head_dim)
-    flush = torch.empty(256 << 20, dtype=torch.int8, device=eng.device)
-    t_flush = graph_ms(lambda: [flush.zero_() for _ in range(rounds)])
+    v_cur = qkv3[:, cfg.n_heads + cfg.n_kv_heads:]
+    gates = s["gate"]
     res = {}
     for kind in ("global", "local"):
         layers = [l for l in range(cfg.n_layers) if cfg.is_global(l) == (kind == "global")]
         S = st.k[layers[0]].size(2)
-        splits = default_splits(B * cfg.n_kv_heads, S, eng.device)
+        ctx = S if kind == "local" else min(int(pos.max().item()) + 1, S)
+        splits = default_splits(B * cfg.n_kv_heads, ctx, eng.device)
         window, ring = (0, False) if kind == "global" else (cfg.window, True)
         ws = eng._workspace(s, B, splits)
+        bufs = [(st.k[l], st.v[l], st.k_scale[l], st.v_scale[l]) for l in layers]
+        per = sum(t.numel() * t.element_size() for t in bufs[0])
+        while per * len(bufs) < (160 << 20):
+            # clones keep the padded row allocation of the originals (slices of a clone of the full storage)
+            k0, v0, ks0, vs0 = bufs[len(bufs) % len(layers)]
+            bufs.append(tuple(_clone_like(t) for t in (k0, v0, ks0, vs0)))
+        kw = dict(v_cur=v_cur, xsa_alpha=eng.xsa[layers[0]] if cfg.xsa else None, xsa_eps=cfg.xsa_eps,
+                  gate_vals=gates if cfg.gate_channels else None, counters=s["counters"], status=s["status"])
 
         def run():
             for _ in range(rounds):
-                flush.zero_()
-                for l in layers:
-                    attn_launch(q, st.k[l], st.v[l], pos, starts, cfg.attn_scale, window, ring, st.k_scale[l],
-                                st.v_scale[l], splits, out, ws, counters=s["counters"])
-        ms = max(graph_ms(run) - t_flush, 1e-6) / (rounds * len(layers))
-        byt = attn_bytes(pos.cpu().numpy(), starts.cpu().numpy(), window)
+                for k, v, ks, vs in bufs:
+                    attn_launch(q, k, v, pos, starts, cfg.attn_scale, window, ring, ks, vs, splits, out, ws, **kw)
+        ms = graph_ms(run) / (rounds * len(bufs))
+        byt = attn_bytes(pos.cpu().numpy(), starts.cpu().numpy(), window if kind == "local" else 0, S, ring)
+        a = attn_args(q, *bufs[0][:2], pos, starts, cfg.attn_scale, window, ring, *bufs[0][2:], splits, out, ws)
+        path = "bulk-copy (TMA) tiles" if _lib.lib().uv_decode_attn_uses_bulk(a) == 1 else "cp.async tiles"
         res[kind] = {"ms": ms, "bytes": byt, "gbs": byt / ms / 1e6, "launches_per_step": len(layers),
-                     "splits": splits}
+                     "splits": splits, "slots_per_row": S, "path": path, "cache_copies_visited": len(bufs)}
     return res
 
 
-def long_context_attention(eng, rounds=4):
+def _clone_like(t):
+    """A copy of a (B, K, S, ...) cache tensor inside an allocation with the same (possibly padded) row length."""
+    import torch
+    inner = t.stride(2)
+    alloc = t.stride(1) // inner
+    full = torch.empty((t.size(0), t.size(1), alloc) + tuple(t.shape[3:]), dtype=t.dtype, device=t.device)
+    out = full[:, :, :t.size(2)]
+    out.copy_(t)
+    return out
+
+
+def long_context_attention(eng, rounds=4, ctx=8192):
     """The long-context stress shape: 64 sequences with 8192 int8 keys each, one global-layer launch per cache copy
     (three 69 MB copies visited in turn: more than L2 holds), captured in a CUDA graph."""
     import torch
     from ultraviolet_b200.kernels.decode_attn import attn_launch, default_splits, workspace_for
-    dev, B, S, ctx, H, hd = eng.device, 64, 8448, 8192, 8, 64
+    dev, B, S, H, hd = eng.device, 64, ctx + 256, 8, 64
     g = torch.Generator(device=dev).manual_seed(1)
     bufs = []
     for _ in range(3):
@@ -235,9 +261,17 @@ def step_shape_attention(eng, rounds=4):
     return {"ms": ms, "bytes": byt, "gbs": byt / ms / 1e6, "splits": 1}
 
 
-def cpu_decode_tokens_per_s(n_steps: int, slots: int = SLOTS, ctx: int = 160, seed: int = 0):
-    """The oracle's (numpy, fp32) int8-KV decode step on the host cores: `slots` sequences at context ~ctx, n_steps
-    steps.  Returns (tokens/s, seconds, threads)."""
+def workload_config(K: int) -> dict:
+    """The workload both arms run (identical dictionaries in the two JSON lines)."""
+    return {"workload": "UV-50M fixed-batch decode (BASELINE configs[1]): 256 sequences/GPU, prompts U[32,128] of "
+                        "uniform token ids, greedy, int8 KV, decode steps after prefill (step = 256 tokens/GPU)",
+            "slots_per_gpu": SLOTS, "vocab": VOCAB, "weights": "random init seed 0",
+            "prompts": "numpy default_rng(100 + rank): lengths then ids"}
+
+
+def port_decode_tokens_per_s(n_steps: int, slots: int = SLOTS, ctx: int = 160, seed: int = 0):
+    """Fallback when oracle/_ref is not installed: the numpy restatement's int8-KV decode step on the host cores
+    (random-filled cache at context ~ctx).  Returns (tokens/s, seconds, threads)."""
     import torch
     from oracle import model as om
     from ultraviolet_b200.model import MathLM, make_config
@@ -262,23 +296,69 @@ def cpu_decode_tokens_per_s(n_steps: int, slots: int = SLOTS, ctx: int = 160, se
     return slots * n_steps / dt, dt, os.cpu_count()
 
 
+def cpu_baseline(n_steps: int, warmup: int = 1) -> dict:
+    """The reference's own CPU decode route (oracle/_ref: MathLM prefill + decode_step_fast with the attention call
+    bound to decode_attention_ref, fp32 torch, every host thread) on the GPU arm's rank-0 prompts; the numpy port
+    only when the reference is not installed.  Returns the cpu_baseline object plus seconds per step."""
+    from oracle import ref_arm
+    if ref_arm.available():
+        r = ref_arm.cpu_decode(make_prompts(SLOTS, PROMPT_LO, PROMPT_HI, seed=100), n_steps, warmup, vocab=VOCAB)
+        return {"value": r["tokens_per_s"], "unit": "tokens/s", "cores": r["threads"], "kind": "reference",
+                "sample": f"{n_steps} greedy decode steps of the same 256 prompts after the reference's own prefill "
+                          f"({r['prefill_s']:.1f} s, not timed), mean context {r['context']:.0f}: ultraviolet "
+                          "decode_step_fast + decode_attention_ref, fp32 torch on "
+                          f"{r['threads']} threads ({r['seconds']:.1f} s timed)",
+                "ms_per_step": r["seconds"] / n_steps * 1e3}
+    v, dt, threads = port_decode_tokens_per_s(n_steps)
+    return {"value": v, "unit": "tokens/s", "cores": threads, "kind": "port",
+            "sample": f"{n_steps} decode steps of 256 sequences at context ~160 (numpy fp32 restatement, BLAS threads; "
+                      f"oracle/_ref not installed) ({dt:.1f} s)", "ms_per_step": dt / n_steps * 1e3}
+
+
+def reference_gpu_attention() -> dict:
+    """Second comparator: the reference's own GPU kernels (Triton, NVRTC) for the attention step on this GPU."""
+    try:
+        import torch
+        from oracle import ref_arm
+        if not (torch.cuda.is_available() and ref_arm.available()):
+            return {"unavailable": "no CUDA device or oracle/_ref not installed"}
+        torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", 0)))
+        return ref_arm.gpu_attention()
+    except Exception as e:  # noqa: BLE001
+        return {"unavailable": f"{type(e).__name__}: {str(e)[:300]}"}
+
+
+def reference_gpu_attention_subprocess(timeout_s: int = 300) -> dict:
+    """The same, run as `bench.py --impl reference --reference-gpu-only` in a child process so that a kernel of the
+    reference that fails to compile or run here cannot take this process down."""
+    try:
+        r = subprocess.run([sys.executable, os.path.abspath(__file__), "--impl", "reference", "--reference-gpu-only"],
+                           capture_output=True, text=True, timeout=timeout_s)
+        for ln in reversed(r.stdout.strip().splitlines()):
+            if ln.startswith("{"):
+                return json.loads(ln)
+        return {"unavailable": f"no output (rc {r.returncode}): {r.stderr[-300:]}"}
+    except Exception as e:  # noqa: BLE001
+        return {"unavailable": f"{type(e).__name__}: {str(e)[:200]}"}
+
+
 def run_reference_arm(args, rank, world):
+    """`--impl reference`: the reference's own CPU implementation of the path on the host cores (rank 0 only)."""
     if rank != 0:
         return
-    steps = max(1, min(args.steps, 64))  # bounded sample: ~15 s of host work at most
-    for _ in range(max(0, min(args.warmup, 1))):
-        cpu_decode_tokens_per_s(1)
-    v, dt, threads = cpu_decode_tokens_per_s(steps)
+    if args.reference_gpu_only:
+        print(json.dumps(reference_gpu_attention()), flush=True)
+        return
+    steps = max(1, min(args.steps, 64))  # bounded sample: the timed part stays within ~10 s of host work
+    cb = cpu_baseline(steps, warmup=max(1, min(args.warmup, 3)))
+    v = cb["value"]
     line = {"impl": "reference", "metric": "rollout decode tokens/s", "value": v, "unit": "tokens/s",
-            "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / steps * 1e3,
+            "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": cb.pop("ms_per_step"),
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp32", "data": "synthetic",
-            "config": {"workload": "fixed-batch decode, UV-50M, 256 sequences, int8 KV, greedy", "slots": SLOTS,
-                       "note": "the reference is Python and cannot travel; this arm times the numpy restatement of "
-                               "its CPU path (oracle/) on the host cores"},
-            "cpu_baseline": {"value": v, "unit": "tokens/s", "cores": threads, "kind": "port",
-                             "sample": f"{steps} decode steps of 256 sequences at context ~160 (numpy fp32, all "
-                                       "host threads via BLAS)"},
+            "config": workload_config(args.steps), "cpu_baseline": cb,
             "e2e": {"value": v, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    if args.reference_gpu:
+        line["attention_reference_gpu"] = reference_gpu_attention()
     print(json.dumps(line), flush=True)
 
 
@@ -358,6 +438,10 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="fixed", choices=["fixed", "continuous", "attn"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--reference-gpu", action="store_true",
+                    help="with --impl reference: also time the reference's Triton / NVRTC attention kernels on the GPU")
+    ap.add_argument("--reference-gpu-only", action="store_true",
+                    help="with --impl reference: print only that GPU comparator object")
     ap.add_argument("--lanes", type=int, default=128,
                     help="continuous workload: extra batch rows that carry prompt tokens of refilling slots (0 = "
                          "one prompt token per slot per step)")
@@ -405,11 +489,15 @@ def main():
     t_bcast = uvdist.broadcast_weights(eng) if world > 1 else 0.0
 
     K, W = args.steps, max(args.warmup, 3)
+    R = 5 if K <= 128 else 1   # short runs: the K-step block is timed R times back to back, the median is reported
     prompts = make_prompts(SLOTS, PROMPT_LO, PROMPT_HI, seed=100 + rank)
-    max_len = PROMPT_HI + K + W + min(K, 64) + 16
+    # cache sized like production (max_prompt + max_new + slack, never below the configuration's 128 + 512): local
+    # layers then keep their full 256-slot ring whatever --steps is
+    max_len = max(PROMPT_HI + R * K + W + min(K, 64) + 16, PROMPT_HI + 512)
     st = m.new_state(SLOTS, max_len)
     from ultraviolet_b200.generate import _left_pad
     idx, starts = _left_pad(prompts, 0, dev)
+    torch.cuda.synchronize()
     t0 = time.perf_counter()
     m.prefill(idx[:, :-1], starts, st)
     torch.cuda.synchronize()
@@ -421,25 +509,27 @@ def main():
     torch.cuda.synchronize()
     pos_begin = st.pos.clone()
 
-    # ---- timed region: K decode steps, device resident
-    if world > 1:
-        dist.barrier()
-    torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    # ---- timed region: K decode steps, device resident (R such blocks, each bracketed; median block reported)
     all_tok = torch.empty(K, SLOTS, dtype=torch.long, device=dev)
+    block_ms = []
     with ClockSampler(local) as clk:
-        e0.record()
-        for i in range(K):
-            tok = runner.step(tok)
-            all_tok[i].copy_(tok)
-        e1.record()
-        torch.cuda.synchronize()
-    ms = e0.elapsed_time(e1)
-    if world > 1:
-        t = torch.tensor([ms], device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t.item())
-        dist.barrier()
+        for _ in range(R):
+            if world > 1:
+                dist.barrier()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for i in range(K):
+                tok = runner.step(tok)
+                all_tok[i].copy_(tok)
+            e1.record()
+            torch.cuda.synchronize()
+            t = torch.tensor([e0.elapsed_time(e1)], device=dev)
+            if world > 1:
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                dist.barrier()
+            block_ms.append(float(t.item()))
+    ms = float(np.median(block_ms))
     value = world * SLOTS * K / (ms / 1e3)
 
     # ---- rollout gather (token ids of every rank to rank 0)
@@ -477,42 +567,46 @@ def main():
     att = time_attention_layers(eng, st, st.pos - 1, st.starts)
     att_mid = att["local"] if att["local"]["ms"] * 8 >= att["global"]["ms"] * 2 else att["global"]
     lc = long_context_attention(eng)
+    lc2 = long_context_attention(eng, ctx=16384)
     # bytes one decode step must move: weights once (99.6 MB bf16) + KV reads + KV appends (132 B per row per layer)
-    kv_read = sum(attn_bytes((st.pos - 1).cpu().numpy(), st.starts.cpu().numpy(),
-                             0 if eng.cfg.is_global(l) else eng.cfg.window) for l in range(eng.cfg.n_layers))
+    kv_read = 8 * att["local"]["bytes"] + 2 * att["global"]["bytes"]
     step_bytes = 99_614_720 + kv_read + SLOTS * 10 * 132
+    status = eng.check_status(SLOTS)
     line = {
         "metric": "rollout decode tokens/s", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": K,
         "warmup": W, "ms_per_step": ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": "UV-50M fixed-batch decode: 256 sequences/GPU, prompts U[32,128], greedy, int8 KV, "
-                               f"{K} decode steps after prefill (step = 256 tokens/GPU)",
-                   "slots_per_gpu": SLOTS, "vocab": VOCAB, "weights": "random init seed 0, bf16",
-                   "l2": "per-step working set (99.6 MB weights + KV of 10 layers) exceeds L2; no flush",
-                   "prefill_s": prefill_s, "context_begin": int(pos_begin.float().mean().item()),
-                   "context_end": int(st.pos.float().mean().item()),
-                   "weight_broadcast_ms": t_bcast * 1e3, "rollout_gather_ms": t_gather * 1e3,
-                   "step_bytes_floor": step_bytes,
-                   "step_hbm_frac": step_bytes / (ms / K / 1e3) / 1e9 / hbm_peak},
+        "dtype": "bf16", "data": "synthetic", "config": workload_config(K),
+        "run": {"timed_blocks_ms": block_ms, "timed": f"median of {R} blocks of {K} steps", "max_len": max_len,
+                "l2": "per-step working set (99.6 MB weights + KV of 10 layers) exceeds L2; no flush",
+                "prefill_s": prefill_s, "prefill_tokens": int(sum(len(p) - 1 for p in prompts)),
+                "context_begin": int(pos_begin.float().mean().item()),
+                "context_end": int(st.pos.float().mean().item()),
+                "weight_broadcast_ms": t_bcast * 1e3, "rollout_gather_ms": t_gather * 1e3,
+                "step_bytes_floor": step_bytes,
+                "step_hbm_frac": step_bytes / (ms / K / 1e3) / 1e9 / hbm_peak,
+                "launches_per_step": eng.launches_per_step() + 1, "device_status": status},
         "e2e": {"value": e2e, "unit": "tokens/s", "h2d_bytes_per_step": SLOTS * 8, "d2h_bytes_per_step": SLOTS * 8,
                 "steps": K2},
-        "gpu_launches": (1 + 5 * eng.cfg.n_layers + 1) * K,
+        "gpu_launches": (eng.launches_per_step() + 1) * K,
         "clocks": clk.summary(),
         "roofline": {"bound": "hbm", "kernel": "attn_split_kernel (local-layer launches, 8 per step)"
                      if att_mid is att["local"] else "attn_split_kernel (global-layer launches, 2 per step)",
                      "achieved": att_mid["gbs"], "peak": hbm_peak, "peak_kind": peak_kind, "unit": "GB/s",
                      "frac": att_mid["gbs"] / hbm_peak,
                      "traffic": att_mid["bytes"] * NCU_TRAFFIC_RATIO["step"],
-                     "bytes_per_launch": att_mid["bytes"], "ms_per_launch": att_mid["ms"]},
+                     "traffic_source": "algorithmic bytes x 0.993, the DRAM-bytes / algorithmic-bytes ratio of the "
+                                       "ncu capture of this launch shape (profiles/attn_split_kernel_step_shape.md)",
+                     "bytes_per_launch": att_mid["bytes"], "ms_per_launch": att_mid["ms"], "path": att_mid["path"]},
         "attention": {"local": att["local"], "global": att["global"], "long_context_64x8192": lc,
                       "long_context_frac_of_measured": lc["gbs"] / hbm_peak,
-                      "long_context_frac_of_nominal_8TBs": lc["gbs"] / 8000.0},
+                      "long_context_frac_of_nominal_8TBs": lc["gbs"] / 8000.0,
+                      "long_context_64x16384": lc2, "long_context_64x16384_frac_of_measured": lc2["gbs"] / hbm_peak},
     }
-    if not args.no_cpu_baseline:
-        v, dt, threads = cpu_decode_tokens_per_s(48)  # ~10 s of host work
-        line["cpu_baseline"] = {"value": v, "unit": "tokens/s", "cores": threads, "kind": "port",
-                                "sample": "48 decode steps of 256 sequences at context ~160-210, numpy fp32 oracle, all "
-                                          f"host threads via BLAS ({dt:.1f} s)"}
+    if not args.no_cpu_baseline and world == 1:
+        cb = cpu_baseline(32)  # the reference's prefill (~10 s) + ~3 s of timed steps on the host cores
+        cb.pop("ms_per_step", None)
+        line["cpu_baseline"] = cb
+        line["attention"]["reference_gpu"] = reference_gpu_attention_subprocess()
     print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()

@@ -102,7 +102,8 @@ typedef struct uv_attn_args {
   int64_t sob, soh;
   int B, H, KH, hd, S;
   int S_alloc;            /* slots allocated per (b, kv head) row, 0 = S.  A linear (non-ring) cache whose rows are
-                             allocated to a multiple of 8 slots takes the TMA path even when S itself is not */
+                             allocated to a multiple of 8 slots takes the TMA path even when S itself is not; a ring
+                             takes it when S is a multiple of 8 */
   int window, ring;
   float scale;
   int num_splits;         /* >= 1.  2..8 splits of a row run as one thread-block cluster and merge through distributed
@@ -133,6 +134,12 @@ size_t uv_decode_attn_workspace_bytes(int B, int KH, int G, int hd, int num_spli
  * most 8 splits (the cluster merge) unless the batch is so small that 8 per row leave most SMs idle. */
 int uv_default_splits(int n_bk, int ctx, int n_sm);
 int uv_decode_attn(const uv_attn_args* args, void* stream);
+/* Which copy path uv_decode_attn takes for these arguments: 1 = bulk-copy (TMA) tiles (linear rows allocated to a
+ * multiple of 8 slots, or a ring whose length is a multiple of 8; 16-byte aligned rows and scale rows), 0 = the
+ * two-stage cp.async path that every other geometry takes; negative = argument error.  Launches nothing.  (The
+ * reference picks its backend the same way, from tensor metadata: decode_attn_cuda.supported, decode_attn_cuda.py:
+ * 262-268.) */
+int uv_decode_attn_uses_bulk(const uv_attn_args* args);
 
 /* uv_decode_attn_static: the same attention, for hosts that cannot allocate device memory.  (No counterpart in the
  * reference: its Python op allocates split partials with torch.empty on every call.)
@@ -246,6 +253,14 @@ int uv_gemm_resid_norm(const void* a, int64_t lda, const void* w, int K, const v
 int uv_sample(const void* x, int x_dtype, int64_t x_stride, int B, int V, int precapped, float cap_a, float cap_b,
               float cap_c, float temperature, float top_p, const float* u, uint64_t seed, const int64_t* row_keys,
               const int64_t* steps, int64_t* tok_out, float* logp_out, int64_t* inc_a, int64_t* inc_b, void* stream);
+/* uv_sample_topk: uv_sample with the top_k filter of sample() (ultraviolet/model.py:1201-1203) applied before the
+ * nucleus: only the top_k largest logits of a row (ties with the k-th kept) can be drawn, and top_p then acts on
+ * that renormalised set.  top_k = 0: no limit (uv_sample is this call with top_k = 0).  logp stays the log-softmax
+ * over the full vocabulary. */
+int uv_sample_topk(const void* x, int x_dtype, int64_t x_stride, int B, int V, int precapped, float cap_a, float cap_b,
+                   float cap_c, float temperature, int top_k, float top_p, const float* u, uint64_t seed,
+                   const int64_t* row_keys, const int64_t* steps, int64_t* tok_out, float* logp_out, int64_t* inc_a,
+                   int64_t* inc_b, void* stream);
 
 /* GEMM on the tcgen05 tensor cores with TMEM accumulators and TMA operand tiles (bf16 only; K % 64 == 0; A (M, K)
  * row stride lda, W (N, K) row stride ldw, 16-byte aligned rows).  The tensor maps are encoded on the host at every

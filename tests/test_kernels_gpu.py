@@ -143,6 +143,36 @@ def test_attention_grid_int8(name, splits):
     np.testing.assert_allclose(out.float().cpu().numpy(), g[name], atol=2e-3, rtol=2e-3)
 
 
+# Ring lengths that are not a multiple of the 128-key tile: multiples of 8 stay on the bulk-copy path (the tile that
+# crosses slot S - 1 arrives in two pieces), the others take the two-stage cp.async path.  Positions wrap the ring
+# several times (reference grid: tests/test_math_kernels.py:55-70).
+@pytest.mark.parametrize("splits", [1, 2, None])
+@pytest.mark.parametrize("S,bulk", [(136, 1), (192, 1), (200, 1), (104, 1), (8, 1), (100, 0), (189, 0), (255, 0)])
+def test_attention_ring_lengths(S, bulk, splits):
+    import ctypes as C
+    from ultraviolet_b200 import _lib
+    from ultraviolet_b200.kernels import decode_attention
+    from ultraviolet_b200.kernels.decode_attn import attn_args
+    r = np.random.default_rng(S)
+    B, H, hd = 12, 8, 64
+    k = r.standard_normal((B, 1, S, hd)).astype(np.float32)
+    v = r.standard_normal((B, 1, S, hd)).astype(np.float32)
+    kq, ks = okv.quantize_kv(k)
+    vq, vs = okv.quantize_kv(v)
+    pos = np.concatenate([[0, S - 1, S, S + 1, 2 * S - 1, 2 * S, 5 * S + 3], r.integers(0, 6 * S, B - 7)]).astype(np.int64)
+    starts = np.where(r.random(B) < 0.5, 0, np.maximum(pos - r.integers(0, S, B), 0)).astype(np.int64)
+    window = S - 3 if S > 16 else S
+    q = T(r.standard_normal((B, H, hd)).astype(np.float32), torch.float16)
+    tk, tv, tks, tvs = T(kq), T(vq), T(ks), T(vs)
+    out = decode_attention(q, tk, tv, T(pos), T(starts), 0.14125, window=window, ring=True, k_scale=tks, v_scale=tvs,
+                           num_splits=splits)
+    ref = oattn.decode_attention_ref(q.float().cpu().numpy(), kq, vq, pos, starts, 0.14125, window=window, ring=True,
+                                     k_scale=ks, v_scale=vs)
+    np.testing.assert_allclose(out.float().cpu().numpy(), ref, atol=2e-3, rtol=2e-3)
+    a = attn_args(q, tk, tv, T(pos), T(starts), 0.14125, window, True, tks, tvs, 1, out)
+    assert _lib.lib().uv_decode_attn_uses_bulk(C.byref(a)) == bulk
+
+
 def test_attention_q_view_and_bf16():
     from ultraviolet_b200.kernels import decode_attention
     c = gi.attn_cases()["uv.global"]
@@ -209,10 +239,18 @@ def _sample(x, **kw):
     lp = torch.empty(B, dtype=torch.float32, device=DEV)
     p = lambda t: None if t is None else t.data_ptr()
     cap = kw.get("cap", (23.0, 5.0, 7.5))
-    rc = _lib.lib().uv_sample(x.data_ptr(), DTYPE_CODE[x.dtype], x.stride(0), B, V, int(kw.get("precapped", False)),
-                              cap[0], cap[1], cap[2], kw.get("T", 1.0), kw.get("top_p", 1.0), p(kw.get("u")),
-                              C.c_uint64(kw.get("seed", 0)), p(kw.get("row_keys")), p(kw.get("steps")),
-                              tok.data_ptr(), lp.data_ptr(), None, None, stream_ptr(torch.device(DEV)))
+    if "top_k" in kw:
+        rc = _lib.lib().uv_sample_topk(x.data_ptr(), DTYPE_CODE[x.dtype], x.stride(0), B, V,
+                                       int(kw.get("precapped", False)), cap[0], cap[1], cap[2], kw.get("T", 1.0),
+                                       int(kw["top_k"]), kw.get("top_p", 1.0), p(kw.get("u")),
+                                       C.c_uint64(kw.get("seed", 0)), p(kw.get("row_keys")), p(kw.get("steps")),
+                                       tok.data_ptr(), lp.data_ptr(), None, None, stream_ptr(torch.device(DEV)))
+    else:
+        rc = _lib.lib().uv_sample(x.data_ptr(), DTYPE_CODE[x.dtype], x.stride(0), B, V,
+                                  int(kw.get("precapped", False)), cap[0], cap[1], cap[2], kw.get("T", 1.0),
+                                  kw.get("top_p", 1.0), p(kw.get("u")), C.c_uint64(kw.get("seed", 0)),
+                                  p(kw.get("row_keys")), p(kw.get("steps")), tok.data_ptr(), lp.data_ptr(), None,
+                                  None, stream_ptr(torch.device(DEV)))
     _lib.check(rc, "uv_sample")
     return tok.cpu().numpy(), lp.cpu().numpy()
 
@@ -279,6 +317,39 @@ def test_sampler_distribution_and_top_p():
     assert nucleus[np.unique(tok)].all()                       # never outside the reference's nucleus
     assert set(np.flatnonzero(nucleus & (p > 1e-3))) <= set(np.unique(tok))
     np.testing.assert_allclose(lp, np.log(p[tok]), atol=3e-5)  # log-prob stays untruncated
+
+
+def test_top_k_support_and_renormalised_nucleus():
+    """top_k of sample() (ultraviolet/model.py:1201-1203): only the k largest logits, ties with the k-th kept, can be
+    drawn; top_p then acts on the renormalised top-k set; the log-prob stays untruncated."""
+    r = np.random.default_rng(8)
+    V, N, k, temp = 256, 1 << 14, 5, 0.9
+    row = (r.standard_normal(V) * 2).astype(np.float32)
+    order = np.argsort(-row)
+    row[order[5]] = row[order[4]]            # a tie at the k-th rank: both stay
+    x = T(np.tile(row, (N, 1)))
+    u = torch.rand(N, device=DEV, generator=torch.Generator(DEV).manual_seed(9))
+    tok, lp = _sample(x, u=u, T=temp, precapped=True, top_k=k)
+    kth = np.sort(row)[-k]
+    keep = row >= kth
+    assert keep.sum() == 6 and set(np.unique(tok)) == set(np.flatnonzero(keep))
+    p = np.exp(row.astype(np.float64) / temp)
+    p /= p.sum()
+    np.testing.assert_allclose(lp, np.log(p[tok]), atol=3e-5)
+    pk = np.where(keep, p, 0) / p[keep].sum()
+    cnt = np.bincount(tok, minlength=V)
+    from scipy import stats
+    chi = (((cnt - pk * N) ** 2 / np.maximum(pk * N, 1e-30))[keep]).sum()
+    assert stats.chi2.sf(chi, keep.sum() - 1) > 1e-3
+    # top_k then top_p: the nucleus of the renormalised top-k distribution (reference order of the two filters)
+    tok2, _ = _sample(x, u=u, T=temp, precapped=True, top_k=k, top_p=0.6)
+    masked = np.where(keep, row, -np.inf)[None]
+    nucleus = om.top_p_keep(masked, temp, 0.6)[0]
+    assert nucleus[np.unique(tok2)].all() and nucleus.sum() < keep.sum()
+    # k >= V and k = 0 are no-ops
+    a, _ = _sample(x[:64], u=u[:64], T=temp, precapped=True, top_k=0)
+    b, _ = _sample(x[:64], u=u[:64], T=temp, precapped=True, top_k=V)
+    assert np.array_equal(a, b)
 
 
 def test_philox_keyed_draws_match_oracle():

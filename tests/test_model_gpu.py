@@ -148,3 +148,51 @@ def test_patch_reference_style_object_and_weight_refresh():
     assert not torch.equal(a, b)
     unpatch_model(m)
     assert "decode_step" not in m.__dict__
+
+
+def test_device_failure_words_are_read_and_raise():
+    """The kernels flag silent failures in two device words (a cache tile copy that timed out, a skipped cache
+    write); the engine reads them.  The words are set by hand here -- no kernel is made to fail."""
+    from ultraviolet_b200 import _lib
+    from ultraviolet_b200.generate import generate
+    spec = gi.model_specs()["tiny"]
+    m = _gpu_model(spec)
+    eng = m.engine
+    out = generate(m, [[1, 2, 3], [4, 5]], 4, temperature=0.0, use_graph=False)
+    assert eng.device_status() == {"attn_status": 0, "kv_oob": 0} and len(out) == 2
+    B = next(iter(eng._scratch))
+    eng.scratch(B)["flags"][0] = 1          # attention status bit 0
+    with pytest.raises(_lib.UvError, match="status"):
+        eng.check_status()
+    assert eng.device_status() == {"attn_status": 0, "kv_oob": 0}   # raising clears the words
+    eng.scratch(B)["flags"][1] = 3          # skipped cache writes
+    with pytest.raises(_lib.UvError, match="3 KV"):
+        eng.check_status(B)
+
+
+def test_seed_rule_top_k_and_skip_attn():
+    from ultraviolet_b200.generate import DecodeRunner, generate
+    spec = gi.model_specs()["tiny"]
+    m = _gpu_model(spec)
+    prompts = [[5, 6, 7, 8], [9, 10, 11], [12, 13, 14, 15, 16]]
+    # no seed: every call draws a fresh Philox seed from torch's generator -> torch.manual_seed reproduces a call
+    # sequence, successive calls differ
+    torch.manual_seed(1)
+    a1 = generate(m, prompts, 24, temperature=1.5, use_graph=False)
+    a2 = generate(m, prompts, 24, temperature=1.5, use_graph=False)
+    torch.manual_seed(1)
+    b1 = generate(m, prompts, 24, temperature=1.5, use_graph=False)
+    assert a1 != a2 and len({tuple(r) for r in a1}) > 1
+    assert b1 == a1
+    c1 = generate(m, prompts, 24, temperature=1.5, use_graph=False, seed=17)
+    c2 = generate(m, prompts, 24, temperature=1.5, use_graph=True, seed=17)
+    assert c1 == c2
+    # top_k = 1 is greedy whatever the temperature
+    greedy = generate(m, prompts, 12, temperature=0.0, use_graph=False)
+    k1 = generate(m, prompts, 12, temperature=2.0, top_k=1, use_graph=False, seed=3)
+    assert k1 == greedy
+    # skip_attn: the profiling switch runs (attention kernel left out) and still produces tokens
+    st = m.new_state(3, 32)
+    runner = DecodeRunner(m, st, bucket=32, use_graph=False, temperature=0.0, skip_attn=True)
+    tok = runner.step(torch.tensor([1, 2, 3], device=DEV)).clone()
+    assert tok.shape == (3,) and int(st.pos[0]) == 1

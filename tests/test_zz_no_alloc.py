@@ -60,6 +60,14 @@ def test_static_scratch_entry_matches_regular_entry_twice():
         torch.cuda.synchronize()
         assert torch.isfinite(out.float()).all()
         torch.testing.assert_close(out.float(), ref.float(), atol=2e-3, rtol=2e-3)
+        # and not only against the sibling entry point: three rows against the CPU oracle on the same bytes
+        from oracle import attn as oattn
+        rows = [0, B // 2, B - 1]
+        want = oattn.decode_attention_ref(q[rows].float().cpu().numpy(), k[rows].cpu().numpy(), v[rows].cpu().numpy(),
+                                          pos[rows].cpu().numpy(), starts[rows].cpu().numpy(), 0.14125,
+                                          k_scale=ks[rows].cpu().numpy(), v_scale=vs[rows].cpu().numpy())
+        got = out[rows].float().cpu().numpy()
+        assert np.abs(got - want).max() <= 2e-2 * np.abs(want).max()   # bf16 queries and output
 
 
 def test_static_scratch_rejects_oversized_problems():

@@ -78,6 +78,7 @@ SIGNATURES = {
     "uv_decode_attn_workspace_bytes": (C.c_size_t, [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int]),
     "uv_default_splits": (C.c_int, [C.c_int, C.c_int, C.c_int]),
     "uv_decode_attn": (C.c_int, [C.POINTER(AttnArgs), C.c_void_p]),
+    "uv_decode_attn_uses_bulk": (C.c_int, [C.POINTER(AttnArgs)]),
     "uv_decode_attn_static": (C.c_int, [C.POINTER(AttnArgs), C.c_void_p]),
     "uv_embed_norm": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int64, C.c_int, C.c_void_p, C.c_void_p, C.c_int,
                                 C.c_void_p]),
@@ -101,6 +102,9 @@ SIGNATURES = {
                                      C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p]),
     "uv_sched_step": (C.c_int, [C.POINTER(SchedArgs), C.c_void_p]),
     "uv_sched_enqueue": (C.c_int, [C.POINTER(SchedArgs), C.c_int, C.c_void_p]),
+    "uv_sample_topk": (C.c_int, [C.c_void_p, C.c_int, C.c_int64, C.c_int, C.c_int, C.c_int, C.c_float, C.c_float,
+                                 C.c_float, C.c_float, C.c_int, C.c_float, C.c_void_p, C.c_uint64, C.c_void_p,
+                                 C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
     "uv_sample": (C.c_int, [C.c_void_p, C.c_int, C.c_int64, C.c_int, C.c_int, C.c_int, C.c_float, C.c_float,
                             C.c_float, C.c_float, C.c_float, C.c_void_p, C.c_uint64, C.c_void_p, C.c_void_p,
                             C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),

@@ -4,9 +4,9 @@
 // 128-key tiles aligned to multiples of 128 in position space; a split owns a contiguous run of tiles.  Tiles
 // stream HBM -> shared memory through the bulk-copy (TMA) engine into a 3-stage ring (cp.async.bulk + mbarrier
 // complete_tx), K / V / both scale vectors as four linear copies per tile, trimmed to the row's valid range at
-// 8-key granularity.  Caches whose geometry breaks the 16-byte rules of the bulk engine (row length not a multiple
-// of 8 slots, ring length not a multiple of 128, unaligned views) take a plain-load path with the same shared
-// memory layout.
+// 8-key granularity; a ring whose length is not a multiple of the tile gets the tile that crosses slot S - 1 as two
+// pieces.  Caches whose geometry breaks the 16-byte rules of the bulk engine (row or ring length not a multiple of
+// 8 slots, unaligned views) take a two-stage cp.async path with the same shared memory layout.
 //
 // Math: the G query heads of a kv group form the M rows of warp-level tensor-core tiles.
 //   S = Q K^T runs on the int8 pipe (mma.sync.m16n8k32.s8): each query head is split once per CTA into two int8
@@ -388,8 +388,17 @@ __global__ void __launch_bounds__(NTHREAD) attn_split_kernel(const __grid_consta
   __shared__ __align__(8) uint64_t bars[NSTAGE];   // "full": a tile has landed (transaction bytes)
   __shared__ __align__(8) uint64_t empty[NSTAGE];  // "empty": every consumer warp is done with the stage
 
+  __shared__ int s_dead;                            // a tile of this CTA never landed (bounded wait ran out)
+
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const bool producer = warp == NWARP;  // the copy-issuing warp never computes
+  // This CTA's split partial for the cluster merge sits behind the stage ring (and the staged q / k / v of the
+  // fused form), never inside it: peers address it at the same offset in every CTA, and a CTA that gave up on a tile
+  // can publish an empty partial without touching shared memory that an abandoned copy may still write.
+  constexpr size_t PART_OFF =
+      ((size_t)(BULK ? NSTAGE : 2) * L::BYTES + (PRE ? (size_t)(ROWS + 2) * HD * sizeof(QT) + 2 * HD + 16 : 0) + 15) &
+      ~(size_t)15;
+  float* const part = reinterpret_cast<float*>(smem + PART_OFF);
   const int r = lane >> 2, c = lane & 3;
   const int bk = blockIdx.x, sid = blockIdx.y;
   const int b = bk / P.KH, h = bk % P.KH;
@@ -473,14 +482,14 @@ __global__ void __launch_bounds__(NTHREAD) attn_split_kernel(const __grid_consta
     }
   }
 
-  if (ntile == 0) {  // empty row or inactive split
+  // An empty row, an inactive split, or a CTA whose tile copy timed out: zeros (unsplit) or an empty partial.
+  auto empty_result = [&]() {
     if (P.splits == 1) {
       for (int i = tid; i < G * HD; i += NTHREAD) {
         QT* o = static_cast<QT*>(P.out) + (int64_t)b * P.sob + (int64_t)(h * G + i / HD) * P.soh;
         o[i % HD] = from_f32<QT>(0.f);
       }
     } else if (P.cluster) {
-      float* part = reinterpret_cast<float*>(smem) + NWARP * ROWS * (HD + 2);
       if (tid < G) {
         part[G * HD + tid] = -INFINITY;
         part[G * HD + G + tid] = 0.f;
@@ -494,6 +503,9 @@ __global__ void __launch_bounds__(NTHREAD) attn_split_kernel(const __grid_consta
       }
       if (P.counters) arrive_and_merge<QT, HD>(P, bk, tid, v_stage);
     }
+  };
+  if (ntile == 0) {
+    empty_result();
     return;
   }
 
@@ -509,6 +521,7 @@ __global__ void __launch_bounds__(NTHREAD) attn_split_kernel(const __grid_consta
 
   if constexpr (BULK) {
     if (tid == 0) {
+      s_dead = 0;
 #pragma unroll
       for (int s = 0; s < NSTAGE; ++s) {
         mbar_init(smem_u32(&bars[s]), 1);
@@ -532,16 +545,33 @@ __global__ void __launch_bounds__(NTHREAD) attn_split_kernel(const __grid_consta
     const uint32_t st = smem_u32(smem + (size_t)s * L::BYTES);
     fence_proxy_async();
     mbar_expect_tx(bar, cnt * (2 * HD + 4));
-    bulk_g2s(st + L::K_OFF + off * HD, kbase + slot * HD, cnt * HD, bar);
-    bulk_g2s(st + L::V_OFF + off * HD, vbase + slot * HD, cnt * HD, bar);
-    bulk_g2s(st + L::KS_OFF + off * 2, ksbase + slot, cnt * 2, bar);
-    bulk_g2s(st + L::VS_OFF + off * 2, vsbase + slot, cnt * 2, bar);
+    // A ring whose length is not a multiple of the tile lets a tile's positions run past slot S - 1: the copy is
+    // cut there and continues at slot 0 (S is a multiple of 8, so both pieces keep the 16-byte rules; a tile spans
+    // at most S + 8 positions, so it wraps once).
+    uint32_t c1 = cnt;
+    if (P.ring && slot + (int64_t)cnt > P.S) c1 = (uint32_t)(P.S - slot);
+    bulk_g2s(st + L::K_OFF + off * HD, kbase + slot * HD, c1 * HD, bar);
+    bulk_g2s(st + L::V_OFF + off * HD, vbase + slot * HD, c1 * HD, bar);
+    bulk_g2s(st + L::KS_OFF + off * 2, ksbase + slot, c1 * 2, bar);
+    bulk_g2s(st + L::VS_OFF + off * 2, vsbase + slot, c1 * 2, bar);
+    if (c1 < cnt) {
+      const uint32_t c2 = cnt - c1, off2 = off + c1;
+      bulk_g2s(st + L::K_OFF + off2 * HD, kbase, c2 * HD, bar);
+      bulk_g2s(st + L::V_OFF + off2 * HD, vbase, c2 * HD, bar);
+      bulk_g2s(st + L::KS_OFF + off2 * 2, ksbase, c2 * 2, bar);
+      bulk_g2s(st + L::VS_OFF + off2 * 2, vsbase, c2 * 2, bar);
+    }
   };
 
-  // plain-load path: every thread copies 16-byte pieces of the valid keys of tile ti into stage 0
-  auto load_generic = [&](int64_t ti) {
+  // plain-load path (caches whose geometry breaks the bulk engine's 16-byte rules): every thread moves 16-byte
+  // pieces of the valid keys of tile ti into stage s with cp.async, so the copy of the next tile runs under the
+  // math of the current one; the 2-byte scales travel through registers (loaded when the tile is requested, stored
+  // one iteration later, just before the tile is consumed).
+  constexpr int SC_PER_THREAD = (2 * TILE + NTHREAD - 1) / NTHREAD;
+  __half sc_reg[SC_PER_THREAD];
+  auto load_generic = [&](int64_t ti, int s) {
     const int64_t T0 = ti * TILE;
-    unsigned char* st = smem;
+    unsigned char* st = smem + (size_t)s * L::BYTES;
     constexpr int CH = HD / 16;  // 16-byte chunks per row
     for (int i = tid; i < TILE * CH * 2; i += NTHREAD) {
       const int which = i / (TILE * CH);
@@ -550,15 +580,28 @@ __global__ void __launch_bounds__(NTHREAD) attn_split_kernel(const __grid_consta
       if (t < lo || t > hi) continue;
       const int64_t slot = P.ring ? t % P.S : t;
       const int8_t* src = which ? vbase + slot * P.svs : kbase + slot * P.sks;
-      *reinterpret_cast<uint4*>(st + (which ? L::V_OFF : L::K_OFF) + j * HD + ch * 16) =
-          *reinterpret_cast<const uint4*>(src + ch * 16);
+      const uint32_t dst = smem_u32(st + (which ? L::V_OFF : L::K_OFF) + j * HD + ch * 16);
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src + ch * 16) : "memory");
     }
-    for (int i = tid; i < TILE * 2; i += NTHREAD) {
+    asm volatile("cp.async.commit_group;" ::: "memory");
+#pragma unroll
+    for (int n = 0; n < SC_PER_THREAD; ++n) {
+      const int i = tid + n * NTHREAD;
       const int which = i / TILE, j = i % TILE;
       const int64_t t = T0 + j;
-      if (t < lo || t > hi) continue;
-      const int64_t slot = P.ring ? t % P.S : t;
-      reinterpret_cast<__half*>(st + (which ? L::VS_OFF : L::KS_OFF))[j] = which ? vsbase[slot] : ksbase[slot];
+      sc_reg[n] = __ushort_as_half(0);
+      if (i < 2 * TILE && t >= lo && t <= hi) {
+        const int64_t slot = P.ring ? t % P.S : t;
+        sc_reg[n] = which ? vsbase[slot] : ksbase[slot];
+      }
+    }
+  };
+  auto store_scales = [&](int s) {
+    unsigned char* st = smem + (size_t)s * L::BYTES;
+#pragma unroll
+    for (int n = 0; n < SC_PER_THREAD; ++n) {
+      const int i = tid + n * NTHREAD;
+      if (i < 2 * TILE) reinterpret_cast<__half*>(st + (i / TILE ? L::VS_OFF : L::KS_OFF))[i % TILE] = sc_reg[n];
     }
   };
 
@@ -812,28 +855,45 @@ __global__ void __launch_bounds__(NTHREAD) attn_split_kernel(const __grid_consta
       }
     }
   } else {
+    // two stages: tile it + 1 is copied while tile it is consumed; one CTA barrier per tile
+    load_generic(t0, 0);
     for (int it = 0; it < ntile; ++it) {
-      __syncthreads();  // every warp is done with the single stage
-      load_generic(t0 + it);
-      __syncthreads();
+      const int s = it & 1;
+      asm volatile("cp.async.wait_group 0;" ::: "memory");  // this thread's pieces of tile it have landed
+      store_scales(s);
+      __syncthreads();  // tile it is complete for everyone, and every warp is done with tile it - 1 (stage s ^ 1)
+      if (it + 1 < ntile) load_generic(t0 + it + 1, s ^ 1);
       if (producer) continue;
+      const unsigned char* st = smem + (size_t)s * L::BYTES;
       const int64_t kb0 = (t0 + it) * TILE + WKEYS * warp;
       if (kb0 + WKEYS - 1 < lo || kb0 > hi) continue;
       if (kb0 < lo || kb0 + WKEYS - 1 > hi) {
         const int64_t lr = lo - kb0, hr_ = hi - kb0;
-        block(smem, lr < 0 ? 0 : (int)lr, hr_ > WKEYS ? WKEYS : (int)hr_, std::true_type{});
+        block(st, lr < 0 ? 0 : (int)lr, hr_ > WKEYS ? WKEYS : (int)hr_, std::true_type{});
       } else {
-        block(smem, 0, WKEYS, std::false_type{});
+        block(st, 0, WKEYS, std::false_type{});
       }
     }
   }
 
   if constexpr (BULK) {
-    if (dead && lane == 0 && P.status) atomicOr(P.status, 1);
+    if (dead && lane == 0) {
+      if (P.status) atomicOr(P.status, 1);
+      s_dead = 1;
+    }
   }
 
-  // ---- merge the warps' states through shared memory (aliases the stage ring: all copies have landed)
   __syncthreads();
+  if constexpr (BULK) {
+    // A tile was abandoned: its copy may still land, so the stage ring is not reused.  The CTA reports an empty
+    // result (the status bit says the launch's output is undefined) and still takes part in the split merge, which
+    // its peers wait for.
+    if (s_dead) {
+      empty_result();
+      return;
+    }
+  }
+  // ---- merge the warps' states through shared memory (aliases the stage ring: every copy has landed)
   float* mg_o = reinterpret_cast<float*>(smem);                    // [NWARP][ROWS][HD]
   float* mg_m = mg_o + NWARP * ROWS * HD;                          // [NWARP][ROWS]
   float* mg_l = mg_m + NWARP * ROWS;
@@ -884,7 +944,6 @@ __global__ void __launch_bounds__(NTHREAD) attn_split_kernel(const __grid_consta
       for (int i = 0; i < EPL; ++i) z[i] *= inv;
       finalize_row<QT, HD>(z, lane, b, h * G + row, h, P, v_stage);
     } else if (P.cluster) {
-      float* part = reinterpret_cast<float*>(smem) + NWARP * ROWS * (HD + 2);
       if (lane == 0) {
         part[G * HD + row] = mx;
         part[G * HD + G + row] = lsum;
@@ -909,8 +968,7 @@ __global__ void __launch_bounds__(NTHREAD) attn_split_kernel(const __grid_consta
   }
   if (P.splits > 1) {
     if (P.cluster)
-      cluster_merge<QT, HD>(P, reinterpret_cast<float*>(smem) + NWARP * ROWS * (HD + 2), bk, sid, warp, lane,
-                            v_stage);
+      cluster_merge<QT, HD>(P, part, bk, sid, warp, lane, v_stage);
     else if (P.counters)
       arrive_and_merge<QT, HD>(P, bk, tid, v_stage);
   }
@@ -927,12 +985,15 @@ static int launch_attn(const AttnParams& P, bool bulk, cudaStream_t st) {
   using L = StageLayout<HD>;
   const bool gp16 = P.G > 8;
   const int rows = gp16 ? 16 : 8;
-  // warp-merge arrays, then (cluster launches) this CTA's split partial
-  const size_t merge = (size_t)(NWARP + 1) * rows * (HD + 2) * sizeof(float);
-  size_t smem = (size_t)(bulk ? NSTAGE : 1) * L::BYTES;
-  if (merge > smem) smem = merge;
-  // staged q heads, key and value (activations), then the quantised key / value and their scales, behind the ring
+  // the stage ring (reused for the warp-merge arrays once every copy has landed) ...
+  const size_t merge = (size_t)NWARP * rows * (HD + 2) * sizeof(float);
+  size_t smem = (size_t)(bulk ? NSTAGE : 2) * L::BYTES;
+  static_assert((size_t)NWARP * 16 * (HD + 2) * sizeof(float) <= 2 * (size_t)L::BYTES, "merge arrays fit the ring");
+  (void)merge;
+  // ... staged q heads, key and value (activations), the quantised key / value and their scales (fused form) ...
   if (P.has_pre) smem += (size_t)(rows + 2) * HD * sizeof(QT) + 2 * HD + 16;
+  // ... and this CTA's split partial for the cluster merge (o[rows][HD], m[rows], l[rows])
+  smem = ((smem + 15) & ~(size_t)15) + (size_t)rows * (HD + 2) * sizeof(float);
   dim3 grid((unsigned)(P.B * P.KH), (unsigned)P.splits);
   const dim3 cluster(1, P.cluster ? (unsigned)P.splits : 1u, 1);
 #define UV_LAUNCH(GP, BK, PR)                                                                              \
@@ -1014,6 +1075,25 @@ extern "C" int uv_default_splits(int n_bk, int ctx, int n_sm) {
   return s < 1 ? 1 : s;
 }
 
+// bulk-copy (TMA) path: tiles must be linear and every piece 16-byte aligned
+static bool attn_bulk_ok(const uv_attn_args* a) {
+  using namespace uv;
+  bool bulk = a->sks == a->hd && a->svs == a->hd;
+  // rows are read in whole 8-slot groups: a linear row's allocation (S_alloc slots, >= S) must cover the group that
+  // holds slot S - 1, a ring's length must be a multiple of 8 (a tile that crosses slot S - 1 is fetched in two pieces)
+  const int s_alloc = a->S_alloc > a->S ? a->S_alloc : a->S;
+  bulk = bulk && (a->ring ? a->S % 8 == 0 : s_alloc % 8 == 0);
+  bulk = bulk && aligned16(a->k_cache) && aligned16(a->v_cache) && ((a->skb | a->skh | a->svb | a->svh) & 15) == 0;
+  bulk = bulk && aligned16(a->k_scale) && aligned16(a->v_scale) &&
+         ((a->ssb | a->ssh | a->stb | a->sth) & 7) == 0;  // scale rows start on 16-byte boundaries (fp16 elements)
+  return bulk;
+}
+
+extern "C" int uv_decode_attn_uses_bulk(const uv_attn_args* a) {
+  if (!a || !a->k_cache || !a->v_cache || !a->k_scale || !a->v_scale) return UV_ERR_ARG;
+  return attn_bulk_ok(a) ? 1 : 0;
+}
+
 // pre != nullptr: the caller wants uv_qkv_post's work done in the kernel's prologue.  *fused tells it whether that
 // happened; when the launch cannot take the fused form (plain-load path, or more than 8 splits without arrival
 // counters) nothing is launched, *fused = false and the caller runs the two-launch form.
@@ -1065,14 +1145,7 @@ static int decode_attn_impl(const uv_attn_args* a, void* stream, bool allow_clus
     P.ws_m = P.ws_o + rows * hd;
     P.ws_l = P.ws_m + rows;
   }
-  // bulk-copy (TMA) path: tiles must be linear and every piece 16-byte aligned
-  bool bulk = a->sks == hd && a->svs == hd;
-  // linear caches are read in whole 8-slot groups: the row allocation (S_alloc slots, >= S) must cover the group
-  // that holds slot S - 1
-  const int s_alloc = a->S_alloc > a->S ? a->S_alloc : a->S;
-  bulk = bulk && (a->ring ? a->S % TILE == 0 : s_alloc % 8 == 0);
-  bulk = bulk && aligned16(a->k_scale) && aligned16(a->v_scale) &&
-         ((a->ssb | a->ssh | a->stb | a->sth) & 7) == 0;  // scale rows start on 16-byte boundaries (fp16 elements)
+  const bool bulk = attn_bulk_ok(a);
   if (pre != nullptr) {
     // one launch needs: the bulk-copy path, a merge that runs inside the launch, and the step's RoPE table
     const bool ok = bulk && (P.splits == 1 || P.cluster || P.counters) && (!pre->inv_freq || pre->rope_cs);
@@ -1172,6 +1245,7 @@ extern "C" int uv_decode_attn_static(const uv_attn_args* a, void* stream) {
   using namespace uv;
   if (!a) return UV_ERR_ARG;
   if (a->B <= 0 || a->KH <= 0 || a->H <= 0 || a->num_splits < 1) return a->B == 0 ? UV_OK : UV_ERR_ARG;
+  if (a->H % a->KH) return UV_ERR_ARG;
   const size_t need = uv_decode_attn_workspace_bytes(a->B, a->KH, a->H / a->KH, a->hd, a->num_splits);
   if (need > UV_STATIC_PARTIAL_BYTES || (int64_t)a->B * a->KH > UV_STATIC_MAX_ROWS) return UV_ERR_STATIC_LIMIT;
   void* base = nullptr;

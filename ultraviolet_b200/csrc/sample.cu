@@ -5,7 +5,8 @@
 //   T  > 0 : e = exp((z - a) / T); token = first index whose running sum of e reaches (1 - u) * sum(e)
 //            (the inverse-CDF draw of fused_sample, ultraviolet/kernels/fused_sample.py:31-58); with top_p < 1 the
 //            draw is restricted to the nucleus of sample() (model.py:1203-1208): tokens whose strictly-larger mass
-//            is below top_p, ties with the cut kept
+//            is below top_p, ties with the cut kept; with top_k > 0 only the k largest logits (ties with the k-th
+//            kept) take part, and top_p then applies to that renormalised set (model.py:1201-1208)
 //   logp   = (z_tok - a) / T - log(sum e)              untruncated softmax, as the rollout log records it
 //                                                      (model.py:1160-1169); T <= 0 reports it at T = 1
 // u comes from the caller (one uniform per row) or from Philox4x32-10 keyed by (seed; row key, step), so a
@@ -40,6 +41,7 @@ struct SampleParams {
   int64_t x_stride;
   int B, V;
   float a, b, c, inv_t, top_p;
+  int top_k;  // 0 = no limit
   int greedy;
   int greedy_fast;  // host-decided: the vectorised arg-max path (needs no shared memory: launched with none)
   int precapped;  // input rows are already softcapped logits z (sample(), model.py:1194-1211); a = row maximum
@@ -225,10 +227,31 @@ __global__ void __launch_bounds__(SAMPLE_THREADS) sample_kernel(const __grid_con
     return;
   }
 
-  // ---- nucleus: smallest cut (as a float bit pattern) whose strictly-larger mass is below top_p * S
+  // ---- top-k: the k-th largest e as a float bit pattern = the smallest cut with fewer than k entries above it
   float cut = 0.f, S = S_full;
+  if (P.top_k > 0 && P.top_k < V) {
+    const float kf = (float)P.top_k;  // counts are exact in fp32 (V < 2^24)
+    uint32_t lo = 0u, hi = 0x3f800001u;  // e <= 1: nothing lies above hi; e > 0 (or 0 when it underflowed)
+    {
+      float n0 = 0.f;
+      for (int j = 0; j < CH; ++j) n0 += chunk[j] > 0.f ? 1.f : 0.f;
+      if (block_sum(n0, red, tid) < kf) hi = 0u;  // fewer than k non-zero entries: everything stays
+    }
+    while (hi - lo > 1u) {
+      const uint32_t mid = lo + (hi - lo) / 2u;
+      const float cm = __uint_as_float(mid);
+      float n = 0.f;
+      for (int j = 0; j < CH; ++j) n += chunk[j] > cm ? 1.f : 0.f;
+      if (block_sum(n, red, tid) < kf) hi = mid;
+      else lo = mid;
+    }
+    cut = __uint_as_float(hi);
+    mine = chunk_sum(cut);
+    S = block_sum(mine, red, tid);
+  }
+  // ---- nucleus: smallest cut whose strictly-larger mass (inside the top-k set) is below top_p * S
   if (P.top_p < 1.0f) {
-    const float lim = P.top_p * S_full;
+    const float lim = P.top_p * S, cut_k = cut;
     uint32_t lo = 0u, hi = 0x3f800001u;  // mass_above(hi) = 0 < lim always (e <= 1)
     while (hi - lo > 1u) {
       const uint32_t mid = lo + (hi - lo) / 2u;
@@ -236,13 +259,13 @@ __global__ void __launch_bounds__(SAMPLE_THREADS) sample_kernel(const __grid_con
       float s = 0.f;
       for (int j = 0; j < CH; ++j) {
         const float e = chunk[j];
-        s += e > cm ? e : 0.f;
+        s += (e > cm && e >= cut_k) ? e : 0.f;
       }
       const float above = block_sum(s, red, tid);
       if (above < lim) hi = mid;
       else lo = mid;
     }
-    cut = __uint_as_float(hi);
+    cut = fmaxf(__uint_as_float(hi), cut_k);
     mine = chunk_sum(cut);
     S = block_sum(mine, red, tid);
   }
@@ -278,7 +301,7 @@ __global__ void __launch_bounds__(SAMPLE_THREADS) sample_kernel(const __grid_con
   __syncthreads();
   if (tid == 0) {
     int t = s_tok;
-    if (P.top_p < 1.0f && e_sm[t + t / CH] < cut) {  // rounding left the target past the last kept entry
+    if (cut > 0.f && e_sm[t + t / CH] < cut) {  // rounding left the target past the last kept entry
       for (t = V - 1; t > 0 && e_sm[t + t / CH] < cut; --t) {}
     }
     P.tok[row] = t;
@@ -294,8 +317,17 @@ extern "C" int uv_sample(const void* x, int x_dtype, int64_t x_stride, int B, in
                          float cap_b, float cap_c, float temperature, float top_p, const float* u, uint64_t seed,
                          const int64_t* row_keys, const int64_t* steps, int64_t* tok_out, float* logp_out,
                          int64_t* inc_a, int64_t* inc_b, void* stream) {
+  return uv_sample_topk(x, x_dtype, x_stride, B, V, precapped, cap_a, cap_b, cap_c, temperature, 0, top_p, u, seed,
+                        row_keys, steps, tok_out, logp_out, inc_a, inc_b, stream);
+}
+
+extern "C" int uv_sample_topk(const void* x, int x_dtype, int64_t x_stride, int B, int V, int precapped, float cap_a,
+                              float cap_b, float cap_c, float temperature, int top_k, float top_p, const float* u,
+                              uint64_t seed, const int64_t* row_keys, const int64_t* steps, int64_t* tok_out,
+                              float* logp_out, int64_t* inc_a, int64_t* inc_b, void* stream) {
   using namespace uv;
   if (B == 0) return UV_OK;
+  if (top_k < 0) return UV_ERR_ARG;
   if (!x || !tok_out || !logp_out || B < 0) return UV_ERR_ARG;
   if (V < SAMPLE_THREADS || V % SAMPLE_THREADS || V > 49152) return UV_ERR_SHAPE;
   const bool greedy = !(temperature > 0.f);
@@ -307,7 +339,7 @@ extern "C" int uv_sample(const void* x, int x_dtype, int64_t x_stride, int B, in
   P.x = x, P.x_stride = x_stride, P.B = B, P.V = V;
   P.a = cap_a, P.b = cap_b, P.c = cap_c;
   P.inv_t = greedy ? 1.0f : 1.0f / temperature;
-  P.top_p = top_p, P.greedy = greedy ? 1 : 0, P.precapped = precapped ? 1 : 0;
+  P.top_p = top_p, P.top_k = top_k, P.greedy = greedy ? 1 : 0, P.precapped = precapped ? 1 : 0;
   P.u = u, P.seed = seed, P.row_keys = row_keys, P.steps = steps, P.tok = tok_out, P.logp = logp_out;
   P.inc_a = inc_a, P.inc_b = inc_b;
   // greedy over 16-bit logits whose rows start on 16-byte boundaries: one vectorised pass, no shared memory, so

@@ -139,12 +139,44 @@ class DecodeEngine:
                      tok=torch.zeros(B, dtype=torch.int64, device=dev),
                      logp=torch.zeros(B, dtype=torch.float32, device=dev),
                      counters=torch.zeros(B * K, dtype=torch.int32, device=dev),
-                     status=torch.zeros(1, dtype=torch.int32, device=dev),
-                     oob=torch.zeros(1, dtype=torch.int32, device=dev),
+                     flags=torch.zeros(2, dtype=torch.int32, device=dev),
                      rope_cs=torch.zeros(B, 2 * max(cfg.rope_pairs, 1), dtype=torch.float32, device=dev),
                      gate=torch.zeros(B, H, dtype=torch.float32, device=dev), ws={})
+            # device words the kernels raise on silent failures: [0] attention status (bit 0: a bulk copy did not
+            # land in time, outputs of that launch are undefined), [1] count of skipped out-of-range KV writes
+            s["status"], s["oob"] = s["flags"][0:1], s["flags"][1:2]
             self._scratch[B] = s
         return s
+
+    def device_status(self, B: int | None = None) -> dict:
+        """The failure words of the scratch set of batch size B (default: all sets), one small D2H each."""
+        out = {"attn_status": 0, "kv_oob": 0}
+        for b, s in self._scratch.items():
+            if B is None or b == B:
+                st, oob = s["flags"].tolist()
+                out["attn_status"] |= st
+                out["kv_oob"] += oob
+        return out
+
+    def check_status(self, B: int | None = None) -> dict:
+        """Raise if a kernel of this engine flagged a silent failure since the words were last cleared: outputs of
+        a launch whose attention status bit is set are undefined, and a skipped KV write corrupts later tokens."""
+        d = self.device_status(B)
+        if d["attn_status"] or d["kv_oob"]:
+            for b, s in self._scratch.items():
+                if B is None or b == B:
+                    s["flags"].zero_()
+            raise _lib.UvError(f"decode kernels reported a device-side failure: attention status word "
+                               f"{d['attn_status']:#x} (bit 0 = a cache tile copy timed out), {d['kv_oob']} KV "
+                               "cache writes skipped as out of range; tokens produced since the last check are invalid")
+        return d
+
+    def launches_per_step(self) -> int:
+        """Kernel launches of one trunk + head call (the sampler is one more)."""
+        n = self.cfg.n_layers
+        if self.fused_gemm:
+            return 1 + 5 * n + 1
+        return 1 + (8 if self.qkv_in_attn else 9) * n + 1
 
     def _workspace(self, s: dict, B: int, splits: int) -> Tensor | None:
         if splits <= 1:
@@ -161,8 +193,6 @@ class DecodeEngine:
         """One token for every batch entry: writes K/V at `pos` and returns the final normed hidden (B, d) (a view
         of engine scratch, overwritten by the next call).  pos/starts are batch-indexed (B,) int64; row_map
         optionally maps batch entries to cache rows."""
-        if skip_attn:
-            raise NotImplementedError("skip_attn (the reference's A/B profiling switch) is not built here")
         cfg, lib, dt = self.cfg, _lib.lib(), DTYPE_CODE[self.dtype]
         B = tok.size(0)
         s = self.scratch(B)
@@ -224,13 +254,21 @@ class DecodeEngine:
                 else:
                     splits = ns.get("local") or default_splits(B * K, S, self.device)
                     window, ring = cfg.window, True
-                attn_launch(q, kc, vc, pos, starts, cfg.attn_scale, window, ring, ks, vs, splits, z3,
-                            self._workspace(s, B, splits), v_cur=v_cur,
-                            xsa_alpha=self.xsa[l] if cfg.xsa else None, xsa_eps=cfg.xsa_eps,
-                            gate_x=xn if cfg.gate_channels else None,
-                            gate_w=w[f"l{l}.attn_gate"] if cfg.gate_channels else None,
-                            counters=s["counters"], status=s["status"], row_map=row_map, pre=pre,
-                            gate_vals=gate_vals)
+                if skip_attn:
+                    # the reference's A/B profiling switch (fast_decode.py:312-313): the step timed without its
+                    # attention kernel -- the "attention output" is the query itself (no XSA, no head gate: both live
+                    # in the attention kernel's epilogue here).  Outputs are meaningless by design.
+                    z3.copy_(q)
+                    if pre is not None:  # the fused launch would also have done the QKV post-processing
+                        _lib.check(lib.uv_qkv_post_args(C.byref(pre), sp), "uv_qkv_post")
+                else:
+                    attn_launch(q, kc, vc, pos, starts, cfg.attn_scale, window, ring, ks, vs, splits, z3,
+                                self._workspace(s, B, splits), v_cur=v_cur,
+                                xsa_alpha=self.xsa[l] if cfg.xsa else None, xsa_eps=cfg.xsa_eps,
+                                gate_x=xn if cfg.gate_channels else None,
+                                gate_w=w[f"l{l}.attn_gate"] if cfg.gate_channels else None,
+                                counters=s["counters"], status=s["status"], row_map=row_map, pre=pre,
+                                gate_vals=gate_vals)
                 lam = self.lambdas[l]
                 if fused:
                     _lib.check(lib.uv_gemm_resid_norm(s["z"].data_ptr(), H * hd, w[f"l{l}.wo"].data_ptr(), H * hd,
@@ -267,8 +305,8 @@ class DecodeEngine:
     def sample(self, head: Tensor, temperature: float, top_p: float = 1.0, u: Tensor | None = None, seed: int = 0,
                row_keys: Tensor | None = None, steps: Tensor | None = None, tok_out: Tensor | None = None,
                logp_out: Tensor | None = None, precapped: bool = False, inc_a: Tensor | None = None,
-               inc_b: Tensor | None = None):
-        """uv_sample on (B, V) head output; returns (tok int64 (B,), logp fp32 (B,)) in engine scratch unless
+               inc_b: Tensor | None = None, top_k: int = 0):
+        """uv_sample_topk on (B, V) head output; returns (tok int64 (B,), logp fp32 (B,)) in engine scratch unless
         output tensors are given."""
         B, V = head.shape
         s = self.scratch(B)
@@ -277,9 +315,10 @@ class DecodeEngine:
         a, b, c = self.cfg.softcap
         p = lambda t: None if t is None else t.data_ptr()
         with torch.cuda.device(self.device):
-            rc = _lib.lib().uv_sample(head.data_ptr(), DTYPE_CODE[head.dtype], head.stride(0), B, V, int(precapped),
-                                      a, b, c, float(temperature), float(top_p), p(u), C.c_uint64(seed & (2**64 - 1)),
-                                      p(row_keys), p(steps), tok_out.data_ptr(), logp_out.data_ptr(), p(inc_a),
-                                      p(inc_b), stream_ptr(self.device))
-        _lib.check(rc, "uv_sample")
+            rc = _lib.lib().uv_sample_topk(head.data_ptr(), DTYPE_CODE[head.dtype], head.stride(0), B, V,
+                                           int(precapped), a, b, c, float(temperature), int(top_k or 0), float(top_p),
+                                           p(u), C.c_uint64(seed & (2**64 - 1)), p(row_keys), p(steps),
+                                           tok_out.data_ptr(), logp_out.data_ptr(), p(inc_a), p(inc_b),
+                                           stream_ptr(self.device))
+        _lib.check(rc, "uv_sample_topk")
         return tok_out, logp_out

@@ -2,6 +2,8 @@
 1075-1354) on the B200 decode engine."""
 from __future__ import annotations
 
+import os
+
 import numpy as np
 import torch
 from torch import Tensor
@@ -10,12 +12,20 @@ from .fast_decode import _engine
 from .scheduler import GpuScheduler
 
 
+def fresh_seed() -> int:
+    """Philox seed for a call that was given none: drawn from torch's global generator, so ``torch.manual_seed``
+    governs it and successive calls see fresh noise (as the reference's ``torch.rand_like`` draws do); the
+    distributed rank is mixed in so that ranks seeded alike do not replay one stream."""
+    s = int(torch.randint(0, 2 ** 62, (1,)).item())
+    rank = int(os.environ.get("RANK", "0") or 0)
+    return (s ^ (rank * 0xD1B54A32D192ED03)) & (2 ** 63 - 1)
+
+
 def sample(logits: Tensor, temperature: float, top_k: int = 0, top_p: float = 1.0) -> Tensor:
     """model.py:1194-1211 on softcapped logits (B, V): temperature <= 0 -> argmax, else a draw from
-    softmax(logits / T) restricted to the top_p nucleus.  One uniform per row from torch's CUDA generator (so
-    torch.manual_seed governs it), inverse-CDF instead of Gumbel-max.  top_k is not built."""
-    if top_k:
-        raise NotImplementedError("top_k sampling is not built in ultraviolet_b200")
+    softmax(logits / T) restricted to the top_k largest logits (ties with the k-th kept) and then to the top_p
+    nucleus.  One uniform per row from torch's CUDA generator (so torch.manual_seed governs it), inverse-CDF instead
+    of Gumbel-max: the same distribution from a different random stream."""
     from . import _lib
     from .kernels._util import DTYPE_CODE, need_cuda, stream_ptr
     import ctypes as C
@@ -27,11 +37,11 @@ def sample(logits: Tensor, temperature: float, top_k: int = 0, top_p: float = 1.
     lp = torch.empty(B, dtype=torch.float32, device=logits.device)
     u = torch.rand(B, device=logits.device, dtype=torch.float32) if temperature > 0 else None
     with torch.cuda.device(logits.device):
-        rc = _lib.lib().uv_sample(logits.data_ptr(), DTYPE_CODE[logits.dtype], logits.stride(0), B, V, 1, 0.0, 0.0,
-                                  1.0, float(temperature), float(top_p), None if u is None else u.data_ptr(),
-                                  C.c_uint64(0), None, None, tok.data_ptr(), lp.data_ptr(), None, None,
-                                  stream_ptr(logits.device))
-    _lib.check(rc, "uv_sample")
+        rc = _lib.lib().uv_sample_topk(logits.data_ptr(), DTYPE_CODE[logits.dtype], logits.stride(0), B, V, 1, 0.0,
+                                       0.0, 1.0, float(temperature), int(top_k or 0), float(top_p),
+                                       None if u is None else u.data_ptr(), C.c_uint64(0), None, None,
+                                       tok.data_ptr(), lp.data_ptr(), None, None, stream_ptr(logits.device))
+    _lib.check(rc, "uv_sample_topk")
     return tok
 
 
@@ -41,13 +51,15 @@ class DecodeRunner:
     already a fixed kernel sequence."""
 
     def __init__(self, model, st, bucket: int = 1024, use_graph: bool = True, temperature: float = 1.0,
-                 top_k: int = 0, compile: bool = False, skip_attn: bool = False, top_p: float = 1.0, seed: int = 0):
-        if top_k:
-            raise NotImplementedError("top_k sampling is not built in ultraviolet_b200")
+                 top_k: int = 0, compile: bool = False, skip_attn: bool = False, top_p: float = 1.0,
+                 seed: int | None = None):
+        """seed: Philox key of this runner's draws; None (the default) takes a fresh one from torch's generator
+        (``fresh_seed``), an int makes the token streams reproducible."""
         self.m, self.st, self.bucket = model, st, bucket
         self.eng = _engine(model)
         self.use_graph = use_graph
-        self.temperature, self.top_k, self.top_p, self.seed = temperature, top_k, top_p, seed
+        self.temperature, self.top_k, self.top_p = temperature, int(top_k or 0), top_p
+        self.seed = fresh_seed() if seed is None else int(seed)
         dev = st.pos.device
         self.tok = torch.zeros(st.B, dtype=torch.long, device=dev)
         # The sampler writes the new tokens straight into the step's input buffer: feeding step() its own output
@@ -73,7 +85,8 @@ class DecodeRunner:
         h = eng.trunk(self.tok, st, st.pos, st.starts, g_len=g_len, num_splits=self.m.__dict__.get(
             "decode_num_splits", getattr(type(self.m), "decode_num_splits", None)), skip_attn=self.skip_attn)
         eng.sample(eng.head(h), self.temperature, self.top_p, seed=self.seed, row_keys=self.row_keys,
-                   steps=self.steps, tok_out=self.tok, inc_a=st.pos, inc_b=self.steps)  # advances both counters
+                   steps=self.steps, tok_out=self.tok, inc_a=st.pos, inc_b=self.steps,  # advances both counters
+                   top_k=self.top_k)
 
     def step(self, tok: Tensor) -> Tensor:
         p = int(self.st.host_pos.max())
@@ -100,6 +113,7 @@ class DecodeRunner:
                 with torch.cuda.graph(g, capture_error_mode="thread_local"):
                     self._body(gl)
                 self.graphs[gl] = g
+                self.eng.check_status(self.st.B)  # the warm-up run of a new bucket is also the failure check
             g.replay()
         self.st.host_pos += 1
         return self.out_tok
@@ -118,8 +132,9 @@ def _left_pad(prompts, pad_id, dev):
 @torch.no_grad()
 def generate(model, prompts, max_new: int, temperature: float = 1.0, top_k: int = 0, eos_id: int | None = None,
              pad_id: int = 0, max_len: int | None = None, use_graph: bool = True, bucket: int = 1024,
-             dtype=None, compile: bool = True, top_p: float = 1.0):
-    """Static-batch generation (model.py:1228-1263): left-padded prefill, lockstep decode, rows cut after EOS."""
+             dtype=None, compile: bool = True, top_p: float = 1.0, seed: int | None = None):
+    """Static-batch generation (model.py:1228-1263): left-padded prefill, lockstep decode, rows cut after EOS.
+    seed: None draws a fresh Philox seed per call from torch's generator; an int reproduces the streams."""
     eng = _engine(model)
     dev = eng.device
     B = len(prompts)
@@ -127,7 +142,7 @@ def generate(model, prompts, max_new: int, temperature: float = 1.0, top_k: int 
     max_len = max_len or (idx.size(1) + max_new)
     st = model.new_state(B, max_len, eng.dtype, dev)
     runner = DecodeRunner(model, st, bucket=bucket, use_graph=use_graph, temperature=temperature, top_k=top_k,
-                          top_p=top_p)
+                          top_p=top_p, seed=seed)
     # prefill every position but the last through the decode kernels, then let the runner take the last prompt
     # token so that token 0 is drawn by the same fused sampler as every later token
     T = idx.size(1)
@@ -148,6 +163,7 @@ def generate(model, prompts, max_new: int, temperature: float = 1.0, top_k: int 
             done |= tok == eos_id
             if i % 64 == 63 and bool(done.all()):
                 break
+    eng.check_status(B)  # raises if a kernel flagged a timed-out tile copy or a skipped cache write
     res = []
     for row in torch.stack(out, 1).tolist():
         if eos_id is not None and eos_id in row:
@@ -160,19 +176,19 @@ def generate(model, prompts, max_new: int, temperature: float = 1.0, top_k: int 
 def generate_continuous(model, prompts, max_new: int, batch: int, temperature: float = 1.0, top_k: int = 0,
                         eos_id: int | None = None, pad_id: int = 0, check_every: int = 16, use_graph: bool = True,
                         bucket: int = 1024, dtype=None, compile: bool = True, target_lens=None, stats=None,
-                        top_p: float = 1.0, seed: int = 0, prefill_lanes: int = 0):
+                        top_p: float = 1.0, seed: int | None = None, prefill_lanes: int = 0):
     """Continuous batching over `batch` cache slots (model.py:1266-1354), scheduled on the device; completions in
-    prompt order.  target_lens[i] caps request i's length (the reference's benchmarking hook, model.py:1312)."""
-    if top_k:
-        raise NotImplementedError("top_k sampling is not built in ultraviolet_b200")
+    prompt order.  target_lens[i] caps request i's length (the reference's benchmarking hook, model.py:1312).
+    seed: None draws a fresh Philox seed per call from torch's generator (request i's stream is keyed by (seed, i));
+    an int reproduces the streams whatever slot a request lands in."""
     eng = _engine(model)
     n = len(prompts)
     B = min(batch, n)
     max_prompt = max(len(p) for p in prompts)
     st = model.new_state(GpuScheduler.state_rows(B, prefill_lanes), max_prompt + max_new + check_every, eng.dtype,
                          eng.device)
-    sched = GpuScheduler(eng, st, max_new=max_new, temperature=temperature, top_p=top_p, eos_id=eos_id,
-                         pad_id=pad_id, seed=seed, q_cap=max(n, 2), max_prompt=max_prompt, use_graph=use_graph,
+    sched = GpuScheduler(eng, st, max_new=max_new, temperature=temperature, top_p=top_p, top_k=top_k, eos_id=eos_id,
+                         pad_id=pad_id, seed=fresh_seed() if seed is None else int(seed), q_cap=max(n, 2), max_prompt=max_prompt, use_graph=use_graph,
                          prefill_lanes=prefill_lanes,
                          tok_cap=sum(len(p) for p in prompts) + 1,
                          out_cap=(int(np.minimum(np.asarray(target_lens), max_new).sum()) if target_lens is not None

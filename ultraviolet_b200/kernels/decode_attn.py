@@ -21,7 +21,8 @@ def _n_sm(dev: torch.device) -> int:
 
 def default_splits(n_bk: int, ctx: int, device=None, min_chunk: int | None = None, waves: int | None = None) -> int:
     """Splits per (row, kv head) (role of decode_attn.py:121-129).  min_chunk / waves are accepted for signature
-    compatibility; the heuristic is the library's (64-key TMA tiles, ~4 CTAs per SM, >= 256 keys per split)."""
+    compatibility and not used: the heuristic is the library's own (uv_default_splits: 128-key tiles, every CTA
+    resident in one wave, a split only when it takes at least four tiles off every CTA)."""
     dev = torch.device(device or "cuda")
     return int(_lib.lib().uv_default_splits(int(n_bk), int(ctx), _n_sm(dev)))
 
@@ -42,14 +43,13 @@ def _row_alloc(k_cache: Tensor, v_cache: Tensor, k_scale: Tensor, v_scale: Tenso
     return alloc
 
 
-def attn_launch(q: Tensor, k_cache: Tensor, v_cache: Tensor, pos: Tensor, starts: Tensor, scale: float, window: int,
-                ring: bool, k_scale: Tensor, v_scale: Tensor, num_splits: int, out: Tensor,
-                workspace: Tensor | None = None, v_cur: Tensor | None = None, xsa_alpha: Tensor | None = None,
-                xsa_eps: float = 1e-4, gate_x: Tensor | None = None, gate_w: Tensor | None = None,
-                counters: Tensor | None = None, status: Tensor | None = None,
-                row_map: Tensor | None = None, pre=None, gate_vals: Tensor | None = None) -> Tensor:
-    """Raw launch: fills uv_attn_args from tensor metadata.  q / out (B, H, hd) with unit inner stride.
-    pre: a filled _lib.QkvArgs -> uv_qkv_attn (uv_qkv_post's work done inside the attention launch)."""
+def attn_args(q: Tensor, k_cache: Tensor, v_cache: Tensor, pos: Tensor, starts: Tensor, scale: float, window: int,
+              ring: bool, k_scale: Tensor, v_scale: Tensor, num_splits: int, out: Tensor,
+              workspace: Tensor | None = None, v_cur: Tensor | None = None, xsa_alpha: Tensor | None = None,
+              xsa_eps: float = 1e-4, gate_x: Tensor | None = None, gate_w: Tensor | None = None,
+              counters: Tensor | None = None, status: Tensor | None = None,
+              row_map: Tensor | None = None, gate_vals: Tensor | None = None) -> "_lib.AttnArgs":
+    """uv_attn_args filled from tensor metadata.  q / out (B, H, hd) with unit inner stride."""
     B, H, hd = q.shape
     KH, S = k_cache.shape[1], k_cache.shape[2]
     a = _lib.AttnArgs()
@@ -65,7 +65,8 @@ def attn_launch(q: Tensor, k_cache: Tensor, v_cache: Tensor, pos: Tensor, starts
     a.S_alloc = _row_alloc(k_cache, v_cache, k_scale, v_scale, S)
     a.window, a.ring, a.scale, a.num_splits = int(window), int(bool(ring)), float(scale), int(num_splits)
     if num_splits > 1:
-        a.workspace, a.workspace_bytes = workspace.data_ptr(), workspace.numel() * workspace.element_size()
+        if workspace is not None:
+            a.workspace, a.workspace_bytes = workspace.data_ptr(), workspace.numel() * workspace.element_size()
         if counters is not None:
             if counters.numel() < B * KH or counters.dtype != torch.int32:
                 raise ValueError("counters must hold B*KH int32 zeros")
@@ -82,6 +83,16 @@ def attn_launch(q: Tensor, k_cache: Tensor, v_cache: Tensor, pos: Tensor, starts
     elif gate_w is not None:
         a.gate_x, a.gate_x_stride = gate_x.data_ptr(), gate_x.stride(0)
         a.gate_w, a.gate_ch = gate_w.data_ptr(), gate_w.size(-1)
+    return a
+
+
+def attn_launch(q: Tensor, k_cache: Tensor, v_cache: Tensor, pos: Tensor, starts: Tensor, scale: float, window: int,
+                ring: bool, k_scale: Tensor, v_scale: Tensor, num_splits: int, out: Tensor,
+                workspace: Tensor | None = None, pre=None, **epilogue) -> Tensor:
+    """Raw launch of uv_decode_attn (arguments as ``attn_args``).
+    pre: a filled _lib.QkvArgs -> uv_qkv_attn (uv_qkv_post's work done inside the attention launch)."""
+    a = attn_args(q, k_cache, v_cache, pos, starts, scale, window, ring, k_scale, v_scale, num_splits, out,
+                  workspace, **epilogue)
     with torch.cuda.device(q.device):
         if pre is not None:
             rc = _lib.lib().uv_qkv_attn(C.byref(pre), C.byref(a), stream_ptr(q.device))
@@ -120,7 +131,7 @@ def decode_attention(q: Tensor, k_cache: Tensor, v_cache: Tensor, pos: Tensor, s
     q (B, H, hd) fp16 / bf16 (a (B, 1, H, hd) view is accepted); k_cache, v_cache (B, K, S, hd) int8 with
     k_scale / v_scale (B, K, S) fp16; pos (B,) = position of the newest key (already written); keys attended are
     positions max(starts[b], pos[b] - window + 1, 0) .. pos[b]; ring: slot of position t is t % S (default:
-    window > 0).  block_n / num_warps / backend are accepted and ignored (one kernel, fixed 64-key tiles).
+    window > 0).  block_n / num_warps / backend are accepted and ignored (one kernel, fixed 128-key tiles).
     Registered as the torch custom op ``uvb200::decode_attn`` (opaque to torch.compile, graph-capturable).
     """
     if q.dim() == 4:

@@ -29,9 +29,14 @@ def sync_weights_inplace(gen_m, raw) -> None:
 
 class StreamGen:
     def __init__(self, model, slots, max_prompt, max_new, temperature, eos_id, check_every=16, compile=True,
-                 use_graph=True, pad_id=0, dtype=torch.float16, bucket=1024, top_p: float = 1.0, seed: int = 0,
-                 queue_capacity: int = 8192, prefill_lanes: int | None = None):
+                 use_graph=True, pad_id=0, dtype=torch.float16, bucket=1024, top_p: float = 1.0,
+                 seed: int | None = None, queue_capacity: int = 8192, prefill_lanes: int | None = None):
+        """seed: Philox key of this generator's draws (request n's stream is keyed by (seed, n)).  None (default)
+        takes a fresh seed from torch's generator mixed with the distributed rank, as the reference's sampler draws
+        from torch's global generator; pass an int for reproducible rollouts."""
         assert temperature > 0
+        from .generate import fresh_seed
+        seed = fresh_seed() if seed is None else int(seed)
         self.m, self.B, self.max_new, self.T, self.eos = model, slots, max_new, temperature, eos_id
         self.ce, self.pad, self.dtype, self.max_prompt = check_every, pad_id, dtype, max_prompt
         eng = _engine(model)

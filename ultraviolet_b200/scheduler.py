@@ -27,7 +27,7 @@ class GpuScheduler:
     def __init__(self, engine, st, *, max_new: int, temperature: float, top_p: float = 1.0, eos_id: int | None = 0,
                  pad_id: int = 0, seed: int = 0, q_cap: int = 8192, tok_cap: int | None = None,
                  out_cap: int | None = None, max_prompt: int = 256, force_eos: bool = False, use_graph: bool = True,
-                 num_splits: dict | None = None, prefill_lanes: int = 0, lane_chunk: int = 8):
+                 num_splits: dict | None = None, prefill_lanes: int = 0, lane_chunk: int = 8, top_k: int = 0):
         """prefill_lanes > 0: the decode step runs on slots + prefill_lanes batch rows; the extra rows carry further
         prompt tokens of slots that are still prefilling (up to lane_chunk tokens per slot per step).  The state must
         then hold one spare cache row: st.B == slots + 1 (see ``state_rows``)."""
@@ -36,6 +36,7 @@ class GpuScheduler:
         self.B = st.B - 1 if self.L > 0 else st.B
         self.dev = engine.device
         self.max_new, self.T, self.top_p, self.seed = int(max_new), float(temperature), float(top_p), int(seed)
+        self.top_k = int(top_k or 0)
         self.eos = -1 if eos_id is None else int(eos_id)
         self.pad, self.force_eos = int(pad_id), bool(force_eos)
         self.q_cap = _pow2(q_cap)
@@ -61,6 +62,7 @@ class GpuScheduler:
         self.out_lp = torch.zeros(self.out_cap, dtype=torch.float32, device=dev)
         self.ctl = i64(16)
         sc = engine.scratch(B)
+        self.st_rows = B + self.L  # batch rows of one step = the engine scratch set the step's kernels flag into
         self.samp_tok, self.samp_lp = sc["tok"], sc["logp"]
         st.pos.zero_()
         st.starts.zero_()
@@ -152,7 +154,8 @@ class GpuScheduler:
         else:
             h = eng.trunk(self.cur_tok, st, st.pos, st.starts, g_len=st.max_len, num_splits=self.num_splits)
         head = eng.head(h)
-        eng.sample(head, self.T, self.top_p, seed=self.seed, row_keys=self.row_key, steps=self.step_ctr)
+        eng.sample(head, self.T, self.top_p, seed=self.seed, row_keys=self.row_key, steps=self.step_ctr,
+                   top_k=self.top_k)
         self._sched_step()
 
     def prime(self) -> None:
@@ -199,6 +202,7 @@ class GpuScheduler:
         fin = int(self.ctl[CTL_FIN].item())
         if fin == self.n_harvested:
             return None
+        self.eng.check_status(self.st_rows)  # rollouts from a step whose kernels flagged a failure are not handed out
         k = torch.arange(self.n_harvested, fin, device=self.dev) % self.q_cap
         rid = self.fin_ring[k].long()
         ri = rid % self.q_cap
