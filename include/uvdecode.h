@@ -219,10 +219,44 @@ typedef struct uv_qkv_args { /* the parameters of uv_qkv_post, by name */
   const void* gate_w;     /* optional, uv_qkv_post_args only: (H, gate_ch) attention output gate weights; the kernel */
   float* gate_out;        /* also writes gate_out (B, H) = 2*sigmoid(xn[b, :gate_ch] . gate_w[head]) for the */
   int gate_ch;            /* attention launch that follows (uv_attn_args.gate_vals) */
+  const int64_t* last_pos; /* optional (B,), packed prefill: the last position of batch entry b's sequence in THIS
+                             launch.  A ring cache then keeps only the newest S positions of a sequence (entries with
+                             pos + S <= last_pos are not written), as _write_kv_layers does (ultraviolet/kernels/
+                             fast_decode.py:166-207), so that no two rows of one launch write the same slot */
 } uv_qkv_args;
 int uv_qkv_attn(const uv_qkv_args* qkv, const uv_attn_args* attn, void* stream);
 /* uv_qkv_post with its parameters by name; with rope_cs set the rotation reads the step's table. */
 int uv_qkv_post_args(const uv_qkv_args* qkv, void* stream);
+
+/* ---------------------------------------------------------------------------------------------------------------
+ * (f1) Packed variable-length prefill attention.  Replaces the attention of the reference's prompt prefill: SDPA
+ * over the left-padded batch in prefill_fast (ultraviolet/kernels/fast_decode.py:70-114) and varlen_attention over
+ * the packed batch in _prefill_packed (fast_decode.py:117-163, ultraviolet/kernels/varlen_attn.py:38-92).
+ *
+ * qkv (M, (H + 2K) * hd) holds the post-processed rows of ALL prompts of a refill batch back to back (q heads, then
+ * k heads, then v heads, as uv_qkv_post leaves them: normalised / rotated q and k, v with its value embedding).
+ * cu_seqlens (n_seq + 1) int32: first row of every sequence; tile_cu (n_seq + 1) int32: tile_cu[s] = sum over
+ * s' < s of ceil(len_s' / 16) (the kernel works in 16-token query tiles; max_tiles >= tile_cu[n_seq] is the grid,
+ * blocks beyond the last tile exit, so both arrays may be built on the device).  Token i of a sequence attends to
+ * tokens max(0, i - window + 1) .. i of the same sequence (window 0 = unlimited) with the UNQUANTISED keys / values
+ * of the chunk; out (M, H * hd) gets softmax(scale * q.K^T) V per query head, followed by the optional epilogue of
+ * uv_attn_args (XSA with the token's own v, then gate_vals (M, H)).  hd in {16, 32, 64, 128}, H / K <= 16. */
+typedef struct uv_prefill_attn_args {
+  const void* qkv;
+  int dtype;              /* UV_F16 | UV_BF16 */
+  int64_t ld;             /* row stride of qkv in elements (ld * 2 bytes a multiple of 16) */
+  const int32_t* cu_seqlens;
+  const int32_t* tile_cu;
+  int n_seq, max_tiles;
+  void* out;
+  int64_t ldo;
+  int H, K, hd, window;
+  float scale;
+  const float* xsa_alpha; /* (H,) fp32, already tanh'ed, or NULL */
+  float xsa_eps;
+  const float* gate_vals; /* (M, H) fp32 or NULL */
+} uv_prefill_attn_args;
+int uv_prefill_attn(const uv_prefill_attn_args* args, void* stream);
 
 /* GEMMs of the decode step with the row-wise kernels above fused into their epilogues (hand-written mma.sync
  * mainloop; same results as library GEMM + the separate kernel up to the summation order of the fp32 accumulation).
@@ -240,6 +274,37 @@ int uv_gemm_swiglu(const void* hn, int64_t ldh, const void* w_gu, void* act, int
                    void* stream);
 int uv_gemm_resid_norm(const void* a, int64_t lda, const void* w, int K, const void* x, const float* lambdas, void* h,
                        void* hn, int dtype, int B, int d, void* stream);
+
+/* Decode-step GEMMs on the tcgen05 tensor cores with the row-wise kernels fused into their epilogues (the default
+ * GEMM path of the engine for bf16 models whose shapes fit: head_dim 64, K % 64 == 0, N % 128 == 0).  They replace the
+ * library GEMMs of decode_step_fast (ultraviolet/kernels/fast_decode.py:303-330: the fused wqkv / wo / gate|up / down
+ * matmuls of Attention.qkv, Attention.post, MLP.forward and Block.finish, ultraviolet/model.py:302-335, :388-391,
+ * :567-571) together with the elementwise ops between them.
+ *
+ * Tiling: 128 weight rows per CTA on the TMEM lanes, a tile of bn batch rows as the MMA's N (bn_hint 32 / 64 / 128,
+ * 0 = automatic); ks_hint splits K over a thread-block cluster (0 = automatic, <= 8) with the partials summed
+ * through distributed shared memory.  Weights are requested before griddepcontrol.wait, activations after it.
+ *
+ * Deferred RMS norm: ss_in (ss_parts, ss_ld) fp32 holds per-feature-tile sums of squares of the INPUT rows (written
+ * by uv_gemm_sw_resid or uv_embed_norm_ss); the kernel multiplies row b of its result by
+ * rsqrt(sum_j ss_in[j][b] / K + 2^-23), i.e. it computes rms_norm(x) . w^T from the un-normalised x.  ss_in = NULL:
+ * no scaling.
+ *   uv_gemm_sw         c (M, N) = [rms_norm](x) . w^T                                   (building block)
+ *   uv_gemm_sw_qkv     the QKV projection + everything uv_qkv_post_args does (args->xn is ignored: the gates read
+ *                      x scaled on the fly; args->rope_cs is required on RoPE layers)
+ *   uv_gemm_sw_swiglu  act (M, f) = silu(g) * u, [g | u] = rms_norm(h) . w_gu^T, w_gu = [Wg ; Wu] (2f, K), f % 64 == 0
+ *   uv_gemm_sw_resid   h = lambdas[0] * x + lambdas[1] * (a . w^T) (each product and the sum rounded, Block.finish)
+ *                      and ss_out[tile][b] = sum over the tile's 128 features of h[b]^2 (N / 128 tiles)
+ * status (optional device word): bit 2 is set when a bounded wait ran out (outputs then undefined). */
+int uv_gemm_sw(const void* x, int64_t ldx, const void* w, void* c, int64_t ldc, int dtype, int M, int N, int K,
+               const float* ss_in, int ss_parts, int ss_ld, int bn_hint, int ks_hint, int* status, void* stream);
+int uv_gemm_sw_qkv(const void* x, int64_t ldx, const void* wqkv, const uv_qkv_args* args, const float* ss_in,
+                   int ss_parts, int ss_ld, int bn_hint, int ks_hint, int* status, void* stream);
+int uv_gemm_sw_swiglu(const void* h, int64_t ldh, const void* w_gu, void* act, int dtype, int M, int K, int f,
+                      const float* ss_in, int ss_parts, int ss_ld, int bn_hint, int* status, void* stream);
+int uv_gemm_sw_resid(const void* a, int64_t lda, const void* w, const void* x, const float* lambdas, void* h,
+                     int64_t ldh, float* ss_out, int ss_out_ld, int dtype, int M, int N, int K, int bn_hint,
+                     int ks_hint, int* status, void* stream);
 
 /* uv_sample: softcap + token draw + behaviour log-prob per row of the LM-head output x (B, V), V % 256 == 0.
  * Replaces fused_sample (ultraviolet/kernels/fused_sample.py:68-78) and sample + the log-prob gather

@@ -54,3 +54,31 @@ def decode_attention_ref(q, k_cache, v_cache, pos, starts, scale, *, window: int
     e = np.exp(s - m)
     w = e / e.sum(-1, keepdims=True)
     return np.einsum("bkgs,bksd->bkgd", w.astype(np.float32), vf, optimize=True).reshape(B, H, hd)
+
+
+def varlen_attention_ref(q, k, v, cu_seqlens, scale, window=None) -> np.ndarray:
+    """fp32 packed causal attention, restating ``varlen_attention_ref`` (ultraviolet/kernels/varlen_attn.py:94-114):
+    q (N, H, hd), k / v (N, K, hd) packed along N, cu_seqlens (S + 1,) segment boundaries; query i of a segment sees
+    keys j of the same segment with 0 <= i - j < window (window None / 0: all j <= i).  Returns (N, H, hd)."""
+    q, k, v = (np.asarray(a, dtype=np.float32) for a in (q, k, v))
+    H, K = q.shape[1], k.shape[1]
+    G = H // K
+    out = np.zeros_like(q)
+    cu = [int(c) for c in cu_seqlens]
+    for a, b in zip(cu[:-1], cu[1:]):
+        L = b - a
+        if L == 0:
+            continue
+        kk = np.repeat(k[a:b], G, axis=1)          # (L, H, hd): kv head h serves query heads h*G .. h*G + G - 1
+        vv = np.repeat(v[a:b], G, axis=1)
+        s = np.einsum("ihd,jhd->hij", q[a:b], kk, optimize=True) * np.float32(scale)
+        i = np.arange(L)
+        d = i[:, None] - i[None, :]
+        m = d >= 0
+        if window:
+            m = m & (d < window)
+        s = np.where(m[None], s, -np.inf).astype(np.float32)
+        e = np.exp(s - s.max(-1, keepdims=True))
+        w = e / e.sum(-1, keepdims=True)
+        out[a:b] = np.einsum("hij,jhd->ihd", w.astype(np.float32), vv, optimize=True)
+    return out

@@ -82,17 +82,35 @@ def cpu_decode(prompts, n_steps: int, warmup: int = 1, vocab: int = 16384, seed:
             "context": ctx0, "steps": n_steps}
 
 
-def _time_cuda(fn, reps: int) -> float:
+def _time_cuda(fn, reps: int):
+    """(milliseconds per call of fn, whether it was graph-timed): captured once into a CUDA graph (after an eager call that compiles / warms the
+    kernels) and replayed, so the figure is device time and not the host's launch rate; eager timing if the
+    function cannot be captured."""
     import torch
     fn()
     torch.cuda.synchronize()
+    g = None
+    try:
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            fn()
+        torch.cuda.current_stream().wait_stream(side)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            fn()
+        g.replay()
+        torch.cuda.synchronize()
+    except Exception:  # noqa: BLE001
+        g = None
+        torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(reps):
-        fn()
+        g.replay() if g is not None else fn()
     e1.record()
     torch.cuda.synchronize()
-    return e0.elapsed_time(e1) / reps
+    return e0.elapsed_time(e1) / reps, g is not None
 
 
 def gpu_attention(shapes=("long", "step"), reps: int = 4) -> dict:
@@ -132,8 +150,10 @@ def gpu_attention(shapes=("long", "step"), reps: int = 4) -> dict:
                     decode_attention(q, k, v, pos, st0, 0.14125, window=window, ring=ring, k_scale=ks, v_scale=vs,
                                      ctx_hint=S, backend=backend)
             try:
-                ms = _time_cuda(run, reps) / len(bufs)
-                res[name] = {"us": ms * 1e3, "gbs": res["bytes"] / ms / 1e6}
+                ms, graphed = _time_cuda(run, reps)
+                ms /= len(bufs)
+                res[name] = {"us": ms * 1e3, "gbs": res["bytes"] / ms / 1e6,
+                             "timed": "CUDA graph replays" if graphed else "eager launches"}
             except Exception as e:  # noqa: BLE001  (a backend that cannot compile here is reported, not fatal)
                 res[name] = {"unavailable": f"{type(e).__name__}: {str(e)[:300]}"}
         out[shape] = res

@@ -93,6 +93,13 @@ def make_attn():
                                    ring=c["ring"], k_scale=ks, v_scale=vs)
         out[name] = ref.numpy()
         out[name + ".in_sha"] = np.array(gi.sha(c["q"], c["k"], c["v"], c["pos"], c["starts"]))
+    # packed varlen attention of the prefill (varlen_attn.py:94-114)
+    from ultraviolet.kernels.varlen_attn import varlen_attention_ref
+    c = gi.varlen_case()
+    for name, window in (("varlen.window", c["window"]), ("varlen.full", None)):
+        out[name] = varlen_attention_ref(T(c["q"])[None], T(c["k"])[None], T(c["v"])[None], T(c["cu"]), c["scale"],
+                                         window)[0].numpy()
+    out["varlen.in_sha"] = np.array(gi.sha(c["q"], c["k"], c["v"], c["cu"]))
     save("attn", **out)
 
 

@@ -203,3 +203,15 @@ def top_p_case():
     lg = (r.standard_normal((6, 12)) * 2).astype(np.float32)
     lg[1, 3] = lg[1, 5]  # a tie at some rank
     return lg, 0.8, 0.9, 4000
+
+
+def varlen_case():
+    """Packed causal attention with a window (prompt prefill): ragged segments including an empty one."""
+    r = np.random.default_rng(31)
+    lens = [5, 0, 33, 70]
+    N, H, K, hd = sum(lens), 4, 2, 16
+    q = r.standard_normal((N, H, hd)).astype(np.float32)
+    k = r.standard_normal((N, K, hd)).astype(np.float32)
+    v = r.standard_normal((N, K, hd)).astype(np.float32)
+    cu = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
+    return dict(q=q, k=k, v=v, cu=cu, scale=0.25, window=24)

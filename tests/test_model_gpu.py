@@ -55,13 +55,16 @@ def test_teacher_forced_logits(name):
     assert err.max() <= 2e-2 * np.abs(olg).max(), (err.max(), np.abs(olg).max())
     assert np.array_equal(st.pos.cpu().numpy(), ost.pos) and np.array_equal(st.starts.cpu().numpy(), ost.starts)
     # int8 cache of the first layer: same bytes up to bf16 rounding of the projections (one quantisation step)
+    # (slots of real tokens only: the packed prefill never computes or writes the left padding, exactly as the
+    # reference's packed route does not -- rows read keys >= start; max_len stays below the ring length here, so
+    # slot == position on local layers too)
     d = np.abs(st.k[0].cpu().numpy().astype(np.int16) - ost.k[0].astype(np.int16))
-    valid = np.arange(max_len)[None, :] >= starts[:, None]
-    d = d[:, :, :ost.k[0].shape[2]]
-    if not m.cfg.is_global(0):
-        valid = np.ones(d.shape[:1] + d.shape[2:3], bool)
-    dv = d[np.broadcast_to(valid[:, None, :d.shape[2], None], d.shape)]
-    assert dv.max() <= 3 and (dv != 0).mean() < 0.35, (dv.max(), (dv != 0).mean())
+    S0 = ost.k[0].shape[2]
+    assert max_len <= S0 or m.cfg.is_global(0)
+    valid = (np.arange(S0)[None, :] >= starts[:, None]) & (np.arange(S0)[None, :] < ost.pos[:, None])
+    d = d[:, :, :S0]
+    dv = d[np.broadcast_to(valid[:, None, :, None], d.shape)]
+    assert dv.max() <= 1 and (dv != 0).mean() < 0.05, (dv.max(), (dv != 0).mean())
 
 
 def test_greedy_stream_random_init_128_tokens():

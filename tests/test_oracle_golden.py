@@ -146,3 +146,13 @@ def test_philox_known_answers():
     for ctr, key, out in kat:
         assert tuple(int(x) for x in philox.philox4x32_10(ctr, key)) == out
     assert 0.0 <= float(philox.uniform(7, 3, 11)) < 1.0
+
+
+def test_varlen_attention_restatement_matches_reference():
+    from oracle import attn as oattn
+    g = golden("attn")
+    c = gi.varlen_case()
+    assert gi.sha(c["q"], c["k"], c["v"], c["cu"]) == str(g["varlen.in_sha"])
+    for name, window in (("varlen.window", c["window"]), ("varlen.full", None)):
+        out = oattn.varlen_attention_ref(c["q"], c["k"], c["v"], c["cu"], c["scale"], window)
+        np.testing.assert_allclose(out, g[name], atol=3e-6, rtol=1e-5)

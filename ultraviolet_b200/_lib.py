@@ -52,6 +52,17 @@ class QkvArgs(C.Structure):
         ("B", C.c_int), ("H", C.c_int), ("K", C.c_int), ("hd", C.c_int), ("d", C.c_int), ("S", C.c_int),
         ("S_alloc", C.c_int), ("ring", C.c_int), ("ve_ch", C.c_int), ("n_pairs", C.c_int),
         ("rope_cs", C.c_void_p), ("gate_w", C.c_void_p), ("gate_out", C.c_void_p), ("gate_ch", C.c_int),
+        ("last_pos", C.c_void_p),
+    ]
+
+
+class PrefillAttnArgs(C.Structure):
+    """uv_prefill_attn_args (include/uvdecode.h)."""
+    _fields_ = [
+        ("qkv", C.c_void_p), ("dtype", C.c_int), ("ld", C.c_int64), ("cu_seqlens", C.c_void_p),
+        ("tile_cu", C.c_void_p), ("n_seq", C.c_int), ("max_tiles", C.c_int), ("out", C.c_void_p), ("ldo", C.c_int64),
+        ("H", C.c_int), ("K", C.c_int), ("hd", C.c_int), ("window", C.c_int), ("scale", C.c_float),
+        ("xsa_alpha", C.c_void_p), ("xsa_eps", C.c_float), ("gate_vals", C.c_void_p),
     ]
 
 
@@ -86,6 +97,7 @@ SIGNATURES = {
                                      C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]),
     "uv_qkv_post": (C.c_int, [C.c_void_p] * 13 + [C.c_int, C.c_int64] + [C.c_int] * 10 + [C.c_void_p]),
     "uv_qkv_post_args": (C.c_int, [C.POINTER(QkvArgs), C.c_void_p]),
+    "uv_prefill_attn": (C.c_int, [C.POINTER(PrefillAttnArgs), C.c_void_p]),
     "uv_qkv_attn": (C.c_int, [C.POINTER(QkvArgs), C.POINTER(AttnArgs), C.c_void_p]),
     "uv_resid_norm": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_int,
                                 C.c_void_p]),
@@ -96,6 +108,15 @@ SIGNATURES = {
                              C.c_int, C.c_int, C.c_void_p, C.c_void_p]),
     "uv_gemm_tc_swiglu": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int,
                                     C.c_void_p, C.c_void_p]),
+    "uv_gemm_sw": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_int64, C.c_int, C.c_int, C.c_int,
+                             C.c_int, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p]),
+    "uv_gemm_sw_qkv": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.POINTER(QkvArgs), C.c_void_p, C.c_int, C.c_int,
+                                 C.c_int, C.c_int, C.c_void_p, C.c_void_p]),
+    "uv_gemm_sw_swiglu": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int,
+                                    C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p]),
+    "uv_gemm_sw_resid": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64,
+                                   C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
+                                   C.c_void_p, C.c_void_p]),
     "uv_gemm_swiglu": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int,
                                  C.c_void_p]),
     "uv_gemm_resid_norm": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p,

@@ -261,6 +261,7 @@ extern "C" int uv_qkv_post_args(const uv_qkv_args* a, void* stream) {
     if (!a->gate_w || !a->xn || a->gate_ch < 1 || a->gate_ch > a->d) return UV_ERR_ARG;
     P.gate_w = a->gate_w, P.gate_out = a->gate_out, P.gate_ch = a->gate_ch;
   }
+  P.last_pos = a->last_pos;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (a->dtype == UV_F16) return launch_qkv_post<__half>(P, a->hd, st);
   if (a->dtype == UV_BF16) return launch_qkv_post<__nv_bfloat16>(P, a->hd, st);

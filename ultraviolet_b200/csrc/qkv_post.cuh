@@ -36,14 +36,23 @@ struct QkvPostParams {
   const void* gate_w;        // (H, gate_ch)
   float* gate_out;           // (B, H)
   int gate_ch;
+  // optional, packed prefill: last position of the row's sequence in this launch; ring caches then keep only the
+  // newest S positions of a sequence (no two rows of one launch write one slot)
+  const int64_t* last_pos;
 };
 
 // The head gate of Attention.post (ultraviolet/model.py:330-333) with its rounding points; lane-strided products,
 // then a warp sum.  Full warp; every lane returns the gate.
+// scaled: gx is the UN-normalised activation row and xs its RMS-norm factor; the normalised value is formed (and
+// rounded, as the stored one would be) on the fly.
 template <typename T>
-__device__ __forceinline__ float head_gate(const T* gx, const T* gw, int gate_ch, int lane) {
+__device__ __forceinline__ float head_gate(const T* gx, const T* gw, int gate_ch, int lane, float xs = 1.0f,
+                                           bool scaled = false) {
   float acc = 0.f;
-  for (int ch = lane; ch < gate_ch; ch += 32) acc += to_f32<T>(gx[ch]) * to_f32<T>(gw[ch]);
+  for (int ch = lane; ch < gate_ch; ch += 32) {
+    const float xv = scaled ? rnd<T>(to_f32<T>(gx[ch]) * xs) : to_f32<T>(gx[ch]);
+    acc += xv * to_f32<T>(gw[ch]);
+  }
   acc = rnd<T>(warp_sum(acc));
   return rnd<T>(2.0f * rnd<T>(1.0f / (1.0f + __expf(-acc))));
 }
@@ -77,9 +86,11 @@ inline int qkv_post_params(QkvPostParams* out, void* qkv, const void* xn, const 
 // post-processed values.  Called by a full warp.
 // TABLE: the rotation always reads P.rope_cs (the caller checked that it is there), so that no cosf / sinf code
 // is compiled into the kernel.
+// scaled: P.xn holds the un-normalised activation rows and xs is row b's RMS-norm factor (see head_gate).
 template <typename T, int HD, bool TABLE = false>
 __device__ __forceinline__ void qkv_post_compute(const QkvPostParams& P, int b, int hs, int lane,
-                                                 float (&x)[HD >= 32 ? HD / 32 : 1]) {
+                                                 float (&x)[HD >= 32 ? HD / 32 : 1], float xs = 1.0f,
+                                                 bool scaled = false) {
   constexpr int E = HD >= 32 ? HD / 32 : 1;
   const bool act = lane * E < HD;
   if (hs >= P.H + P.K) {
@@ -88,7 +99,10 @@ __device__ __forceinline__ void qkv_post_compute(const QkvPostParams& P, int b, 
       const T* xr = static_cast<const T*>(P.xn) + (int64_t)b * P.d;
       const T* gw = static_cast<const T*>(P.ve_gate) + (int64_t)kh * P.ve_ch;
       float acc = 0.f;
-      for (int ch = lane; ch < P.ve_ch; ch += 32) acc += to_f32<T>(xr[ch]) * to_f32<T>(gw[ch]);
+      for (int ch = lane; ch < P.ve_ch; ch += 32) {
+        const float xv = scaled ? rnd<T>(to_f32<T>(xr[ch]) * xs) : to_f32<T>(xr[ch]);
+        acc += xv * to_f32<T>(gw[ch]);
+      }
       acc = rnd<T>(warp_sum(acc));
       const float g = rnd<T>(2.0f * rnd<T>(1.0f / (1.0f + __expf(-acc))));
       int64_t t = P.tok[b];
@@ -142,7 +156,10 @@ __device__ __forceinline__ void qkv_post_store(const QkvPostParams& P, int b, in
   const bool isv = hs >= P.H + P.K;
   const int kh = isv ? hs - P.H - P.K : hs - P.H;
   int64_t p = P.pos[b];
-  if (P.ring) p = ((p % P.S) + P.S) % P.S;
+  if (P.ring) {
+    if (P.last_pos != nullptr && p + P.S <= P.last_pos[b]) return;  // a newer token of this launch owns the slot
+    p = ((p % P.S) + P.S) % P.S;
+  }
   if (p < 0 || p >= P.S) {
     if (lane == 0 && P.oob) atomicAdd(P.oob, 1);
     return;

@@ -128,14 +128,25 @@ class DecodeEngine:
         return self.arena.numel() * self.arena.element_size() + self.arena32.numel() * 4
 
     # ------------------------------------------------------------------------------------------------ scratch
+    BIG_ROWS = 2048  # batches above this (packed prompt prefill) share bucketed buffers instead of one set per size
+
     def scratch(self, B: int) -> dict:
+        if B > self.BIG_ROWS:
+            # prefill batches come in every size: one allocation per 4096-row bucket, handed out as [:B] views
+            cap = (B + 4095) // 4096 * 4096
+            big = self._scratch.get(cap) or self.scratch_exact(cap)
+            return {k: (v[:B] if isinstance(v, Tensor) and v.dim() >= 1 and v.size(0) == cap and k not in
+                        ("flags", "status", "oob") else v) for k, v in big.items()}
+        return self.scratch_exact(B)
+
+    def scratch_exact(self, B: int) -> dict:
         s = self._scratch.get(B)
         if s is None:
             cfg, dt, dev = self.cfg, self.dtype, self.device
             d, hd, H, K, f = cfg.d_model, cfg.head_dim, cfg.n_heads, cfg.n_kv_heads, cfg.d_ff
             e = lambda *shape: torch.empty(*shape, dtype=dt, device=dev)
             s = dict(x=e(B, d), xn=e(B, d), qkv=e(B, (H + 2 * K) * hd), z=e(B, H * hd), a=e(B, d), h=e(B, d),
-                     hn=e(B, d), gu=e(B, 2 * f), act=e(B, f), m=e(B, d), head=e(B, cfg.vocab_size),
+                     hn=e(B, d), gu=e(B, 2 * f), act=e(B, f), m=e(B, d),
                      tok=torch.zeros(B, dtype=torch.int64, device=dev),
                      logp=torch.zeros(B, dtype=torch.float32, device=dev),
                      counters=torch.zeros(B * K, dtype=torch.int32, device=dev),
@@ -189,10 +200,17 @@ class DecodeEngine:
 
     # ------------------------------------------------------------------------------------------------ one step
     def trunk(self, tok: Tensor, st, pos: Tensor, starts: Tensor, g_len: int | None = None,
-              num_splits: dict | None = None, row_map: Tensor | None = None, skip_attn: bool = False) -> Tensor:
+              num_splits: dict | None = None, row_map: Tensor | None = None, skip_attn: bool = False,
+              packed: dict | None = None) -> Tensor:
         """One token for every batch entry: writes K/V at `pos` and returns the final normed hidden (B, d) (a view
         of engine scratch, overwritten by the next call).  pos/starts are batch-indexed (B,) int64; row_map
-        optionally maps batch entries to cache rows."""
+        optionally maps batch entries to cache rows.
+
+        packed (prompt prefill): the batch entries are the tokens of whole prompts packed back to back --
+        dict(cu=int32 (n + 1,) first row of each prompt, tile_cu=int32 (n + 1,) first 16-token tile of each prompt,
+        n_seq, max_tiles, last_pos=int64 (B,) last position of the entry's prompt).  Attention then runs over the
+        unquantised keys / values of the batch itself (uv_prefill_attn) instead of the cache, and ring caches keep
+        only the newest positions of each prompt."""
         cfg, lib, dt = self.cfg, _lib.lib(), DTYPE_CODE[self.dtype]
         B = tok.size(0)
         s = self.scratch(B)
@@ -201,7 +219,8 @@ class DecodeEngine:
         w = self.w
         ns = num_splits or {}
         rm = row_map.data_ptr() if row_map is not None else None
-        fused = self.fused_gemm
+        fused = self.fused_gemm and packed is None
+        qkv_in_attn = self.qkv_in_attn and packed is None
         with torch.cuda.device(self.device):
             use_table = self.rope_table and not fused and cfg.rope_pairs > 0
             if use_table:  # one cos / sin table per step instead of cosf / sinf in every layer's prologue
@@ -239,11 +258,13 @@ class DecodeEngine:
                      qa.B, qa.H, qa.K, qa.hd, qa.d, qa.S, qa.S_alloc, qa.ring, qa.ve_ch,
                      qa.n_pairs) = (s["qkv"].data_ptr(), xn.data_ptr(), *post_args[:-1])
                     qa.rope_cs = s["rope_cs"].data_ptr() if use_table else None
-                    if self.qkv_in_attn:  # the attention launch below does uv_qkv_post's work in its prologue
+                    if packed is not None:
+                        qa.last_pos = packed["last_pos"].data_ptr()
+                    if qkv_in_attn:  # the attention launch below does uv_qkv_post's work in its prologue
                         pre = qa
                     else:
-                        if cfg.gate_channels and self.gate_pre:  # the gates depend on xn only: computed here, off the
-                            qa.gate_w = w[f"l{l}.attn_gate"].data_ptr()  # attention kernel's critical tail
+                        if cfg.gate_channels and (self.gate_pre or packed is not None):  # gates depend on xn only:
+                            qa.gate_w = w[f"l{l}.attn_gate"].data_ptr()  # computed off the attention kernel's tail
                             qa.gate_out, qa.gate_ch = s["gate"].data_ptr(), cfg.gate_channels
                             gate_vals = s["gate"]
                         _lib.check(lib.uv_qkv_post_args(C.byref(qa), sp), "uv_qkv_post")
@@ -254,7 +275,22 @@ class DecodeEngine:
                 else:
                     splits = ns.get("local") or default_splits(B * K, S, self.device)
                     window, ring = cfg.window, True
-                if skip_attn:
+                if packed is not None and not skip_attn:
+                    pa = _lib.PrefillAttnArgs()
+                    pa.qkv, pa.dtype, pa.ld = s["qkv"].data_ptr(), dt, s["qkv"].stride(0)
+                    pa.cu_seqlens, pa.tile_cu = packed["cu"].data_ptr(), packed["tile_cu"].data_ptr()
+                    pa.n_seq, pa.max_tiles = int(packed["n_seq"]), int(packed["max_tiles"])
+                    pa.out, pa.ldo = s["z"].data_ptr(), s["z"].stride(0)
+                    pa.H, pa.K, pa.hd, pa.window = H, K, hd, (0 if glob else cfg.window)
+                    pa.scale = cfg.attn_scale
+                    if cfg.xsa:
+                        pa.xsa_alpha, pa.xsa_eps = self.xsa[l].data_ptr(), cfg.xsa_eps
+                    if gate_vals is not None:
+                        pa.gate_vals = gate_vals.data_ptr()
+                    elif cfg.gate_channels:
+                        raise RuntimeError("packed prefill needs the precomputed head gates (UVDECODE_GATE_PRE=1)")
+                    _lib.check(lib.uv_prefill_attn(C.byref(pa), sp), "uv_prefill_attn")
+                elif skip_attn:
                     # the reference's A/B profiling switch (fast_decode.py:312-313): the step timed without its
                     # attention kernel -- the "attention output" is the query itself (no XSA, no head gate: both live
                     # in the attention kernel's epilogue here).  Outputs are meaningless by design.
@@ -292,8 +328,15 @@ class DecodeEngine:
 
     def head(self, hfin: Tensor) -> Tensor:
         """Raw tied-head output (B, V) in the activation dtype (the GEMM of MathLM.logits, model.py:826)."""
-        s = self.scratch(hfin.size(0))
-        torch.mm(hfin, self.w["embed"].t(), out=s["head"])
+        out = self.head_buffer(hfin.size(0))
+        torch.mm(hfin, self.w["embed"].t(), out=out)
+        return out
+
+    def head_buffer(self, B: int) -> Tensor:
+        """(B, V) buffer of the raw head output (allocated on first use: packed prefill batches never need it)."""
+        s = self.scratch(B)
+        if "head" not in s:
+            s["head"] = torch.empty(B, self.cfg.vocab_size, dtype=self.dtype, device=self.device)
         return s["head"]
 
     def logits(self, h: Tensor) -> Tensor:

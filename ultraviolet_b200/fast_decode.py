@@ -4,12 +4,11 @@
 int8 ``(B, K, S, hd)`` with S = max_len (global layers) or min(window, max_len) (local ring), ``k_scale[l],
 v_scale[l]`` fp16 ``(B, K, S)``, ``pos`` / ``starts`` int64 ``(B,)``, ``host_pos``.
 
-``decode_step_fast`` is one call of ``DecodeEngine.trunk`` (+ head).  ``prefill_fast`` feeds the left-padded prompt
-through the SAME decode kernels one position at a time ("prefill as decode"): row i starts consuming at position
-starts[i], so positions, ring slots, ``st.pos`` / ``st.starts`` and the int8 cache layout are those of the reference's
-padded prefill; prompt tokens attend to the int8-quantised keys of their prefix instead of the unquantised ones the
-reference's SDPA prefill sees (same model, int8 rounding noise only).  A packed varlen prefill kernel is the next
-step of this path and is not built yet.
+``decode_step_fast`` is one call of ``DecodeEngine.trunk`` (+ head).  ``prefill_fast`` packs the prompts of a batch
+back to back and runs them through the same GEMMs and row kernels as ONE batch of sum(len) rows, with a packed
+varlen attention kernel (uv_prefill_attn) over the unquantised keys / values and the int8 cache written by the same
+fused quantise + append as in decode; positions, ring slots, ``st.pos`` / ``st.starts`` and the cache layout are those
+of the reference's left-padded prefill.
 """
 from __future__ import annotations
 
@@ -80,63 +79,77 @@ def decode_step_fast(self, tok: Tensor, st: KernelDecodeState, g_len: int, skip_
     return h if return_hidden else eng.logits(h)
 
 
+PREFILL_CHUNK_TOKENS = 32768   # packed rows per pass (activations of one pass: ~19 KB per row)
+
+
 @torch.no_grad()
 def prefill_fast(self, idx: Tensor, starts: Tensor, st: KernelDecodeState, rows: Tensor | None = None) -> Tensor:
     """idx (n, T) left-padded; writes the cache rows `rows` (default all) from position starts[i] on, sets their
-    pos = T / starts, returns the last-position logits (n, V) (contract of fast_decode.py:70-114)."""
+    pos = T / starts, returns the last-position logits (n, V) (contract of fast_decode.py:70-114).
+
+    The prompts are packed back to back (pad columns are never computed) and go through the step's kernels as one
+    batch of sum(len) rows per pass, with attention by the packed varlen kernel over the unquantised keys / values
+    (the packed route of the reference, fast_decode.py:117-163, :210-269); positions are those of the left-padded
+    frame (token j of row i sits at starts[i] + j), so ring slots and the int8 cache layout are the reference's."""
     eng = _engine(self)
     n, T = idx.shape
     if T > st.max_len:
         raise AssertionError("prompt longer than the cache")
+    dev = idx.device
     full = rows is None
     if full:
         if n != st.B:
             raise AssertionError("prefill without rows needs one prompt per cache row")
-        rows = torch.arange(n, device=idx.device)
+        rows = torch.arange(n, device=dev)
     rows = rows.to(torch.int64)
     starts = starts.to(torch.int64).contiguous()
-    idx_t = idx.t().contiguous()  # (T, n): one contiguous token vector per position
-    h = _prefill_positions(eng, st, idx_t, starts, None if full else rows, T)
+    lens_h = (T - starts).clamp_(min=0).cpu().numpy()   # the one host round trip (the reference has one too, :111)
+    hfin = torch.zeros(n, eng.cfg.d_model, dtype=eng.dtype, device=dev)
+    # passes over whole prompts, at most PREFILL_CHUNK_TOKENS packed rows each (one prompt alone may exceed it)
+    a = 0
+    while a < n:
+        b, tot = a, 0
+        while b < n and (b == a or tot + int(lens_h[b]) <= PREFILL_CHUNK_TOKENS):
+            tot += int(lens_h[b])
+            b += 1
+        if tot > 0:
+            hfin[a:b] = prefill_packed(eng, st, idx[a:b], starts[a:b], rows[a:b], lens_h[a:b])
+        a = b
     st.starts[rows] = starts
     st.pos[rows] = T
     st.host_pos[rows.cpu().numpy()] = T
-    return eng.logits(h)
+    return eng.logits(hfin)
 
 
-def _prefill_positions(eng, st, idx_t: Tensor, starts: Tensor, rows, T: int) -> Tensor:
-    """Feed positions 0..T-1 of a left-padded sub-batch through the decode kernels.  The step for one position is
-    captured once as a CUDA graph reading a static token / position pair and replayed T times (positions differ
-    only through those two device tensors); short prompts run eagerly."""
-    n = idx_t.size(1)
-    dev = idx_t.device
-    pos = torch.zeros(n, dtype=torch.int64, device=dev)
-    if T < 8:
-        h = None
-        for t in range(T):
-            pos.fill_(t)
-            h = eng.trunk(idx_t[t], st, pos, starts, g_len=T, row_map=rows)
-        return h
-    tok = torch.zeros(n, dtype=torch.int64, device=dev)
-    out = {}
+def pack_prompts(idx: Tensor, starts: Tensor, rows: Tensor, lens_h) -> dict:
+    """Packed description of a left-padded (n, T) prompt batch: per packed row its token, position and cache row,
+    plus the prefix sums the varlen attention kernel walks.  lens_h: host array of prompt lengths (T - starts)."""
+    n, T = idx.shape
+    dev = idx.device
+    t = torch.arange(T, device=dev)
+    keep = t[None, :] >= starts[:, None]                      # row-major selection = prompt after prompt
+    tok = idx[keep].contiguous()
+    pos = t.expand(n, T)[keep].contiguous()
+    cache_row = rows[:, None].expand(n, T)[keep].contiguous()
+    lens = np.asarray(lens_h, dtype=np.int64)
+    cu = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
+    tile_cu = np.concatenate([[0], np.cumsum((lens + 15) // 16)]).astype(np.int32)
+    M = int(cu[-1])
+    return dict(tok=tok, pos=pos, rows=cache_row, M=M, n_seq=n, max_tiles=int(tile_cu[-1]),
+                cu=torch.from_numpy(cu).to(dev), tile_cu=torch.from_numpy(tile_cu).to(dev),
+                last_pos=torch.full((M,), T - 1, dtype=torch.int64, device=dev),
+                last_row=torch.from_numpy(np.maximum(cu[1:].astype(np.int64) - 1, 0)).to(dev),
+                empty=torch.from_numpy(lens == 0).to(dev))
 
-    def body():
-        out["h"] = eng.trunk(tok, st, pos, starts, g_len=T, row_map=rows)
-        pos.add_(1)
 
-    tok.copy_(idx_t[0])
-    side = torch.cuda.Stream(dev)
-    side.wait_stream(torch.cuda.current_stream(dev))
-    with torch.cuda.stream(side):   # warm-up run of position 0 (allocates scratch); it is simply redone below
-        body()
-        pos.zero_()
-    torch.cuda.current_stream(dev).wait_stream(side)
-    g = torch.cuda.CUDAGraph()
-    with torch.cuda.graph(g, capture_error_mode="thread_local"):
-        body()
-    for t in range(T):
-        tok.copy_(idx_t[t])
-        g.replay()
-    return out["h"].clone()  # the graph's private pool goes away with the graph
+def prefill_packed(eng, st, idx: Tensor, starts: Tensor, rows: Tensor, lens_h) -> Tensor:
+    """One packed pass: returns the final normed hidden state of every prompt's last token (n, d) (zeros for an
+    empty prompt)."""
+    pk = pack_prompts(idx, starts, rows, lens_h)
+    zero = torch.zeros(pk["M"], dtype=torch.int64, device=idx.device)
+    h = eng.trunk(pk["tok"], st, pk["pos"], zero, g_len=idx.size(1), row_map=pk["rows"], packed=pk)
+    out = h[pk["last_row"]]
+    return out.masked_fill(pk["empty"][:, None], 0)
 
 
 def patch_model(model, kv_dtype: str = "int8", num_splits: dict | None = None, backend: str = "auto",

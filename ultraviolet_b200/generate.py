@@ -78,7 +78,7 @@ class DecodeRunner:
     def out_logits(self) -> Tensor:
         """fp32 softcapped logits of the last step (computed on demand from the raw head output)."""
         a, b, c = self.eng.cfg.softcap
-        return a * torch.sigmoid((self.eng.scratch(self.st.B)["head"].float() + b) / c)
+        return a * torch.sigmoid((self.eng.head_buffer(self.st.B).float() + b) / c)
 
     def _body(self, g_len: int) -> None:
         st, eng = self.st, self.eng
