@@ -181,6 +181,11 @@ int uv_embed_norm(const int64_t* tok, const void* embed, int dtype, int64_t voca
  * n_pairs, then the sines, each rounded to dtype (the cos / sin operands of apply_rope, fast_decode.py:286-290). */
 int uv_embed_norm_rope(const int64_t* tok, const void* embed, int dtype, int64_t vocab, int d, void* x, void* xn,
                        int B, const int64_t* pos, const float* inv_freq, int n_pairs, float* rope_cs, void* stream);
+/* The same kernel for the tensor-core GEMM path: also writes the sum of squares of every x row as ss_out (ss_parts,
+ * ss_ld) fp32 (the whole sum in part 0, zeros in the rest), the form uv_gemm_sw* take as ss_in; xn may then be NULL. */
+int uv_embed_norm_ss(const int64_t* tok, const void* embed, int dtype, int64_t vocab, int d, void* x, void* xn, int B,
+                     const int64_t* pos, const float* inv_freq, int n_pairs, float* rope_cs, float* ss_out,
+                     int ss_parts, int ss_ld, void* stream);
 int uv_qkv_post(void* qkv, const void* xn, const int64_t* tok, const void* value_embed, const void* ve_gate,
                 const float* inv_freq, const int64_t* pos, int8_t* k_cache, int8_t* v_cache, uint16_t* k_scale,
                 uint16_t* v_scale, const int64_t* row_map, int* oob_count, int dtype, int64_t vocab, int B, int H, int K,

@@ -161,9 +161,9 @@ def test_gemm_sw_qkv_equals_gemm_then_qkv_post():
         res[fused] = (qkv.float(), kc.clone(), vc.clone(), ks.float(), vs.float(), gates.clone())
     a, b = res[False], res[True]
     assert (a[0] - b[0]).abs().max().item() <= a[0].abs().max().item() * 2.0 ** -6
-    for i in (1, 2):                                   # int8 cache bytes: at most one step on a small fraction
-        dq = (a[i].int() - b[i].int()).abs()
-        assert int(dq.max()) <= 1 and (dq > 0).float().mean().item() < 0.05
+    for i in (1, 2):   # int8 cache bytes: a step on a small fraction (the deferred norm moves the projection by one
+        dq = (a[i].int() - b[i].int()).abs()   # bf16 rounding, which the per-head norm and RoPE can double)
+        assert int(dq.max()) <= 2 and (dq > 0).float().mean().item() < 0.05 and (dq > 1).float().mean().item() < 1e-3
     for i in (3, 4):
         torch.testing.assert_close(a[i], b[i], rtol=2e-2, atol=1e-6)
     torch.testing.assert_close(a[5], b[5], rtol=2e-2, atol=2e-2)

@@ -105,7 +105,7 @@ def test_packed_prefill_vs_oracle_prefill(name):
     max_len = T + 4
     st = m.new_state(n, max_len)
     lg = m.prefill(torch.from_numpy(idx).to(DEV), torch.from_numpy(starts).to(DEV), st).float().cpu().numpy()
-    W = oracle_weights(m, "bf16")
+    W = oracle_weights(build_model(spec), "bf16")
     ost = om.State(cfg, n, max_len)
     ref = om.prefill(W, cfg, idx, starts, ost)
     assert np.abs(lg - ref).max() <= 5e-2 * np.abs(ref).max(), np.abs(lg - ref).max()

@@ -27,6 +27,9 @@ class _FakeEngine:
     def scratch(self, B):
         return self._s
 
+    def check_status(self, B=None):
+        return {"attn_status": 0, "kv_oob": 0}
+
 
 def _fake_token(req, gen, eos_every):
     t = (req * 7919 + gen * 104729) % 1000 + 1

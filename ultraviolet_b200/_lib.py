@@ -95,6 +95,9 @@ SIGNATURES = {
                                 C.c_void_p]),
     "uv_embed_norm_rope": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int64, C.c_int, C.c_void_p, C.c_void_p,
                                      C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]),
+    "uv_embed_norm_ss": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int64, C.c_int, C.c_void_p, C.c_void_p,
+                                   C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_int,
+                                   C.c_void_p]),
     "uv_qkv_post": (C.c_int, [C.c_void_p] * 13 + [C.c_int, C.c_int64] + [C.c_int] * 10 + [C.c_void_p]),
     "uv_qkv_post_args": (C.c_int, [C.POINTER(QkvArgs), C.c_void_p]),
     "uv_prefill_attn": (C.c_int, [C.POINTER(PrefillAttnArgs), C.c_void_p]),

@@ -52,7 +52,8 @@ __global__ void __launch_bounds__(128) embed_norm_kernel(const int64_t* __restri
                                                          int64_t vocab, int d, T* __restrict__ x, T* __restrict__ xn,
                                                          int B, const int64_t* __restrict__ pos,
                                                          const float* __restrict__ inv_freq, int n_pairs,
-                                                         float* __restrict__ rope_cs) {
+                                                         float* __restrict__ rope_cs, float* __restrict__ ss_out,
+                                                         int ss_parts, int ss_ld) {
   const int lane = threadIdx.x & 31;
   const int row = blockIdx.x * 4 + (threadIdx.x >> 5);
   pdl_wait();
@@ -94,15 +95,23 @@ __global__ void __launch_bounds__(128) embed_norm_kernel(const int64_t* __restri
       }
     }
   }
-  inv = rsqrtf(warp_sum(ss) / (float)d + RMS_EPS);
+  ss = warp_sum(ss);
+  if (ss_out != nullptr && lane < ss_parts) {
+    // the row's sum of squares in the per-tile form the tensor-core GEMMs read (deferred RMS norm): all of it in
+    // part 0, zeros in the others
+    ss_out[(int64_t)lane * ss_ld + row] = lane == 0 ? ss : 0.f;
+  }
+  inv = rsqrtf(ss / (float)d + RMS_EPS);
 #pragma unroll
   for (int j = 0; j < ROW_J; ++j) {
     const int i = 8 * lane + 256 * j;
     if (i < d) {
       st8<T>(x + (int64_t)row * d + i, v[j]);
+      if (xn != nullptr) {
 #pragma unroll
-      for (int k = 0; k < 8; ++k) v[j][k] *= inv;
-      st8<T>(xn + (int64_t)row * d + i, v[j]);
+        for (int k = 0; k < 8; ++k) v[j][k] *= inv;
+        st8<T>(xn + (int64_t)row * d + i, v[j]);
+      }
     }
   }
 }
@@ -226,19 +235,30 @@ using namespace uv;
 extern "C" int uv_embed_norm_rope(const int64_t* tok, const void* embed, int dtype, int64_t vocab, int d, void* x,
                                   void* xn, int B, const int64_t* pos, const float* inv_freq, int n_pairs,
                                   float* rope_cs, void* stream) {
+  if (!xn) return B == 0 ? UV_OK : UV_ERR_ARG;
+  return uv_embed_norm_ss(tok, embed, dtype, vocab, d, x, xn, B, pos, inv_freq, n_pairs, rope_cs, nullptr, 0, 0,
+                          stream);
+}
+
+extern "C" int uv_embed_norm_ss(const int64_t* tok, const void* embed, int dtype, int64_t vocab, int d, void* x,
+                                void* xn, int B, const int64_t* pos, const float* inv_freq, int n_pairs,
+                                float* rope_cs, float* ss_out, int ss_parts, int ss_ld, void* stream) {
   if (B == 0) return UV_OK;
-  if (!tok || !embed || !x || !xn || B < 0 || vocab < 1) return UV_ERR_ARG;
+  if (!tok || !embed || !x || B < 0 || vocab < 1) return UV_ERR_ARG;
+  if (!xn && !ss_out) return UV_ERR_ARG;
+  if (ss_out && (ss_parts < 1 || ss_parts > 32 || ss_ld < B)) return UV_ERR_ARG;
   if (rope_cs && (!pos || !inv_freq || n_pairs < 1)) return UV_ERR_ARG;
   if (d < 8 || (d & 7) || d > ROW_MAX) return UV_ERR_SHAPE;  // rows are moved as 16-byte vectors
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const unsigned grid = (unsigned)((B + 3) / 4);
   if (dtype == UV_F16)
     launch_pdl(embed_norm_kernel<__half>, dim3(grid), dim3(128), 0, st, tok, static_cast<const __half*>(embed), vocab,
-               d, static_cast<__half*>(x), static_cast<__half*>(xn), B, pos, inv_freq, n_pairs, rope_cs);
+               d, static_cast<__half*>(x), static_cast<__half*>(xn), B, pos, inv_freq, n_pairs, rope_cs, ss_out, ss_parts,
+               ss_ld);
   else if (dtype == UV_BF16)
     launch_pdl(embed_norm_kernel<__nv_bfloat16>, dim3(grid), dim3(128), 0, st, tok,
                static_cast<const __nv_bfloat16*>(embed), vocab, d, static_cast<__nv_bfloat16*>(x),
-               static_cast<__nv_bfloat16*>(xn), B, pos, inv_freq, n_pairs, rope_cs);
+               static_cast<__nv_bfloat16*>(xn), B, pos, inv_freq, n_pairs, rope_cs, ss_out, ss_parts, ss_ld);
   else return UV_ERR_DTYPE;
   return check_launch();
 }

@@ -10,7 +10,9 @@
 //
 // Split-K: the K range can be cut over a thread-block cluster (grid.z = cluster.z = KS <= 8).  Every CTA leaves its
 // fp32 partial tile in its own shared memory; after one cluster barrier rank r sums batch columns
-// [r * BN / KS, (r + 1) * BN / KS) of all partials through distributed shared memory and runs the epilogue for them.
+// [r * BN / KS, (r + 1) * BN / KS) of all partials through distributed shared memory (all KS loads in flight at once)
+// and runs the epilogue for them.  (Pushing the columns to their owners with st.shared::cluster instead measured
+// 1.5-2 us slower per launch: 32 scalar remote stores per thread.)
 //
 // Epilogues (thread = TMEM lane = feature reads its BN columns, scales them, and parks them transposed in shared
 // memory; then a warp owns a batch row of 128 features):
@@ -113,6 +115,7 @@ __global__ void __launch_bounds__(SW_THREADS) gemm_sw_kernel(const __grid_consta
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = tmem_slot;
+  pdl_trigger();   // the next kernel of the step may be scheduled now: it only touches its own weights until its wait
 
   auto load_w = [&](int kb, int s) {
     const uint32_t bar = tc_smem_u32(&full_bar[s]);
@@ -137,7 +140,6 @@ __global__ void __launch_bounds__(SW_THREADS) gemm_sw_kernel(const __grid_consta
     for (int kb = 0; kb < pre; ++kb) load_w(kb, kb);
   }
   pdl_wait();      // everything below may read what the previous kernel wrote
-  pdl_trigger();
 
   if (warp == 0 && lane == 0) {
     // ---- copy thread
@@ -188,9 +190,11 @@ __global__ void __launch_bounds__(SW_THREADS) gemm_sw_kernel(const __grid_consta
   const bool dead = dead_sm != 0;
   if (dead && tid == 0 && P.status) atomicOr(P.status, 4);
 
-  // ---- stage 1: thread = feature (TMEM lane) parks its BN columns, scaled, as T32[b][feature] (aliases the ring:
-  //      every requested tile has been consumed by an MMA that has completed)
-  float* T32 = reinterpret_cast<float*>(sw_smem + (base - tc_smem_u32(sw_smem)));
+  // ---- stage 1: thread = feature (TMEM lane) parks its BN columns, transposed, as T32[b][feature] behind the
+  //      stage ring
+  const int rows_per = BN / P.ksplit;
+  float* T32 = reinterpret_cast<float*>(sw_smem + (base - tc_smem_u32(sw_smem)) + (size_t)NS * STAGE);
+  const uint32_t t32_addr = tc_smem_u32(T32);
   if (!dead) {
     const uint32_t taddr = tmem + ((uint32_t)(warp * 32) << 16);
 #pragma unroll
@@ -212,21 +216,23 @@ __global__ void __launch_bounds__(SW_THREADS) gemm_sw_kernel(const __grid_consta
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"((uint32_t)TCOLS) : "memory");
   if (P.ksplit > 1) sw_cluster_sync();
 
-  // ---- stage 2: rank kr finishes batch rows [kr * BN / KS, (kr + 1) * BN / KS) of the tile; a warp owns a row,
+  // ---- stage 2: rank kr finishes batch rows [kr * rows_per, (kr + 1) * rows_per) of the tile; a warp owns a row,
   //      a lane 4 consecutive features
-  const int rows_per = BN / P.ksplit;
-  const uint32_t t32_addr = tc_smem_u32(T32);
   if (!dead)
     for (int rr = warp; rr < rows_per; rr += SW_THREADS / 32) {
       const int bl = kr * rows_per + rr, b = b0 + bl;
       if (b >= P.M) continue;  // warp-uniform
       float4 acc;
       if (P.ksplit > 1) {
-        acc = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (int p = 0; p < P.ksplit; ++p) {
-          const float4 q = sw_ld_peer_f4(t32_addr + (uint32_t)(bl * SW_PITCH + 4 * lane) * 4u, (uint32_t)p);
-          acc.x += q.x, acc.y += q.y, acc.z += q.z, acc.w += q.w;
-        }
+        float4 q[8];
+        const uint32_t a = t32_addr + (uint32_t)(bl * SW_PITCH + 4 * lane) * 4u;
+#pragma unroll
+        for (int p = 0; p < 8; ++p)
+          if (p < P.ksplit) q[p] = sw_ld_peer_f4(a, (uint32_t)p);
+        acc = q[0];
+#pragma unroll
+        for (int p = 1; p < 8; ++p)
+          if (p < P.ksplit) acc.x += q[p].x, acc.y += q[p].y, acc.z += q[p].z, acc.w += q[p].w;
       } else {
         acc = *reinterpret_cast<const float4*>(T32 + bl * SW_PITCH + 4 * lane);
       }
@@ -311,7 +317,7 @@ static int launch_sw(const CUtensorMap& tw, const CUtensorMap& tx, const GemmSwP
   auto kern = gemm_sw_kernel<BN, EPI>;
   const size_t ring = (size_t)P.stages * (128 * TC_BK * 2 + BN * TC_BK * 2);
   const size_t t32 = (size_t)BN * SW_PITCH * sizeof(float);
-  const size_t smem = (ring > t32 ? ring : t32) + 1024;
+  const size_t smem = ring + t32 + 1024;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) {
     set_last_cuda_error((int)e);
@@ -334,7 +340,7 @@ static void sw_plan(int M, int n_tiles, int K, int bn_hint, int ks_hint, int* bn
   const int per = (nk + s - 1) / s;
   const size_t stage = (size_t)128 * TC_BK * 2 + (size_t)b * TC_BK * 2;
   int st = per;
-  const int cap = (int)((200 * 1024) / stage);
+  const int cap = (int)((220 * 1024 - (size_t)b * SW_PITCH * sizeof(float)) / stage);
   if (st > cap) st = cap;
   if (st > SW_MAX_STAGES) st = SW_MAX_STAGES;
   if (st < 1) st = 1;

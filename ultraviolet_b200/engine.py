@@ -88,6 +88,16 @@ class DecodeEngine:
         self.rope_table = os.environ.get("UVDECODE_ROPE_TABLE", "1") != "0"
         # attention output gates computed by uv_qkv_post (they depend on xn only) instead of in the attention epilogue
         self.gate_pre = os.environ.get("UVDECODE_GATE_PRE", "1") != "0"
+        # GEMMs on this library's own tcgen05 kernels with the row kernels in their epilogues and the RMS norms
+        # deferred into the consuming GEMM (csrc/gemm_sw.cu): 5 launches per layer instead of 9.  bf16 only, shapes of
+        # the uv-50m family (head_dim 64, every GEMM dimension a multiple of 64 / 128).  UVDECODE_TC_GEMM=0 turns it
+        # off (library GEMMs + row kernels).
+        self.tc_gemm_ok = (dtype == torch.bfloat16 and hd == 64 and d % 128 == 0 and (H * hd) % 64 == 0
+                           and f % 64 == 0 and (H + 2 * K) % 2 == 0 and d // 128 <= 32
+                           and (cfg.rope_pairs == 0 or self.rope_table))
+        self.tc_gemm = os.environ.get("UVDECODE_TC_GEMM", "0") == "1" and self.tc_gemm_ok
+        self.tc_hints = {k: tuple(int(v) for v in os.environ.get(f"UVDECODE_TC_{k.upper()}", d_).split(","))
+                         for k, d_ in (("qkv", "0,0"), ("wo", "0,0"), ("gu", "0,0"), ("down", "0,0"))}
         self.n_sm = torch.cuda.get_device_properties(self.device).multi_processor_count
         _lib.lib()
 
@@ -152,7 +162,9 @@ class DecodeEngine:
                      counters=torch.zeros(B * K, dtype=torch.int32, device=dev),
                      flags=torch.zeros(2, dtype=torch.int32, device=dev),
                      rope_cs=torch.zeros(B, 2 * max(cfg.rope_pairs, 1), dtype=torch.float32, device=dev),
-                     gate=torch.zeros(B, H, dtype=torch.float32, device=dev), ws={})
+                     gate=torch.zeros(B, H, dtype=torch.float32, device=dev), ws={},
+                     ss_x=torch.zeros(max(d // 128, 1), B, dtype=torch.float32, device=dev),
+                     ss_h=torch.zeros(max(d // 128, 1), B, dtype=torch.float32, device=dev))
             # device words the kernels raise on silent failures: [0] attention status (bit 0: a bulk copy did not
             # land in time, outputs of that launch are undefined), [1] count of skipped out-of-range KV writes
             s["status"], s["oob"] = s["flags"][0:1], s["flags"][1:2]
@@ -185,6 +197,8 @@ class DecodeEngine:
     def launches_per_step(self) -> int:
         """Kernel launches of one trunk + head call (the sampler is one more)."""
         n = self.cfg.n_layers
+        if self.tc_gemm:
+            return 1 + 5 * n + 2
         if self.fused_gemm:
             return 1 + 5 * n + 1
         return 1 + (8 if self.qkv_in_attn else 9) * n + 1
@@ -221,6 +235,8 @@ class DecodeEngine:
         rm = row_map.data_ptr() if row_map is not None else None
         fused = self.fused_gemm and packed is None
         qkv_in_attn = self.qkv_in_attn and packed is None
+        if self.tc_gemm and not fused and not qkv_in_attn and B <= self.BIG_ROWS:
+            return self._trunk_tc(tok, st, pos, starts, g_len, ns, rm, row_map, skip_attn, packed)
         with torch.cuda.device(self.device):
             use_table = self.rope_table and not fused and cfg.rope_pairs > 0
             if use_table:  # one cos / sin table per step instead of cosf / sinf in every layer's prologue
@@ -276,20 +292,7 @@ class DecodeEngine:
                     splits = ns.get("local") or default_splits(B * K, S, self.device)
                     window, ring = cfg.window, True
                 if packed is not None and not skip_attn:
-                    pa = _lib.PrefillAttnArgs()
-                    pa.qkv, pa.dtype, pa.ld = s["qkv"].data_ptr(), dt, s["qkv"].stride(0)
-                    pa.cu_seqlens, pa.tile_cu = packed["cu"].data_ptr(), packed["tile_cu"].data_ptr()
-                    pa.n_seq, pa.max_tiles = int(packed["n_seq"]), int(packed["max_tiles"])
-                    pa.out, pa.ldo = s["z"].data_ptr(), s["z"].stride(0)
-                    pa.H, pa.K, pa.hd, pa.window = H, K, hd, (0 if glob else cfg.window)
-                    pa.scale = cfg.attn_scale
-                    if cfg.xsa:
-                        pa.xsa_alpha, pa.xsa_eps = self.xsa[l].data_ptr(), cfg.xsa_eps
-                    if gate_vals is not None:
-                        pa.gate_vals = gate_vals.data_ptr()
-                    elif cfg.gate_channels:
-                        raise RuntimeError("packed prefill needs the precomputed head gates (UVDECODE_GATE_PRE=1)")
-                    _lib.check(lib.uv_prefill_attn(C.byref(pa), sp), "uv_prefill_attn")
+                    self._prefill_attn(s, packed, l, gate_vals, sp)
                 elif skip_attn:
                     # the reference's A/B profiling switch (fast_decode.py:312-313): the step timed without its
                     # attention kernel -- the "attention output" is the query itself (no XSA, no head gate: both live
@@ -325,6 +328,108 @@ class DecodeEngine:
                 _lib.check(lib.uv_resid_norm(h.data_ptr(), s["m"].data_ptr(), lam[2:].data_ptr(), dt, d,
                                              x.data_ptr(), xn.data_ptr(), B, sp), "uv_resid_norm")
         return xn  # rms_norm of the last residual stream == the final norm (fast_decode.py:332-334)
+
+    def _trunk_tc(self, tok, st, pos, starts, g_len, ns, rm, row_map, skip_attn, packed) -> Tensor:
+        """The step on the tensor-core GEMM path: per layer  uv_gemm_sw_qkv -> attention -> uv_gemm_sw_resid (wo) ->
+        uv_gemm_sw_swiglu -> uv_gemm_sw_resid (down); the residual stream stays un-normalised and every consumer
+        applies the RMS norm to its own result (per-tile sums of squares travel in ss_x / ss_h)."""
+        cfg, lib, dt = self.cfg, _lib.lib(), DTYPE_CODE[self.dtype]
+        B = tok.size(0)
+        s = self.scratch(B)
+        d, hd, H, K, f = cfg.d_model, cfg.head_dim, cfg.n_heads, cfg.n_kv_heads, cfg.d_ff
+        sp = stream_ptr(self.device)
+        w = self.w
+        parts = d // 128
+        x, h, xn = s["x"], s["h"], s["xn"]
+        ss_x, ss_h = s["ss_x"], s["ss_h"]
+        ss_ld = ss_x.stride(0)
+        status = s["status"].data_ptr()
+        qkv3 = s["qkv"].view(B, H + 2 * K, hd)
+        q, v_cur = qkv3[:, :H], qkv3[:, H + K:]
+        z3 = s["z"].view(B, H, hd)
+        hq, hw, hg, hdn = (self.tc_hints[k] for k in ("qkv", "wo", "gu", "down"))
+        with torch.cuda.device(self.device):
+            _lib.check(lib.uv_embed_norm_ss(tok.data_ptr(), w["embed"].data_ptr(), dt, cfg.vocab_size, d,
+                                            x.data_ptr(), None, B, pos.data_ptr(), self.inv_freq.data_ptr(),
+                                            cfg.rope_pairs, s["rope_cs"].data_ptr() if cfg.rope_pairs else None,
+                                            ss_x.data_ptr(), parts, ss_ld, sp), "uv_embed_norm_ss")
+            for l in range(cfg.n_layers):
+                glob = cfg.is_global(l)
+                kc, vc, ks, vs = st.k[l], st.v[l], st.k_scale[l], st.v_scale[l]
+                S = kc.size(2)
+                rope = ((not glob) or cfg.global_rope) and cfg.rope_pairs > 0
+                qa = _lib.QkvArgs()
+                qa.qkv, qa.tok, qa.pos = s["qkv"].data_ptr(), tok.data_ptr(), pos.data_ptr()
+                if self.use_ve and cfg.has_ve(l):
+                    qa.value_embed, qa.ve_gate = w["value_embed"].data_ptr(), w[f"l{l}.ve_gate"].data_ptr()
+                if rope:
+                    qa.inv_freq, qa.rope_cs = self.inv_freq.data_ptr(), s["rope_cs"].data_ptr()
+                qa.k_cache, qa.v_cache, qa.k_scale, qa.v_scale = kc.data_ptr(), vc.data_ptr(), ks.data_ptr(), vs.data_ptr()
+                qa.row_map, qa.oob_count, qa.dtype, qa.vocab = rm, s["oob"].data_ptr(), dt, cfg.vocab_size
+                qa.B, qa.H, qa.K, qa.hd, qa.d, qa.S, qa.S_alloc = B, H, K, hd, d, S, kc.stride(1) // hd
+                qa.ring, qa.ve_ch, qa.n_pairs = int(not glob), cfg.ve_gate_channels, cfg.rope_pairs
+                gate_vals = None
+                if cfg.gate_channels:
+                    qa.gate_w, qa.gate_out, qa.gate_ch = w[f"l{l}.attn_gate"].data_ptr(), s["gate"].data_ptr(), \
+                        cfg.gate_channels
+                    gate_vals = s["gate"]
+                if packed is not None:
+                    qa.last_pos = packed["last_pos"].data_ptr()
+                _lib.check(lib.uv_gemm_sw_qkv(x.data_ptr(), d, w[f"l{l}.wqkv"].data_ptr(), C.byref(qa),
+                                              ss_x.data_ptr(), parts, ss_ld, hq[0], hq[1], status, sp),
+                           "uv_gemm_sw_qkv")
+                if skip_attn:
+                    z3.copy_(q)
+                elif packed is not None:
+                    self._prefill_attn(s, packed, l, gate_vals, sp)
+                else:
+                    if glob:
+                        splits = ns.get("global") or default_splits(B * K, min(g_len or S, S), self.device)
+                        window, ring = 0, False
+                    else:
+                        splits = ns.get("local") or default_splits(B * K, S, self.device)
+                        window, ring = cfg.window, True
+                    attn_launch(q, kc, vc, pos, starts, cfg.attn_scale, window, ring, ks, vs, splits, z3,
+                                self._workspace(s, B, splits), v_cur=v_cur,
+                                xsa_alpha=self.xsa[l] if cfg.xsa else None, xsa_eps=cfg.xsa_eps,
+                                counters=s["counters"], status=s["status"], row_map=row_map, gate_vals=gate_vals)
+                lam = self.lambdas[l]
+                _lib.check(lib.uv_gemm_sw_resid(s["z"].data_ptr(), H * hd, w[f"l{l}.wo"].data_ptr(), x.data_ptr(),
+                                                lam.data_ptr(), h.data_ptr(), d, ss_h.data_ptr(), ss_ld, dt, B, d,
+                                                H * hd, hw[0], hw[1], status, sp), "uv_gemm_sw_resid")
+                _lib.check(lib.uv_gemm_sw_swiglu(h.data_ptr(), d, w[f"l{l}.gu"].data_ptr(), s["act"].data_ptr(), dt,
+                                                 B, d, f, ss_h.data_ptr(), parts, ss_ld, hg[0], status, sp),
+                           "uv_gemm_sw_swiglu")
+                _lib.check(lib.uv_gemm_sw_resid(s["act"].data_ptr(), f, w[f"l{l}.down"].data_ptr(), h.data_ptr(),
+                                                lam[2:].data_ptr(), x.data_ptr(), d, ss_x.data_ptr(), ss_ld, dt, B, d,
+                                                f, hdn[0], hdn[1], status, sp), "uv_gemm_sw_resid")
+            # the final norm (fast_decode.py:332-334) for the head: h = 1 * x + 0 * x is x itself, hn its RMS norm
+            _lib.check(lib.uv_resid_norm(x.data_ptr(), x.data_ptr(), self._unit_lambdas().data_ptr(), dt, d,
+                                         h.data_ptr(), xn.data_ptr(), B, sp), "uv_resid_norm")
+        return xn
+
+    def _unit_lambdas(self) -> Tensor:
+        if not hasattr(self, "_unit_lam"):
+            self._unit_lam = torch.tensor([1.0, 0.0], dtype=torch.float32, device=self.device)
+        return self._unit_lam
+
+    def _prefill_attn(self, s, packed, l, gate_vals, sp) -> None:
+        cfg, lib = self.cfg, _lib.lib()
+        pa = _lib.PrefillAttnArgs()
+        pa.qkv, pa.dtype, pa.ld = s["qkv"].data_ptr(), DTYPE_CODE[self.dtype], s["qkv"].stride(0)
+        pa.cu_seqlens, pa.tile_cu = packed["cu"].data_ptr(), packed["tile_cu"].data_ptr()
+        pa.n_seq, pa.max_tiles = int(packed["n_seq"]), int(packed["max_tiles"])
+        pa.out, pa.ldo = s["z"].data_ptr(), s["z"].stride(0)
+        pa.H, pa.K, pa.hd = cfg.n_heads, cfg.n_kv_heads, cfg.head_dim
+        pa.window = 0 if cfg.is_global(l) else cfg.window
+        pa.scale = cfg.attn_scale
+        if cfg.xsa:
+            pa.xsa_alpha, pa.xsa_eps = self.xsa[l].data_ptr(), cfg.xsa_eps
+        if gate_vals is not None:
+            pa.gate_vals = gate_vals.data_ptr()
+        elif cfg.gate_channels:
+            raise RuntimeError("packed prefill needs the precomputed head gates")
+        _lib.check(lib.uv_prefill_attn(C.byref(pa), sp), "uv_prefill_attn")
 
     def head(self, hfin: Tensor) -> Tensor:
         """Raw tied-head output (B, V) in the activation dtype (the GEMM of MathLM.logits, model.py:826)."""
