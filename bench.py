@@ -362,68 +362,126 @@ def run_reference_arm(args, rank, world):
     print(json.dumps(line), flush=True)
 
 
-# ------------------------------------------------------------------------------------------------ continuous batching
-def run_continuous(args, m, rank, world, dev):
-    """4096 synthetic requests sharded i % W == rank, prompts U[16,256], stop length geometric(mean 600) capped at
-    2048 with EOS forced there, 512 slots per GPU, T = 1.0, Philox key per request; slots refilled on the device.
-    A step is one decode step of all 512 slots; `--steps` steps are timed after warm-up (0 = until drained)."""
+# ------------------------------------------------------------------------------------------------ rollout jobs
+def rollout_job(m, rank, world, dev, *, prompts_all, stops_all, slots, max_new, max_prompt, lanes, lane_chunk, seed,
+                force_eos, timed_steps=0, warmup=3, broadcast=False, gather=False):
+    """One rollout round on the device-resident scheduler: the requests are sharded i % W == rank, every rank runs
+    its replica until its share is drained (timed_steps > 0: that many steps only), finished rollouts are harvested
+    as device tensors.  Optionally the weight arena is broadcast from rank 0 first and the rollouts (tokens int32,
+    log-probs fp32, lengths and start versions int32) are gathered to rank 0 afterwards, each collective timed.
+    Windows of 64 steps are timed separately so that the steady state (slot occupancy >= 0.95) can be told from the
+    straggler tail.  Returns a dict on every rank (aggregates are all-reduced)."""
     import torch
     import torch.distributed as dist
     from ultraviolet_b200 import dist as uvdist
     from ultraviolet_b200.scheduler import GpuScheduler
     eng = m.engine
-    n_req, slots, max_new, max_prompt = 4096, 512, 2048, 256
-    r = np.random.default_rng(3)
-    lens = r.integers(16, max_prompt + 1, n_req)
-    stops = np.minimum(r.geometric(1.0 / 600.0, n_req), max_new)
-    prompts_all = [r.integers(1, VOCAB, int(L)).tolist() for L in lens]
+    n_req = len(prompts_all)
     mine = uvdist.shard_requests(n_req, rank, world)
-    t_bcast = uvdist.broadcast_weights(eng) if world > 1 else 0.0
-    st = m.new_state(GpuScheduler.state_rows(slots, args.lanes), max_prompt + max_new + 16)
-    sch = GpuScheduler(eng, st, max_new=max_new, temperature=1.0, eos_id=0, seed=7, q_cap=len(mine),
-                       max_prompt=max_prompt, force_eos=True, tok_cap=int(lens[mine].sum()) + 1,
-                       out_cap=int(stops[mine].sum()) + 1, prefill_lanes=args.lanes, lane_chunk=args.lane_chunk)
-    sch.enqueue([prompts_all[i] for i in mine], limits=stops[mine].tolist(), keys=mine, metas=mine)
-    sch.run(max(args.warmup, 3))
+    t_bcast = uvdist.broadcast_weights(eng) if (world > 1 and broadcast) else 0.0
+    lens = np.array([len(p) for p in prompts_all])
+    lim = np.full(n_req, max_new) if stops_all is None else np.asarray(stops_all)
+    st = m.new_state(GpuScheduler.state_rows(slots, lanes), max_prompt + max_new + 16)
+    sch = GpuScheduler(eng, st, max_new=max_new, temperature=1.0, eos_id=0, seed=seed, q_cap=max(len(mine), 2),
+                       max_prompt=max_prompt, force_eos=force_eos, tok_cap=int(lens[mine].sum()) + 1,
+                       out_cap=int(lim[mine].sum()) + 1, prefill_lanes=lanes, lane_chunk=lane_chunk)
+    sch.enqueue([prompts_all[i] for i in mine], limits=None if stops_all is None else lim[mine].tolist(), keys=mine,
+                metas=mine)
+    sch.run(max(warmup, 3))
     torch.cuda.synchronize()
-    c0 = sch.counters()
+    c_prev = c0 = sch.counters()
     if world > 1:
         dist.barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    done, steps = [], 0
-    with ClockSampler(dev.index or 0) as clk:
-        e0.record()
-        if args.steps > 0:
-            sch.run(args.steps)
-            steps = args.steps
-        else:
-            while len(done) < len(mine):
-                sch.run(64)
-                steps += 64
-                done += sch.harvest()
-        e1.record()
-        torch.cuda.synchronize()
-    ms = e0.elapsed_time(e1)
-    c1 = sch.counters()
-    gen = torch.tensor([c1["generated"] - c0["generated"], c1["slot_steps"] - c0["slot_steps"], steps],
-                       dtype=torch.float64, device=dev)
-    t = torch.tensor([ms], device=dev)
+    packed, windows, steps, n_done = [], [], 0, 0
+    ev = lambda: torch.cuda.Event(enable_timing=True)
+    e_begin, e_end = ev(), ev()
+    e_begin.record()
+    while True:
+        n = 64 if timed_steps <= 0 else min(64, timed_steps - steps)
+        a, b = ev(), ev()
+        a.record()
+        sch.run(n)
+        b.record()
+        steps += n
+        p = sch.harvest_packed()          # syncs: the window's events are complete after it
+        c = sch.counters()
+        windows.append((a.elapsed_time(b), c["generated"] - c_prev["generated"],
+                        (c["slot_steps"] - c_prev["slot_steps"]) / (n * slots)))
+        c_prev = c
+        if p is not None:
+            packed.append(p)
+            n_done += len(p["metas"])
+        if (timed_steps > 0 and steps >= timed_steps) or (timed_steps <= 0 and n_done >= len(mine)):
+            break
+    e_end.record()
+    torch.cuda.synchronize()
+    ms = e_begin.elapsed_time(e_end)
+    steady = [(t, g) for t, g, occ in windows if occ >= 0.95]
+    agg = torch.tensor([c_prev["generated"] - c0["generated"], c_prev["slot_steps"] - c0["slot_steps"], steps,
+                        sum(g for _, g in steady), n_done], dtype=torch.float64, device=dev)
+    mx = torch.tensor([ms, sum(t for t, _ in steady)], dtype=torch.float64, device=dev)
+    t_gather, gathered = 0.0, None
     if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        dist.all_reduce(gen)
+        dist.all_reduce(agg)
+        dist.all_reduce(mx, op=dist.ReduceOp.MAX)
+    if gather and packed:
+        toks = torch.cat([p["tokens"] for p in packed])
+        lps = torch.cat([p["logp"] for p in packed])
+        lens_d = torch.cat([p["offsets"][1:] - p["offsets"][:-1] for p in packed]).to(torch.int32)
+        vers = torch.cat([p["versions"] for p in packed]).to(torch.int32)
+        ids = torch.tensor([i for p in packed for i in p["metas"]], dtype=torch.int32, device=dev)
+        gathered, t_gather = uvdist.gather_packed(toks, lps, lens_d, vers, ids)
+    res = {"tokens_per_s": float(agg[0].item()) / (float(mx[0].item()) / 1e3), "ms": float(mx[0].item()),
+           "generated_tokens": int(agg[0].item()), "requests_finished": int(agg[4].item()),
+           "steps_all_ranks": int(agg[2].item()), "ms_per_step_rank0": ms / max(steps, 1),
+           "slot_occupancy": float(agg[1].item()) / max(float(agg[2].item()) * slots, 1.0),
+           "steady_state_tokens_per_s": (float(agg[3].item()) / (float(mx[1].item()) / 1e3)) if mx[1].item() > 0 else None,
+           "steady_state": "64-step windows with slot occupancy >= 0.95 (max window time over ranks)",
+           "weight_broadcast_ms": t_bcast * 1e3, "rollout_gather_ms": t_gather * 1e3,
+           "device_status": eng.device_status(), "sched_status": c_prev["status"]}
+    if gathered is not None:
+        res["gathered"] = {"requests": int(sum(int(g[2].numel()) for g in gathered)),
+                           "tokens": int(sum(int(g[0].numel()) for g in gathered)),
+                           "payload": "tokens int32 + log-probs fp32 (flat, unpadded) + lengths, start versions, "
+                                      "request ids int32"}
+    del sch, st
+    return res
+
+
+def config3_requests():
+    """BASELINE configs[2]: 4096 requests, prompts U[16,256], stop length Geometric(mean 600) capped at 2048."""
+    r = np.random.default_rng(3)
+    n_req, max_prompt, max_new = 4096, 256, 2048
+    lens = r.integers(16, max_prompt + 1, n_req)
+    stops = np.minimum(r.geometric(1.0 / 600.0, n_req), max_new)
+    return [r.integers(1, VOCAB, int(L)).tolist() for L in lens], stops, max_prompt, max_new
+
+
+def config5_requests():
+    """BASELINE configs[4]: 256 prompts U[64,256] x group 8 = 2048 sequences, max_new 2048, T = 1, top-p 1."""
+    r = np.random.default_rng(5)
+    lens = r.integers(64, 257, 256)
+    base = [r.integers(1, VOCAB, int(L)).tolist() for L in lens]
+    return [p for p in base for _ in range(8)], 256, 2048
+
+
+def run_continuous(args, m, rank, world, dev):
+    """`--workload continuous`: BASELINE configs[2] as the headline line (whole job, or --steps timed steps)."""
+    import torch.distributed as dist
+    prompts, stops, max_prompt, max_new = config3_requests()
+    r = rollout_job(m, rank, world, dev, prompts_all=prompts, stops_all=stops, slots=512, max_new=max_new,
+                    max_prompt=max_prompt, lanes=args.lanes, lane_chunk=args.lane_chunk, seed=7, force_eos=True,
+                    timed_steps=args.steps, warmup=args.warmup, broadcast=True)
     if rank == 0:
-        ms = float(t.item())
-        line = {"metric": "rollout decode tokens/s", "value": float(gen[0].item()) / (ms / 1e3), "unit": "tokens/s",
-                "n_gpus": world, "steps": steps, "warmup": max(args.warmup, 3), "ms_per_step": ms / max(steps, 1),
-                "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
-                "data": "synthetic",
+        line = {"metric": "rollout decode tokens/s", "value": r["tokens_per_s"], "unit": "tokens/s",
+                "n_gpus": world, "steps": r["steps_all_ranks"] // world, "warmup": max(args.warmup, 3),
+                "ms_per_step": r["ms_per_step_rank0"], "higher_is_better": True, "scaling": "strong",
+                "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
                 "config": {"workload": "continuous batching: 4096 requests sharded over ranks, prompts U[16,256], "
                                        "stop ~ Geometric(mean 600) <= 2048 (EOS forced), 512 slots/GPU, T=1.0, "
                                        "device-side retire/refill, prefill through the decode step",
-                           "prefill_lanes": args.lanes, "lane_chunk": args.lane_chunk, "slot_occupancy": float(gen[1].item()) / max(float(gen[2].item()) * slots, 1.0),
-                           "generated_tokens": int(gen[0].item()), "weight_broadcast_ms": t_bcast * 1e3,
-                           "status": c1["status"]},
-                "gpu_launches": (1 + 5 * eng.cfg.n_layers + 2) * steps, "clocks": clk.summary()}
+                           "prefill_lanes": args.lanes, "lane_chunk": args.lane_chunk},
+                "run": r, "gpu_launches": (m.engine.launches_per_step() + 2) * (r["steps_all_ranks"] // world)}
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
@@ -438,6 +496,8 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="fixed", choices=["fixed", "continuous", "attn"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-rollouts", action="store_true",
+                    help="skip the continuous-batching and GRPO-shaped rollout jobs reported beside the headline")
     ap.add_argument("--reference-gpu", action="store_true",
                     help="with --impl reference: also time the reference's Triton / NVRTC attention kernels on the GPU")
     ap.add_argument("--reference-gpu-only", action="store_true",
@@ -558,16 +618,39 @@ def main():
         e2e_s = float(t.item())
     e2e = world * SLOTS * K2 / e2e_s
 
+    # ---- roofline of the dominant kernel of this library (decode attention), at the run's final cache state
+    #      (rank 0 measures; the other ranks wait at the next job's barrier)
+    if rank == 0:
+        att = time_attention_layers(eng, st, st.pos - 1, st.starts)
+        att_mid = att["local"] if att["local"]["ms"] * 8 >= att["global"]["ms"] * 2 else att["global"]
+        lc = long_context_attention(eng)
+        lc2 = long_context_attention(eng, ctx=16384)
+        context_end = int(st.pos.float().mean().item())
+        torch.cuda.empty_cache()
+
+    # ---- the two rollout-shaped jobs of the configuration list, bounded, on all ranks (whole-box tokens/s under
+    #      continuous batching is what the path is for; the fixed workload above is the per-step headline)
+    cont = grpo = None
+    if not args.no_rollouts:
+        prompts3, stops3, mp3, mn3 = config3_requests()
+        cont = rollout_job(m, rank, world, dev, prompts_all=prompts3, stops_all=stops3, slots=512, max_new=mn3,
+                           max_prompt=mp3, lanes=args.lanes, lane_chunk=args.lane_chunk, seed=7, force_eos=True)
+        cont["workload"] = ("BASELINE configs[2]: 4096 requests sharded i % W, prompts U[16,256], stop ~ "
+                            "Geometric(600) <= 2048 (EOS forced), 512 slots/GPU, T = 1.0; whole job until drained")
+        torch.cuda.empty_cache()
+        prompts5, mp5, mn5 = config5_requests()
+        grpo = rollout_job(m, rank, world, dev, prompts_all=prompts5, stops_all=None, slots=512, max_new=mn5,
+                           max_prompt=mp5, lanes=args.lanes, lane_chunk=args.lane_chunk, seed=11, force_eos=False,
+                           broadcast=True, gather=True)
+        grpo["workload"] = ("BASELINE configs[4]: 256 prompts U[64,256] x group 8 = 2048 sequences sharded i % W, "
+                            "max_new 2048, T = 1.0, top-p 1.0, Philox key per sequence; arena broadcast before the "
+                            "round, rollouts (tokens, log-probs, versions) gathered to rank 0 after it")
+
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
         return
 
-    # ---- roofline of the dominant kernel of this library (decode attention), at the run's final cache state
-    att = time_attention_layers(eng, st, st.pos - 1, st.starts)
-    att_mid = att["local"] if att["local"]["ms"] * 8 >= att["global"]["ms"] * 2 else att["global"]
-    lc = long_context_attention(eng)
-    lc2 = long_context_attention(eng, ctx=16384)
     # bytes one decode step must move: weights once (99.6 MB bf16) + KV reads + KV appends (132 B per row per layer)
     kv_read = 8 * att["local"]["bytes"] + 2 * att["global"]["bytes"]
     step_bytes = 99_614_720 + kv_read + SLOTS * 10 * 132
@@ -580,7 +663,7 @@ def main():
                 "l2": "per-step working set (99.6 MB weights + KV of 10 layers) exceeds L2; no flush",
                 "prefill_s": prefill_s, "prefill_tokens": int(sum(len(p) - 1 for p in prompts)),
                 "context_begin": int(pos_begin.float().mean().item()),
-                "context_end": int(st.pos.float().mean().item()),
+                "context_end": context_end,
                 "weight_broadcast_ms": t_bcast * 1e3, "rollout_gather_ms": t_gather * 1e3,
                 "step_bytes_floor": step_bytes,
                 "step_hbm_frac": step_bytes / (ms / K / 1e3) / 1e9 / hbm_peak,
@@ -602,6 +685,7 @@ def main():
                       "long_context_frac_of_nominal_8TBs": lc["gbs"] / 8000.0,
                       "long_context_64x16384": lc2, "long_context_64x16384_frac_of_measured": lc2["gbs"] / hbm_peak},
     }
+    line["continuous"], line["grpo"] = cont, grpo
     if not args.no_cpu_baseline and world == 1:
         cb = cpu_baseline(32)  # the reference's prefill (~10 s) + ~3 s of timed steps on the host cores
         cb.pop("ms_per_step", None)

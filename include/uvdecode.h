@@ -193,6 +193,10 @@ int uv_qkv_post(void* qkv, const void* xn, const int64_t* tok, const void* value
 int uv_resid_norm(const void* x, const void* a, const float* lambdas, int dtype, int d, void* h, void* hn, int B,
                   void* stream);
 int uv_swiglu(const void* gu, int dtype, int f, void* act, int B, void* stream);
+/* uv_swiglu with the deferred RMS norm: gu = h . [Wg ; Wu]^T computed on the UN-normalised rows h (B, d); the kernel
+ * forms rs = rsqrt(mean(h[b]^2) + 2^-23) and returns act = silu(g * rs) * (u * rs) (MLP.forward on rms_norm(h),
+ * ultraviolet/model.py:388-391, :567-571). */
+int uv_swiglu_rs(const void* gu, const void* h, int dtype, int d, int f, void* act, int B, void* stream);
 
 /* uv_qkv_attn: uv_qkv_post followed by uv_decode_attn on the same rows, as ONE launch.  The attention CTAs do the
  * per-head post-processing of their row in their prologue, while the bulk copies of the older cache tiles are already
@@ -228,6 +232,10 @@ typedef struct uv_qkv_args { /* the parameters of uv_qkv_post, by name */
                              launch.  A ring cache then keeps only the newest S positions of a sequence (entries with
                              pos + S <= last_pos are not written), as _write_kv_layers does (ultraviolet/kernels/
                              fast_decode.py:166-207), so that no two rows of one launch write the same slot */
+  int xn_raw;              /* uv_qkv_post_args only.  1: xn holds the UN-normalised residual rows and qkv the projection
+                             of those rows; the kernel forms rs = rsqrt(mean(xn[b]^2) + 2^-23) itself, scales the
+                             projection by it and reads rms_norm(xn) on the fly for the gates (deferred RMS norm: the
+                             step then needs no separate norm kernel in front of the QKV GEMM) */
 } uv_qkv_args;
 int uv_qkv_attn(const uv_qkv_args* qkv, const uv_attn_args* attn, void* stream);
 /* uv_qkv_post with its parameters by name; with rope_cs set the rotation reads the step's table. */

@@ -151,6 +151,36 @@ def make_model():
     save("model", **out)
 
 
+def make_model_bf16():
+    """The same teacher-forced run with the reference itself in bfloat16 on the CPU (weights, activations and the
+    int8 cache path as a bf16 deployment computes them): the GPU path is compared against these bytes much more
+    tightly than against the fp32 run, because both sides round where bf16 rounds."""
+    out = {}
+    for name in ("uv50m", "tiny_hd64"):
+        spec = gi.model_specs()[name]
+        torch.manual_seed(spec["seed"])
+        m = MathLM(make_config(spec["preset"], **spec["over"]))
+        gi.perturb_(m, spec)
+        m.decode_impl = "kernel-int8"
+        m = m.bfloat16().fuse_for_inference(torch.bfloat16)
+        idx, starts, cont, max_len = gi.teacher_inputs(spec)
+        st = m.new_state(idx.shape[0], max_len, torch.bfloat16, "cpu")
+        outs = [m.prefill(T(idx), T(starts), st)]
+        for t in range(cont.shape[1]):
+            outs.append(m.decode_step(T(cont)[:, t], st, max_len))
+        lg = torch.stack(outs, 1).float().numpy()
+        cols = gi.logit_columns(spec, lg.shape[-1])
+        out[name + ".logits"] = lg[..., cols]
+        out[name + ".argmax"] = lg.argmax(-1)
+        for l in spec["cache_layers"]:
+            out[f"{name}.k{l}"] = st.k[l].numpy()
+            out[f"{name}.ks{l}"] = st.k_scale[l].numpy().view(np.uint16)
+            out[f"{name}.v{l}"] = st.v[l].numpy()
+            out[f"{name}.vs{l}"] = st.v_scale[l].numpy().view(np.uint16)
+        out[name + ".pos"] = st.pos.numpy()
+    save("model_bf16", **out)
+
+
 # ------------------------------------------------------------------------------------------------ samplers
 def make_sampler():
     out = {}
@@ -177,4 +207,5 @@ if __name__ == "__main__":
     make_quant()
     make_attn()
     make_model()
+    make_model_bf16()
     make_sampler()

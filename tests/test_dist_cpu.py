@@ -42,6 +42,24 @@ def _worker(rank, world, port, q):
                 assert torch.equal(l, torch.arange(1, nr + 1))
         else:
             assert res is None
+        # packed rollouts (tokens + log-probs + lengths + versions + ids), ragged per rank
+        lens = torch.tensor([3, 1 + rank], dtype=torch.int32)
+        nt = int(lens.sum())
+        toks = (torch.arange(nt) + 100 * rank).to(torch.int32)
+        lps = -(torch.arange(nt).float() + rank)
+        vers = torch.tensor([rank, rank + 5], dtype=torch.int32)
+        ids = torch.tensor([10 * rank, 10 * rank + 1], dtype=torch.int32)
+        res, _ = uvdist.gather_packed(toks, lps, lens, vers, ids, dst=0)
+        if rank == 0:
+            assert len(res) == world
+            for r, (t, l, n_, v, i) in enumerate(res):
+                k = 3 + 1 + r
+                assert t.dtype == torch.int32 and l.dtype == torch.float32
+                assert torch.equal(t, (torch.arange(k) + 100 * r).to(torch.int32))
+                assert torch.equal(l, -(torch.arange(k).float() + r))
+                assert n_.tolist() == [3, 1 + r] and v.tolist() == [r, r + 5] and i.tolist() == [10 * r, 10 * r + 1]
+        else:
+            assert res is None
         q.put((rank, uvdist.shard_requests(11, rank, world)))
     finally:
         dist.destroy_process_group()

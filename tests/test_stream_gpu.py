@@ -161,3 +161,37 @@ def test_fused_sample_api():
     assert fused_sample_ok(x, 16384, (23.0, 5.0, 7.5), 1.0) and not fused_sample_ok("cpu", 16384, (23.0, 5.0, 7.5), 1.0)
     tok, lp = fused_sample(x, u, (23.0, 5.0, 7.5), 1.0)
     assert tok.dtype == torch.int64 and lp.dtype == torch.float32 and tok.shape == (5,) and bool((lp < 0).all())
+
+
+def test_grpo_group_of_identical_prompts_gets_distinct_streams():
+    """The GRPO rollout shape (scripts/rl_grpo.py:1181: every prompt is sampled `group` times): 8 copies of one
+    prompt carry 8 Philox keys, so they produce 8 different rollouts, and a copy's rollout depends on its key alone --
+    the same (seed, request order) through another slot count, with and without prefill lanes, gives the same
+    rollouts."""
+    from ultraviolet_b200.rl_stream import StreamGen
+    m = _model()
+    r = np.random.default_rng(21)
+    base = [r.integers(1, 500, r.integers(3, 9)).tolist() for _ in range(3)]
+    reqs = [(p, (gi_, c)) for gi_, p in enumerate(base) for c in range(8)]      # 3 groups of 8
+
+    def rollouts(slots, lanes):
+        gen = StreamGen(m, slots=slots, max_prompt=9, max_new=10, temperature=1.2, eos_id=0, check_every=4, seed=77,
+                        prefill_lanes=lanes)
+        for p, meta in reqs:
+            gen.add(p, meta)
+        got = {}
+        while gen.n_outstanding():
+            for meta, toks, lp, v0 in gen.chunk():
+                assert meta not in got and len(toks) == len(lp) and v0 == 0
+                got[meta] = toks
+        return got
+
+    a = rollouts(4, 0)
+    assert sorted(a) == sorted(meta for _, meta in reqs)
+    for g_ in range(3):
+        assert len({tuple(a[(g_, c)]) for c in range(8)}) >= 7     # identical prompts, different keys: different text
+    b = rollouts(24, 0)
+    c = rollouts(7, 4)
+    for other in (b, c):
+        same = np.mean([a[k] == other[k] for k in a])
+        assert same >= 0.75, same    # equal unless a batch-size dependent bf16 rounding flips a draw

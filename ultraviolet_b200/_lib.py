@@ -52,7 +52,7 @@ class QkvArgs(C.Structure):
         ("B", C.c_int), ("H", C.c_int), ("K", C.c_int), ("hd", C.c_int), ("d", C.c_int), ("S", C.c_int),
         ("S_alloc", C.c_int), ("ring", C.c_int), ("ve_ch", C.c_int), ("n_pairs", C.c_int),
         ("rope_cs", C.c_void_p), ("gate_w", C.c_void_p), ("gate_out", C.c_void_p), ("gate_ch", C.c_int),
-        ("last_pos", C.c_void_p),
+        ("last_pos", C.c_void_p), ("xn_raw", C.c_int),
     ]
 
 
@@ -105,6 +105,7 @@ SIGNATURES = {
     "uv_resid_norm": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_int,
                                 C.c_void_p]),
     "uv_swiglu": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_int, C.c_void_p]),
+    "uv_swiglu_rs": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_int, C.c_void_p]),
     "uv_gemm_qkv": (C.c_int, [C.c_void_p, C.c_int64] + [C.c_void_p] * 13 + [C.c_int, C.c_int64] + [C.c_int] * 10
                     + [C.c_void_p]),
     "uv_gemm_tc": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_int, C.c_int,

@@ -176,6 +176,39 @@ __global__ void __launch_bounds__(256) swiglu_kernel(const T* __restrict__ gu, i
   st2<T>(act + row * f + col, s0 * u.x, s1 * u.y);
 }
 
+// act = silu(g) * u of the gate|up projection of UN-normalised rows h: [g | u] = (h . W^T) * rs with
+// rs = rsqrt(mean(h^2) + eps) formed here (one CTA per row: the row's sum of squares, then its f features)
+template <typename T>
+__global__ void __launch_bounds__(128) swiglu_rs_kernel(const T* __restrict__ gu, const T* __restrict__ hrow, int d,
+                                                        int f, T* __restrict__ act) {
+  __shared__ float red[4];
+  const int row = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  pdl_wait();
+  pdl_trigger();
+  const T* hr = hrow + (int64_t)row * d;
+  float ss = 0.f;
+  for (int i = 8 * tid; i < d; i += 8 * 128) {
+    const uint4 u = *reinterpret_cast<const uint4*>(hr + i);
+    const T* v = reinterpret_cast<const T*>(&u);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const float x = to_f32<T>(v[k]);
+      ss += x * x;
+    }
+  }
+  ss = warp_sum(ss);
+  if (lane == 0) red[warp] = ss;
+  __syncthreads();
+  const float rs = rsqrtf((red[0] + red[1] + red[2] + red[3]) / (float)d + RMS_EPS);
+  const T* g = gu + (int64_t)row * 2 * f;
+  for (int c = 2 * tid; c < f; c += 2 * 128) {
+    const float2 gv = ld2<T>(g + c), uv = ld2<T>(g + f + c);
+    const float g0 = rnd<T>(gv.x * rs), g1 = rnd<T>(gv.y * rs), u0 = rnd<T>(uv.x * rs), u1 = rnd<T>(uv.y * rs);
+    const float s0 = rnd<T>(g0 / (1.0f + __expf(-g0))), s1 = rnd<T>(g1 / (1.0f + __expf(-g1)));
+    st2<T>(act + (int64_t)row * f + c, s0 * u0, s1 * u1);
+  }
+}
+
 // ------------------------------------------------------------------------------------------------ QKV post
 // One warp per (row b, head slot), in place on the packed GEMM output; the arithmetic lives in qkv_post.cuh.
 template <typename T, int HD, bool TABLE>
@@ -189,10 +222,13 @@ __global__ void __launch_bounds__(128) qkv_post_kernel(const __grid_constant__ Q
   pdl_trigger();
   if (item >= P.B * per_row) return;
   const int b = item / per_row, hs = item % per_row;
+  const bool raw = P.xn_raw != 0;
+  const float rs = raw ? row_rms_factor<T>(static_cast<const T*>(P.xn) + (int64_t)b * P.d, P.d, lane) : 1.0f;
   if (hs >= slots) {
     const int head = hs - slots;
     const float g = head_gate<T>(static_cast<const T*>(P.xn) + (int64_t)b * P.d,
-                                 static_cast<const T*>(P.gate_w) + (int64_t)head * P.gate_ch, P.gate_ch, lane);
+                                 static_cast<const T*>(P.gate_w) + (int64_t)head * P.gate_ch, P.gate_ch, lane, rs,
+                                 raw);
     if (lane == 0) P.gate_out[(int64_t)b * P.H + head] = g;
     return;
   }
@@ -201,7 +237,11 @@ __global__ void __launch_bounds__(128) qkv_post_kernel(const __grid_constant__ Q
   float x[E];
 #pragma unroll
   for (int i = 0; i < E; ++i) x[i] = act ? to_f32<T>(vec[lane * E + i]) : 0.f;
-  qkv_post_compute<T, HD, TABLE>(P, b, hs, lane, x);
+  if (raw) {  // the projection of the un-normalised row, scaled: what the GEMM on the normalised row would hold
+#pragma unroll
+    for (int i = 0; i < E; ++i) x[i] = rnd<T>(x[i] * rs);
+  }
+  qkv_post_compute<T, HD, TABLE>(P, b, hs, lane, x, rs, raw);
 #pragma unroll
   for (int i = 0; i < E; ++i)
     if (act) vec[lane * E + i] = from_f32<T>(x[i]);
@@ -282,6 +322,10 @@ extern "C" int uv_qkv_post_args(const uv_qkv_args* a, void* stream) {
     P.gate_w = a->gate_w, P.gate_out = a->gate_out, P.gate_ch = a->gate_ch;
   }
   P.last_pos = a->last_pos;
+  if (a->xn_raw) {
+    if (!a->xn || a->d < 8 || (a->d & 7) || !aligned16(a->xn)) return UV_ERR_ARG;
+    P.xn_raw = 1;
+  }
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (a->dtype == UV_F16) return launch_qkv_post<__half>(P, a->hd, st);
   if (a->dtype == UV_BF16) return launch_qkv_post<__nv_bfloat16>(P, a->hd, st);
@@ -319,6 +363,23 @@ extern "C" int uv_swiglu(const void* gu, int dtype, int f, void* act, int B, voi
   else if (dtype == UV_BF16)
     launch_pdl(swiglu_kernel<__nv_bfloat16>, dim3(grid), dim3(256), 0, st, static_cast<const __nv_bfloat16*>(gu), f,
                static_cast<__nv_bfloat16*>(act), n);
+  else return UV_ERR_DTYPE;
+  return check_launch();
+}
+
+extern "C" int uv_swiglu_rs(const void* gu, const void* h, int dtype, int d, int f, void* act, int B, void* stream) {
+  if (B == 0) return UV_OK;
+  if (!gu || !h || !act || B < 0) return UV_ERR_ARG;
+  if (f < 2 || (f & 1) || d < 8 || (d & 7)) return UV_ERR_SHAPE;
+  if (!aligned16(h)) return UV_ERR_ALIGN;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (dtype == UV_F16)
+    launch_pdl(swiglu_rs_kernel<__half>, dim3((unsigned)B), dim3(128), 0, st, static_cast<const __half*>(gu),
+               static_cast<const __half*>(h), d, f, static_cast<__half*>(act));
+  else if (dtype == UV_BF16)
+    launch_pdl(swiglu_rs_kernel<__nv_bfloat16>, dim3((unsigned)B), dim3(128), 0, st,
+               static_cast<const __nv_bfloat16*>(gu), static_cast<const __nv_bfloat16*>(h), d, f,
+               static_cast<__nv_bfloat16*>(act));
   else return UV_ERR_DTYPE;
   return check_launch();
 }

@@ -39,7 +39,26 @@ struct QkvPostParams {
   // optional, packed prefill: last position of the row's sequence in this launch; ring caches then keep only the
   // newest S positions of a sequence (no two rows of one launch write one slot)
   const int64_t* last_pos;
+  // xn holds the UN-normalised residual rows: every warp forms its row's RMS-norm factor itself, scales the raw
+  // projection by it (the GEMM ran on the un-normalised rows) and reads normalised gate inputs on the fly
+  int xn_raw;
 };
+
+// rsqrt(mean(row^2) + eps) of one activation row of d elements (d % 8 == 0, 16-byte aligned rows); full warp
+template <typename T>
+__device__ __forceinline__ float row_rms_factor(const T* row, int d, int lane) {
+  float ss = 0.f;
+  for (int i = 8 * lane; i < d; i += 256) {
+    const uint4 u = *reinterpret_cast<const uint4*>(row + i);
+    const T* v = reinterpret_cast<const T*>(&u);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const float f = to_f32<T>(v[k]);
+      ss += f * f;
+    }
+  }
+  return rsqrtf(warp_sum(ss) / (float)d + RMS_EPS);
+}
 
 // The head gate of Attention.post (ultraviolet/model.py:330-333) with its rounding points; lane-strided products,
 // then a warp sum.  Full warp; every lane returns the gate.

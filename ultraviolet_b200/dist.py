@@ -95,3 +95,46 @@ def gather_rollouts(tokens: torch.Tensor, lengths: torch.Tensor | None = None, d
         k = int(s[0].item())
         res.append((out[r][:k, :l_max], out[r][:k, l_max]))
     return res, dt
+
+
+def gather_packed(tokens: torch.Tensor, logp: torch.Tensor, lengths: torch.Tensor, versions: torch.Tensor,
+                  ids: torch.Tensor, dst: int = 0):
+    """Finished rollouts of this rank, as GpuScheduler.harvest_packed() hands them over, to rank `dst`: flat int32
+    tokens and fp32 behaviour log-probs (sum(lengths),), and per rollout its length, the weight version it started
+    under and its request id (int32) -- the record the reference gathers with all_gather_object (scripts/rl_grpo.py:
+    1458-1464), as three sized buffers instead of pickled Python objects.  Counts travel first (one all_gather of
+    two integers), then each buffer is gathered padded to the largest rank's size.  Returns (list over ranks of
+    (tokens, logp, lengths, versions, ids) on `dst`, else None; seconds)."""
+    rank, W = world()
+    dev = tokens.device
+    _sync(tokens)
+    t0 = time.perf_counter()
+    if W == 1:
+        return [(tokens, logp, lengths, versions, ids)], 0.0
+    size = torch.tensor([tokens.numel(), lengths.numel()], dtype=torch.int64, device=dev)
+    sizes = [torch.zeros_like(size) for _ in range(W)]
+    dist.all_gather(sizes, size)
+    sizes_h = torch.stack(sizes).cpu()
+    t_max, n_max = int(sizes_h[:, 0].max()), int(sizes_h[:, 1].max())
+
+    def padded(x, n, dtype):
+        out = torch.zeros(n, dtype=dtype, device=dev)
+        out[:x.numel()] = x.to(dtype)
+        return out
+    tok_p, lp_p = padded(tokens, t_max, torch.int32), padded(logp, t_max, torch.float32)
+    meta_p = torch.stack([padded(lengths, n_max, torch.int32), padded(versions, n_max, torch.int32),
+                          padded(ids, n_max, torch.int32)])
+    outs = []
+    for buf in (tok_p, lp_p, meta_p):
+        dest = [torch.empty_like(buf) for _ in range(W)] if rank == dst else None
+        dist.gather(buf, dest, dst=dst)
+        outs.append(dest)
+    _sync(tokens)
+    dt = time.perf_counter() - t0
+    if rank != dst:
+        return None, dt
+    res = []
+    for r in range(W):
+        nt, nr = int(sizes_h[r, 0]), int(sizes_h[r, 1])
+        res.append((outs[0][r][:nt], outs[1][r][:nt], outs[2][r][0, :nr], outs[2][r][1, :nr], outs[2][r][2, :nr]))
+    return res, dt

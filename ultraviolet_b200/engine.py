@@ -98,6 +98,15 @@ class DecodeEngine:
         self.tc_gemm = os.environ.get("UVDECODE_TC_GEMM", "0") == "1" and self.tc_gemm_ok
         self.tc_hints = {k: tuple(int(v) for v in os.environ.get(f"UVDECODE_TC_{k.upper()}", d_).split(","))
                          for k, d_ in (("qkv", "0,0"), ("wo", "0,0"), ("gu", "0,0"), ("down", "0,0"))}
+        # Folded residual stream (default): the step carries y = x / s_l, s_l the running product of the residual
+        # lambdas, so that  h = l0 x + l1 a  becomes  y += a'  with l1 / s folded into wo (and into w_down for the MLP
+        # branch) when the weights are fused.  Every consumer of the stream is an RMS norm, which does not see the
+        # scale, and the norm itself is deferred into the kernel that follows the consuming GEMM (uv_qkv_post_args
+        # with xn_raw, uv_swiglu_rs).  The two residual + norm launches of a layer disappear: the residual add is
+        # the GEMM's own accumulate (C += A . B), 7 launches per layer instead of 9.  UVDECODE_FOLD=0: the
+        # reference's literal op order (separate uv_resid_norm launches).
+        self.fold = (os.environ.get("UVDECODE_FOLD", "1") != "0" and not self.fused_gemm and not self.tc_gemm
+                     and not self.qkv_in_attn and d % 8 == 0)
         self.n_sm = torch.cuda.get_device_properties(self.device).multi_processor_count
         _lib.lib()
 
@@ -118,12 +127,27 @@ class DecodeEngine:
         w["embed"].copy_(model.embed.weight)
         if self.use_ve:
             w["value_embed"].copy_(model.value_embed.weight)
+        scale = 1.0   # s_l: the residual stream the kernels carry is x / s_l (folded mode)
         for l, blk in enumerate(model.blocks):
             at, mlp = blk.attn, blk.mlp
             w[f"l{l}.wqkv"].copy_((torch.cat([at.wq, at.wk, at.wv]) * at.qkv_scale).to(dt))
-            w[f"l{l}.wo"].copy_((at.wo * at.o_scale).to(dt))
+            lam_h = [float(v.detach().to(dt).float()) for v in (blk.resid_attn, blk.post_attn, blk.resid_mlp,
+                                                                 blk.post_mlp)]
+            if self.fold:
+                if min(abs(lam_h[0]), abs(lam_h[2])) < 2.0 ** -6:
+                    raise ValueError(f"layer {l}: a residual lambda is ~0, the folded residual stream cannot "
+                                     "represent it; set UVDECODE_FOLD=0")
+                scale *= lam_h[0]
+                w[f"l{l}.wo"].copy_((at.wo.float() * float(at.o_scale) * (lam_h[1] / scale)).to(dt))
+                scale *= lam_h[2]
+                w[f"l{l}.down"].copy_((mlp.w_down.float() * (lam_h[3] / scale)).to(dt))
+                if not (2.0 ** -24 < abs(scale) < 2.0 ** 24):
+                    raise ValueError("the product of the residual lambdas leaves the range the folded residual "
+                                     "stream keeps in half precision; set UVDECODE_FOLD=0")
+            else:
+                w[f"l{l}.wo"].copy_((at.wo * at.o_scale).to(dt))
+                w[f"l{l}.down"].copy_(mlp.w_down.to(dt))
             w[f"l{l}.gu"].copy_(torch.cat([mlp.w_gate, mlp.w_up]).to(dt))
-            w[f"l{l}.down"].copy_(mlp.w_down.to(dt))
             if cfg.has_ve(l):
                 w[f"l{l}.ve_gate"].copy_(at.ve_gate.to(dt))
             if cfg.gate_channels:
@@ -201,6 +225,8 @@ class DecodeEngine:
             return 1 + 5 * n + 2
         if self.fused_gemm:
             return 1 + 5 * n + 1
+        if self.fold:
+            return 1 + 7 * n + 2
         return 1 + (8 if self.qkv_in_attn else 9) * n + 1
 
     def _workspace(self, s: dict, B: int, splits: int) -> Tensor | None:
@@ -235,6 +261,7 @@ class DecodeEngine:
         rm = row_map.data_ptr() if row_map is not None else None
         fused = self.fused_gemm and packed is None
         qkv_in_attn = self.qkv_in_attn and packed is None
+        fold = self.fold
         if self.tc_gemm and not fused and not qkv_in_attn and B <= self.BIG_ROWS:
             return self._trunk_tc(tok, st, pos, starts, g_len, ns, rm, row_map, skip_attn, packed)
         with torch.cuda.device(self.device):
@@ -267,19 +294,21 @@ class DecodeEngine:
                     _lib.check(lib.uv_gemm_qkv(xn.data_ptr(), d, w[f"l{l}.wqkv"].data_ptr(), s["qkv"].data_ptr(),
                                                *post_args), "uv_gemm_qkv")
                 else:
-                    torch.mm(xn, w[f"l{l}.wqkv"].t(), out=s["qkv"])
+                    gin = x if fold else xn   # folded: the GEMM reads the un-normalised stream, uv_qkv_post norms
+                    torch.mm(gin, w[f"l{l}.wqkv"].t(), out=s["qkv"])
                     qa = _lib.QkvArgs()
                     (qa.qkv, qa.xn, qa.tok, qa.value_embed, qa.ve_gate, qa.inv_freq, qa.pos, qa.k_cache,
                      qa.v_cache, qa.k_scale, qa.v_scale, qa.row_map, qa.oob_count, qa.dtype, qa.vocab,
                      qa.B, qa.H, qa.K, qa.hd, qa.d, qa.S, qa.S_alloc, qa.ring, qa.ve_ch,
-                     qa.n_pairs) = (s["qkv"].data_ptr(), xn.data_ptr(), *post_args[:-1])
+                     qa.n_pairs) = (s["qkv"].data_ptr(), gin.data_ptr(), *post_args[:-1])
+                    qa.xn_raw = int(fold)
                     qa.rope_cs = s["rope_cs"].data_ptr() if use_table else None
                     if packed is not None:
                         qa.last_pos = packed["last_pos"].data_ptr()
                     if qkv_in_attn:  # the attention launch below does uv_qkv_post's work in its prologue
                         pre = qa
                     else:
-                        if cfg.gate_channels and (self.gate_pre or packed is not None):  # gates depend on xn only:
+                        if cfg.gate_channels and (self.gate_pre or packed is not None or fold):  # depend on xn only:
                             qa.gate_w = w[f"l{l}.attn_gate"].data_ptr()  # computed off the attention kernel's tail
                             qa.gate_out, qa.gate_ch = s["gate"].data_ptr(), cfg.gate_channels
                             gate_vals = s["gate"]
@@ -319,6 +348,13 @@ class DecodeEngine:
                                                       h.data_ptr(), lam[2:].data_ptr(), x.data_ptr(), xn.data_ptr(),
                                                       dt, B, d, sp), "uv_gemm_resid_norm")
                     continue
+                if fold:
+                    x.addmm_(s["z"], w[f"l{l}.wo"].t())                       # y += z . wo'^T  (lambdas folded in)
+                    torch.mm(x, w[f"l{l}.gu"].t(), out=s["gu"])
+                    _lib.check(lib.uv_swiglu_rs(s["gu"].data_ptr(), x.data_ptr(), dt, d, f, s["act"].data_ptr(), B,
+                                                sp), "uv_swiglu_rs")
+                    x.addmm_(s["act"], w[f"l{l}.down"].t())                   # y += act . down'^T
+                    continue
                 torch.mm(s["z"], w[f"l{l}.wo"].t(), out=s["a"])
                 _lib.check(lib.uv_resid_norm(x.data_ptr(), s["a"].data_ptr(), lam.data_ptr(), dt, d, h.data_ptr(),
                                              hn.data_ptr(), B, sp), "uv_resid_norm")
@@ -327,6 +363,9 @@ class DecodeEngine:
                 torch.mm(s["act"], w[f"l{l}.down"].t(), out=s["m"])
                 _lib.check(lib.uv_resid_norm(h.data_ptr(), s["m"].data_ptr(), lam[2:].data_ptr(), dt, d,
                                              x.data_ptr(), xn.data_ptr(), B, sp), "uv_resid_norm")
+            if fold:  # the final norm (fast_decode.py:332-334): h = 1 * y + 0 * y is y itself, hn its RMS norm
+                _lib.check(lib.uv_resid_norm(x.data_ptr(), x.data_ptr(), self._unit_lambdas().data_ptr(), dt, d,
+                                             h.data_ptr(), xn.data_ptr(), B, sp), "uv_resid_norm")
         return xn  # rms_norm of the last residual stream == the final norm (fast_decode.py:332-334)
 
     def _trunk_tc(self, tok, st, pos, starts, g_len, ns, rm, row_map, skip_attn, packed) -> Tensor:
