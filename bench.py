@@ -381,7 +381,8 @@ def rollout_job(m, rank, world, dev, *, prompts_all, stops_all, slots, max_new, 
     t_bcast = uvdist.broadcast_weights(eng) if (world > 1 and broadcast) else 0.0
     lens = np.array([len(p) for p in prompts_all])
     lim = np.full(n_req, max_new) if stops_all is None else np.asarray(stops_all)
-    st = m.new_state(GpuScheduler.state_rows(slots, lanes), max_prompt + max_new + 16)
+    st = m.new_state(GpuScheduler.state_rows(slots, lanes), max_prompt + max_new + 16,
+                     ring_extra=GpuScheduler.ring_extra(lanes, lane_chunk))
     sch = GpuScheduler(eng, st, max_new=max_new, temperature=1.0, eos_id=0, seed=seed, q_cap=max(len(mine), 2),
                        max_prompt=max_prompt, force_eos=force_eos, tok_cap=int(lens[mine].sum()) + 1,
                        out_cap=int(lim[mine].sum()) + 1, prefill_lanes=lanes, lane_chunk=lane_chunk)

@@ -202,6 +202,20 @@ def make_sampler():
     save("sampler", **out)
 
 
+def make_packing():
+    """The trainer-side micro-batch layout (ultraviolet/perf.py:55-95) on seeded rollouts."""
+    from ultraviolet.perf import build_packed
+    items, budget, pad_id, seg_max = gi.packing_case()
+    out = {"n": np.array(0)}
+    mbs = build_packed(items, budget, pad_id, seg_max=seg_max)
+    out["n"] = np.array(len(mbs))
+    for i, mb in enumerate(mbs):
+        for k in ("x", "y", "A", "OL", "pos", "cu", "tgt"):
+            out[f"mb{i}.{k}"] = np.asarray(mb[k])
+        out[f"mb{i}.max_seqlen"] = np.array(mb["max_seqlen"])
+    save("packing", **out)
+
+
 if __name__ == "__main__":
     torch.set_grad_enabled(False)
     make_quant()
@@ -209,3 +223,4 @@ if __name__ == "__main__":
     make_model()
     make_model_bf16()
     make_sampler()
+    make_packing()

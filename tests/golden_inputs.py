@@ -215,3 +215,15 @@ def varlen_case():
     v = r.standard_normal((N, K, hd)).astype(np.float32)
     cu = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
     return dict(q=q, k=k, v=v, cu=cu, scale=0.25, window=24)
+
+
+def packing_case():
+    """Rollouts for the trainer's packed micro-batches (layout test of the reference, tests/test_perf_opt.py:93-118):
+    (tokens, prompt length, advantage, behaviour log-probs) per rollout, budget 1024, pad segments of 512."""
+    rng = np.random.default_rng(0)
+    items = []
+    for i in range(20):
+        L, s = int(rng.integers(5, 300)), int(rng.integers(2, 5))
+        t = rng.integers(1, 100, size=L)
+        items.append((t, s, float(i + 1), rng.normal(size=L - s).astype(np.float32)))
+    return items, 1024, 0, 512

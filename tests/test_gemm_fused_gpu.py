@@ -29,6 +29,8 @@ def test_fused_gemm_step_matches_unfused_step(B):
     m = build_model(spec).to(DEV).to(torch.bfloat16).fuse_for_inference(torch.bfloat16)
     eng = m.engine
     assert eng.fused_gemm_ok
+    eng.fold = False          # both sides on the reference's literal op order (the arena then holds unfolded weights)
+    eng.load_from(m)
     a, sa = _run(eng, m, True, B, 6, 1)
     b, sb = _run(eng, m, False, B, 6, 1)
     eng.fused_gemm = True
@@ -50,6 +52,8 @@ def test_fused_gemm_step_matches_oracle():
     W = oracle_weights(mc, "bf16")
     m = build_model(spec).to(DEV).to(torch.bfloat16).fuse_for_inference(torch.bfloat16)
     assert m.engine.fused_gemm_ok
+    m.engine.fold = False     # the fused-epilogue kernels apply the residual lambdas themselves: unfolded weights
+    m.engine.load_from(m)
     m.engine.fused_gemm = True
     B, steps = 5, 4
     r = np.random.default_rng(2)

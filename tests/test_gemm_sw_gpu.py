@@ -180,3 +180,43 @@ def test_gemm_sw_rejects_bad_arguments():
                           None) != 0                        # fp16 is not built
     assert lib.uv_gemm_sw(a.data_ptr(), 64, a.data_ptr(), c.data_ptr(), 128, 2, 128, 96, 64, None, 0, 0, 0, 0, None,
                           None) == -3                       # N % 128
+
+
+def _steps(m, B, steps, seed):
+    st = m.new_state(B, 64)
+    g = torch.Generator(device=DEV).manual_seed(seed)
+    out = []
+    for _ in range(steps):
+        tok = torch.randint(1, m.cfg.vocab_size, (B,), device=DEV, generator=g)
+        out.append(m.decode_step(tok, st, 64).float().cpu().numpy())
+    return np.stack(out), st
+
+
+@pytest.mark.parametrize("B", [5, 256])
+def test_three_step_paths_agree(B):
+    """One model, three ways to run the step: the reference's literal op order (library GEMMs + separate residual /
+    norm kernels), the folded residual stream with deferred norms (the default), and the tcgen05 GEMMs with fused
+    epilogues.  Logits agree within the path's 2e-2 tolerance; first-layer cache bytes within a step."""
+    from tests import golden_inputs as gi
+    from tests.helpers import build_model
+    spec = gi.model_specs()["uv50m"]
+    m = build_model(spec).to(DEV).to(torch.bfloat16).fuse_for_inference(torch.bfloat16)
+    eng = m.engine
+    assert eng.fold and eng.tc_gemm_ok
+    res = {}
+    for name, fold, tc in (("fold", True, False), ("literal", False, False), ("tc", False, True)):
+        eng.fold, eng.tc_gemm = fold, tc
+        eng.load_from(m)
+        res[name] = _steps(m, B, 5, 3)
+        assert eng.device_status() == {"attn_status": 0, "kv_oob": 0}
+    eng.fold, eng.tc_gemm = True, False
+    eng.load_from(m)
+    ref, sref = res["literal"]
+    for name in ("fold", "tc"):
+        lg, st = res[name]
+        assert np.isfinite(lg).all()
+        err = np.abs(lg - ref)
+        assert err.max() <= 2e-2 * np.abs(ref).max(), (name, err.max(), np.abs(ref).max())
+        assert (lg.argmax(-1) == ref.argmax(-1)).mean() > 0.9
+        d = (st.k[0].int() - sref.k[0].int()).abs()
+        assert int(d.max()) <= 2 and (d > 0).float().mean().item() < 0.05, (name, int(d.max()))

@@ -64,3 +64,32 @@ def test_missing_library_fails_loudly(monkeypatch, tmp_path):
     monkeypatch.setattr(_lib, "LIB_PATH", str(tmp_path / "libuvdecode.so"))
     with pytest.raises(_lib.UvError):
         _lib.lib()
+
+
+def test_device_handoff_layout_matches_reference_micro_batches():
+    """handoff.build_packed_device lays finished rollouts out exactly as the reference's host-side build_packed does
+    (golden: tests/golden/packing.npz, produced by ultraviolet/perf.py:55-95 itself).  Pure index arithmetic on
+    tensors, so the layout logic is checked here on CPU tensors; the GPU tests feed it real harvests."""
+    import numpy as np
+    import torch
+    from tests.helpers import golden
+    from ultraviolet_b200.handoff import build_packed_device, pack_bins
+    g = golden("packing")
+    items, budget, pad_id, seg_max = gi.packing_case()
+    p = dict(tokens=torch.from_numpy(np.concatenate([t[s:] for t, s, _, _ in items]).astype(np.int32)),
+             logp=torch.from_numpy(np.concatenate([b for *_, b in items])),
+             offsets=torch.from_numpy(np.concatenate([[0], np.cumsum([len(t) - s for t, s, _, _ in items])])),
+             prompt_tokens=torch.from_numpy(np.concatenate([t[:s] for t, s, _, _ in items]).astype(np.int32)),
+             prompt_offsets=torch.from_numpy(np.concatenate([[0], np.cumsum([s for _, s, _, _ in items])])),
+             metas=list(range(len(items))))
+    mbs = build_packed_device(p, [a for _, _, a, _ in items], budget, pad_id, seg_max)
+    assert len(mbs) == int(g["n"])
+    for i, mb in enumerate(mbs):
+        for k in ("x", "y", "pos", "cu", "tgt"):
+            assert np.array_equal(mb[k].numpy(), g[f"mb{i}.{k}"]), (i, k)
+        for k in ("A", "OL"):
+            np.testing.assert_allclose(mb[k].numpy(), g[f"mb{i}.{k}"], rtol=0, atol=0)
+        assert mb["max_seqlen"] == int(g[f"mb{i}.max_seqlen"])
+    bins = pack_bins([5, 900, 200, 100, 1024], 1024)
+    assert sorted(sum(bins, [])) == [0, 1, 2, 3, 4] and all(sum([5, 900, 200, 100, 1024][i] for i in b) <= 1024
+                                                           for b in bins)

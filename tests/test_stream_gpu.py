@@ -195,3 +195,55 @@ def test_grpo_group_of_identical_prompts_gets_distinct_streams():
     for other in (b, c):
         same = np.mean([a[k] == other[k] for k in a])
         assert same >= 0.75, same    # equal unless a batch-size dependent bf16 rounding flips a draw
+
+
+def test_device_handoff_of_a_real_harvest_and_direct_weight_publication():
+    """harvest_packed(with_prompts=True) -> build_packed_device: the micro-batches hold exactly the prompts,
+    generated tokens and behaviour log-probs of the finished rollouts, all on the device.  publish_weights writes the
+    trainer's parameters straight into the arena (same arena contents as sync_weights_inplace, same pointer)."""
+    from ultraviolet_b200.handoff import build_packed_device
+    from ultraviolet_b200.rl_stream import StreamGen, publish_weights, sync_weights_inplace
+    m = _model()
+    gen = StreamGen(m, slots=6, max_prompt=9, max_new=12, temperature=1.0, eos_id=0, check_every=4, seed=5)
+    r = np.random.default_rng(4)
+    prompts = {i: r.integers(1, 500, r.integers(2, 9)).tolist() for i in range(15)}
+    for i, p in prompts.items():
+        gen.add(p, meta=i)
+    gen._upload()
+    seen = {}
+    for _ in range(200):
+        gen._upload()
+        gen.sched.run(4)
+        p = gen.sched.harvest_packed(with_prompts=True)
+        if p is None:
+            if len(seen) == len(prompts):
+                break
+            continue
+        assert p["tokens"].is_cuda and p["prompt_tokens"].is_cuda
+        adv = [float(mm) + 1 for mm in p["metas"]]
+        for mb in build_packed_device(p, adv, budget=64, pad_id=0, seg_max=16):
+            assert mb["x"].is_cuda and mb["x"].shape == (1, 64) and int(mb["cu"][-1]) == 64
+            x, y, A, OL, cu = (mb[k].cpu().numpy() for k in ("x", "y", "A", "OL", "cu"))
+            for a, b in zip(cu[:-1], cu[1:]):
+                if A[0, a] <= 0:
+                    continue          # a pad segment
+                i = int(A[0, a]) - 1
+                pr = prompts[i]
+                n_gen = (b - a) + 1 - len(pr)
+                assert list(x[0, a:a + len(pr)]) == pr and (y[0, a:a + len(pr) - 1] == -1).all()
+                gen_toks = list(y[0, a + len(pr) - 1:b])
+                assert len(gen_toks) == n_gen and i not in seen
+                seen[i] = (gen_toks, OL[0, a + len(pr) - 1:b].copy())
+    assert sorted(seen) == sorted(prompts)
+    for i, (toks, lps) in seen.items():
+        assert 1 <= len(toks) <= 12 and (lps < 0).all() and (0 not in toks[:-1])
+    # direct publication == the reference-style sync, same arena pointer
+    raw = build_model(gi.model_specs()["tiny"]).to(DEV)
+    with torch.no_grad():
+        raw.blocks[1].mlp.w_down.mul_(1.5)
+    eng = m._uvb200_engine
+    ptr, v0 = eng.arena.data_ptr(), eng.version
+    publish_weights(m, raw)
+    a = eng.arena.clone()
+    sync_weights_inplace(m, raw)
+    assert eng.arena.data_ptr() == ptr and torch.equal(a, eng.arena) and eng.version == v0 + 2

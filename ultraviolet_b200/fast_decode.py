@@ -22,13 +22,20 @@ from .config import MathConfig, config_from
 
 
 class KernelDecodeState:
-    def __init__(self, cfg: MathConfig, B: int, max_len: int, dtype, device, kv_dtype: str = "int8"):
+    def __init__(self, cfg: MathConfig, B: int, max_len: int, dtype, device, kv_dtype: str = "int8",
+                 ring_extra: int = 0):
+        """ring_extra > 0 (not in the reference): local-layer rings get window + ring_extra slots (rounded up to a
+        multiple of 8) instead of window.  A step that writes up to ring_extra + 1 consecutive positions of one
+        sequence (prefill lanes) then never overwrites a key that another row of the same step still attends to,
+        for prompts of any length."""
         cfg = config_from(cfg)
         if kv_dtype != "int8":
             raise NotImplementedError("ultraviolet_b200 keeps the KV cache in int8 (kv_dtype='int8')")
         self.cfg, self.B, self.max_len, self.dtype = cfg, B, max_len, dtype
         self.kv_dtype = kv_dtype
         self.local_len = min(cfg.window, max_len)
+        if ring_extra > 0:
+            self.local_len = min((cfg.window + int(ring_extra) + 7) // 8 * 8, max(max_len, cfg.window))
         self.k, self.v, self.k_scale, self.v_scale = [], [], [], []
         self.mix: dict[int, dict] = {}
         for l in range(cfg.n_layers):
@@ -166,8 +173,9 @@ def patch_model(model, kv_dtype: str = "int8", num_splits: dict | None = None, b
     eng = DecodeEngine.from_model(model, dt)
     model.__dict__["_uvb200_engine"] = eng
 
-    def new_state(self, batch, max_len, dtype=None, device=None):
-        return KernelDecodeState(eng.cfg, batch, max_len, dtype or eng.dtype, device or eng.device, kv_dtype)
+    def new_state(self, batch, max_len, dtype=None, device=None, ring_extra=0):
+        return KernelDecodeState(eng.cfg, batch, max_len, dtype or eng.dtype, device or eng.device, kv_dtype,
+                                 ring_extra=ring_extra)
 
     def decode_step(self, tok, st, g_len, skip_attn=False):
         return decode_step_fast(self, tok, st, g_len, skip_attn, num_splits, backend)

@@ -119,6 +119,17 @@ class DecodeRunner:
         return self.out_tok
 
 
+def _new_state(model, rows, max_len, eng, ring_extra):
+    """model.new_state with the extra ring slots prefill lanes want; models patched by another library's
+    patch_model (no ring_extra argument) get the plain state, and lanes then stop at the window as before."""
+    if ring_extra:
+        try:
+            return model.new_state(rows, max_len, eng.dtype, eng.device, ring_extra=ring_extra)
+        except TypeError:
+            pass
+    return model.new_state(rows, max_len, eng.dtype, eng.device)
+
+
 def _left_pad(prompts, pad_id, dev):
     Tp = max(len(p) for p in prompts)
     idx = torch.full((len(prompts), Tp), pad_id, dtype=torch.long)
@@ -185,8 +196,8 @@ def generate_continuous(model, prompts, max_new: int, batch: int, temperature: f
     n = len(prompts)
     B = min(batch, n)
     max_prompt = max(len(p) for p in prompts)
-    st = model.new_state(GpuScheduler.state_rows(B, prefill_lanes), max_prompt + max_new + check_every, eng.dtype,
-                         eng.device)
+    st = _new_state(model, GpuScheduler.state_rows(B, prefill_lanes), max_prompt + max_new + check_every, eng,
+                    GpuScheduler.ring_extra(prefill_lanes))
     sched = GpuScheduler(eng, st, max_new=max_new, temperature=temperature, top_p=top_p, top_k=top_k, eos_id=eos_id,
                          pad_id=pad_id, seed=fresh_seed() if seed is None else int(seed), q_cap=max(n, 2), max_prompt=max_prompt, use_graph=use_graph,
                          prefill_lanes=prefill_lanes,

@@ -132,14 +132,14 @@ class MathLM(nn.Module):
         impl = self.decode_impl
         return "kernel-int8" if impl == "auto" else impl
 
-    def new_state(self, batch: int, max_len: int, dtype=None, device=None):
+    def new_state(self, batch: int, max_len: int, dtype=None, device=None, ring_extra: int = 0):
         from .fast_decode import KernelDecodeState
         eng = self.engine
         impl = self.resolve_decode_impl(dtype or eng.dtype, device or eng.device)
         if not impl.startswith("kernel-"):
             raise NotImplementedError(f"decode_impl {impl!r}: only the kernel KV states exist in ultraviolet_b200")
         return KernelDecodeState(self.cfg, batch, max_len, dtype or eng.dtype, device or eng.device,
-                                 kv_dtype=impl.split("-")[1])
+                                 kv_dtype=impl.split("-")[1], ring_extra=ring_extra)
 
     @torch.no_grad()
     def prefill(self, idx: Tensor, starts: Tensor, st, rows: Tensor | None = None) -> Tensor:

@@ -27,6 +27,20 @@ def sync_weights_inplace(gen_m, raw) -> None:
     torch.cuda.synchronize(gen_m.embed.weight.device)
 
 
+@torch.no_grad()
+def publish_weights(gen_m, raw, sync: bool = True) -> None:
+    """In-place weight publication without the intermediate copy: the fused inference weights (wqkv * qkv_scale,
+    wo * o_scale, [w_gate; w_up], w_down, tanh(xsa_alpha), the residual lambdas; Attention.fuse / MLP.fuse,
+    ultraviolet/model.py:289-300, :384-386) are computed from the TRAINER's parameters `raw` and written straight
+    into gen_m's arena.  gen_m's own parameter tensors are not touched (nothing on the decode path reads them), so
+    the O(params) parameter copy of sync_weights_inplace (rl_stream.py:23-36) disappears; pointers, captured graphs
+    and in-flight rows behave exactly as there.  Follow it with ``dist.broadcast_weights`` when only rank 0 holds
+    the trainer."""
+    _engine(gen_m).load_from(raw)
+    if sync:
+        torch.cuda.synchronize(_engine(gen_m).device)
+
+
 class StreamGen:
     def __init__(self, model, slots, max_prompt, max_new, temperature, eos_id, check_every=16, compile=True,
                  use_graph=True, pad_id=0, dtype=torch.float16, bucket=1024, top_p: float = 1.0,
@@ -43,8 +57,9 @@ class StreamGen:
         self.dev = eng.device
         if prefill_lanes is None:  # a quarter more batch rows for prompt tokens once the batch is large enough
             prefill_lanes = slots // 4 if slots >= 32 else 0
-        self.st = model.new_state(GpuScheduler.state_rows(slots, prefill_lanes), max_prompt + max_new + check_every,
-                                  eng.dtype, self.dev)
+        from .generate import _new_state
+        self.st = _new_state(model, GpuScheduler.state_rows(slots, prefill_lanes), max_prompt + max_new + check_every,
+                             eng, GpuScheduler.ring_extra(prefill_lanes))
         self.sched = GpuScheduler(eng, self.st, max_new=max_new, temperature=temperature, top_p=top_p, eos_id=eos_id,
                                   pad_id=pad_id, seed=seed, q_cap=queue_capacity, max_prompt=max_prompt,
                                   use_graph=use_graph, prefill_lanes=prefill_lanes)

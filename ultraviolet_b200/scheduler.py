@@ -69,7 +69,13 @@ class GpuScheduler:
         a = self.args = _lib.SchedArgs()
         if self.L > 0:
             a.row_map, a.lanes, a.lane_chunk = self.row_map.data_ptr(), self.L, int(lane_chunk)
-            a.ring_len = min(int(k.size(2)) for k in st.k)
+            # A chunk of lane_chunk consecutive positions of one sequence must not overwrite a ring slot that a row
+            # of the same step still reads.  Rings with at least window + lane_chunk - 1 slots (new_state(...,
+            # ring_extra=lane_chunk)) can never do that; shorter ones only take chunks while the ring has not
+            # wrapped yet (prompts up to the ring length).
+            ring = min(int(k.size(2)) for k in st.k)
+            window = int(getattr(getattr(st, "cfg", None), "window", 0) or 0)
+            a.ring_len = (1 << 40) if window > 0 and ring >= window + int(lane_chunk) - 1 else ring
         for name in ("req", "fed", "gen", "cur_tok", "row_key", "step_ctr", "prompt_off", "prompt_len", "limit",
                      "key", "out_off", "out_len", "start_version", "tokens", "out_tok", "out_lp", "fin_ring", "ctl",
                      "samp_tok", "samp_lp"):
@@ -89,6 +95,12 @@ class GpuScheduler:
         self.graph = None
         self.steps_run = 0
         self._primed = False
+
+    @staticmethod
+    def ring_extra(prefill_lanes: int = 0, lane_chunk: int = 8) -> int:
+        """Extra local-ring slots a state should be created with (new_state(..., ring_extra=...)) so that prefill
+        lanes keep working on prompts longer than the attention window."""
+        return int(lane_chunk) if prefill_lanes > 0 else 0
 
     @staticmethod
     def state_rows(slots: int, prefill_lanes: int = 0) -> int:
@@ -193,12 +205,14 @@ class GpuScheduler:
                     active=int(c[CTL_ACTIVE]), status=int(c[CTL_STATUS]), steps=int(c[CTL_STEPS]),
                     generated=int(c[CTL_GENERATED]), slot_steps=int(c[CTL_SLOT_STEPS]))
 
-    def harvest_packed(self):
+    def harvest_packed(self, with_prompts: bool = False):
         """Finished requests since the last call as DEVICE tensors (the packed hand-off a trainer consumes without a
         host round trip of the payload; role of perf.py:55-95's packed micro-batches): dict with ``tokens`` int32 and
         ``logp`` fp32 (total,), ``offsets`` int64 (n + 1,) delimiting each request's span, ``versions`` int32 (n,),
-        ``requests`` int64 (n,) request indices in finishing order, and ``metas`` (host list).  One small D2H (the
-        finished count and the span lengths' total); None when nothing finished."""
+        ``requests`` int64 (n,) request indices in finishing order, and ``metas`` (host list); with_prompts adds the
+        requests' prompt tokens in the same form (``prompt_tokens`` int32, ``prompt_offsets`` int64), read from the
+        device-side prompt ring before its space is released (``handoff.build_packed_device`` wants them).  One
+        small D2H (the finished count and the span lengths' total); None when nothing finished."""
         fin = int(self.ctl[CTL_FIN].item())
         if fin == self.n_harvested:
             return None
@@ -212,6 +226,14 @@ class GpuScheduler:
         seg = torch.repeat_interleave(torch.arange(rid.numel(), device=self.dev), lens, output_size=total)
         within = torch.arange(total, device=self.dev) - (ends - lens)[seg]
         flat = (offs[seg] + within) % self.out_cap
+        extra = {}
+        if with_prompts:
+            pl, po = self.prompt_len[ri].long(), self.prompt_off[ri]
+            pends = torch.cumsum(pl, 0)
+            ptotal = int(pends[-1].item())
+            pseg = torch.repeat_interleave(torch.arange(rid.numel(), device=self.dev), pl, output_size=ptotal)
+            pflat = (po[pseg] + torch.arange(ptotal, device=self.dev) - (pends - pl)[pseg]) % self.tok_cap
+            extra = dict(prompt_tokens=self.tokens[pflat], prompt_offsets=torch.cat([pends.new_zeros(1), pends]))
         rid_h = rid.cpu().tolist()
         metas = [self.meta.pop(r) for r in rid_h]
         for r in rid_h:
@@ -220,7 +242,7 @@ class GpuScheduler:
         while self._oldest < self.n_enqueued and self._oldest not in self._span:
             self._oldest += 1
         return dict(tokens=self.out_tok[flat], logp=self.out_lp[flat],
-                    offsets=torch.cat([ends.new_zeros(1), ends]), versions=ver, requests=rid, metas=metas)
+                    offsets=torch.cat([ends.new_zeros(1), ends]), versions=ver, requests=rid, metas=metas, **extra)
 
     def harvest(self):
         """Return the requests that finished since the last call as [(meta, tokens list, logp float32 array,
