@@ -560,6 +560,10 @@ def main():
     idx, starts = _left_pad(prompts, 0, dev)
     torch.cuda.synchronize()
     t0 = time.perf_counter()
+    m.prefill(idx[:, :-1], starts, m.new_state(SLOTS, max_len))   # first call: buffers, library handles, kernel loads
+    torch.cuda.synchronize()
+    prefill_first_s = time.perf_counter() - t0
+    t0 = time.perf_counter()
     m.prefill(idx[:, :-1], starts, st)
     torch.cuda.synchronize()
     prefill_s = time.perf_counter() - t0
@@ -662,7 +666,7 @@ def main():
         "dtype": "bf16", "data": "synthetic", "config": workload_config(K),
         "run": {"timed_blocks_ms": block_ms, "timed": f"median of {R} blocks of {K} steps", "max_len": max_len,
                 "l2": "per-step working set (99.6 MB weights + KV of 10 layers) exceeds L2; no flush",
-                "prefill_s": prefill_s, "prefill_tokens": int(sum(len(p) - 1 for p in prompts)),
+                "prefill_s": prefill_s, "prefill_first_call_s": prefill_first_s, "prefill_tokens": int(sum(len(p) - 1 for p in prompts)),
                 "context_begin": int(pos_begin.float().mean().item()),
                 "context_end": context_end,
                 "weight_broadcast_ms": t_bcast * 1e3, "rollout_gather_ms": t_gather * 1e3,

@@ -373,6 +373,7 @@ int uv_gemm_tc_swiglu(const void* a, int64_t lda, const void* w_gu, void* act, i
  * ctl (int64[16]): [0] head  [1] tail  [2] finished count  [3] weight version (host-written)  [4] active slots
  *                  [5] status bits  [6] steps run  [7] prompt-token tail  [8] output-slot tail
  *                  [9] tokens generated so far  [10] active slots summed over steps (occupancy = [10] / ([6] * B))
+ *                  [11] packed prefill rows used by uv_sched_admit passes  [12] admission passes run
  */
 typedef struct uv_sched_args {
   int* req; int* fed; int* gen;                 /* per slot (B,) */
@@ -397,9 +398,28 @@ typedef struct uv_sched_args {
   int64_t* row_map;
   int lanes, lane_chunk;
   int64_t ring_len;
+  /* 1: uv_sched_step only retires (freed slots are parked); queued requests enter through uv_sched_admit passes */
+  int no_admit;
+  int reserved_;
 } uv_sched_args;
 
 int uv_sched_step(const uv_sched_args* args, void* stream);
+
+/* uv_sched_admit: one admission pass of the no_admit mode -- the device-side counterpart of StreamGen._refill's
+ * batched prefill (scripts/rl_stream.py:76-101; packed form: ultraviolet/kernels/fast_decode.py:210-269).  Queued
+ * requests, in queue order, take the free slots, in slot order, while their prompts fit `cap` packed rows (the
+ * admitted set is a prefix of the queue).  A request of P prompt tokens contributes tokens 0 .. P - 2 as packed rows
+ * (tok / pos / row / last_pos, the inputs of one packed prefill pass: uv_prefill_attn with cu / tile_cu as its
+ * cu_seqlens / tile_cu over n_seq = B sequences, unused entries empty) and its slot is left with the last prompt
+ * token at position P - 1 for the next decode step.  Unused rows carry the pad token on cache row B (a spare row the
+ * caller allocates).  ctl[0] (head) advances by the number admitted; ctl[11] accumulates the rows used. */
+typedef struct uv_sched_admit_args {
+  int64_t* tok; int64_t* pos; int64_t* row; int64_t* last_pos;   /* (cap,) */
+  int32_t* cu; int32_t* tile_cu;                                 /* (B + 1,) */
+  int cap;
+  int reserved_;
+} uv_sched_admit_args;
+int uv_sched_admit(const uv_sched_args* args, const uv_sched_admit_args* pass, void* stream);
 int uv_sched_enqueue(const uv_sched_args* args, int n, void* stream);
 
 #ifdef __cplusplus

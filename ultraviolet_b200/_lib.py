@@ -73,7 +73,13 @@ class SchedArgs(C.Structure):
         "fin_ring", "ctl")] + [("B", C.c_int), ("q_cap", C.c_int), ("tok_cap", C.c_int64), ("out_cap", C.c_int64),
                                ("eos", C.c_int), ("pad", C.c_int), ("force_eos", C.c_int), ("max_len", C.c_int64),
                                ("row_map", C.c_void_p), ("lanes", C.c_int), ("lane_chunk", C.c_int),
-                               ("ring_len", C.c_int64)]
+                               ("ring_len", C.c_int64), ("no_admit", C.c_int), ("reserved_", C.c_int)]
+
+
+class SchedAdmitArgs(C.Structure):
+    """uv_sched_admit_args (include/uvdecode.h)."""
+    _fields_ = [("tok", C.c_void_p), ("pos", C.c_void_p), ("row", C.c_void_p), ("last_pos", C.c_void_p),
+                ("cu", C.c_void_p), ("tile_cu", C.c_void_p), ("cap", C.c_int), ("reserved_", C.c_int)]
 
 
 # name -> (restype, argtypes); every symbol include/uvdecode.h declares
@@ -126,6 +132,7 @@ SIGNATURES = {
     "uv_gemm_resid_norm": (C.c_int, [C.c_void_p, C.c_int64, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p,
                                      C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p]),
     "uv_sched_step": (C.c_int, [C.POINTER(SchedArgs), C.c_void_p]),
+    "uv_sched_admit": (C.c_int, [C.POINTER(SchedArgs), C.POINTER(SchedAdmitArgs), C.c_void_p]),
     "uv_sched_enqueue": (C.c_int, [C.POINTER(SchedArgs), C.c_int, C.c_void_p]),
     "uv_sample_topk": (C.c_int, [C.c_void_p, C.c_int, C.c_int64, C.c_int, C.c_int, C.c_int, C.c_float, C.c_float,
                                  C.c_float, C.c_float, C.c_int, C.c_float, C.c_void_p, C.c_uint64, C.c_void_p,

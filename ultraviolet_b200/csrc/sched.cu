@@ -64,10 +64,26 @@ struct SchedParams {
   int lanes, lane_chunk;
   int64_t ring_len;    // length of the shortest ring cache: a chunk never wraps it (a wrapped write would destroy
                        // keys that the chunk's earlier positions still attend to)
+  // 1: the step kernel only retires; freed slots are parked and queued requests wait for an admission pass
+  // (sched_admit_kernel + packed prefill) that the host launches between steps
+  int no_admit;
+  int reserved_;
+};
+
+// One admission pass: packed prefill inputs for the requests it admits.
+struct AdmitParams {
+  int64_t* tok;        // (cap,) token of every packed row
+  int64_t* pos;        // (cap,) its position inside its prompt
+  int64_t* row;        // (cap,) its cache row (the slot); unused rows point at the spare row B
+  int64_t* last_pos;   // (cap,) last prefilled position of its prompt
+  int* cu;             // (B + 1,) first packed row of the q-th admitted request (unused entries = rows used)
+  int* tile_cu;        // (B + 1,) first 16-token tile likewise
+  int cap;             // packed rows available in this pass
+  int reserved_;
 };
 
 enum { CTL_HEAD = 0, CTL_TAIL, CTL_FIN, CTL_VERSION, CTL_ACTIVE, CTL_STATUS, CTL_STEPS, CTL_TOK_TAIL, CTL_OUT_TAIL,
-       CTL_GENERATED, CTL_SLOT_STEPS };
+       CTL_GENERATED, CTL_SLOT_STEPS, CTL_PREFILL_ROWS, CTL_ADMIT_PASSES };
 
 __device__ __forceinline__ int block_excl_scan(int v, int* warp_tot, int tid, int& total) {
   const int lane = tid & 31, warp = tid >> 5;
@@ -185,7 +201,7 @@ __global__ void __launch_bounds__(SCHED_THREADS) sched_step_kernel(const __grid_
     generated += field(tot3, 1);
     // ---- admit queued requests into the free slots of this chunk, in slot order
     const int rank = field(pre3, 2), total_free = field(tot3, 2);
-    const int64_t avail = tail - head;
+    const int64_t avail = P.no_admit ? 0 : tail - head;
     if (in && freed) {
       if (rank < avail) {
         const int64_t r = head + rank;
@@ -266,6 +282,86 @@ __global__ void __launch_bounds__(SCHED_THREADS) sched_step_kernel(const __grid_
   }
 }
 
+// Admission pass (no_admit mode): queued requests, in queue order, take the free slots, in slot order, as long as
+// their prompts fit the pass's packed rows.  A request of P prompt tokens contributes its first P - 1 tokens as
+// packed rows (positions 0 .. P - 2 of its slot's cache row; the packed trunk that follows prefills them in one
+// pass) and its slot is left holding the LAST prompt token at position P - 1, which the next decode step consumes
+// like any other token -- the sampler's output of that step is generated token 0.  The admitted set is always a
+// prefix of the queue: request k is taken iff the prompts of requests 0 .. k fit together.
+__global__ void __launch_bounds__(SCHED_THREADS) sched_admit_kernel(const __grid_constant__ SchedParams P,
+                                                                    const __grid_constant__ AdmitParams A) {
+  __shared__ unsigned long long warp_tot3[SCHED_THREADS / 32];
+  const int tid = threadIdx.x;
+  pdl_wait();
+  pdl_trigger();
+  const int64_t head = P.ctl[CTL_HEAD], tail = P.ctl[CTL_TAIL];
+  const int version = (int)P.ctl[CTL_VERSION];
+  int nseq = 0, rows = 0, tiles = 0;
+  bool stop = false;
+  for (int base = 0; base < P.B; base += SCHED_THREADS) {  // uniform trip count and uniform `stop`
+    const int s = base + tid;
+    const bool freed = s < P.B && P.req[s] < 0;
+    unsigned long long tot;
+    // (1) rank among the chunk's free slots -> candidate request
+    const unsigned long long pre_a = block_excl_scan3(pack3(freed ? 1 : 0, 0, 0), warp_tot3, tid, tot);
+    const int rank = field(pre_a, 0);
+    const int64_t r = head + nseq + rank;
+    const bool has = !stop && freed && r < tail;
+    const int ri = has ? (int)(r % P.q_cap) : 0;
+    const int plen = has ? P.prompt_len[ri] : 0;
+    const int w = has ? plen - 1 : 0;
+    // (2) does the queue prefix up to this request fit?  (inclusive prefix sums are monotone: the set is a prefix)
+    const unsigned long long pre_b = block_excl_scan3(pack3(w, has ? 1 : 0, 0), warp_tot3, tid, tot);
+    const bool ok = has && rows + field(pre_b, 0) + w <= A.cap;
+    const int n_has = field(tot, 1);
+    // (3) offsets of the admitted ones
+    const unsigned long long pre_c = block_excl_scan3(pack3(ok ? w : 0, ok ? (w + 15) / 16 : 0, ok ? 1 : 0), warp_tot3,
+                                                      tid, tot);
+    if (ok) {
+      const int q = nseq + field(pre_c, 2), row0 = rows + field(pre_c, 0);
+      A.cu[q] = row0;
+      A.tile_cu[q] = tiles + field(pre_c, 1);
+      const int64_t toff = P.prompt_off[ri];
+      for (int j = 0; j < w; ++j) {
+        A.tok[row0 + j] = P.tokens[(toff + j) % P.tok_cap];
+        A.pos[row0 + j] = j;
+        A.row[row0 + j] = s;
+        A.last_pos[row0 + j] = w - 1;
+      }
+      P.req[s] = (int)r;
+      P.fed[s] = plen;
+      P.gen[s] = 0;
+      P.cur_tok[s] = P.tokens[(toff + plen - 1) % P.tok_cap];
+      P.pos[s] = plen - 1;
+      P.starts[s] = 0;
+      P.row_key[s] = P.key[ri];
+      P.step_ctr[s] = 0;
+      P.start_version[ri] = version;
+    }
+    rows += field(tot, 0);
+    tiles += field(tot, 1);
+    const int n_ok = field(tot, 2);
+    nseq += n_ok;
+    if (n_ok < n_has) stop = true;  // the next request does not fit: later (shorter) ones must not overtake it
+  }
+  // unused sequence entries and packed rows
+  for (int q = nseq + tid; q <= P.B; q += SCHED_THREADS) {
+    A.cu[q] = rows;
+    A.tile_cu[q] = tiles;
+  }
+  for (int i = rows + tid; i < A.cap; i += SCHED_THREADS) {
+    A.tok[i] = P.pad;
+    A.pos[i] = 0;
+    A.row[i] = P.B;      // the spare cache row
+    A.last_pos[i] = 0;
+  }
+  if (tid == 0) {
+    P.ctl[CTL_HEAD] = head + nseq;
+    P.ctl[CTL_PREFILL_ROWS] += rows;
+    P.ctl[CTL_ADMIT_PASSES] += 1;
+  }
+}
+
 // Append n requests whose prompt_len / limit / key entries and prompt tokens the host has already copied into the
 // rings at [tail, tail + n) and [tok_tail, tok_tail + sum(len)): computes their prompt and output offsets by prefix
 // sum, clears out_len, then publishes the new tail.
@@ -315,6 +411,23 @@ extern "C" int uv_sched_step(const uv_sched_args* a, void* stream) {
   static_assert(sizeof(SchedParams) == sizeof(uv_sched_args), "uv_sched_args mirrors SchedParams");
   memcpy(&P, a, sizeof(P));
   launch_pdl(sched_step_kernel, dim3(1), dim3(SCHED_THREADS), 0, static_cast<cudaStream_t>(stream), P);
+  return check_launch();
+}
+
+extern "C" int uv_sched_admit(const uv_sched_args* a, const uv_sched_admit_args* p, void* stream) {
+  using namespace uv;
+  if (!a || !p) return UV_ERR_ARG;
+  if (a->B < 1 || a->q_cap < 1 || a->tok_cap < 1) return UV_ERR_ARG;
+  if (!a->req || !a->fed || !a->gen || !a->cur_tok || !a->pos || !a->starts || !a->row_key || !a->step_ctr ||
+      !a->prompt_off || !a->prompt_len || !a->key || !a->start_version || !a->tokens || !a->ctl)
+    return UV_ERR_ARG;
+  if (!p->tok || !p->pos || !p->row || !p->last_pos || !p->cu || !p->tile_cu || p->cap < 0) return UV_ERR_ARG;
+  SchedParams P;
+  AdmitParams A;
+  static_assert(sizeof(AdmitParams) == sizeof(uv_sched_admit_args), "uv_sched_admit_args mirrors AdmitParams");
+  memcpy(&P, a, sizeof(P));
+  memcpy(&A, p, sizeof(A));
+  launch_pdl(sched_admit_kernel, dim3(1), dim3(SCHED_THREADS), 0, static_cast<cudaStream_t>(stream), P, A);
   return check_launch();
 }
 
