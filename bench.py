@@ -364,12 +364,12 @@ def run_reference_arm(args, rank, world):
 
 # ------------------------------------------------------------------------------------------------ rollout jobs
 def rollout_job(m, rank, world, dev, *, prompts_all, stops_all, slots, max_new, max_prompt, lanes, lane_chunk, seed,
-                force_eos, timed_steps=0, warmup=3, broadcast=False, gather=False):
+                force_eos, timed_steps=0, warmup=3, broadcast=False, gather=False, packed=True):
     """One rollout round on the device-resident scheduler: the requests are sharded i % W == rank, every rank runs
     its replica until its share is drained (timed_steps > 0: that many steps only), finished rollouts are harvested
     as device tensors.  Optionally the weight arena is broadcast from rank 0 first and the rollouts (tokens int32,
     log-probs fp32, lengths and start versions int32) are gathered to rank 0 afterwards, each collective timed.
-    Windows of 64 steps are timed separately so that the steady state (slot occupancy >= 0.95) can be told from the
+    Windows of 16 (packed admission) or 64 steps are timed separately so that the steady state (slot occupancy >= 0.95) can be told from the
     straggler tail.  Returns a dict on every rank (aggregates are all-reduced)."""
     import torch
     import torch.distributed as dist
@@ -381,11 +381,15 @@ def rollout_job(m, rank, world, dev, *, prompts_all, stops_all, slots, max_new, 
     t_bcast = uvdist.broadcast_weights(eng) if (world > 1 and broadcast) else 0.0
     lens = np.array([len(p) for p in prompts_all])
     lim = np.full(n_req, max_new) if stops_all is None else np.asarray(stops_all)
-    st = m.new_state(GpuScheduler.state_rows(slots, lanes), max_prompt + max_new + 16,
+    if packed:
+        lanes = 0
+    st = m.new_state(GpuScheduler.state_rows(slots, lanes, packed), max_prompt + max_new + 16,
                      ring_extra=GpuScheduler.ring_extra(lanes, lane_chunk))
     sch = GpuScheduler(eng, st, max_new=max_new, temperature=1.0, eos_id=0, seed=seed, q_cap=max(len(mine), 2),
                        max_prompt=max_prompt, force_eos=force_eos, tok_cap=int(lens[mine].sum()) + 1,
-                       out_cap=int(lim[mine].sum()) + 1, prefill_lanes=lanes, lane_chunk=lane_chunk)
+                       out_cap=int(lim[mine].sum()) + 1, prefill_lanes=lanes, lane_chunk=lane_chunk,
+                       packed_prefill=packed)
+    W_STEPS = 16 if packed else 64   # steps between harvests (= between admission passes in packed mode)
     sch.enqueue([prompts_all[i] for i in mine], limits=None if stops_all is None else lim[mine].tolist(), keys=mine,
                 metas=mine)
     sch.run(max(warmup, 3))
@@ -398,7 +402,7 @@ def rollout_job(m, rank, world, dev, *, prompts_all, stops_all, slots, max_new, 
     e_begin, e_end = ev(), ev()
     e_begin.record()
     while True:
-        n = 64 if timed_steps <= 0 else min(64, timed_steps - steps)
+        n = W_STEPS if timed_steps <= 0 else min(W_STEPS, timed_steps - steps)
         a, b = ev(), ev()
         a.record()
         sch.run(n)
@@ -437,7 +441,9 @@ def rollout_job(m, rank, world, dev, *, prompts_all, stops_all, slots, max_new, 
            "steps_all_ranks": int(agg[2].item()), "ms_per_step_rank0": ms / max(steps, 1),
            "slot_occupancy": float(agg[1].item()) / max(float(agg[2].item()) * slots, 1.0),
            "steady_state_tokens_per_s": (float(agg[3].item()) / (float(mx[1].item()) / 1e3)) if mx[1].item() > 0 else None,
-           "steady_state": "64-step windows with slot occupancy >= 0.95 (max window time over ranks)",
+           "steady_state": f"{W_STEPS}-step windows with slot occupancy >= 0.95 (max window time over ranks)",
+           "prefill": "packed admission passes" if packed else (f"{lanes} prefill lanes" if lanes else "decode step"),
+           "admission_passes": getattr(sch, "n_admit_passes", 0),
            "weight_broadcast_ms": t_bcast * 1e3, "rollout_gather_ms": t_gather * 1e3,
            "device_status": eng.device_status(), "sched_status": c_prev["status"]}
     if gathered is not None:
@@ -472,7 +478,7 @@ def run_continuous(args, m, rank, world, dev):
     prompts, stops, max_prompt, max_new = config3_requests()
     r = rollout_job(m, rank, world, dev, prompts_all=prompts, stops_all=stops, slots=512, max_new=max_new,
                     max_prompt=max_prompt, lanes=args.lanes, lane_chunk=args.lane_chunk, seed=7, force_eos=True,
-                    timed_steps=args.steps, warmup=args.warmup, broadcast=True)
+                    timed_steps=args.steps, warmup=args.warmup, broadcast=True, packed=args.prefill == "packed")
     if rank == 0:
         line = {"metric": "rollout decode tokens/s", "value": r["tokens_per_s"], "unit": "tokens/s",
                 "n_gpus": world, "steps": r["steps_all_ranks"] // world, "warmup": max(args.warmup, 3),
@@ -497,12 +503,17 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="fixed", choices=["fixed", "continuous", "attn"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--profile", action="store_true",
+                    help="profiling runs (under ncu): one round of the attention timing loops instead of four")
     ap.add_argument("--no-rollouts", action="store_true",
                     help="skip the continuous-batching and GRPO-shaped rollout jobs reported beside the headline")
     ap.add_argument("--reference-gpu", action="store_true",
                     help="with --impl reference: also time the reference's Triton / NVRTC attention kernels on the GPU")
     ap.add_argument("--reference-gpu-only", action="store_true",
                     help="with --impl reference: print only that GPU comparator object")
+    ap.add_argument("--prefill", default="packed", choices=["packed", "lanes"],
+                    help="rollout jobs: how prompts enter the cache (packed admission passes, or prefill lanes through "
+                         "the decode step)")
     ap.add_argument("--lanes", type=int, default=128,
                     help="continuous workload: extra batch rows that carry prompt tokens of refilling slots (0 = "
                          "one prompt token per slot per step)")
@@ -626,10 +637,10 @@ def main():
     # ---- roofline of the dominant kernel of this library (decode attention), at the run's final cache state
     #      (rank 0 measures; the other ranks wait at the next job's barrier)
     if rank == 0:
-        att = time_attention_layers(eng, st, st.pos - 1, st.starts)
+        att = time_attention_layers(eng, st, st.pos - 1, st.starts, rounds=1 if args.profile else 4)
         att_mid = att["local"] if att["local"]["ms"] * 8 >= att["global"]["ms"] * 2 else att["global"]
-        lc = long_context_attention(eng)
-        lc2 = long_context_attention(eng, ctx=16384)
+        lc = long_context_attention(eng, rounds=1 if args.profile else 4)
+        lc2 = lc if args.profile else long_context_attention(eng, ctx=16384)
         context_end = int(st.pos.float().mean().item())
         torch.cuda.empty_cache()
 
@@ -639,14 +650,15 @@ def main():
     if not args.no_rollouts:
         prompts3, stops3, mp3, mn3 = config3_requests()
         cont = rollout_job(m, rank, world, dev, prompts_all=prompts3, stops_all=stops3, slots=512, max_new=mn3,
-                           max_prompt=mp3, lanes=args.lanes, lane_chunk=args.lane_chunk, seed=7, force_eos=True)
+                           max_prompt=mp3, lanes=args.lanes, lane_chunk=args.lane_chunk, seed=7, force_eos=True,
+                           packed=args.prefill == "packed")
         cont["workload"] = ("BASELINE configs[2]: 4096 requests sharded i % W, prompts U[16,256], stop ~ "
                             "Geometric(600) <= 2048 (EOS forced), 512 slots/GPU, T = 1.0; whole job until drained")
         torch.cuda.empty_cache()
         prompts5, mp5, mn5 = config5_requests()
         grpo = rollout_job(m, rank, world, dev, prompts_all=prompts5, stops_all=None, slots=512, max_new=mn5,
                            max_prompt=mp5, lanes=args.lanes, lane_chunk=args.lane_chunk, seed=11, force_eos=False,
-                           broadcast=True, gather=True)
+                           broadcast=True, gather=True, packed=args.prefill == "packed")
         grpo["workload"] = ("BASELINE configs[4]: 256 prompts U[64,256] x group 8 = 2048 sequences sharded i % W, "
                             "max_new 2048, T = 1.0, top-p 1.0, Philox key per sequence; arena broadcast before the "
                             "round, rollouts (tokens, log-probs, versions) gathered to rank 0 after it")

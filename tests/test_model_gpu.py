@@ -134,7 +134,7 @@ def test_continuous_with_prefill_lanes_matches_without():
     prompts = [r.integers(1, 500, r.integers(3, 40)).tolist() for _ in range(14)]
     kw = dict(batch=4, temperature=0.0, eos_id=c["eos_id"], check_every=4)
     s0 = {}
-    base = generate_continuous(m, prompts, 10, stats=s0, **kw)
+    base = generate_continuous(m, prompts, 10, stats=s0, packed_prefill=False, **kw)
     for graph in (False, True):
         s1 = {}
         lanes = generate_continuous(m, prompts, 10, prefill_lanes=6, use_graph=graph, stats=s1, **kw)
@@ -256,3 +256,31 @@ def test_cache_bytes_against_the_reference_in_bf16(name):
         # deeper layers: the residual stream is carried with the lambdas folded into the weights, so it rounds at
         # other points than the reference's op-by-op bf16 chain (measured: up to 4 steps, ~42 % of the bytes)
         assert mx <= 5 and frac < 0.5, stats
+
+
+def test_continuous_with_packed_admission_matches_static_generation():
+    """Packed admission passes (the default of generate_continuous): requests enter through one packed prefill batch
+    per refill, the way generate() prefills.  Per-request greedy outputs agree with static generation (the frames
+    differ -- position 0 here, left-padded there -- so only bf16 rounding separates them) and with the
+    decode-step route; every request comes back with its length; far fewer steps than feeding prompts token by token."""
+    from ultraviolet_b200.generate import generate, generate_continuous
+    spec = gi.model_specs()["tiny"]
+    m = _gpu_model(spec)
+    r = np.random.default_rng(9)
+    prompts = [r.integers(1, 500, r.integers(1, 40)).tolist() for _ in range(19)]    # includes 1-token prompts
+    lens = r.integers(1, 12, len(prompts)).tolist()
+    s_p, s_s = {}, {}
+    for graph in (False, True):
+        got = generate_continuous(m, prompts, 12, batch=5, temperature=0.0, eos_id=None, check_every=4,
+                                  target_lens=lens, stats=s_p, use_graph=graph)
+        assert [len(x) for x in got] == lens
+        sames = []
+        for i, p in enumerate(prompts):
+            solo = generate(m, [p], lens[i], temperature=0.0, use_graph=False)[0]
+            sames += [a == b for a, b in zip(solo, got[i])]
+        assert np.mean(sames) > 0.8, (graph, np.mean(sames))
+    step = generate_continuous(m, prompts, 12, batch=5, temperature=0.0, eos_id=None, check_every=4,
+                               target_lens=lens, stats=s_s, packed_prefill=False)
+    assert [len(x) for x in step] == lens
+    assert np.mean([a == b for x, y in zip(step, got) for a, b in zip(x, y)]) > 0.6
+    assert s_p["steps"] < 0.6 * s_s["steps"], (s_p, s_s)

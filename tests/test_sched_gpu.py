@@ -234,3 +234,60 @@ def test_harvest_packed_is_the_same_payload_on_the_device():
 
     a, b = drive(False), drive(True)
     assert len(a) == n and a == b
+
+
+@pytest.mark.parametrize("B,cap,busy", [(6, 256, (1, 4)), (40, 64, ()), (1500, 4096, tuple(range(0, 1500, 7)))])
+def test_admission_pass_kernel_matches_host_model(B, cap, busy):
+    """uv_sched_admit alone: queued requests take the free slots in order while their prompts fit the packed rows;
+    packed rows, prefix sums, slot state and the queue head against a host model."""
+    import ctypes as C
+    from ultraviolet_b200 import _lib
+    from ultraviolet_b200.kernels._util import stream_ptr
+    from ultraviolet_b200.scheduler import GpuScheduler
+    r = np.random.default_rng(B)
+    n = B + 9
+    prompts = [r.integers(1, 900, r.integers(1, 30)).tolist() for _ in range(n)]
+    st, eng = _FakeState(B + 1, 64), _FakeEngine(B)
+    sch = GpuScheduler(eng, st, max_new=8, temperature=1.0, eos_id=0, q_cap=max(4096, n), max_prompt=32,
+                       use_graph=False, packed_prefill=True, prefill_cap=cap)
+    sch.enqueue(prompts)
+    for s_ in busy:
+        sch.req[s_] = 10 ** 6 + s_          # slots that hold some other request
+    p = _lib.SchedAdmitArgs()
+    p.tok, p.pos, p.row, p.last_pos = (t.data_ptr() for t in (sch.pk_tok, sch.pk_pos, sch.pk_row, sch.pk_last))
+    p.cu, p.tile_cu, p.cap = sch.pk_cu.data_ptr(), sch.pk_tile_cu.data_ptr(), cap
+    _lib.check(_lib.lib().uv_sched_admit(C.byref(sch.args), C.byref(p), stream_ptr(torch.device(DEV))), "admit")
+    torch.cuda.synchronize()
+    # host model
+    free = [s_ for s_ in range(B) if s_ not in busy]
+    rows, k = 0, 0
+    exp = dict(tok=[], pos=[], row=[], last=[], cu=[], tcu=[], slot={})
+    tiles = 0
+    for s_, pr in zip(free, prompts):
+        w = len(pr) - 1
+        if rows + w > cap:
+            break
+        exp["cu"].append(rows)
+        exp["tcu"].append(tiles)
+        exp["tok"] += pr[:-1]
+        exp["pos"] += list(range(w))
+        exp["row"] += [s_] * w
+        exp["last"] += [w - 1] * w
+        exp["slot"][s_] = (k, pr[-1], w)
+        rows, tiles, k = rows + w, tiles + (w + 15) // 16, k + 1
+    assert k > 0
+    assert int(sch.ctl[0].item()) == k and int(sch.ctl[11].item()) == rows
+    assert sch.pk_tok[:rows].tolist() == exp["tok"] and sch.pk_pos[:rows].tolist() == exp["pos"]
+    assert sch.pk_row[:rows].tolist() == exp["row"] and sch.pk_last[:rows].tolist() == exp["last"]
+    assert (sch.pk_row[rows:cap] == B).all() and (sch.pk_pos[rows:cap] == 0).all()
+    assert sch.pk_cu[:k].tolist() == exp["cu"] and (sch.pk_cu[k:] == rows).all()
+    assert sch.pk_tile_cu[:k].tolist() == exp["tcu"] and (sch.pk_tile_cu[k:] == tiles).all()
+    req, cur, pos, fed = (t.cpu().numpy() for t in (sch.req, sch.cur_tok, st.pos, sch.fed))
+    for s_ in range(B):
+        if s_ in exp["slot"]:
+            q, last_tok, w = exp["slot"][s_]
+            assert req[s_] == q and cur[s_] == last_tok and pos[s_] == w and fed[s_] == w + 1
+        elif s_ in busy:
+            assert req[s_] == 10 ** 6 + s_
+        else:
+            assert req[s_] == -1

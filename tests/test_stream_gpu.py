@@ -92,8 +92,9 @@ def test_streamgen_with_prefill_lanes_contract():
     from ultraviolet_b200.rl_stream import StreamGen
     m = _model()
     T, max_new = 1.0, 8
-    gen = StreamGen(m, slots=32, max_prompt=30, max_new=max_new, temperature=T, eos_id=0, check_every=4, seed=9)
-    assert gen.sched.L == 8
+    gen = StreamGen(m, slots=32, max_prompt=30, max_new=max_new, temperature=T, eos_id=0, check_every=4, seed=9,
+                    packed_prefill=False)
+    assert gen.sched.L == 8 and not gen.sched.packed
     r = np.random.default_rng(12)
     prompts = {i: r.integers(1, 500, r.integers(2, 31)).tolist() for i in range(48)}
     for i, p in prompts.items():
@@ -174,9 +175,10 @@ def test_grpo_group_of_identical_prompts_gets_distinct_streams():
     base = [r.integers(1, 500, r.integers(3, 9)).tolist() for _ in range(3)]
     reqs = [(p, (gi_, c)) for gi_, p in enumerate(base) for c in range(8)]      # 3 groups of 8
 
-    def rollouts(slots, lanes):
+    def rollouts(slots, lanes, packed):
         gen = StreamGen(m, slots=slots, max_prompt=9, max_new=10, temperature=1.2, eos_id=0, check_every=4, seed=77,
-                        prefill_lanes=lanes)
+                        prefill_lanes=lanes, packed_prefill=packed)
+        assert gen.sched.packed == packed
         for p, meta in reqs:
             gen.add(p, meta)
         got = {}
@@ -186,15 +188,16 @@ def test_grpo_group_of_identical_prompts_gets_distinct_streams():
                 got[meta] = toks
         return got
 
-    a = rollouts(4, 0)
+    a = rollouts(4, 0, True)       # packed admission passes (the default)
     assert sorted(a) == sorted(meta for _, meta in reqs)
     for g_ in range(3):
         assert len({tuple(a[(g_, c)]) for c in range(8)}) >= 7     # identical prompts, different keys: different text
-    b = rollouts(24, 0)
-    c = rollouts(7, 4)
-    for other in (b, c):
-        same = np.mean([a[k] == other[k] for k in a])
-        assert same >= 0.75, same    # equal unless a batch-size dependent bf16 rounding flips a draw
+    b = rollouts(24, 0, True)
+    c = rollouts(7, 4, False)      # prompts through the decode step, with lanes ...
+    d = rollouts(5, 0, False)      # ... and one token per step
+    for x, y in ((a, b), (c, d), (a, d)):
+        same = np.mean([x[k] == y[k] for k in x])
+        assert same >= 0.75, same    # equal unless a bf16 rounding (batch size, prefill route) flips a draw
 
 
 def test_device_handoff_of_a_real_harvest_and_direct_weight_publication():

@@ -187,20 +187,27 @@ def generate(model, prompts, max_new: int, temperature: float = 1.0, top_k: int 
 def generate_continuous(model, prompts, max_new: int, batch: int, temperature: float = 1.0, top_k: int = 0,
                         eos_id: int | None = None, pad_id: int = 0, check_every: int = 16, use_graph: bool = True,
                         bucket: int = 1024, dtype=None, compile: bool = True, target_lens=None, stats=None,
-                        top_p: float = 1.0, seed: int | None = None, prefill_lanes: int = 0):
+                        top_p: float = 1.0, seed: int | None = None, prefill_lanes: int = 0,
+                        packed_prefill: bool | None = None):
     """Continuous batching over `batch` cache slots (model.py:1266-1354), scheduled on the device; completions in
     prompt order.  target_lens[i] caps request i's length (the reference's benchmarking hook, model.py:1312).
     seed: None draws a fresh Philox seed per call from torch's generator (request i's stream is keyed by (seed, i));
-    an int reproduces the streams whatever slot a request lands in."""
+    an int reproduces the streams whatever slot a request lands in.
+    Prompts enter the cache through packed prefill passes at admission (packed_prefill, the default: every
+    check_every steps the freed slots are refilled in one packed batch, as the reference refills with a batched
+    prefill), or through the decode step itself (packed_prefill=False; prefill_lanes > 0 then feeds several prompt
+    tokens of a slot per step)."""
+    if packed_prefill is None:
+        packed_prefill = prefill_lanes == 0
     eng = _engine(model)
     n = len(prompts)
     B = min(batch, n)
     max_prompt = max(len(p) for p in prompts)
-    st = _new_state(model, GpuScheduler.state_rows(B, prefill_lanes), max_prompt + max_new + check_every, eng,
-                    GpuScheduler.ring_extra(prefill_lanes))
+    st = _new_state(model, GpuScheduler.state_rows(B, prefill_lanes, packed_prefill),
+                    max_prompt + max_new + check_every, eng, GpuScheduler.ring_extra(prefill_lanes))
     sched = GpuScheduler(eng, st, max_new=max_new, temperature=temperature, top_p=top_p, top_k=top_k, eos_id=eos_id,
                          pad_id=pad_id, seed=fresh_seed() if seed is None else int(seed), q_cap=max(n, 2), max_prompt=max_prompt, use_graph=use_graph,
-                         prefill_lanes=prefill_lanes,
+                         prefill_lanes=prefill_lanes, packed_prefill=packed_prefill,
                          tok_cap=sum(len(p) for p in prompts) + 1,
                          out_cap=(int(np.minimum(np.asarray(target_lens), max_new).sum()) if target_lens is not None
                                   else n * max_new) + 1)

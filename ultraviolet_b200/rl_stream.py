@@ -44,7 +44,8 @@ def publish_weights(gen_m, raw, sync: bool = True) -> None:
 class StreamGen:
     def __init__(self, model, slots, max_prompt, max_new, temperature, eos_id, check_every=16, compile=True,
                  use_graph=True, pad_id=0, dtype=torch.float16, bucket=1024, top_p: float = 1.0,
-                 seed: int | None = None, queue_capacity: int = 8192, prefill_lanes: int | None = None):
+                 seed: int | None = None, queue_capacity: int = 8192, prefill_lanes: int | None = None,
+                 packed_prefill: bool | None = None):
         """seed: Philox key of this generator's draws (request n's stream is keyed by (seed, n)).  None (default)
         takes a fresh seed from torch's generator mixed with the distributed rank, as the reference's sampler draws
         from torch's global generator; pass an int for reproducible rollouts."""
@@ -55,14 +56,22 @@ class StreamGen:
         self.ce, self.pad, self.dtype, self.max_prompt = check_every, pad_id, dtype, max_prompt
         eng = _engine(model)
         self.dev = eng.device
-        if prefill_lanes is None:  # a quarter more batch rows for prompt tokens once the batch is large enough
+        # How prompts enter the cache.  Default: packed prefill passes -- at every chunk() the slots that the last
+        # harvest saw free are refilled by one packed batch through the prefill kernels (the device picks requests
+        # and slots; unquantised keys in the prompt's own attention, as in the reference's refill).  packed_prefill
+        # = False feeds prompts through the decode step instead, prefill_lanes > 0 several tokens per slot and step.
+        if packed_prefill is None:
+            packed_prefill = not prefill_lanes
+        if packed_prefill:
+            prefill_lanes = 0
+        elif prefill_lanes is None:  # a quarter more batch rows for prompt tokens once the batch is large enough
             prefill_lanes = slots // 4 if slots >= 32 else 0
         from .generate import _new_state
-        self.st = _new_state(model, GpuScheduler.state_rows(slots, prefill_lanes), max_prompt + max_new + check_every,
-                             eng, GpuScheduler.ring_extra(prefill_lanes))
+        self.st = _new_state(model, GpuScheduler.state_rows(slots, prefill_lanes, packed_prefill),
+                             max_prompt + max_new + check_every, eng, GpuScheduler.ring_extra(prefill_lanes))
         self.sched = GpuScheduler(eng, self.st, max_new=max_new, temperature=temperature, top_p=top_p, eos_id=eos_id,
                                   pad_id=pad_id, seed=seed, q_cap=queue_capacity, max_prompt=max_prompt,
-                                  use_graph=use_graph, prefill_lanes=prefill_lanes)
+                                  use_graph=use_graph, prefill_lanes=prefill_lanes, packed_prefill=packed_prefill)
         self.queue = collections.deque()   # host-side FIFO of (prompt_ids, meta) not yet on the device
         self._version = 0
         self.n_decode_steps = 0

@@ -16,7 +16,7 @@ from . import _lib
 from .kernels._util import stream_ptr
 
 (CTL_HEAD, CTL_TAIL, CTL_FIN, CTL_VERSION, CTL_ACTIVE, CTL_STATUS, CTL_STEPS, CTL_TOK_TAIL, CTL_OUT_TAIL,
- CTL_GENERATED, CTL_SLOT_STEPS) = range(11)
+ CTL_GENERATED, CTL_SLOT_STEPS, CTL_PREFILL_ROWS, CTL_ADMIT_PASSES) = range(13)
 
 
 def _pow2(n: int) -> int:
@@ -27,13 +27,24 @@ class GpuScheduler:
     def __init__(self, engine, st, *, max_new: int, temperature: float, top_p: float = 1.0, eos_id: int | None = 0,
                  pad_id: int = 0, seed: int = 0, q_cap: int = 8192, tok_cap: int | None = None,
                  out_cap: int | None = None, max_prompt: int = 256, force_eos: bool = False, use_graph: bool = True,
-                 num_splits: dict | None = None, prefill_lanes: int = 0, lane_chunk: int = 8, top_k: int = 0):
+                 num_splits: dict | None = None, prefill_lanes: int = 0, lane_chunk: int = 8, top_k: int = 0,
+                 packed_prefill: bool = False, prefill_cap: int = 16384):
         """prefill_lanes > 0: the decode step runs on slots + prefill_lanes batch rows; the extra rows carry further
         prompt tokens of slots that are still prefilling (up to lane_chunk tokens per slot per step).  The state must
-        then hold one spare cache row: st.B == slots + 1 (see ``state_rows``)."""
+        then hold one spare cache row: st.B == slots + 1 (see ``state_rows``).
+
+        packed_prefill: the step only retires; queued requests are admitted by ADMISSION PASSES that ``run`` launches
+        before its steps -- uv_sched_admit picks the requests and slots on the device and lays their prompts out as
+        one packed batch, which goes through the prefill path (packed varlen attention over unquantised keys, int8
+        cache written on the way) in a single pass of up to prefill_cap rows.  The host only chooses how many packed
+        rows the pass gets, from the queue's prompt lengths and the head / finished counters it read at the last
+        harvest.  Needs the spare cache row too; excludes prefill_lanes."""
         self.eng, self.st = engine, st
         self.L = int(prefill_lanes)
-        self.B = st.B - 1 if self.L > 0 else st.B
+        self.packed = bool(packed_prefill)
+        if self.packed and self.L:
+            raise ValueError("packed_prefill and prefill_lanes are two ways to prefill: choose one")
+        self.B = st.B - 1 if (self.L > 0 or self.packed) else st.B
         self.dev = engine.device
         self.max_new, self.T, self.top_p, self.seed = int(max_new), float(temperature), float(top_p), int(seed)
         self.top_k = int(top_k or 0)
@@ -54,6 +65,18 @@ class GpuScheduler:
             self.pos_all, self.starts_all = i64(B + self.L), i64(B + self.L)
             self.row_map = torch.cat([torch.arange(B, dtype=torch.int64, device=dev), i64(self.L, B)])
             st.pos, st.starts = self.pos_all[:B], self.starts_all[:B]
+        if self.packed:
+            st.pos, st.starts = i64(B), i64(B)      # the decode step runs on the B slots (cache rows 0 .. B - 1)
+            self.prefill_cap = max(256, _pow2(int(prefill_cap)))
+            cap = self.prefill_cap
+            self.pk_tok, self.pk_pos, self.pk_row, self.pk_last = i64(cap), i64(cap), i64(cap, B), i64(cap)
+            self.pk_zero = i64(cap)
+            self.pk_cu, self.pk_tile_cu = i32(B + 1), i32(B + 1)
+            self._plen: dict[int, int] = {}          # request -> prompt length (host copy of the queue)
+            self._head_h = self._fin_h = 0           # head / finished counters as last read from the device
+            self._ctl_fresh = True
+            self._admit_graphs: dict[int, torch.cuda.CUDAGraph] = {}
+            self.n_admit_passes = 0
         self.prompt_off, self.key, self.out_off = i64(Q), i64(Q), i64(Q)
         self.prompt_len, self.limit, self.out_len, self.start_version = i32(Q), i32(Q), i32(Q, -1), i32(Q)
         self.fin_ring = i32(Q, -1)
@@ -83,6 +106,7 @@ class GpuScheduler:
         a.pos, a.starts = st.pos.data_ptr(), st.starts.data_ptr()  # (with lanes: the first rows of pos_all / starts_all)
         a.B, a.q_cap, a.tok_cap, a.out_cap = B, Q, self.tok_cap, self.out_cap
         a.eos, a.pad, a.force_eos, a.max_len = self.eos, self.pad, int(self.force_eos), st.max_len
+        a.no_admit = int(self.packed)
         # host mirrors
         self.n_enqueued = 0       # == ctl[TAIL]
         self.n_harvested = 0      # finished requests already returned
@@ -103,9 +127,10 @@ class GpuScheduler:
         return int(lane_chunk) if prefill_lanes > 0 else 0
 
     @staticmethod
-    def state_rows(slots: int, prefill_lanes: int = 0) -> int:
-        """Cache rows the decode state needs for `slots` sequences: one spare row when prefill lanes are on."""
-        return slots + (1 if prefill_lanes > 0 else 0)
+    def state_rows(slots: int, prefill_lanes: int = 0, packed_prefill: bool = False) -> int:
+        """Cache rows the decode state needs for `slots` sequences: one spare row when prefill lanes or packed
+        admission passes are on (idle lanes / unused packed rows are parked there)."""
+        return slots + (1 if (prefill_lanes > 0 or packed_prefill) else 0)
 
     # ------------------------------------------------------------------------------------------------ queue
     def set_version(self, v: int) -> None:
@@ -149,6 +174,8 @@ class GpuScheduler:
         for i in range(n):
             self.meta[r0 + i] = metas[i] if metas is not None else r0 + i
             self._span[r0 + i] = (int(t_off[i]), int(o_off[i]))
+            if self.packed:
+                self._plen[r0 + i] = int(lens[i])
         self.n_enqueued += n
         self.tok_tail += int(lens.sum())
         self.out_tail += int(lim.sum())
@@ -170,10 +197,86 @@ class GpuScheduler:
                    top_k=self.top_k)
         self._sched_step()
 
+    # ------------------------------------------------------------------------------------------------ admission
+    def _admit_body(self, cap: int) -> None:
+        eng, st = self.eng, self.st
+        p = _lib.SchedAdmitArgs()
+        p.tok, p.pos, p.row, p.last_pos = (t.data_ptr() for t in (self.pk_tok, self.pk_pos, self.pk_row, self.pk_last))
+        p.cu, p.tile_cu, p.cap = self.pk_cu.data_ptr(), self.pk_tile_cu.data_ptr(), cap
+        with torch.cuda.device(self.dev):
+            _lib.check(_lib.lib().uv_sched_admit(C.byref(self.args), C.byref(p), stream_ptr(self.dev)),
+                       "uv_sched_admit")
+        eng.trunk(self.pk_tok[:cap], st, self.pk_pos[:cap], self.pk_zero[:cap], g_len=st.max_len,
+                  row_map=self.pk_row[:cap],
+                  packed=dict(cu=self.pk_cu, tile_cu=self.pk_tile_cu, n_seq=self.B, max_tiles=cap // 16 + self.B,
+                              last_pos=self.pk_last[:cap]))
+
+    def _admit_pass(self, cap: int) -> None:
+        """One admission pass of `cap` packed rows (a power of two): captured once per size, replayed after."""
+        if not self.use_graph:
+            self._admit_body(cap)
+        else:
+            g = self._admit_graphs.get(cap)
+            if g is None:
+                # warm-up on a side stream with the queue hidden (tail = head: nothing is admitted, every packed
+                # row is a pad row on the spare cache row), then capture
+                s = torch.cuda.Stream(self.dev)
+                s.wait_stream(torch.cuda.current_stream(self.dev))
+                with torch.cuda.stream(s):
+                    tail = self.ctl[CTL_TAIL].clone()
+                    self.ctl[CTL_TAIL] = self.ctl[CTL_HEAD]
+                    self._admit_body(cap)
+                    self.ctl[CTL_TAIL] = tail
+                torch.cuda.current_stream(self.dev).wait_stream(s)
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, capture_error_mode="thread_local"):
+                    self._admit_body(cap)
+                self._admit_graphs[cap] = g
+            g.replay()
+        self.n_admit_passes += 1
+        self._ctl_fresh = False
+
+    def _read_ctl(self) -> None:
+        c = self.ctl[:CTL_FIN + 1].cpu()
+        self._head_h, self._fin_h = int(c[CTL_HEAD]), int(c[CTL_FIN])
+        self._ctl_fresh = True
+
+    def _plan_admission(self) -> int:
+        """Packed rows the next pass should get (0: nothing to admit), from the host's copy of the queue and the
+        counters of the last read: the first min(free slots, queued) requests, rounded up to a power of two."""
+        pending = self.n_enqueued - self._head_h
+        free = self.B - (self._head_h - self._fin_h)
+        k = min(pending, free)
+        if k <= 0:
+            return 0
+        need = sum(self._plen[self._head_h + i] - 1 for i in range(k))
+        return min(self.prefill_cap, max(256, _pow2(max(need, 1))))
+
+    def admit(self, drain: bool = False) -> None:
+        """Launch an admission pass if the last counters say requests are waiting and slots are free.  drain: keep
+        going (one counter read per pass) until nothing more can be admitted -- used when the batch is first filled."""
+        if not self.packed:
+            return
+        while True:
+            if not self._ctl_fresh:
+                if not drain:
+                    return
+                self._read_ctl()
+            cap = self._plan_admission()
+            if cap == 0:
+                return
+            self._admit_pass(cap)
+            if not drain:
+                return
+
     def prime(self) -> None:
         """First scheduling pass (admits queued requests into the idle slots) and graph capture."""
         if not self._primed:
-            self._sched_step()
+            if self.packed:
+                self.st.pos.zero_()
+                self.admit(drain=True)
+            else:
+                self._sched_step()
             self._primed = True
         if self.use_graph and self.graph is None:
             # Warm up on a side stream, then capture.  The warm-up steps are real steps (state advances): nothing is
@@ -191,6 +294,7 @@ class GpuScheduler:
 
     def run(self, n_steps: int) -> None:
         self.prime()
+        self.admit()   # packed prefill mode: refill the slots that the last harvest saw free
         for _ in range(n_steps):
             if self.graph is not None:
                 self.graph.replay()
@@ -213,7 +317,11 @@ class GpuScheduler:
         requests' prompt tokens in the same form (``prompt_tokens`` int32, ``prompt_offsets`` int64), read from the
         device-side prompt ring before its space is released (``handoff.build_packed_device`` wants them).  One
         small D2H (the finished count and the span lengths' total); None when nothing finished."""
-        fin = int(self.ctl[CTL_FIN].item())
+        if self.packed:
+            self._read_ctl()   # head and finished count in one small D2H: the next admission pass is planned on them
+            fin = self._fin_h
+        else:
+            fin = int(self.ctl[CTL_FIN].item())
         if fin == self.n_harvested:
             return None
         self.eng.check_status(self.st_rows)  # rollouts from a step whose kernels flagged a failure are not handed out
@@ -238,6 +346,8 @@ class GpuScheduler:
         metas = [self.meta.pop(r) for r in rid_h]
         for r in rid_h:
             self._span.pop(r, None)
+            if self.packed:
+                self._plen.pop(r, None)
         self.n_harvested = fin
         while self._oldest < self.n_enqueued and self._oldest not in self._span:
             self._oldest += 1
