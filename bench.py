@@ -369,7 +369,8 @@ def rollout_job(m, rank, world, dev, *, prompts_all, stops_all, slots, max_new, 
     its replica until its share is drained (timed_steps > 0: that many steps only), finished rollouts are harvested
     as device tensors.  Optionally the weight arena is broadcast from rank 0 first and the rollouts (tokens int32,
     log-probs fp32, lengths and start versions int32) are gathered to rank 0 afterwards, each collective timed.
-    Windows of 16 (packed admission) or 64 steps are timed separately so that the steady state (slot occupancy >= 0.95) can be told from the
+    Windows of 16 (packed admission) or 64 steps are timed separately so that the steady state (slot occupancy >=
+    0.95) can be told from the
     straggler tail.  Returns a dict on every rank (aggregates are all-reduced)."""
     import torch
     import torch.distributed as dist
@@ -397,7 +398,7 @@ def rollout_job(m, rank, world, dev, *, prompts_all, stops_all, slots, max_new, 
     c_prev = c0 = sch.counters()
     if world > 1:
         dist.barrier()
-    packed, windows, steps, n_done = [], [], 0, 0
+    harvested, windows, steps, n_done = [], [], 0, 0
     ev = lambda: torch.cuda.Event(enable_timing=True)
     e_begin, e_end = ev(), ev()
     e_begin.record()
@@ -414,7 +415,7 @@ def rollout_job(m, rank, world, dev, *, prompts_all, stops_all, slots, max_new, 
                         (c["slot_steps"] - c_prev["slot_steps"]) / (n * slots)))
         c_prev = c
         if p is not None:
-            packed.append(p)
+            harvested.append(p)
             n_done += len(p["metas"])
         if (timed_steps > 0 and steps >= timed_steps) or (timed_steps <= 0 and n_done >= len(mine)):
             break
@@ -429,12 +430,12 @@ def rollout_job(m, rank, world, dev, *, prompts_all, stops_all, slots, max_new, 
     if world > 1:
         dist.all_reduce(agg)
         dist.all_reduce(mx, op=dist.ReduceOp.MAX)
-    if gather and packed:
-        toks = torch.cat([p["tokens"] for p in packed])
-        lps = torch.cat([p["logp"] for p in packed])
-        lens_d = torch.cat([p["offsets"][1:] - p["offsets"][:-1] for p in packed]).to(torch.int32)
-        vers = torch.cat([p["versions"] for p in packed]).to(torch.int32)
-        ids = torch.tensor([i for p in packed for i in p["metas"]], dtype=torch.int32, device=dev)
+    if gather and harvested:
+        toks = torch.cat([p["tokens"] for p in harvested])
+        lps = torch.cat([p["logp"] for p in harvested])
+        lens_d = torch.cat([p["offsets"][1:] - p["offsets"][:-1] for p in harvested]).to(torch.int32)
+        vers = torch.cat([p["versions"] for p in harvested]).to(torch.int32)
+        ids = torch.tensor([i for p in harvested for i in p["metas"]], dtype=torch.int32, device=dev)
         gathered, t_gather = uvdist.gather_packed(toks, lps, lens_d, vers, ids)
     res = {"tokens_per_s": float(agg[0].item()) / (float(mx[0].item()) / 1e3), "ms": float(mx[0].item()),
            "generated_tokens": int(agg[0].item()), "requests_finished": int(agg[4].item()),
