@@ -177,35 +177,77 @@ __global__ void __launch_bounds__(256) swiglu_kernel(const T* __restrict__ gu, i
 }
 
 // act = silu(g) * u of the gate|up projection of UN-normalised rows h: [g | u] = (h . W^T) * rs with
-// rs = rsqrt(mean(h^2) + eps) formed here (one CTA per row: the row's sum of squares, then its f features)
+// rs = rsqrt(mean(h^2) + eps) formed here.  A row is cut over SWR_SPLIT CTAs of SWR_THREADS threads (each re-forms rs
+// from the 1-2 KB row: cheaper than one long CTA per row).  Every thread first requests everything it will need -- its
+// 16-byte pieces of h and of g and u -- so the sum of squares and the projection arrive in one round trip.
+constexpr int SWR_THREADS = 64;
+constexpr int SWR_SPLIT = 4;
+constexpr int SWR_HV = 2;     // 16-byte pieces of h per thread: d <= 8 * 64 * 2 = 1024 without the tail loop
+constexpr int SWR_VMAX = 2;   // 8-feature vectors per thread: f <= 8 * 64 * 2 * SWR_SPLIT = 4096 on this path
+
 template <typename T>
-__global__ void __launch_bounds__(128) swiglu_rs_kernel(const T* __restrict__ gu, const T* __restrict__ hrow, int d,
-                                                        int f, T* __restrict__ act) {
-  __shared__ float red[4];
-  const int row = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+__global__ void __launch_bounds__(SWR_THREADS) swiglu_rs_kernel(const T* __restrict__ gu, const T* __restrict__ hrow,
+                                                                int d, int f, T* __restrict__ act) {
+  __shared__ float red[SWR_THREADS / 32];
+  const int row = blockIdx.x / SWR_SPLIT, part = blockIdx.x % SWR_SPLIT;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   pdl_wait();
   pdl_trigger();
   const T* hr = hrow + (int64_t)row * d;
-  float ss = 0.f;
-  for (int i = 8 * tid; i < d; i += 8 * 128) {
-    const uint4 u = *reinterpret_cast<const uint4*>(hr + i);
-    const T* v = reinterpret_cast<const T*>(&u);
+  const T* g = gu + (int64_t)row * 2 * f;
+  const int nvec = f / 8;
+  const int per = (nvec + SWR_SPLIT - 1) / SWR_SPLIT, v0 = part * per;
+  const int v1 = v0 + per < nvec ? v0 + per : nvec;
+  float hv[SWR_HV][8], gv[SWR_VMAX][8], uv[SWR_VMAX][8];
+  // all loads first
 #pragma unroll
-    for (int k = 0; k < 8; ++k) {
-      const float x = to_f32<T>(v[k]);
-      ss += x * x;
+  for (int j = 0; j < SWR_HV; ++j) {
+    const int i = 8 * (tid + j * SWR_THREADS);
+    if (i < d) {
+      ld8<T>(hr + i, hv[j]);
+    } else {
+#pragma unroll
+      for (int k = 0; k < 8; ++k) hv[j][k] = 0.f;
     }
+  }
+#pragma unroll
+  for (int j = 0; j < SWR_VMAX; ++j) {
+    const int v = v0 + tid + j * SWR_THREADS;
+    if (v < v1) {
+      ld8<T>(g + 8 * v, gv[j]);
+      ld8<T>(g + f + 8 * v, uv[j]);
+    }
+  }
+  float ss = 0.f;
+#pragma unroll
+  for (int j = 0; j < SWR_HV; ++j)
+#pragma unroll
+    for (int k = 0; k < 8; ++k) ss += hv[j][k] * hv[j][k];
+  for (int i = 8 * (tid + SWR_HV * SWR_THREADS); i < d; i += 8 * SWR_THREADS) {  // rows wider than 1024 elements
+    float more[8];
+    ld8<T>(hr + i, more);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) ss += more[k] * more[k];
   }
   ss = warp_sum(ss);
   if (lane == 0) red[warp] = ss;
   __syncthreads();
-  const float rs = rsqrtf((red[0] + red[1] + red[2] + red[3]) / (float)d + RMS_EPS);
-  const T* g = gu + (int64_t)row * 2 * f;
-  for (int c = 2 * tid; c < f; c += 2 * 128) {
-    const float2 gv = ld2<T>(g + c), uv = ld2<T>(g + f + c);
-    const float g0 = rnd<T>(gv.x * rs), g1 = rnd<T>(gv.y * rs), u0 = rnd<T>(uv.x * rs), u1 = rnd<T>(uv.y * rs);
-    const float s0 = rnd<T>(g0 / (1.0f + __expf(-g0))), s1 = rnd<T>(g1 / (1.0f + __expf(-g1)));
-    st2<T>(act + (int64_t)row * f + c, s0 * u0, s1 * u1);
+  float tot = 0.f;
+#pragma unroll
+  for (int w = 0; w < SWR_THREADS / 32; ++w) tot += red[w];
+  const float rs = rsqrtf(tot / (float)d + RMS_EPS);
+#pragma unroll
+  for (int j = 0; j < SWR_VMAX; ++j) {
+    const int v = v0 + tid + j * SWR_THREADS;
+    if (v < v1) {
+      float o[8];
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        const float g0 = rnd<T>(gv[j][k] * rs), u0 = rnd<T>(uv[j][k] * rs);
+        o[k] = rnd<T>(g0 / (1.0f + __expf(-g0))) * u0;
+      }
+      st8<T>(act + (int64_t)row * f + 8 * v, o);
+    }
   }
 }
 
@@ -223,6 +265,14 @@ __global__ void __launch_bounds__(128) qkv_post_kernel(const __grid_constant__ Q
   if (item >= P.B * per_row) return;
   const int b = item / per_row, hs = item % per_row;
   const bool raw = P.xn_raw != 0;
+  // the slot's own values are requested before the row reduction below needs its loads: one round trip, not two
+  const bool act0 = lane * E < HD;
+  float x0[E];
+  if (hs < slots) {
+    const T* vec0 = static_cast<const T*>(P.qkv) + ((int64_t)b * slots + hs) * HD;
+#pragma unroll
+    for (int i = 0; i < E; ++i) x0[i] = act0 ? to_f32<T>(vec0[lane * E + i]) : 0.f;
+  }
   const float rs = raw ? row_rms_factor<T>(static_cast<const T*>(P.xn) + (int64_t)b * P.d, P.d, lane) : 1.0f;
   if (hs >= slots) {
     const int head = hs - slots;
@@ -236,7 +286,7 @@ __global__ void __launch_bounds__(128) qkv_post_kernel(const __grid_constant__ Q
   T* vec = static_cast<T*>(P.qkv) + ((int64_t)b * slots + hs) * HD;
   float x[E];
 #pragma unroll
-  for (int i = 0; i < E; ++i) x[i] = act ? to_f32<T>(vec[lane * E + i]) : 0.f;
+  for (int i = 0; i < E; ++i) x[i] = x0[i];
   if (raw) {  // the projection of the un-normalised row, scaled: what the GEMM on the normalised row would hold
 #pragma unroll
     for (int i = 0; i < E; ++i) x[i] = rnd<T>(x[i] * rs);
@@ -370,14 +420,14 @@ extern "C" int uv_swiglu(const void* gu, int dtype, int f, void* act, int B, voi
 extern "C" int uv_swiglu_rs(const void* gu, const void* h, int dtype, int d, int f, void* act, int B, void* stream) {
   if (B == 0) return UV_OK;
   if (!gu || !h || !act || B < 0) return UV_ERR_ARG;
-  if (f < 2 || (f & 1) || d < 8 || (d & 7)) return UV_ERR_SHAPE;
-  if (!aligned16(h)) return UV_ERR_ALIGN;
+  if (f < 8 || (f & 7) || f > 8 * SWR_THREADS * SWR_VMAX * SWR_SPLIT || d < 8 || (d & 7)) return UV_ERR_SHAPE;
+  if (!aligned16(h) || !aligned16(gu) || !aligned16(act)) return UV_ERR_ALIGN;  // rows move as 16-byte vectors
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (dtype == UV_F16)
-    launch_pdl(swiglu_rs_kernel<__half>, dim3((unsigned)B), dim3(128), 0, st, static_cast<const __half*>(gu),
+    launch_pdl(swiglu_rs_kernel<__half>, dim3((unsigned)B * SWR_SPLIT), dim3(SWR_THREADS), 0, st, static_cast<const __half*>(gu),
                static_cast<const __half*>(h), d, f, static_cast<__half*>(act));
   else if (dtype == UV_BF16)
-    launch_pdl(swiglu_rs_kernel<__nv_bfloat16>, dim3((unsigned)B), dim3(128), 0, st,
+    launch_pdl(swiglu_rs_kernel<__nv_bfloat16>, dim3((unsigned)B * SWR_SPLIT), dim3(SWR_THREADS), 0, st,
                static_cast<const __nv_bfloat16*>(gu), static_cast<const __nv_bfloat16*>(h), d, f,
                static_cast<__nv_bfloat16*>(act));
   else return UV_ERR_DTYPE;

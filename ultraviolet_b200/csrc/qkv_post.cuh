@@ -48,9 +48,25 @@ struct QkvPostParams {
 template <typename T>
 __device__ __forceinline__ float row_rms_factor(const T* row, int d, int lane) {
   float ss = 0.f;
-  for (int i = 8 * lane; i < d; i += 256) {
-    const uint4 u = *reinterpret_cast<const uint4*>(row + i);
-    const T* v = reinterpret_cast<const T*>(&u);
+  // rows of up to 1024 elements: four guarded 16-byte loads per lane, all in flight together
+  uint4 u[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const int i = 8 * lane + 256 * j;
+    u[j] = i < d ? *reinterpret_cast<const uint4*>(row + i) : make_uint4(0u, 0u, 0u, 0u);
+  }
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const T* v = reinterpret_cast<const T*>(&u[j]);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const float f = to_f32<T>(v[k]);
+      ss += f * f;
+    }
+  }
+  for (int i = 8 * lane + 1024; i < d; i += 256) {
+    const uint4 w = *reinterpret_cast<const uint4*>(row + i);
+    const T* v = reinterpret_cast<const T*>(&w);
 #pragma unroll
     for (int k = 0; k < 8; ++k) {
       const float f = to_f32<T>(v[k]);
