@@ -362,6 +362,84 @@ def run_reference_arm(args, rank, world):
     print(json.dumps(line), flush=True)
 
 
+# ------------------------------------------------------------------------------------------------ GEMM micro-benchmark
+def run_gemm_workload(args, dev):
+    """`--workload gemm`: the four GEMM shapes of a layer at `--rows` batch rows, as dependent launches inside one
+    CUDA graph over rotating weight copies: library GEMM alone, library GEMM + the row kernel that follows it in the
+    step, and this library's fused-epilogue tcgen05 kernel in several tilings (batch tile, split-K).  Microseconds
+    per launch (or per pair)."""
+    import torch
+    from ultraviolet_b200 import _lib
+    L, lib = _lib, _lib.lib()
+    sp = lambda: torch.cuda.current_stream().cuda_stream
+    M, NW = args.rows, 20
+    d, f = 640, 1664
+    lam = torch.tensor([0.9, 1.1], device=dev)
+    res = {}
+    for name, N, K, cfgs in (("qkv", 640, 640, ((32, 1), (32, 2), (32, 4), (64, 2), (64, 4))),
+                             ("wo", 640, 512, ((32, 1), (32, 2), (32, 4), (64, 4))),
+                             ("down", 640, 1664, ((32, 2), (32, 4), (64, 4), (64, 8))),
+                             ("gate_up", 2 * f, 640, ((32, 1), (64, 1), (128, 1)))):
+        ws = [(torch.randn(N, K, device=dev) * 0.05).bfloat16() for _ in range(NW)]
+        x = torch.randn(M, K, device=dev).bfloat16()
+        c = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+        xr = torch.randn(M, d, device=dev).bfloat16()
+        h, hn = torch.empty_like(xr), torch.empty_like(xr)
+        ss = torch.ones(d // 128, M, device=dev)
+        act = torch.empty(M, f, device=dev, dtype=torch.bfloat16)
+
+        def lib_chain():
+            for w in ws:
+                torch.mm(x, w.t(), out=c)
+        res[name + ".library"] = graph_ms(lib_chain) * 1e3 / NW
+        if name in ("wo", "down"):
+            def acc_chain():
+                for w in ws:
+                    xr.addmm_(x, w.t())
+            res[name + ".library_accumulate"] = graph_ms(acc_chain) * 1e3 / NW
+
+            def pair():
+                for w in ws:
+                    torch.mm(x, w.t(), out=c)
+                    lib.uv_resid_norm(xr.data_ptr(), c.data_ptr(), lam.data_ptr(), 2, d, h.data_ptr(), hn.data_ptr(), M,
+                                      sp())
+            res[name + ".library+resid_norm"] = graph_ms(pair) * 1e3 / NW
+        if name == "gate_up":
+            def pair():
+                for w in ws:
+                    torch.mm(x, w.t(), out=c)
+                    lib.uv_swiglu(c.data_ptr(), 2, f, act.data_ptr(), M, sp())
+            res[name + ".library+swiglu"] = graph_ms(pair) * 1e3 / NW
+
+            def pair2():
+                for w in ws:
+                    torch.mm(x, w.t(), out=c)
+                    lib.uv_swiglu_rs(c.data_ptr(), x.data_ptr(), 2, d, f, act.data_ptr(), M, sp())
+            res[name + ".library+swiglu_rs"] = graph_ms(pair2) * 1e3 / NW
+        for bn, ks in cfgs:
+            if name in ("wo", "down"):
+                def own():
+                    for w in ws:
+                        L.check(lib.uv_gemm_sw_resid(x.data_ptr(), K, w.data_ptr(), xr.data_ptr(), lam.data_ptr(),
+                                                     h.data_ptr(), d, ss.data_ptr(), M, 2, M, N, K, bn, ks, None, sp()),
+                                "uv_gemm_sw_resid")
+            elif name == "gate_up":
+                def own():
+                    for w in ws:
+                        L.check(lib.uv_gemm_sw_swiglu(x.data_ptr(), K, w.data_ptr(), act.data_ptr(), 2, M, K, f,
+                                                      ss.data_ptr(), d // 128, M, bn, None, sp()), "uv_gemm_sw_swiglu")
+            else:
+                def own():
+                    for w in ws:
+                        L.check(lib.uv_gemm_sw(x.data_ptr(), K, w.data_ptr(), c.data_ptr(), N, 2, M, N, K,
+                                               ss.data_ptr(), d // 128, M, bn, ks, None, sp()), "uv_gemm_sw")
+            res[f"{name}.own_fused.bn{bn}.ks{ks}"] = graph_ms(own) * 1e3 / NW
+    print(json.dumps({"metric": "GEMM us per launch", "rows": M, "pdl": os.environ.get("UVDECODE_PDL", "0"),
+                      "unit": "us", "config": {"workload": "decode-step GEMM shapes, dependent launches in a CUDA "
+                                                            "graph, 20 rotating weight copies"},
+                      "us_per_launch": {k: round(v, 2) for k, v in res.items()}}), flush=True)
+
+
 # ------------------------------------------------------------------------------------------------ rollout jobs
 def rollout_job(m, rank, world, dev, *, prompts_all, stops_all, slots, max_new, max_prompt, lanes, lane_chunk, seed,
                 force_eos, timed_steps=0, warmup=3, broadcast=False, gather=False, packed=True):
@@ -502,7 +580,8 @@ def main():
     ap.add_argument("--steps", type=int, default=512)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default="fixed", choices=["fixed", "continuous", "attn"])
+    ap.add_argument("--workload", default="fixed", choices=["fixed", "continuous", "attn", "gemm"])
+    ap.add_argument("--rows", type=int, default=256, help="--workload gemm: batch rows")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--profile", action="store_true",
                     help="profiling runs (under ncu): one round of the attention timing loops instead of four")
@@ -543,6 +622,10 @@ def main():
     eng = m.engine
     hbm_peak, peak_kind = measured_peaks()
 
+    if args.workload == "gemm":
+        if rank == 0:
+            run_gemm_workload(args, dev)
+        return
     if args.workload == "attn":
         res = long_context_attention(eng, rounds=max(1, min(args.steps, 8)))
         stp = step_shape_attention(eng, rounds=max(1, min(args.steps, 4)))

@@ -220,3 +220,73 @@ def test_three_step_paths_agree(B):
         assert (lg.argmax(-1) == ref.argmax(-1)).mean() > 0.9
         d = (st.k[0].int() - sref.k[0].int()).abs()
         assert int(d.max()) <= 2 and (d > 0).float().mean().item() < 0.05, (name, int(d.max()))
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("M,d,f", [(256, 640, 1664), (7, 64, 128), (33, 1280, 4096)])
+def test_swiglu_with_deferred_norm(M, d, f, dtype):
+    """uv_swiglu_rs(gu, h) = silu(g * rs) * (u * rs), rs = rsqrt(mean(h^2) + eps), with the reference's rounding
+    points (the scaled projection and silu(g) are rounded to the activation dtype)."""
+    L, lib = _lib()
+    code = {torch.float16: 1, torch.bfloat16: 2}[dtype]
+    g = torch.Generator(device=DEV).manual_seed(M + f)
+    h = (torch.randn(M, d, device=DEV, generator=g) * 3).to(dtype)
+    gu = torch.randn(M, 2 * f, device=DEV, generator=g).to(dtype)
+    act = torch.full((M, f), 7.0, device=DEV, dtype=dtype)
+    L.check(lib.uv_swiglu_rs(gu.data_ptr(), h.data_ptr(), code, d, f, act.data_ptr(), M, _sp()), "uv_swiglu_rs")
+    rs = torch.rsqrt(h.float().pow(2).mean(1, keepdim=True) + torch.finfo(torch.float32).eps)
+    gs = (gu.float() * rs).to(dtype).float()
+    ref = (torch.nn.functional.silu(gs[:, :f]).to(dtype).float() * gs[:, f:]).to(dtype)
+    torch.cuda.synchronize()
+    assert (act.float() - ref.float()).abs().max().item() <= ref.float().abs().max().item() * 2.0 ** -7
+    assert (act == ref).float().mean().item() > 0.98
+
+
+def test_qkv_post_on_unnormalised_rows_equals_normalise_first():
+    """uv_qkv_post_args with xn_raw: qkv holds the projection of the UN-normalised rows; the kernel scales it by the
+    row's RMS factor and reads normalised gate inputs on the fly -- same q / k / v, cache bytes and gates as the
+    projection of the normalised rows with xn_raw = 0, up to one bf16 rounding of the projection."""
+    L, lib = _lib()
+    g = torch.Generator(device=DEV).manual_seed(11)
+    B, H, K, hd, d, S, vocab, n_pairs, ve_ch, gate_ch = 130, 8, 1, 64, 640, 264, 300, 16, 12, 128
+    y = (torch.randn(B, d, device=DEV, generator=g) * 2.5).bfloat16()
+    yn = torch.nn.functional.rms_norm(y.float(), (d,), eps=torch.finfo(torch.float32).eps).bfloat16()
+    w = (torch.randn((H + 2 * K) * hd, d, device=DEV, generator=g) * 0.06).bfloat16()
+    tok = torch.randint(0, vocab, (B,), device=DEV, generator=g)
+    ve = torch.randn(vocab, K * hd, device=DEV, generator=g).bfloat16()
+    ve_gate = (torch.randn(K, ve_ch, device=DEV, generator=g) * 0.3).bfloat16()
+    gate_w = (torch.randn(H, gate_ch, device=DEV, generator=g) * 0.2).bfloat16()
+    pos = torch.randint(0, 900, (B,), device=DEV, generator=g)
+    inv_freq = ((1.0 / 1024) ** torch.linspace(0, 1, n_pairs)).to(DEV)
+    th = pos.float()[:, None] * inv_freq[None]
+    rope_cs = torch.cat([th.cos().bfloat16().float(), th.sin().bfloat16().float()], 1).contiguous()
+    res = {}
+    for raw in (0, 1):
+        kc = torch.zeros(B, K, S, hd, dtype=torch.int8, device=DEV)
+        vc = torch.zeros_like(kc)
+        ks = torch.zeros(B, K, S, dtype=torch.float16, device=DEV)
+        vs = torch.zeros_like(ks)
+        oob = torch.zeros(1, dtype=torch.int32, device=DEV)
+        gates = torch.zeros(B, H, device=DEV)
+        src = y if raw else yn
+        qkv = torch.mm(src, w.t())
+        qa = L.QkvArgs()
+        qa.qkv, qa.xn, qa.tok, qa.value_embed, qa.ve_gate = qkv.data_ptr(), src.data_ptr(), tok.data_ptr(), \
+            ve.data_ptr(), ve_gate.data_ptr()
+        qa.inv_freq, qa.pos, qa.rope_cs = inv_freq.data_ptr(), pos.data_ptr(), rope_cs.data_ptr()
+        qa.k_cache, qa.v_cache, qa.k_scale, qa.v_scale = kc.data_ptr(), vc.data_ptr(), ks.data_ptr(), vs.data_ptr()
+        qa.oob_count, qa.dtype, qa.vocab = oob.data_ptr(), 2, vocab
+        qa.B, qa.H, qa.K, qa.hd, qa.d, qa.S, qa.S_alloc, qa.ring, qa.ve_ch, qa.n_pairs = B, H, K, hd, d, S, S, 1, \
+            ve_ch, n_pairs
+        qa.gate_w, qa.gate_out, qa.gate_ch, qa.xn_raw = gate_w.data_ptr(), gates.data_ptr(), gate_ch, raw
+        L.check(lib.uv_qkv_post_args(C.byref(qa), _sp()), "uv_qkv_post_args")
+        torch.cuda.synchronize()
+        assert int(oob.item()) == 0
+        res[raw] = (qkv.float(), kc, vc, ks.float(), vs.float(), gates)
+    a, b = res[0], res[1]
+    assert (a[0] - b[0]).abs().max().item() <= a[0].abs().max().item() * 2.0 ** -6
+    for i in (1, 2):
+        dq = (a[i].int() - b[i].int()).abs()
+        assert int(dq.max()) <= 2 and (dq > 0).float().mean().item() < 0.05 and (dq > 1).float().mean().item() < 1e-3
+    torch.testing.assert_close(a[5], b[5], rtol=2e-2, atol=2e-2)
+    assert b[1].any() and b[5].abs().sum() > 0

@@ -40,9 +40,12 @@ def test_teacher_forced_logits(name):
     cols = gi.logit_columns(spec, lg.shape[-1])
     ref = g[name + ".logits"]
     err = np.abs(lg[..., cols] - ref)
-    assert err.max() <= 2e-2 * np.abs(ref).max(), (err.max(), np.abs(ref).max())
-    assert err.mean() < 0.03
-    assert (lg.argmax(-1) == g[name + ".argmax"]).mean() > 0.9
+    # the path's stated tolerance is 2e-2 relative; measured on B200: 0.6e-3 .. 1.3e-3 of the largest logit, and the
+    # same elementwise (|err| / max(|ref|, 1) <= 1.9e-3), so the bound is set four times tighter than stated
+    assert err.max() <= 5e-3 * np.abs(ref).max(), (err.max(), np.abs(ref).max())
+    assert (err / np.maximum(np.abs(ref), 1.0)).max() <= 5e-3
+    assert err.mean() < 0.01
+    assert (lg.argmax(-1) == g[name + ".argmax"]).mean() > 0.98
     # (2) the oracle on the same bf16-rounded weights
     mc = build_model(spec)
     W = oracle_weights(mc, "bf16")
@@ -52,7 +55,7 @@ def test_teacher_forced_logits(name):
         outs.append(om.decode_step(W, mc.cfg, cont[:, i], ost))
     olg = np.stack(outs, 1)
     err = np.abs(lg - olg)
-    assert err.max() <= 2e-2 * np.abs(olg).max(), (err.max(), np.abs(olg).max())
+    assert err.max() <= 5e-3 * np.abs(olg).max(), (err.max(), np.abs(olg).max())
     assert np.array_equal(st.pos.cpu().numpy(), ost.pos) and np.array_equal(st.starts.cpu().numpy(), ost.starts)
     # int8 cache of the first layer: same bytes up to bf16 rounding of the projections (one quantisation step)
     # (slots of real tokens only: the packed prefill never computes or writes the left padding, exactly as the
@@ -101,15 +104,23 @@ def test_generate_and_continuous_tiny():
     ref = gi.unpack_lists(g["tiny.generate"])
     assert [len(r) for r in out] == [len(r) for r in ref]
     agree = np.mean([a == b for r, s in zip(out, ref) for a, b in zip(r, s)])
-    assert agree > 0.8, agree   # bf16 + int8-prefill rounding can flip near-ties of a random tiny model
+    assert agree > 0.95, agree  # measured on B200: identical to the reference's streams (a bf16 near-tie may flip)
     eager = generate(m, ge["prompts"], ge["max_new"], temperature=0.0, use_graph=False)
     assert eager == out         # graph replay == eager launches (tests/test_math_kernels.py:176-189)
+    cref = gi.unpack_lists(g["tiny.continuous"])
+    # prompts through the decode step: measured identical to the reference's continuous streams
+    step = generate_continuous(m, c["prompts"], c["max_new"], batch=c["batch"], temperature=0.0, eos_id=c["eos_id"],
+                               check_every=c["check_every"], target_lens=c["target_lens"], packed_prefill=False)
+    assert [len(r) for r in step] == c["target_lens"]
+    agree = np.mean([a == b for r, s in zip(step, cref) for a, b in zip(r, s)])
+    assert agree > 0.95, agree
+    # packed admission passes (the default): the prompts' keys come out of GEMMs over a few hundred packed rows
+    # instead of the slots' rows, so a near-tie of this random tiny model can flip (measured agreement 0.82)
     cont = generate_continuous(m, c["prompts"], c["max_new"], batch=c["batch"], temperature=0.0,
                                eos_id=c["eos_id"], check_every=c["check_every"], target_lens=c["target_lens"])
     assert [len(r) for r in cont] == c["target_lens"]
-    cref = gi.unpack_lists(g["tiny.continuous"])
     agree = np.mean([a == b for r, s in zip(cont, cref) for a, b in zip(r, s)])
-    assert agree > 0.8, agree
+    assert agree > 0.7, agree
     # continuous batching vs static generation per prompt (tests/test_math_model.py:198-210).  The two prefill
     # differently here -- generate() through the packed kernel over unquantised keys, the device scheduler through the
     # decode step over the int8 cache -- so a near-tie of this random tiny model can flip and the greedy tails then
@@ -284,3 +295,37 @@ def test_continuous_with_packed_admission_matches_static_generation():
     assert [len(x) for x in step] == lens
     assert np.mean([a == b for x, y in zip(step, got) for a, b in zip(x, y)]) > 0.6
     assert s_p["steps"] < 0.6 * s_s["steps"], (s_p, s_s)
+
+
+def test_admission_pass_writes_the_same_cache_as_host_prefill():
+    """The cache an admission pass leaves (device-built packed batch, padded to a power of two of rows, slots chosen
+    on the device) against prefill() of the same prompts (host-built packed batch): same positions, same slots,
+    bytes equal up to the GEMMs' batch-size dependent rounding; the slot holds the last prompt token at position
+    P - 1."""
+    from ultraviolet_b200.scheduler import GpuScheduler
+    spec = gi.model_specs()["tiny_hd64"]
+    m = _gpu_model(spec)
+    cfg, eng = m.cfg, m.engine
+    r = np.random.default_rng(23)
+    n, P = 6, 21                                  # equal lengths: the left-padded frame is the position frame
+    prompts = [r.integers(1, cfg.vocab_size, P).tolist() for _ in range(n)]
+    idx = torch.tensor(prompts, device=DEV)
+    ref = m.new_state(n, 64)
+    m.prefill(idx[:, :-1], torch.zeros(n, dtype=torch.long, device=DEV), ref)
+    st = m.new_state(GpuScheduler.state_rows(n, 0, True), 64)
+    sch = GpuScheduler(eng, st, max_new=4, temperature=1.0, eos_id=0, seed=1, q_cap=16, max_prompt=32,
+                       packed_prefill=True, use_graph=False)
+    sch.enqueue(prompts)
+    sch.prime()
+    torch.cuda.synchronize()
+    assert sch.n_admit_passes == 1 and sch.counters()["head"] == n
+    assert st.pos.tolist() == [P - 1] * n and sch.cur_tok[:n].tolist() == [p[-1] for p in prompts]
+    for l in range(cfg.n_layers):
+        S = ref.k[l].shape[2]
+        t = np.arange(max(0, P - 1 - S) if not cfg.is_global(l) else 0, P - 1)
+        sl = t % S if not cfg.is_global(l) else t
+        for a, b in ((st.k[l], ref.k[l]), (st.v[l], ref.v[l])):
+            d = (a[:n][:, :, sl].int() - b[:, :, sl].int()).abs()
+            assert int(d.max()) <= (1 if l == 0 else 3) and (d > 0).float().mean().item() < (0.02 if l == 0 else 0.3), \
+                (l, int(d.max()), (d > 0).float().mean().item())
+    eng.check_status()

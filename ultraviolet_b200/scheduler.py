@@ -151,6 +151,9 @@ class GpuScheduler:
             raise ValueError("token limits must be >= 1")
         if int((lens + lim).max()) > self.st.max_len:
             raise ValueError("prompt + limit exceeds the cache length")
+        if self.packed and int(lens.max()) - 1 > self.prefill_cap:
+            raise ValueError(f"a prompt of {int(lens.max())} tokens does not fit one admission pass "
+                             f"(prefill_cap = {self.prefill_cap} packed rows)")
         in_flight = self.n_enqueued - self.n_harvested
         if in_flight + n > self.q_cap:
             raise RuntimeError(f"request ring full ({in_flight} in flight + {n} new > {self.q_cap})")
@@ -324,7 +327,8 @@ class GpuScheduler:
             fin = int(self.ctl[CTL_FIN].item())
         if fin == self.n_harvested:
             return None
-        self.eng.check_status(self.st_rows)  # rollouts from a step whose kernels flagged a failure are not handed out
+        # rollouts from a step (or an admission pass) whose kernels flagged a failure are not handed out
+        self.eng.check_status(None if self.packed else self.st_rows)
         k = torch.arange(self.n_harvested, fin, device=self.dev) % self.q_cap
         rid = self.fin_ring[k].long()
         ri = rid % self.q_cap
