@@ -141,7 +141,8 @@ class DecodeEngine:
                 w[f"l{l}.wo"].copy_((at.wo.float() * float(at.o_scale) * (lam_h[1] / scale)).to(dt))
                 scale *= lam_h[2]
                 w[f"l{l}.down"].copy_((mlp.w_down.float() * (lam_h[3] / scale)).to(dt))
-                if not (2.0 ** -24 < abs(scale) < 2.0 ** 24):
+                lim = 2.0 ** (24 if dt == torch.bfloat16 else 6)   # fp16 has 5 exponent bits: keep y near x
+                if not (1.0 / lim < abs(scale) < lim):
                     raise ValueError("the product of the residual lambdas leaves the range the folded residual "
                                      "stream keeps in half precision; set UVDECODE_FOLD=0")
             else:
