@@ -242,13 +242,14 @@ def test_swiglu_with_deferred_norm(M, d, f, dtype):
     assert (act == ref).float().mean().item() > 0.98
 
 
-def test_qkv_post_on_unnormalised_rows_equals_normalise_first():
+@pytest.mark.parametrize("H,K", [(8, 1), (28, 2)])   # 11 warps per row (row-per-CTA layout) / 33 (item-per-warp layout)
+def test_qkv_post_on_unnormalised_rows_equals_normalise_first(H, K):
     """uv_qkv_post_args with xn_raw: qkv holds the projection of the UN-normalised rows; the kernel scales it by the
     row's RMS factor and reads normalised gate inputs on the fly -- same q / k / v, cache bytes and gates as the
     projection of the normalised rows with xn_raw = 0, up to one bf16 rounding of the projection."""
     L, lib = _lib()
     g = torch.Generator(device=DEV).manual_seed(11)
-    B, H, K, hd, d, S, vocab, n_pairs, ve_ch, gate_ch = 130, 8, 1, 64, 640, 264, 300, 16, 12, 128
+    B, hd, d, S, vocab, n_pairs, ve_ch, gate_ch = 130, 64, 640, 264, 300, 16, 12, 128
     y = (torch.randn(B, d, device=DEV, generator=g) * 2.5).bfloat16()
     yn = torch.nn.functional.rms_norm(y.float(), (d,), eps=torch.finfo(torch.float32).eps).bfloat16()
     w = (torch.randn((H + 2 * K) * hd, d, device=DEV, generator=g) * 0.06).bfloat16()

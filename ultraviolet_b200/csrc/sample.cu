@@ -11,6 +11,8 @@
 //                                                      (model.py:1160-1169); T <= 0 reports it at T = 1
 // u comes from the caller (one uniform per row) or from Philox4x32-10 keyed by (seed; row key, step), so a
 // sequence's random stream depends only on its own key and token index, never on the slot or batch it runs in.
+#include <stdlib.h>
+
 #include "common.cuh"
 
 namespace uv {
@@ -44,6 +46,7 @@ struct SampleParams {
   int top_k;  // 0 = no limit
   int greedy;
   int greedy_fast;  // host-decided: the vectorised arg-max path (needs no shared memory: launched with none)
+  int plain_fast;   // host-decided: T > 0 without top-k / top-p over 16-bit logits: the draw without shared memory
   int precapped;  // input rows are already softcapped logits z (sample(), model.py:1194-1211); a = row maximum
   const float* u;
   uint64_t seed;
@@ -144,6 +147,111 @@ __global__ void __launch_bounds__(SAMPLE_THREADS) sample_kernel(const __grid_con
       P.tok[row] = best_i;
       P.logp[row] = (best - P.a) * P.inv_t - logf(S_all);
       if (P.inc_a) P.inc_a[row] += 1;
+      if (P.inc_b) P.inc_b[row] += 1;
+    }
+    return;
+  }
+
+  if constexpr (sizeof(T) == 2)
+  if (P.plain_fast) {
+    // T > 0, no truncation: nothing is parked in shared memory.  Element i belongs to (slab k, thread t, j) with
+    // i = k * 2048 + t * 8 + j, so index order is slab-major, then thread, then j.  Pass 1 keeps one partial sum per
+    // slab in registers (coalesced 16-byte loads); one batched block reduction gives every slab's sum; the slab that
+    // holds the target is re-read (it sits in L2), scanned over the threads in order, and the owning thread walks its
+    // eight values.  Same rule as the general path: first index whose running sum reaches (1 - u) * S.
+    constexpr int SLAB = SAMPLE_THREADS * 8, KMAX = 24;   // V <= 49152
+    __shared__ float slab_w[SAMPLE_THREADS / 32][KMAX];
+    __shared__ float slab_s[KMAX];
+    const int nslab = V / SLAB;
+    float part[KMAX];
+#pragma unroll
+    for (int k = 0; k < KMAX; ++k) part[k] = 0.f;
+    auto e8 = [&](const uint4& u4, float (&e)[8]) {
+      const T* v = reinterpret_cast<const T*>(&u4);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float z = __fdividef(P.a, 1.0f + __expf(-(to_f32<T>(v[j]) + P.b) * inv_c));
+        e[j] = __expf((z - P.a) * P.inv_t);
+      }
+    };
+#pragma unroll
+    for (int k0 = 0; k0 < KMAX; k0 += 4) {
+      uint4 u4[4];
+#pragma unroll
+      for (int q = 0; q < 4; ++q)
+        if (k0 + q < nslab) u4[q] = *reinterpret_cast<const uint4*>(xr + (k0 + q) * SLAB + tid * 8);
+#pragma unroll
+      for (int q = 0; q < 4; ++q)
+        if (k0 + q < nslab) {
+          float e[8];
+          e8(u4[q], e);
+          part[k0 + q] = ((e[0] + e[1]) + (e[2] + e[3])) + ((e[4] + e[5]) + (e[6] + e[7]));
+        }
+    }
+#pragma unroll
+    for (int k = 0; k < KMAX; ++k)
+      if (k < nslab) {
+        const float w = warp_sum(part[k]);
+        if (lane == 0) slab_w[warp][k] = w;
+      }
+    if (tid == 0) s_tok = V - 1;
+    __syncthreads();
+    if (tid < nslab) {
+      float t = 0.f;
+#pragma unroll
+      for (int w = 0; w < SAMPLE_THREADS / 32; ++w) t += slab_w[w][tid];
+      slab_s[tid] = t;
+    }
+    __syncthreads();
+    float S_all = 0.f;
+    for (int k = 0; k < nslab; ++k) S_all += slab_s[k];
+    const float u = P.u ? P.u[row] : philox_uniform(P.seed, (uint64_t)P.row_keys[row], (uint64_t)P.steps[row]);
+    const float target = (1.0f - u) * S_all;
+    int ks = nslab - 1;
+    float base = 0.f, run = 0.f;
+    for (int k = 0; k < nslab; ++k) {  // the first slab whose cumulative sum reaches the target (uniform in the CTA)
+      if (run + slab_s[k] >= target) {
+        ks = k;
+        break;
+      }
+      run += slab_s[k];
+    }
+    base = run;
+    // ---- the slab: per-thread sums in index order, block scan, then the owner's eight values
+    float e[8];
+    e8(*reinterpret_cast<const uint4*>(xr + ks * SLAB + tid * 8), e);
+    const float mine = ((e[0] + e[1]) + (e[2] + e[3])) + ((e[4] + e[5]) + (e[6] + e[7]));
+    float incl = mine;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const float v = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += v;
+    }
+    if (lane == 31) scan_w[warp] = incl;
+    __syncthreads();
+    float wbase = 0.f;
+    for (int w = 0; w < warp; ++w) wbase += scan_w[w];
+    incl += wbase + base;
+    const float excl = incl - mine;
+    if (excl < target && target <= incl) {
+      float cs = excl;
+      int found = ks * SLAB + tid * 8 + 7;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        cs += e[j];
+        if (cs >= target) {
+          found = ks * SLAB + tid * 8 + j;
+          break;
+        }
+      }
+      atomicMin(&s_tok, found);
+    }
+    __syncthreads();
+    if (tid == 0) {
+      const int t = s_tok;
+      P.tok[row] = t;
+      P.logp[row] = (zof(t) - P.a) * P.inv_t - logf(S_all);
+      if (P.inc_a) P.inc_a[row] += 1;  // every thread read steps[row] before the barrier above
       if (P.inc_b) P.inc_b[row] += 1;
     }
     return;
@@ -313,6 +421,16 @@ __global__ void __launch_bounds__(SAMPLE_THREADS) sample_kernel(const __grid_con
 
 }  // namespace uv
 
+namespace uv {
+static bool plain_fast_disabled() {
+  static const bool off = [] {
+    const char* v = getenv("UVDECODE_SAMPLE_PLAIN_FAST");  // "0": always the general (shared-memory) path
+    return v && v[0] == '0';
+  }();
+  return off;
+}
+}  // namespace uv
+
 extern "C" int uv_sample(const void* x, int x_dtype, int64_t x_stride, int B, int V, int precapped, float cap_a,
                          float cap_b, float cap_c, float temperature, float top_p, const float* u, uint64_t seed,
                          const int64_t* row_keys, const int64_t* steps, int64_t* tok_out, float* logp_out,
@@ -346,7 +464,11 @@ extern "C" int uv_sample_topk(const void* x, int x_dtype, int64_t x_stride, int 
   // more rows are resident per SM
   P.greedy_fast = greedy && !precapped && x_dtype != UV_F32 && (reinterpret_cast<uintptr_t>(x) & 15) == 0 &&
                   (x_stride * 2) % 16 == 0 && V % 8 == 0;
-  const size_t smem = P.greedy_fast ? 0 : (size_t)(V + V / (V / SAMPLE_THREADS) + 1) * sizeof(float);
+  // T > 0 without truncation over 16-bit logits in whole 2048-element slabs: the draw needs no shared memory either
+  P.plain_fast = !greedy && !precapped && top_k == 0 && !(top_p < 1.0f) && x_dtype != UV_F32 &&
+                 (reinterpret_cast<uintptr_t>(x) & 15) == 0 && (x_stride * 2) % 16 == 0 &&
+                 V % (SAMPLE_THREADS * 8) == 0 && V / (SAMPLE_THREADS * 8) <= 24 && !plain_fast_disabled();
+  const size_t smem = (P.greedy_fast || P.plain_fast) ? 0 : (size_t)(V + V / (V / SAMPLE_THREADS) + 1) * sizeof(float);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
 #define UV_GO(T)                                                                                              \
   do {                                                                                                        \
