@@ -242,7 +242,7 @@ def test_swiglu_with_deferred_norm(M, d, f, dtype):
     assert (act == ref).float().mean().item() > 0.98
 
 
-@pytest.mark.parametrize("H,K", [(8, 1), (28, 2)])   # 11 warps per row (row-per-CTA layout) / 33 (item-per-warp layout)
+@pytest.mark.parametrize("H,K", [(8, 1), (28, 2)])
 def test_qkv_post_on_unnormalised_rows_equals_normalise_first(H, K):
     """uv_qkv_post_args with xn_raw: qkv holds the projection of the UN-normalised rows; the kernel scales it by the
     row's RMS factor and reads normalised gate inputs on the fly -- same q / k / v, cache bytes and gates as the

@@ -254,14 +254,6 @@ __global__ void __launch_bounds__(SWR_THREADS) swiglu_rs_kernel(const T* __restr
 }
 
 // ------------------------------------------------------------------------------------------------ QKV post
-static bool qkv_post_row_layout_disabled() {
-  static const bool off = [] {
-    const char* v = getenv("UVDECODE_QKV_POST_ROWS");  // "0": the item-per-warp layout for every shape
-    return v && v[0] == '0';
-  }();
-  return off;
-}
-
 // One warp per (row b, head slot), in place on the packed GEMM output; the arithmetic lives in qkv_post.cuh.
 template <typename T, int HD, bool TABLE>
 __global__ void __launch_bounds__(128) qkv_post_kernel(const __grid_constant__ QkvPostParams P) {
@@ -308,99 +300,8 @@ __global__ void __launch_bounds__(128) qkv_post_kernel(const __grid_constant__ Q
   if (hs >= P.H && P.k_cache != nullptr) qkv_post_append<T, HD>(P, b, hs, lane, x);
 }
 
-// The same work with one CTA per batch row: warp w < H + 2K post-processes head slot w, one more warp computes all
-// H head gates (the gate input row is loaded once, the H weight rows are all requested before any is used).  Against
-// the item-per-warp layout above this halves the warps per row (11 instead of 18 for 8 + 2 slots and 8 gates) and
-// keeps a row's loads in one SM's L1.  Used when H + 2K + 1 <= 32 warps.
-template <typename T, int HD, bool TABLE>
-__global__ void __launch_bounds__(1024) qkv_post_row_kernel(const __grid_constant__ QkvPostParams P) {
-  constexpr int E = HD >= 32 ? HD / 32 : 1;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int slots = P.H + 2 * P.K;
-  const int b = blockIdx.x;
-  pdl_wait();
-  pdl_trigger();
-  const bool raw = P.xn_raw != 0;
-  const T* xrow = static_cast<const T*>(P.xn) + (int64_t)b * P.d;
-  if (warp >= slots) {
-    // ---- all head gates: 2 * sigmoid(xn[b, :gate_ch] . gate_w[head]) with the reference's rounding points
-    constexpr int GMAX = 8;  // channel pieces per lane held in registers: gate_ch <= 256 on the register path
-    const int npc = (P.gate_ch + 31) / 32;
-    const float rs = raw ? row_rms_factor<T>(xrow, P.d, lane) : 1.0f;
-    if (npc <= GMAX) {
-      float gx[GMAX];
-#pragma unroll
-      for (int i = 0; i < GMAX; ++i) {
-        const int ch = lane + 32 * i;
-        float v = (i < npc && ch < P.gate_ch) ? to_f32<T>(xrow[ch]) : 0.f;
-        gx[i] = raw ? rnd<T>(v * rs) : v;
-      }
-      for (int h0 = 0; h0 < P.H; h0 += 4) {  // four heads' weight rows in flight at once
-        float acc[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          if (h0 + q >= P.H) break;
-          const T* gw = static_cast<const T*>(P.gate_w) + (int64_t)(h0 + q) * P.gate_ch;
-#pragma unroll
-          for (int i = 0; i < GMAX; ++i) {
-            const int ch = lane + 32 * i;
-            if (i < npc && ch < P.gate_ch) acc[q] += gx[i] * to_f32<T>(gw[ch]);
-          }
-        }
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          if (h0 + q >= P.H) break;
-          const float a = rnd<T>(warp_sum(acc[q]));
-          const float g = rnd<T>(2.0f * rnd<T>(1.0f / (1.0f + __expf(-a))));
-          if (lane == 0) P.gate_out[(int64_t)b * P.H + h0 + q] = g;
-        }
-      }
-    } else {
-      for (int head = 0; head < P.H; ++head) {
-        const float g = head_gate<T>(xrow, static_cast<const T*>(P.gate_w) + (int64_t)head * P.gate_ch, P.gate_ch,
-                                     lane, rs, raw);
-        if (lane == 0) P.gate_out[(int64_t)b * P.H + head] = g;
-      }
-    }
-    return;
-  }
-  const int hs = warp;
-  const bool act = lane * E < HD;
-  T* vec = static_cast<T*>(P.qkv) + ((int64_t)b * slots + hs) * HD;
-  float x[E];
-#pragma unroll
-  for (int i = 0; i < E; ++i) x[i] = act ? to_f32<T>(vec[lane * E + i]) : 0.f;   // requested before the row reduction
-  const float rs = raw ? row_rms_factor<T>(xrow, P.d, lane) : 1.0f;
-  if (raw) {
-#pragma unroll
-    for (int i = 0; i < E; ++i) x[i] = rnd<T>(x[i] * rs);
-  }
-  qkv_post_compute<T, HD, TABLE>(P, b, hs, lane, x, rs, raw);
-#pragma unroll
-  for (int i = 0; i < E; ++i)
-    if (act) vec[lane * E + i] = from_f32<T>(x[i]);
-  if (hs >= P.H && P.k_cache != nullptr) qkv_post_append<T, HD>(P, b, hs, lane, x);
-}
-
 template <typename T>
 static int launch_qkv_post(const QkvPostParams& P, int hd, cudaStream_t st) {
-  const int row_warps = P.H + 2 * P.K + (P.gate_out ? 1 : 0);
-  if (row_warps <= 32 && !qkv_post_row_layout_disabled()) {
-#define UV_QKV_ROW(HD_)                                                                                          \
-  case HD_:                                                                                                      \
-    if (P.rope_cs) launch_pdl(qkv_post_row_kernel<T, HD_, true>, dim3((unsigned)P.B), dim3(32 * row_warps), 0, st, P);   \
-    else launch_pdl(qkv_post_row_kernel<T, HD_, false>, dim3((unsigned)P.B), dim3(32 * row_warps), 0, st, P);    \
-    break;
-    switch (hd) {
-      UV_QKV_ROW(16)
-      UV_QKV_ROW(32)
-      UV_QKV_ROW(64)
-      UV_QKV_ROW(128)
-      default: return UV_ERR_SHAPE;
-    }
-#undef UV_QKV_ROW
-    return check_launch();
-  }
   const unsigned grid = (unsigned)(((int64_t)P.B * (P.H + 2 * P.K + (P.gate_out ? P.H : 0)) + 3) / 4);
   // with the step's RoPE table the kernel carries no cosf / sinf code at all
 #define UV_QKV_POST(HD_)                                                                        \
