@@ -275,6 +275,10 @@ __global__ void __launch_bounds__(128) qkv_post_kernel(const __grid_constant__ Q
 #pragma unroll
     for (int i = 0; i < E; ++i) x0[i] = act0 ? to_f32<T>(vec0[lane * E + i]) : 0.f;
   }
+  // so is where a key / value slot will land (position, cache row): three more loads off the tail of the chain
+  QkvSlot dest{};
+  const bool appends = hs >= P.H && hs < slots && P.k_cache != nullptr;
+  if (appends) dest = qkv_post_slot(P, b);
   const float rs = raw ? row_rms_factor<T>(static_cast<const T*>(P.xn) + (int64_t)b * P.d, P.d, lane) : 1.0f;
   if (hs >= slots) {
     const int head = hs - slots;
@@ -297,7 +301,7 @@ __global__ void __launch_bounds__(128) qkv_post_kernel(const __grid_constant__ Q
 #pragma unroll
   for (int i = 0; i < E; ++i)
     if (act) vec[lane * E + i] = from_f32<T>(x[i]);
-  if (hs >= P.H && P.k_cache != nullptr) qkv_post_append<T, HD>(P, b, hs, lane, x);
+  if (appends) qkv_post_append<T, HD>(P, b, hs, lane, x, &dest);
 }
 
 template <typename T>

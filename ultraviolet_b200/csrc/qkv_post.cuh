@@ -133,6 +133,13 @@ __device__ __forceinline__ void qkv_post_compute(const QkvPostParams& P, int b, 
       const int kh = hs - P.H - P.K;
       const T* xr = static_cast<const T*>(P.xn) + (int64_t)b * P.d;
       const T* gw = static_cast<const T*>(P.ve_gate) + (int64_t)kh * P.ve_ch;
+      // the embedding row hangs off the token id (two dependent loads): started before the gate's reduction
+      int64_t t = P.tok[b];
+      if (t < 0 || t >= P.vocab) t = 0;
+      const T* ve = static_cast<const T*>(P.value_embed) + (t * P.K + kh) * HD;
+      float vev[E];
+#pragma unroll
+      for (int i = 0; i < E; ++i) vev[i] = act ? to_f32<T>(ve[lane * E + i]) : 0.f;
       float acc = 0.f;
       for (int ch = lane; ch < P.ve_ch; ch += 32) {
         const float xv = scaled ? rnd<T>(to_f32<T>(xr[ch]) * xs) : to_f32<T>(xr[ch]);
@@ -140,14 +147,24 @@ __device__ __forceinline__ void qkv_post_compute(const QkvPostParams& P, int b, 
       }
       acc = rnd<T>(warp_sum(acc));
       const float g = rnd<T>(2.0f * rnd<T>(1.0f / (1.0f + __expf(-acc))));
-      int64_t t = P.tok[b];
-      if (t < 0 || t >= P.vocab) t = 0;
-      const T* ve = static_cast<const T*>(P.value_embed) + (t * P.K + kh) * HD;
 #pragma unroll
       for (int i = 0; i < E; ++i)
-        if (act) x[i] = rnd<T>(x[i] + rnd<T>(g * to_f32<T>(ve[lane * E + i])));
+        if (act) x[i] = rnd<T>(x[i] + rnd<T>(g * vev[i]));
     }
     return;
+  }
+  // the rotation's table entries do not depend on x: requested before the norm's reduction, not after it
+  float cs_pre[E], sn_pre[E];
+  const bool table = P.inv_freq != nullptr && (TABLE || P.rope_cs != nullptr);
+#pragma unroll
+  for (int i = 0; i < E; ++i) {
+    cs_pre[i] = 1.f, sn_pre[i] = 0.f;
+    const int dim = lane * E + i;
+    if (table && dim < 2 * P.n_pairs) {
+      const int j = dim < P.n_pairs ? dim : dim - P.n_pairs;
+      cs_pre[i] = P.rope_cs[(int64_t)b * 2 * P.n_pairs + j];
+      sn_pre[i] = P.rope_cs[(int64_t)b * 2 * P.n_pairs + P.n_pairs + j];
+    }
   }
   float ss = 0.f;
 #pragma unroll
@@ -158,7 +175,7 @@ __device__ __forceinline__ void qkv_post_compute(const QkvPostParams& P, int b, 
   if (P.inv_freq != nullptr) {
     // half-split pairing: dim j < n_pairs rotates with dim j + n_pairs (apply_rope, model.py:219-226)
     const int pl = P.n_pairs / E;  // lanes holding x1
-    const float pf = (float)P.pos[b];
+    const float pf = table ? 0.f : (float)P.pos[b];
 #pragma unroll
     for (int i = 0; i < E; ++i) {
       const float other = __shfl_xor_sync(0xffffffffu, x[i], pl);
@@ -166,9 +183,8 @@ __device__ __forceinline__ void qkv_post_compute(const QkvPostParams& P, int b, 
       if (dim < 2 * P.n_pairs) {
         const int j = dim < P.n_pairs ? dim : dim - P.n_pairs;
         float cs, sn;
-        if (TABLE || P.rope_cs != nullptr) {
-          cs = P.rope_cs[(int64_t)b * 2 * P.n_pairs + j];
-          sn = P.rope_cs[(int64_t)b * 2 * P.n_pairs + P.n_pairs + j];
+        if (table) {
+          cs = cs_pre[i], sn = sn_pre[i];
         } else {
           const float th = pf * P.inv_freq[j];
           cs = rnd<T>(cosf(th)), sn = rnd<T>(sinf(th));
@@ -183,23 +199,38 @@ __device__ __forceinline__ void qkv_post_compute(const QkvPostParams& P, int b, 
 
 // Store a quantised key / value slot (lane owns bytes [lane*E, lane*E + E)) and its scale at the cache row of batch
 // entry b.  Full warp.
+// Where batch entry b's key / value lands: its position, its cache row and (packed prefill) the last position of its
+// sequence -- three independent loads a caller can request early and hand to qkv_post_store.
+struct QkvSlot {
+  int64_t pos, row, last;
+};
+__device__ __forceinline__ QkvSlot qkv_post_slot(const QkvPostParams& P, int b) {
+  QkvSlot q;
+  q.pos = P.pos[b];
+  q.row = P.row_map ? P.row_map[b] : b;
+  q.last = (P.ring && P.last_pos != nullptr) ? P.last_pos[b] : -1;
+  return q;
+}
+
 template <int HD>
 __device__ __forceinline__ void qkv_post_store(const QkvPostParams& P, int b, int hs, int lane,
-                                               const int8_t (&q8)[HD >= 32 ? HD / 32 : 1], uint16_t s) {
+                                               const int8_t (&q8)[HD >= 32 ? HD / 32 : 1], uint16_t s,
+                                               const QkvSlot* pre = nullptr) {
   constexpr int E = HD >= 32 ? HD / 32 : 1;
   const bool act = lane * E < HD;
   const bool isv = hs >= P.H + P.K;
   const int kh = isv ? hs - P.H - P.K : hs - P.H;
-  int64_t p = P.pos[b];
+  const QkvSlot sl = pre ? *pre : qkv_post_slot(P, b);
+  int64_t p = sl.pos;
   if (P.ring) {
-    if (P.last_pos != nullptr && p + P.S <= P.last_pos[b]) return;  // a newer token of this launch owns the slot
+    if (sl.last >= 0 && p + P.S <= sl.last) return;  // a newer token of this launch owns the slot
     p = ((p % P.S) + P.S) % P.S;
   }
   if (p < 0 || p >= P.S) {
     if (lane == 0 && P.oob) atomicAdd(P.oob, 1);
     return;
   }
-  const int64_t cb = P.row_map ? P.row_map[b] : b;
+  const int64_t cb = sl.row;
   const int64_t dst = (cb * P.K + kh) * P.S_alloc + p;  // rows may be allocated longer than S
   int8_t* crow = (isv ? P.v_cache : P.k_cache) + dst * HD;
   if (act) {
@@ -213,11 +244,12 @@ __device__ __forceinline__ void qkv_post_store(const QkvPostParams& P, int b, in
 // Quantise a post-processed key / value slot and append it to the cache row of batch entry b.  Full warp.
 template <typename T, int HD>
 __device__ __forceinline__ void qkv_post_append(const QkvPostParams& P, int b, int hs, int lane,
-                                                const float (&x)[HD >= 32 ? HD / 32 : 1]) {
+                                                const float (&x)[HD >= 32 ? HD / 32 : 1],
+                                                const QkvSlot* pre = nullptr) {
   constexpr int E = HD >= 32 ? HD / 32 : 1;
   int8_t q8[E];
   const uint16_t s = quantize_lane<E>(x, q8);
-  qkv_post_store<HD>(P, b, hs, lane, q8, s);
+  qkv_post_store<HD>(P, b, hs, lane, q8, s, pre);
 }
 
 }  // namespace uv
