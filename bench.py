@@ -442,11 +442,13 @@ def run_gemm_workload(args, dev):
 
 # ------------------------------------------------------------------------------------------------ rollout jobs
 def rollout_job(m, rank, world, dev, *, prompts_all, stops_all, slots, max_new, max_prompt, lanes, lane_chunk, seed,
-                force_eos, timed_steps=0, warmup=3, broadcast=False, gather=False, packed=True):
+                force_eos, timed_steps=0, warmup=3, broadcast=False, gather=False, packed=True, compact=True, overlap=True):
     """One rollout round on the device-resident scheduler: the requests are sharded i % W == rank, every rank runs
     its replica until its share is drained (timed_steps > 0: that many steps only), finished rollouts are harvested
     as device tensors.  Optionally the weight arena is broadcast from rank 0 first and the rollouts (tokens int32,
     log-probs fp32, lengths and start versions int32) are gathered to rank 0 afterwards, each collective timed.
+    overlap: each window of steps is launched before the payload of the requests that finished in the window before
+    it is gathered (GpuScheduler.window), so the device does not wait for the host's harvest.
     Windows of 16 (packed admission) or 64 steps are timed separately so that the steady state (slot occupancy >=
     0.95) can be told from the
     straggler tail.  Returns a dict on every rank (aggregates are all-reduced)."""
@@ -467,8 +469,9 @@ def rollout_job(m, rank, world, dev, *, prompts_all, stops_all, slots, max_new, 
     sch = GpuScheduler(eng, st, max_new=max_new, temperature=1.0, eos_id=0, seed=seed, q_cap=max(len(mine), 2),
                        max_prompt=max_prompt, force_eos=force_eos, tok_cap=int(lens[mine].sum()) + 1,
                        out_cap=int(lim[mine].sum()) + 1, prefill_lanes=lanes, lane_chunk=lane_chunk,
-                       packed_prefill=packed)
+                       packed_prefill=packed, compact=compact)
     W_STEPS = 16 if packed else 64   # steps between harvests (= between admission passes in packed mode)
+    sch.warm()                       # every step / admission graph captured before the job, as a server would
     sch.enqueue([prompts_all[i] for i in mine], limits=None if stops_all is None else lim[mine].tolist(), keys=mine,
                 metas=mine)
     sch.run(max(warmup, 3))
@@ -480,23 +483,42 @@ def rollout_job(m, rank, world, dev, *, prompts_all, stops_all, slots, max_new, 
     ev = lambda: torch.cuda.Event(enable_timing=True)
     e_begin, e_end = ev(), ev()
     e_begin.record()
+    last = None   # (start event, end event, steps) of the window in flight
+
+    def close_window(c):
+        nonlocal c_prev
+        a_, b_, n_ = last
+        windows.append((a_.elapsed_time(b_), c["generated"] - c_prev["generated"],
+                        (c["slot_steps"] - c_prev["slot_steps"]) / (n_ * slots)))
+        c_prev = c
     while True:
         n = W_STEPS if timed_steps <= 0 else min(W_STEPS, timed_steps - steps)
         a, b = ev(), ev()
         a.record()
-        sch.run(n)
+        # launches the window, then gathers -- while it runs -- what had finished when it was launched; the
+        # counters it read (one small D2H, which waited for the window before) close that window's record
+        p = sch.window(n) if overlap else sch.run(n)
         b.record()
         steps += n
-        p = sch.harvest_packed()          # syncs: the window's events are complete after it
-        c = sch.counters()
-        windows.append((a.elapsed_time(b), c["generated"] - c_prev["generated"],
-                        (c["slot_steps"] - c_prev["slot_steps"]) / (n * slots)))
-        c_prev = c
+        if overlap:
+            if last is not None:
+                close_window(sch.counters(cached=True))
+            last = (a, b, n)
+        else:
+            p = sch.harvest_packed()      # syncs: the window's events are complete after it
+            last = (a, b, n)
+            close_window(sch.counters())
         if p is not None:
             harvested.append(p)
             n_done += len(p["metas"])
         if (timed_steps > 0 and steps >= timed_steps) or (timed_steps <= 0 and n_done >= len(mine)):
             break
+    if overlap:
+        p = sch.harvest_packed()          # what finished during the last window
+        close_window(sch.counters())
+        if p is not None:
+            harvested.append(p)
+            n_done += len(p["metas"])
     e_end.record()
     torch.cuda.synchronize()
     ms = e_begin.elapsed_time(e_end)
@@ -523,6 +545,7 @@ def rollout_job(m, rank, world, dev, *, prompts_all, stops_all, slots, max_new, 
            "steady_state": f"{W_STEPS}-step windows with slot occupancy >= 0.95 (max window time over ranks)",
            "prefill": "packed admission passes" if packed else (f"{lanes} prefill lanes" if lanes else "decode step"),
            "admission_passes": getattr(sch, "n_admit_passes", 0),
+           "steps_by_batch_rows_rank0": {str(k): v for k, v in sorted(sch.bucket_steps.items())},
            "weight_broadcast_ms": t_bcast * 1e3, "rollout_gather_ms": t_gather * 1e3,
            "device_status": eng.device_status(), "sched_status": c_prev["status"]}
     if gathered is not None:
@@ -557,7 +580,8 @@ def run_continuous(args, m, rank, world, dev):
     prompts, stops, max_prompt, max_new = config3_requests()
     r = rollout_job(m, rank, world, dev, prompts_all=prompts, stops_all=stops, slots=512, max_new=max_new,
                     max_prompt=max_prompt, lanes=args.lanes, lane_chunk=args.lane_chunk, seed=7, force_eos=True,
-                    timed_steps=args.steps, warmup=args.warmup, broadcast=True, packed=args.prefill == "packed")
+                    timed_steps=args.steps, warmup=args.warmup, broadcast=True, packed=args.prefill == "packed",
+                    compact=not args.no_compact, overlap=not args.no_overlap)
     if rank == 0:
         line = {"metric": "rollout decode tokens/s", "value": r["tokens_per_s"], "unit": "tokens/s",
                 "n_gpus": world, "steps": r["steps_all_ranks"] // world, "warmup": max(args.warmup, 3),
@@ -594,6 +618,10 @@ def main():
     ap.add_argument("--prefill", default="packed", choices=["packed", "lanes"],
                     help="rollout jobs: how prompts enter the cache (packed admission passes, or prefill lanes through "
                          "the decode step)")
+    ap.add_argument("--no-overlap", action="store_true",
+                    help="rollout jobs: harvest after every window of steps instead of while the next one runs")
+    ap.add_argument("--no-compact", action="store_true",
+                    help="rollout jobs: keep every slot in the step (no slot compaction / smaller step graphs)")
     ap.add_argument("--lanes", type=int, default=128,
                     help="continuous workload: extra batch rows that carry prompt tokens of refilling slots (0 = "
                          "one prompt token per slot per step)")
@@ -735,14 +763,15 @@ def main():
         prompts3, stops3, mp3, mn3 = config3_requests()
         cont = rollout_job(m, rank, world, dev, prompts_all=prompts3, stops_all=stops3, slots=512, max_new=mn3,
                            max_prompt=mp3, lanes=args.lanes, lane_chunk=args.lane_chunk, seed=7, force_eos=True,
-                           packed=args.prefill == "packed")
+                           packed=args.prefill == "packed", compact=not args.no_compact, overlap=not args.no_overlap)
         cont["workload"] = ("BASELINE configs[2]: 4096 requests sharded i % W, prompts U[16,256], stop ~ "
                             "Geometric(600) <= 2048 (EOS forced), 512 slots/GPU, T = 1.0; whole job until drained")
         torch.cuda.empty_cache()
         prompts5, mp5, mn5 = config5_requests()
         grpo = rollout_job(m, rank, world, dev, prompts_all=prompts5, stops_all=None, slots=512, max_new=mn5,
                            max_prompt=mp5, lanes=args.lanes, lane_chunk=args.lane_chunk, seed=11, force_eos=False,
-                           broadcast=True, gather=True, packed=args.prefill == "packed")
+                           broadcast=True, gather=True, packed=args.prefill == "packed",
+                           compact=not args.no_compact, overlap=not args.no_overlap)
         grpo["workload"] = ("BASELINE configs[4]: 256 prompts U[64,256] x group 8 = 2048 sequences sharded i % W, "
                             "max_new 2048, T = 1.0, top-p 1.0, Philox key per sequence; arena broadcast before the "
                             "round, rollouts (tokens, log-probs, versions) gathered to rank 0 after it")

@@ -400,7 +400,11 @@ typedef struct uv_sched_args {
   int64_t ring_len;
   /* 1: uv_sched_step only retires (freed slots are parked); queued requests enter through uv_sched_admit passes */
   int no_admit;
-  int reserved_;
+  /* 1 (needs no_admit = 1, lanes = 0, row_map (B,) initialised to the identity, B <= 4096): a step that retires
+   * something moves the live slots down to batch rows [0, active), keeping their order; row_map[b] stays the cache
+   * row of batch row b (a permutation of [0, B); uv_sched_admit hands it to the packed prefill), so the caller can
+   * run the decode step on the first n >= active rows only.  Request outputs do not depend on it. */
+  int compact;
 } uv_sched_args;
 
 int uv_sched_step(const uv_sched_args* args, void* stream);

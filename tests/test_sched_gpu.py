@@ -291,3 +291,58 @@ def test_admission_pass_kernel_matches_host_model(B, cap, busy):
             assert req[s_] == 10 ** 6 + s_
         else:
             assert req[s_] == -1
+
+
+@pytest.mark.parametrize("B,n", [(6, 40), (64, 300), (1500, 4000)])
+def test_compaction_keeps_live_slots_dense_and_changes_no_output(B, n):
+    """Slot compaction of the packed-admission mode, on the scheduler alone with the fake sampler: after every step
+    the live slots are batch rows [0, active) in their previous order, row_map stays a permutation of the cache rows
+    and a request keeps one cache row for its whole life; per-request outputs equal the run without compaction; the
+    host's bound on the live rows never undercounts."""
+    from ultraviolet_b200.scheduler import GpuScheduler
+    r = np.random.default_rng(B)
+    prompts = [r.integers(1, 900, r.integers(1, 12)).tolist() for _ in range(n)]
+    limits = r.integers(1, 14, n).tolist()
+
+    class _Eng(_FakeEngine):
+        def trunk(self, *a, **k):
+            return None
+
+    def drive(compact):
+        st, eng = _FakeState(B + 1, 32), _Eng(B)
+        sch = GpuScheduler(eng, st, max_new=14, temperature=1.0, eos_id=0, q_cap=max(4096, n), max_prompt=16,
+                           use_graph=False, packed_prefill=True, prefill_cap=4096, compact=compact)
+        assert sch.compact == compact
+        sch.enqueue(prompts[:n // 2], limits=limits[:n // 2])
+        sch.st.pos.zero_()
+        sch.admit(drain=True)
+        sch._primed = True
+        out, row_of, step = {}, {}, 0
+        while len(out) < n and step < 4000:
+            if step == 7:
+                sch.enqueue(prompts[n // 2:], limits=limits[n // 2:])
+            req, gen = sch.req.cpu().numpy(), sch.gen.cpu().numpy()
+            if compact:
+                live = req >= 0
+                k = int(live.sum())
+                assert live[:k].all() and not live[k:].any(), step
+                assert k <= sch.live_bound() <= B and sch.rows_needed() >= k
+                rm = sch.row_map.cpu().numpy()
+                assert sorted(rm.tolist()) == list(range(B))
+                for s_ in range(k):
+                    assert row_of.setdefault(int(req[s_]), int(rm[s_])) == int(rm[s_]), (step, s_)
+                assert (np.diff(req[:k]) > 0).all()     # admission order = queue order, and moves keep the order
+            eng._s["tok"].copy_(torch.from_numpy(_fake_token(req.astype(np.int64), gen.astype(np.int64), 7)
+                                                 .astype(np.int64)))
+            eng._s["logp"].copy_(torch.from_numpy((-(req + 1) - gen / 100).astype(np.float32)))
+            sch._sched_step()
+            step += 1
+            if step % 3 == 0:
+                for m, toks, lps, ver in sch.harvest():
+                    out[m] = (toks, lps.tolist())
+                sch.admit()
+        return out, step
+
+    (a, steps_a), (b, steps_b) = drive(False), drive(True)
+    assert len(a) == n and len(b) == n
+    assert a == b

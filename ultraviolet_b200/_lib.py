@@ -73,7 +73,7 @@ class SchedArgs(C.Structure):
         "fin_ring", "ctl")] + [("B", C.c_int), ("q_cap", C.c_int), ("tok_cap", C.c_int64), ("out_cap", C.c_int64),
                                ("eos", C.c_int), ("pad", C.c_int), ("force_eos", C.c_int), ("max_len", C.c_int64),
                                ("row_map", C.c_void_p), ("lanes", C.c_int), ("lane_chunk", C.c_int),
-                               ("ring_len", C.c_int64), ("no_admit", C.c_int), ("reserved_", C.c_int)]
+                               ("ring_len", C.c_int64), ("no_admit", C.c_int), ("compact", C.c_int)]
 
 
 class SchedAdmitArgs(C.Structure):

@@ -67,8 +67,15 @@ struct SchedParams {
   // 1: the step kernel only retires; freed slots are parked and queued requests wait for an admission pass
   // (sched_admit_kernel + packed prefill) that the host launches between steps
   int no_admit;
-  int reserved_;
+  // 1 (with no_admit): after a step that retired something, the live slots are moved down so that they occupy
+  // batch rows [0, active) in their old order.  A slot's cache row moves with it through row_map, which stays a
+  // permutation of [0, B) (the rows of retired slots go to the tail); outputs and Philox streams are addressed by
+  // request, not by slot, so nothing a request produces depends on the move.  The host can then run the decode
+  // step on the first n >= active batch rows only.
+  int compact;
 };
+
+constexpr int COMPACT_MAX_SLOTS = 4096;  // the new row_map is staged in shared memory
 
 // One admission pass: packed prefill inputs for the requests it admits.
 struct AdmitParams {
@@ -147,7 +154,8 @@ __global__ void __launch_bounds__(SCHED_THREADS) sched_step_kernel(const __grid_
   const int64_t head0 = P.ctl[CTL_HEAD], tail = P.ctl[CTL_TAIL];
   const int version = (int)P.ctl[CTL_VERSION];
   int64_t head = head0;
-  int64_t fin_base = P.ctl[CTL_FIN];
+  const int64_t fin0 = P.ctl[CTL_FIN];
+  int64_t fin_base = fin0;
   int active = 0, generated = 0;
   for (int base = 0; base < P.B; base += SCHED_THREADS) {  // uniform trip count: every thread joins every scan
     const int s = base + tid;
@@ -226,6 +234,39 @@ __global__ void __launch_bounds__(SCHED_THREADS) sched_step_kernel(const __grid_
     // slots of this chunk that hold a request after the step: the ones that kept theirs plus the admissions
     const int n_in = P.B - base < SCHED_THREADS ? P.B - base : SCHED_THREADS;
     active += n_in - total_free + admitted;
+  }
+  // ---- compaction (see SchedParams::compact): stable partition of the slots into live ones, then free ones
+  if (P.compact && fin_base != fin0) {  // uniform: every thread has the same totals
+    __shared__ int rm_new[COMPACT_MAX_SLOTS];
+    int live_before = 0;
+    for (int base = 0; base < P.B; base += SCHED_THREADS) {
+      const int s = base + tid;
+      const bool in = s < P.B;
+      const int r = in ? P.req[s] : -1;
+      const bool live = r >= 0;
+      int fed = 0, gen = 0, rm = 0;
+      int64_t ct = 0, po = 0, sta = 0, rk = 0, sc = 0;
+      if (in) rm = (int)P.row_map[s];
+      if (live) fed = P.fed[s], gen = P.gen[s], ct = P.cur_tok[s], po = P.pos[s], sta = P.starts[s],
+                rk = P.row_key[s], sc = P.step_ctr[s];
+      int total;
+      const int rank = block_excl_scan(live ? 1 : 0, warp_tot, tid, total);  // its barriers order reads before writes
+      if (in) {
+        // live slots only ever move down (dst <= s), onto slots of this or an earlier chunk, all read by now
+        const int dst = live ? live_before + rank : active + (s - live_before - rank);
+        rm_new[dst] = rm;
+        if (live && dst != s) {
+          P.req[dst] = r, P.fed[dst] = fed, P.gen[dst] = gen, P.cur_tok[dst] = ct, P.pos[dst] = po;
+          P.starts[dst] = sta, P.row_key[dst] = rk, P.step_ctr[dst] = sc;
+        }
+      }
+      live_before += total;
+    }
+    __syncthreads();
+    for (int s = tid; s < P.B; s += SCHED_THREADS) {
+      P.row_map[s] = rm_new[s];
+      if (s >= active) P.req[s] = -1, P.cur_tok[s] = P.pad, P.pos[s] = 0, P.starts[s] = 0;
+    }
   }
   // ---- prefill lanes (see SchedParams): hand out the lane rows in slot order by prefix sum
   if (P.lanes > 0) {
@@ -325,7 +366,7 @@ __global__ void __launch_bounds__(SCHED_THREADS) sched_admit_kernel(const __grid
       for (int j = 0; j < w; ++j) {
         A.tok[row0 + j] = P.tokens[(toff + j) % P.tok_cap];
         A.pos[row0 + j] = j;
-        A.row[row0 + j] = s;
+        A.row[row0 + j] = P.row_map ? P.row_map[s] : (int64_t)s;  // the slot's cache row
         A.last_pos[row0 + j] = w - 1;
       }
       P.req[s] = (int)r;
@@ -407,6 +448,7 @@ extern "C" int uv_sched_step(const uv_sched_args* a, void* stream) {
       !a->out_len || !a->start_version || !a->tokens || !a->out_tok || !a->out_lp || !a->fin_ring || !a->ctl)
     return UV_ERR_ARG;
   if (a->lanes < 0 || (a->lanes > 0 && (!a->row_map || a->lane_chunk < 2 || a->ring_len < 1))) return UV_ERR_ARG;
+  if (a->compact && (!a->row_map || a->lanes > 0 || !a->no_admit || a->B > COMPACT_MAX_SLOTS)) return UV_ERR_ARG;
   SchedParams P;
   static_assert(sizeof(SchedParams) == sizeof(uv_sched_args), "uv_sched_args mirrors SchedParams");
   memcpy(&P, a, sizeof(P));

@@ -28,7 +28,7 @@ class GpuScheduler:
                  pad_id: int = 0, seed: int = 0, q_cap: int = 8192, tok_cap: int | None = None,
                  out_cap: int | None = None, max_prompt: int = 256, force_eos: bool = False, use_graph: bool = True,
                  num_splits: dict | None = None, prefill_lanes: int = 0, lane_chunk: int = 8, top_k: int = 0,
-                 packed_prefill: bool = False, prefill_cap: int = 16384):
+                 packed_prefill: bool = False, prefill_cap: int = 16384, compact: bool = True):
         """prefill_lanes > 0: the decode step runs on slots + prefill_lanes batch rows; the extra rows carry further
         prompt tokens of slots that are still prefilling (up to lane_chunk tokens per slot per step).  The state must
         then hold one spare cache row: st.B == slots + 1 (see ``state_rows``).
@@ -38,7 +38,12 @@ class GpuScheduler:
         one packed batch, which goes through the prefill path (packed varlen attention over unquantised keys, int8
         cache written on the way) in a single pass of up to prefill_cap rows.  The host only chooses how many packed
         rows the pass gets, from the queue's prompt lengths and the head / finished counters it read at the last
-        harvest.  Needs the spare cache row too; excludes prefill_lanes."""
+        harvest.  Needs the spare cache row too; excludes prefill_lanes.
+
+        compact (packed_prefill only, up to 4096 slots): the step kernel keeps the live slots in batch rows
+        [0, active) (a slot's cache row follows it through ``row_map``), and ``run`` replays a step graph over the
+        smallest power-of-two fraction of the slots that still covers them -- when the queue has run dry, the tail
+        of a job steps 256, 128, ... rows instead of every slot."""
         self.eng, self.st = engine, st
         self.L = int(prefill_lanes)
         self.packed = bool(packed_prefill)
@@ -73,10 +78,18 @@ class GpuScheduler:
             self.pk_zero = i64(cap)
             self.pk_cu, self.pk_tile_cu = i32(B + 1), i32(B + 1)
             self._plen: dict[int, int] = {}          # request -> prompt length (host copy of the queue)
-            self._head_h = self._fin_h = 0           # head / finished counters as last read from the device
             self._ctl_fresh = True
             self._admit_graphs: dict[int, torch.cuda.CUDAGraph] = {}
             self.n_admit_passes = 0
+            self.row_map = torch.arange(B, dtype=torch.int64, device=dev)   # batch row -> cache row
+        self.compact = bool(compact) and self.packed and B <= 4096
+        # batch rows a step may run on: all slots, or (compact) a halving ladder down to 32 rows
+        self.buckets = sorted({B} | ({B >> k for k in range(1, 12) if (B >> k) >= 32} if self.compact else set()))
+        self._head_h = self._fin_h = 0   # head / finished counters as last read from the device
+        self._ctl_h = None               # the control words as last read (numpy)
+        self._graphs: dict[int, torch.cuda.CUDAGraph] = {}
+        self._side = None         # stream of window()'s overlapped harvest
+        self.bucket_steps: dict[int, int] = {}   # steps run per batch-row count
         self.prompt_off, self.key, self.out_off = i64(Q), i64(Q), i64(Q)
         self.prompt_len, self.limit, self.out_len, self.start_version = i32(Q), i32(Q), i32(Q, -1), i32(Q)
         self.fin_ring = i32(Q, -1)
@@ -107,6 +120,8 @@ class GpuScheduler:
         a.B, a.q_cap, a.tok_cap, a.out_cap = B, Q, self.tok_cap, self.out_cap
         a.eos, a.pad, a.force_eos, a.max_len = self.eos, self.pad, int(self.force_eos), st.max_len
         a.no_admit = int(self.packed)
+        if self.packed:
+            a.row_map, a.compact = self.row_map.data_ptr(), int(self.compact)
         # host mirrors
         self.n_enqueued = 0       # == ctl[TAIL]
         self.n_harvested = 0      # finished requests already returned
@@ -116,7 +131,6 @@ class GpuScheduler:
         self._span: dict[int, tuple[int, int]] = {}   # request -> (prompt offset, output offset)
         self._oldest = 0
         self.meta: dict[int, object] = {}
-        self.graph = None
         self.steps_run = 0
         self._primed = False
 
@@ -188,16 +202,19 @@ class GpuScheduler:
         with torch.cuda.device(self.dev):
             _lib.check(_lib.lib().uv_sched_step(C.byref(self.args), stream_ptr(self.dev)), "uv_sched_step")
 
-    def _step_body(self) -> None:
+    def _step_body(self, n: int | None = None) -> None:
+        """One decode step on the first n batch rows (default: every slot) + the scheduler kernel over all slots."""
         eng, st = self.eng, self.st
+        n = self.B if n is None else n
         if self.L > 0:
             h = eng.trunk(self.cur_tok, st, self.pos_all, self.starts_all, g_len=st.max_len,
                           num_splits=self.num_splits, row_map=self.row_map)[:self.B]  # only slots are sampled
         else:
-            h = eng.trunk(self.cur_tok, st, st.pos, st.starts, g_len=st.max_len, num_splits=self.num_splits)
+            h = eng.trunk(self.cur_tok[:n], st, st.pos[:n], st.starts[:n], g_len=st.max_len,
+                          num_splits=self.num_splits, row_map=self.row_map[:n] if self.packed else None)
         head = eng.head(h)
-        eng.sample(head, self.T, self.top_p, seed=self.seed, row_keys=self.row_key, steps=self.step_ctr,
-                   top_k=self.top_k)
+        eng.sample(head, self.T, self.top_p, seed=self.seed, row_keys=self.row_key[:n], steps=self.step_ctr[:n],
+                   tok_out=self.samp_tok[:n], logp_out=self.samp_lp[:n], top_k=self.top_k)
         self._sched_step()
 
     # ------------------------------------------------------------------------------------------------ admission
@@ -240,7 +257,7 @@ class GpuScheduler:
         self._ctl_fresh = False
 
     def _read_ctl(self) -> None:
-        c = self.ctl[:CTL_FIN + 1].cpu()
+        c = self._ctl_h = self.ctl.cpu().numpy()
         self._head_h, self._fin_h = int(c[CTL_HEAD]), int(c[CTL_FIN])
         self._ctl_fresh = True
 
@@ -281,36 +298,113 @@ class GpuScheduler:
             else:
                 self._sched_step()
             self._primed = True
-        if self.use_graph and self.graph is None:
-            # Warm up on a side stream, then capture.  The warm-up steps are real steps (state advances): nothing is
-            # rolled back, they simply count towards the run.
-            s = torch.cuda.Stream(self.dev)
-            s.wait_stream(torch.cuda.current_stream(self.dev))
-            with torch.cuda.stream(s):
-                self._step_body()
-                self.steps_run += 1
-            torch.cuda.current_stream(self.dev).wait_stream(s)
-            g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g, capture_error_mode="thread_local"):
-                self._step_body()
-            self.graph = g
+        if self.use_graph and not self._graphs:
+            self._step_graph(self.rows_needed())
+
+    def warm(self) -> None:
+        """Capture every graph a job can need -- the step over each batch-row bucket, the admission pass at each
+        packed-row capacity -- while no request is live, so that none of these one-time costs (buffer allocation,
+        library handles, capture, instantiation) lands between two steps of a running job.  The steps run here
+        touch parked slots only (cache position 0 of idle rows); the counters they advance are reset."""
+        if not self.use_graph:
+            return
+        if self.n_enqueued or self._primed:
+            raise RuntimeError("warm() must run before the first request is enqueued")
+        for n in self.buckets:
+            self._step_graph(n)
+        if self.packed:
+            cap = 256
+            while cap <= self.prefill_cap:
+                self._admit_pass(cap)
+                cap *= 2
+            self.n_admit_passes = 0
+        self.steps_run = 0
+        self.bucket_steps.clear()
+        for w in (CTL_STEPS, CTL_SLOT_STEPS, CTL_PREFILL_ROWS, CTL_ADMIT_PASSES, CTL_GENERATED, CTL_ACTIVE):
+            self.ctl[w] = 0
+        self.st.pos.zero_()
+        self._ctl_fresh = True
+        self.eng.check_status(None if self.packed else self.st_rows)
+
+    def _step_graph(self, n: int) -> int:
+        """Capture the step over n batch rows if it has not been yet; returns the steps that took (the warm-up on
+        a side stream is a real step: state advances, nothing is rolled back, it counts towards the run)."""
+        if n in self._graphs:
+            return 0
+        s = torch.cuda.Stream(self.dev)
+        s.wait_stream(torch.cuda.current_stream(self.dev))
+        with torch.cuda.stream(s):
+            self._step_body(n)
+        torch.cuda.current_stream(self.dev).wait_stream(s)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, capture_error_mode="thread_local"):
+            self._step_body(n)
+        self._graphs[n] = g
+        self.steps_run += 1
+        self.bucket_steps[n] = self.bucket_steps.get(n, 0) + 1
+        return 1
+
+    def rows_needed(self) -> int:
+        """Batch rows the next steps run on: the smallest bucket that covers every slot that can be live."""
+        if not self.compact:
+            return self.B
+        return next(b for b in self.buckets if b >= self.live_bound())
+
+    def live_bound(self) -> int:
+        """Upper bound of the live slots: requests enqueued minus requests known to have finished (the finished
+        count may be stale; it only grows).  Whatever an admission pass takes from the queue is covered."""
+        return min(self.B, self.n_enqueued - self._fin_h)
 
     def run(self, n_steps: int) -> None:
         self.prime()
         self.admit()   # packed prefill mode: refill the slots that the last harvest saw free
-        for _ in range(n_steps):
-            if self.graph is not None:
-                self.graph.replay()
-            else:
-                self._step_body()
+        n = self.rows_needed()
+        if self.use_graph:
+            n_steps -= min(n_steps, self._step_graph(n))
+            g = self._graphs[n]
+            for _ in range(n_steps):
+                g.replay()
+        else:
+            for _ in range(n_steps):
+                self._step_body(n)
         self.steps_run += n_steps
+        self.bucket_steps[n] = self.bucket_steps.get(n, 0) + n_steps
 
     # ------------------------------------------------------------------------------------------------ harvest
-    def counters(self) -> dict:
-        c = self.ctl.cpu().numpy()
+    def counters(self, cached: bool = False) -> dict:
+        """The control words; cached: as last read by a harvest / window call (no device access)."""
+        c = self._ctl_h if (cached and self._ctl_h is not None) else self.ctl.cpu().numpy()
         return dict(head=int(c[CTL_HEAD]), tail=int(c[CTL_TAIL]), finished=int(c[CTL_FIN]),
                     active=int(c[CTL_ACTIVE]), status=int(c[CTL_STATUS]), steps=int(c[CTL_STEPS]),
                     generated=int(c[CTL_GENERATED]), slot_steps=int(c[CTL_SLOT_STEPS]))
+
+    def window(self, n_steps: int, with_prompts: bool = False):
+        """``run(n_steps)`` and, overlapped with it, the harvest of everything that had finished when it was
+        launched: one small D2H of the counters (which waits for the steps launched earlier), then the next steps
+        and admission pass go to the device, and only then is the finished requests' payload gathered -- on a side
+        stream, while those steps run, so the device does not idle while the host collects rollouts.  Returns what
+        ``harvest_packed`` returns (requests that finish during the steps launched here come with the next call;
+        call ``harvest_packed`` after the last window)."""
+        self.prime()
+        if self.packed:
+            self._read_ctl()
+            fin = self._fin_h
+        else:
+            fin = int(self.ctl[CTL_FIN].item())
+        self.run(n_steps)
+        if fin == self.n_harvested:
+            return None
+        if self._side is None:
+            self._side = torch.cuda.Stream(self.dev, priority=-1)
+        main = torch.cuda.current_stream(self.dev)
+        with torch.cuda.stream(self._side):
+            # everything this reads was complete before the counters were read: no event to wait for
+            p = self._collect(fin, with_prompts)
+        for v in p.values():
+            if isinstance(v, torch.Tensor):
+                v.record_stream(main)
+        main.wait_stream(self._side)   # later work of the caller's stream (enqueue reuses ring space) comes after
+        return p
 
     def harvest_packed(self, with_prompts: bool = False):
         """Finished requests since the last call as DEVICE tensors (the packed hand-off a trainer consumes without a
@@ -327,6 +421,10 @@ class GpuScheduler:
             fin = int(self.ctl[CTL_FIN].item())
         if fin == self.n_harvested:
             return None
+        return self._collect(fin, with_prompts)
+
+    def _collect(self, fin: int, with_prompts: bool) -> dict:
+        """Payload of the requests [n_harvested, fin) of the finishing order, gathered on the current stream."""
         # rollouts from a step (or an admission pass) whose kernels flagged a failure are not handed out
         self.eng.check_status(None if self.packed else self.st_rows)
         k = torch.arange(self.n_harvested, fin, device=self.dev) % self.q_cap
