@@ -175,9 +175,9 @@ def test_grpo_group_of_identical_prompts_gets_distinct_streams():
     base = [r.integers(1, 500, r.integers(3, 9)).tolist() for _ in range(3)]
     reqs = [(p, (gi_, c)) for gi_, p in enumerate(base) for c in range(8)]      # 3 groups of 8
 
-    def rollouts(slots, lanes, packed):
+    def rollouts(slots, lanes, packed, overlap=False):
         gen = StreamGen(m, slots=slots, max_prompt=9, max_new=10, temperature=1.2, eos_id=0, check_every=4, seed=77,
-                        prefill_lanes=lanes, packed_prefill=packed)
+                        prefill_lanes=lanes, packed_prefill=packed, overlap_harvest=overlap, warm=overlap)
         assert gen.sched.packed == packed
         for p, meta in reqs:
             gen.add(p, meta)
@@ -193,9 +193,11 @@ def test_grpo_group_of_identical_prompts_gets_distinct_streams():
     for g_ in range(3):
         assert len({tuple(a[(g_, c)]) for c in range(8)}) >= 7     # identical prompts, different keys: different text
     b = rollouts(24, 0, True)
+    a2 = rollouts(4, 0, True, overlap=True)    # harvest overlapped with the next chunk's steps
+    assert sorted(a2) == sorted(a)
     c = rollouts(7, 4, False)      # prompts through the decode step, with lanes ...
     d = rollouts(5, 0, False)      # ... and one token per step
-    for x, y in ((a, b), (c, d), (a, d)):
+    for x, y in ((a, b), (a, a2), (c, d), (a, d)):
         same = np.mean([x[k] == y[k] for k in x])
         assert same >= 0.75, same    # equal unless a bf16 rounding (batch size, prefill route) flips a draw
 

@@ -3,9 +3,10 @@ the GPU-resident scheduler: slots are retired and refilled on the device after e
 loop every ``check_every`` steps.
 
 Differences a caller can observe, all within the reference's contract (rl_stream.py:1-12): a finished row is retired
-at the step it finishes (no tokens are decoded past EOS), a request is prefilled through the decode step starting at
-position 0 (no left padding), and the sampler draws by inverse CDF from Philox keyed by the request (a different
-random stream from Gumbel-max, as the reference's own fused sampler already is, fused_sample.py:13-15).
+at the step it finishes (no tokens are decoded past EOS), a request's cache starts at position 0 (no left padding;
+prompts enter through packed prefill passes at every chunk, or through the decode step), and the sampler draws by
+inverse CDF from Philox keyed by the request (a different random stream from Gumbel-max, as the reference's own fused
+sampler already is, fused_sample.py:13-15).
 """
 from __future__ import annotations
 
@@ -45,10 +46,14 @@ class StreamGen:
     def __init__(self, model, slots, max_prompt, max_new, temperature, eos_id, check_every=16, compile=True,
                  use_graph=True, pad_id=0, dtype=torch.float16, bucket=1024, top_p: float = 1.0,
                  seed: int | None = None, queue_capacity: int = 8192, prefill_lanes: int | None = None,
-                 packed_prefill: bool | None = None):
+                 packed_prefill: bool | None = None, overlap_harvest: bool = False, warm: bool = False):
         """seed: Philox key of this generator's draws (request n's stream is keyed by (seed, n)).  None (default)
         takes a fresh seed from torch's generator mixed with the distributed rank, as the reference's sampler draws
-        from torch's global generator; pass an int for reproducible rollouts."""
+        from torch's global generator; pass an int for reproducible rollouts.
+
+        overlap_harvest: chunk() launches its decode steps first and collects, while they run, what had finished
+        before them (GpuScheduler.window) -- a finished rollout is returned one chunk later and the device never
+        waits for the host.  warm: capture every step / admission graph now instead of at first use."""
         assert temperature > 0
         from .generate import fresh_seed
         seed = fresh_seed() if seed is None else int(seed)
@@ -72,6 +77,9 @@ class StreamGen:
         self.sched = GpuScheduler(eng, self.st, max_new=max_new, temperature=temperature, top_p=top_p, eos_id=eos_id,
                                   pad_id=pad_id, seed=seed, q_cap=queue_capacity, max_prompt=max_prompt,
                                   use_graph=use_graph, prefill_lanes=prefill_lanes, packed_prefill=packed_prefill)
+        self.overlap = bool(overlap_harvest)
+        if warm:
+            self.sched.warm()
         self.queue = collections.deque()   # host-side FIFO of (prompt_ids, meta) not yet on the device
         self._version = 0
         self.n_decode_steps = 0
@@ -101,7 +109,10 @@ class StreamGen:
     def _upload(self):
         """Move host-queued requests to the device queue (bounded so that at most 2 * slots wait on the device, which
         keeps drop_queued meaningful for everything behind them)."""
-        waiting = self.sched.n_enqueued - self.sched.n_harvested - self.sched.n_active()
+        # (overlapped harvest: the live count as of the last counter read, so that the steps in flight are not
+        # waited for)
+        active = self.sched.counters(cached=True)["active"] if self.overlap else self.sched.n_active()
+        waiting = self.sched.n_enqueued - self.sched.n_harvested - active
         room = max(0, 2 * self.B - max(waiting, 0))
         n = min(room, len(self.queue))
         if n:
@@ -114,9 +125,15 @@ class StreamGen:
         self._upload()
         if self.sched.n_enqueued == self.sched.n_harvested:
             return []
-        self.sched.run(self.ce)
-        self.n_decode_steps += self.ce
-        out = self.sched.harvest()
+        if self.overlap and self.sched._primed and self.sched.live_bound() == 0:
+            out = self.sched.harvest()         # every request is known to have finished: nothing left to step
+        elif self.overlap:
+            out = self.sched.unpack(self.sched.window(self.ce))
+            self.n_decode_steps += self.ce
+        else:
+            self.sched.run(self.ce)
+            self.n_decode_steps += self.ce
+            out = self.sched.harvest()
         self.n_tokens += sum(len(t) for _, t, _, _ in out)
         return out
 

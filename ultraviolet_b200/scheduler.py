@@ -459,7 +459,11 @@ class GpuScheduler:
     def harvest(self):
         """Return the requests that finished since the last call as [(meta, tokens list, logp float32 array,
         start_version)] in finishing order (one small D2H for the counters, one gather + D2H for the payload)."""
-        p = self.harvest_packed()
+        return self.unpack(self.harvest_packed())
+
+    @staticmethod
+    def unpack(p):
+        """Host view of a harvest_packed() / window() result: [(meta, tokens, logp, start_version)]."""
         if p is None:
             return []
         toks, lps = p["tokens"].cpu().numpy(), p["logp"].cpu().numpy()
