@@ -304,7 +304,11 @@ int uv_gemm_resid_norm(const void* a, int64_t lda, const void* w, int K, const v
  * no scaling.
  *   uv_gemm_sw         c (M, N) = [rms_norm](x) . w^T                                   (building block)
  *   uv_gemm_sw_qkv     the QKV projection + everything uv_qkv_post_args does (args->xn is ignored: the gates read
- *                      x scaled on the fly; args->rope_cs is required on RoPE layers)
+ *                      x scaled on the fly; args->rope_cs is required on RoPE layers).  ss_in = NULL here means
+ *                      "nobody left sums of squares behind": the kernel forms sum(x[b]^2) itself from the
+ *                      activation tiles it stages (all K blocks of a CTA must fit its stage ring, else
+ *                      UV_ERR_SHAPE) and the launch carries the programmatic-dependent-launch attribute so that
+ *                      its weight tiles are requested while the previous kernel drains (ss_parts = -1: without it)
  *   uv_gemm_sw_swiglu  act (M, f) = silu(g) * u, [g | u] = rms_norm(h) . w_gu^T, w_gu = [Wg ; Wu] (2f, K), f % 64 == 0
  *   uv_gemm_sw_resid   h = lambdas[0] * x + lambdas[1] * (a . w^T) (each product and the sum rounded, Block.finish)
  *                      and ss_out[tile][b] = sum over the tile's 128 features of h[b]^2 (N / 128 tiles)

@@ -262,7 +262,10 @@ def test_qkv_post_on_unnormalised_rows_equals_normalise_first(H, K):
     th = pos.float()[:, None] * inv_freq[None]
     rope_cs = torch.cat([th.cos().bfloat16().float(), th.sin().bfloat16().float()], 1).contiguous()
     res = {}
-    for raw in (0, 1):
+    # 0: normalise first; 1: raw rows + xn_raw; 2..: ONE launch of uv_gemm_sw_qkv on the raw rows with no sums of
+    # squares handed in (the kernel forms them from its own activation tiles), several tilings / cluster splits
+    sw_hints = {2: (0, 0), 3: (32, 1), 4: (32, 4), 5: (64, 2), 6: (128, 4)}
+    for raw in (0, 1, 2, 3, 4, 5, 6):
         kc = torch.zeros(B, K, S, hd, dtype=torch.int8, device=DEV)
         vc = torch.zeros_like(kc)
         ks = torch.zeros(B, K, S, dtype=torch.float16, device=DEV)
@@ -270,7 +273,7 @@ def test_qkv_post_on_unnormalised_rows_equals_normalise_first(H, K):
         oob = torch.zeros(1, dtype=torch.int32, device=DEV)
         gates = torch.zeros(B, H, device=DEV)
         src = y if raw else yn
-        qkv = torch.mm(src, w.t())
+        qkv = torch.mm(src, w.t()) if raw < 2 else torch.zeros(B, (H + 2 * K) * hd, dtype=torch.bfloat16, device=DEV)
         qa = L.QkvArgs()
         qa.qkv, qa.xn, qa.tok, qa.value_embed, qa.ve_gate = qkv.data_ptr(), src.data_ptr(), tok.data_ptr(), \
             ve.data_ptr(), ve_gate.data_ptr()
@@ -279,8 +282,16 @@ def test_qkv_post_on_unnormalised_rows_equals_normalise_first(H, K):
         qa.oob_count, qa.dtype, qa.vocab = oob.data_ptr(), 2, vocab
         qa.B, qa.H, qa.K, qa.hd, qa.d, qa.S, qa.S_alloc, qa.ring, qa.ve_ch, qa.n_pairs = B, H, K, hd, d, S, S, 1, \
             ve_ch, n_pairs
-        qa.gate_w, qa.gate_out, qa.gate_ch, qa.xn_raw = gate_w.data_ptr(), gates.data_ptr(), gate_ch, raw
-        L.check(lib.uv_qkv_post_args(C.byref(qa), _sp()), "uv_qkv_post_args")
+        qa.gate_w, qa.gate_out, qa.gate_ch, qa.xn_raw = gate_w.data_ptr(), gates.data_ptr(), gate_ch, min(raw, 1)
+        if raw < 2:
+            L.check(lib.uv_qkv_post_args(C.byref(qa), _sp()), "uv_qkv_post_args")
+        else:
+            status = torch.zeros(1, dtype=torch.int32, device=DEV)
+            bn, ks_ = sw_hints[raw]
+            L.check(lib.uv_gemm_sw_qkv(y.data_ptr(), d, w.data_ptr(), C.byref(qa), None, -1 if raw == 3 else 0, 0, bn,
+                                       ks_, status.data_ptr(), _sp()), "uv_gemm_sw_qkv")
+            torch.cuda.synchronize()
+            assert int(status.item()) == 0
         torch.cuda.synchronize()
         assert int(oob.item()) == 0
         res[raw] = (qkv.float(), kc, vc, ks.float(), vs.float(), gates)
@@ -291,3 +302,11 @@ def test_qkv_post_on_unnormalised_rows_equals_normalise_first(H, K):
         assert int(dq.max()) <= 2 and (dq > 0).float().mean().item() < 0.05 and (dq > 1).float().mean().item() < 1e-3
     torch.testing.assert_close(a[5], b[5], rtol=2e-2, atol=2e-2)
     assert b[1].any() and b[5].abs().sum() > 0
+    for v in sw_hints:
+        c = res[v]
+        assert (c[0] - b[0]).abs().max().item() <= b[0].abs().max().item() * 2.0 ** -6, v
+        for i in (1, 2):
+            dq = (c[i].int() - b[i].int()).abs()
+            assert int(dq.max()) <= 3 and (dq > 0).float().mean().item() < 0.05 and \
+                (dq > 1).float().mean().item() < 1e-3, (v, i)
+        torch.testing.assert_close(c[5], b[5], rtol=2e-2, atol=2e-2)

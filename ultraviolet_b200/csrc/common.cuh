@@ -43,14 +43,15 @@ inline void launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t sme
 }
 
 // launch_pdl plus a thread-block cluster shape (cluster.x * y * z == 1: no cluster attribute)
+// (pdl: -1 = the process-wide setting, 0 / 1 = this launch without / with the attribute)
 template <typename... KArgs, typename... Args>
-inline void launch_cluster(void (*kern)(KArgs...), dim3 grid, dim3 block, dim3 cluster, size_t smem, cudaStream_t st,
-                           Args... args) {
+inline void launch_cluster_pdl(int pdl, void (*kern)(KArgs...), dim3 grid, dim3 block, dim3 cluster, size_t smem,
+                               cudaStream_t st, Args... args) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid, cfg.blockDim = block, cfg.dynamicSmemBytes = smem, cfg.stream = st;
   cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
+  attr[0].val.programmaticStreamSerializationAllowed = (pdl < 0 ? pdl_enabled() : pdl != 0) ? 1 : 0;
   int n = 1;
   if (cluster.x * cluster.y * cluster.z > 1) {
     attr[1].id = cudaLaunchAttributeClusterDimension;
@@ -59,6 +60,12 @@ inline void launch_cluster(void (*kern)(KArgs...), dim3 grid, dim3 block, dim3 c
   }
   cfg.attrs = attr, cfg.numAttrs = n;
   cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
+
+template <typename... KArgs, typename... Args>
+inline void launch_cluster(void (*kern)(KArgs...), dim3 grid, dim3 block, dim3 cluster, size_t smem, cudaStream_t st,
+                           Args... args) {
+  launch_cluster_pdl(-1, kern, grid, block, cluster, smem, st, args...);
 }
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }

@@ -46,6 +46,11 @@ struct GemmSwParams {
   // deferred norm of the INPUT activation: rs[b] = rsqrt(sum_j ss_in[j * ss_in_ld + b] / ss_in_dim + eps)
   const float* ss_in;
   int ss_in_parts, ss_in_ld, ss_in_dim;
+  // 1: no producer left sums of squares behind -- the CTA forms sum(x[b]^2) over its K range from the activation
+  // tiles it holds in shared memory anyway (every K block of the CTA must stay resident: stages >= its K blocks)
+  // and the ranks of a split-K cluster add their parts up through distributed shared memory
+  int ss_self;
+  int pdl;                 // host side only: -1 process default, 0 / 1 launch without / with the PDL attribute
   // STORE / SWIGLU / RESID output (M, ldo)
   void* out;
   int64_t ldo;
@@ -62,6 +67,20 @@ struct GemmSwParams {
 __device__ __forceinline__ void sw_cluster_sync() {
   asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
+__device__ __forceinline__ float sw_ld_peer_f1(uint32_t local_addr, uint32_t rank) {
+  uint32_t remote;
+  float v;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+  return v;
+}
+__device__ __forceinline__ float2 sw_ld_peer_f2(uint32_t local_addr, uint32_t rank) {
+  uint32_t remote;
+  float2 v;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
+  asm volatile("ld.shared::cluster.v2.f32 {%0, %1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(remote) : "memory");
+  return v;
+}
 __device__ __forceinline__ float4 sw_ld_peer_f4(uint32_t local_addr, uint32_t rank) {
   uint32_t remote;
   float4 v;
@@ -72,10 +91,14 @@ __device__ __forceinline__ float4 sw_ld_peer_f4(uint32_t local_addr, uint32_t ra
 }
 
 // grid (N / 128 [SWIGLU: f / 64], ceil(M / BN), ksplit); cluster (1, 1, ksplit)
-template <int BN, int EPI>
-__global__ void __launch_bounds__(SW_THREADS) gemm_sw_kernel(const __grid_constant__ CUtensorMap tm_w,
-                                                             const __grid_constant__ CUtensorMap tm_x,
-                                                             const GemmSwParams P) {
+// NT threads: warps 0..3 run the main loop (copy thread, MMA thread, row factors) and read the accumulator out of
+// TMEM; warps 4.. (QKV epilogue only) do nothing until the accumulator is parked in shared memory and then take
+// their share of the epilogue's (row, head slot) items, each of which is a ~1 us chain of dependent shuffles and
+// loads that only parallelism across warps hides.
+template <int BN, int EPI, int NT>
+__global__ void __launch_bounds__(NT) gemm_sw_kernel(const __grid_constant__ CUtensorMap tm_w,
+                                                     const __grid_constant__ CUtensorMap tm_x,
+                                                     const GemmSwParams P) {
   using T = __nv_bfloat16;
   constexpr int W_BYTES = 128 * TC_BK * 2;   // 16 KB of weights per K block
   constexpr int X_BYTES = BN * TC_BK * 2;
@@ -85,6 +108,7 @@ __global__ void __launch_bounds__(SW_THREADS) gemm_sw_kernel(const __grid_consta
   __shared__ __align__(8) uint64_t full_bar[SW_MAX_STAGES], empty_bar[SW_MAX_STAGES], accum_bar;
   __shared__ uint32_t tmem_slot;
   __shared__ float rs_sm[BN];
+  __shared__ float ssp_sm[BN];   // ss_self: this CTA's share of sum(x[b]^2)
   __shared__ int dead_sm;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int ft = blockIdx.x, b0 = blockIdx.y * BN, kr = blockIdx.z;
@@ -170,8 +194,48 @@ __global__ void __launch_bounds__(SW_THREADS) gemm_sw_kernel(const __grid_consta
       tc_commit(tc_smem_u32(&empty_bar[s]));
     }
     if (ok && nk > 0) tc_commit(tc_smem_u32(&accum_bar));
-  } else if (warp >= 2) {
-    // ---- the other warps: rs[b] of this CTA's batch rows from the producer's per-tile sums of squares
+  } else if (warp == 2 || warp == 3) {
+    // ---- the other two main-loop warps: rs[b] of this CTA's batch rows from the producer's per-tile sums of squares, or
+    //      (ss_self) the sums of squares themselves, read off the activation tiles as they land: a batch row of a K
+    //      block is one 128-byte row of the tile (the swizzle permutes 16-byte pieces inside it, which a sum ignores)
+    if (P.ss_self) {
+      // 8 lanes share a row (one 16-byte piece each: a warp reads 4 whole rows = 512 contiguous bytes per load)
+      constexpr int PASSES = (BN + 7) / 8;   // 64 threads cover 8 rows per pass
+      float part[PASSES];
+#pragma unroll
+      for (int i = 0; i < PASSES; ++i) part[i] = 0.f;
+      const int t64 = tid - 64;
+      for (int kb = 0; kb < nk && ok; ++kb) {
+        const int s = kb % NS;
+        if (!tc_mbar_wait(tc_smem_u32(&full_bar[s]), (uint32_t)((kb / NS) & 1))) {
+          ok = false;
+          break;
+        }
+        const unsigned char* xt = sw_smem + (base - tc_smem_u32(sw_smem)) + (size_t)s * STAGE + W_BYTES;
+#pragma unroll
+        for (int i = 0; i < PASSES; ++i) {
+          const int j = i * 8 + (t64 >> 3);
+          if (j < BN) {
+            const uint4 u = *reinterpret_cast<const uint4*>(xt + (size_t)j * 128 + (t64 & 7) * 16);
+            const uint32_t w4[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w4[e]));
+              part[i] += f.x * f.x + f.y * f.y;
+            }
+          }
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < PASSES; ++i) {
+        float v = part[i];
+        v += __shfl_xor_sync(0xffffffffu, v, 1);
+        v += __shfl_xor_sync(0xffffffffu, v, 2);
+        v += __shfl_xor_sync(0xffffffffu, v, 4);
+        const int j = i * 8 + (t64 >> 3);
+        if ((t64 & 7) == 0 && j < BN) ssp_sm[j] = v;
+      }
+    }
     for (int j = tid - 64; j < BN; j += 64) {
       float r = 1.0f;
       if (P.ss_in != nullptr && b0 + j < P.M) {
@@ -183,7 +247,43 @@ __global__ void __launch_bounds__(SW_THREADS) gemm_sw_kernel(const __grid_consta
     }
   }
   __syncwarp();
-  if (nk > 0) ok = tc_mbar_wait(tc_smem_u32(&accum_bar), 0) && ok;
+  const int rows_per = BN / P.ksplit;
+  if constexpr (EPI == SW_EPI_QKV) {
+    // While the accumulator is still being formed: pull what this warp's epilogue rows will read (positions, cache
+    // rows, the rotation table row, the gate inputs and weights, the value-embedding row) towards the SM, so that the
+    // epilogue's dependent loads find them close by instead of paying an L2 round trip each, item after item.
+    const QkvPostParams& Q = P.post;
+    auto pf = [](const void* p) { asm volatile("prefetch.global.L1 [%0];" ::"l"(p)); };
+    const int slots = Q.H + 2 * Q.K;
+    for (int it = warp; it < 2 * rows_per; it += NT / 32) {
+      const int b = b0 + kr * rows_per + (it >> 1);
+      if (b >= P.M) continue;
+      if (lane == 0) pf(Q.pos + b);
+      if (lane == 1 && Q.row_map) pf(Q.row_map + b);
+      if (lane == 2 && Q.last_pos) pf(Q.last_pos + b);
+      if (lane == 3 && Q.rope_cs) pf(Q.rope_cs + (int64_t)b * 2 * Q.n_pairs);
+      if (lane >= 4 && lane < 8 && Q.xn) {  // the first channels of the row: head gates and the value-embedding gate
+        const int off = (lane - 4) * 64;
+        if (off < Q.d) pf(static_cast<const T*>(Q.xn) + (int64_t)b * Q.d + off);
+      }
+      if (lane >= 8 && lane < 10) {         // gate weights of the item's head slot
+        const int hs = 2 * ft + (it & 1), off = (lane - 8) * 64;
+        if (hs < Q.H && Q.gate_out != nullptr && off < Q.gate_ch)
+          pf(static_cast<const T*>(Q.gate_w) + (int64_t)hs * Q.gate_ch + off);
+      }
+      if (lane == 12 && Q.ve_gate != nullptr) {
+        const int hs = 2 * ft + (it & 1);
+        if (hs >= Q.H + Q.K && hs < slots) {
+          const int kh = hs - Q.H - Q.K;
+          pf(static_cast<const T*>(Q.ve_gate) + (int64_t)kh * Q.ve_ch);
+          int64_t t = Q.tok[b];
+          if (t < 0 || t >= Q.vocab) t = 0;
+          pf(static_cast<const T*>(Q.value_embed) + (t * Q.K + kh) * 64);
+        }
+      }
+    }
+  }
+  if (nk > 0 && warp < 4) ok = tc_mbar_wait(tc_smem_u32(&accum_bar), 0) && ok;  // warps 4.. sleep at the barrier below
   if (!ok) dead_sm = 1;
   tc_fence_after();
   __syncthreads();
@@ -192,10 +292,9 @@ __global__ void __launch_bounds__(SW_THREADS) gemm_sw_kernel(const __grid_consta
 
   // ---- stage 1: thread = feature (TMEM lane) parks its BN columns, transposed, as T32[b][feature] behind the
   //      stage ring
-  const int rows_per = BN / P.ksplit;
   float* T32 = reinterpret_cast<float*>(sw_smem + (base - tc_smem_u32(sw_smem)) + (size_t)NS * STAGE);
   const uint32_t t32_addr = tc_smem_u32(T32);
-  if (!dead) {
+  if (!dead && warp < 4) {
     const uint32_t taddr = tmem + ((uint32_t)(warp * 32) << 16);
 #pragma unroll
     for (int c0 = 0; c0 < BN; c0 += 32) {
@@ -218,8 +317,60 @@ __global__ void __launch_bounds__(SW_THREADS) gemm_sw_kernel(const __grid_consta
 
   // ---- stage 2: rank kr finishes batch rows [kr * rows_per, (kr + 1) * rows_per) of the tile; a warp owns a row,
   //      a lane 4 consecutive features
-  if (!dead)
-    for (int rr = warp; rr < rows_per; rr += SW_THREADS / 32) {
+  auto row_factor = [&](int bl) {
+    float rs = rs_sm[bl];
+    if (P.ss_self) {
+      float ss = 0.f;
+      if (P.ksplit > 1) {
+        const uint32_t a = tc_smem_u32(&ssp_sm[bl]);
+#pragma unroll
+        for (int p = 0; p < 8; ++p)
+          if (p < P.ksplit) ss += sw_ld_peer_f1(a, (uint32_t)p);
+      } else {
+        ss = ssp_sm[bl];
+      }
+      rs = rsqrtf(ss / (float)P.K + RMS_EPS);
+    }
+    return rs;
+  };
+  if constexpr (EPI == SW_EPI_QKV) {
+    // an item = one 64-wide head slot of one batch row (two slots per 128-feature tile); lane l holds features
+    // 2l, 2l + 1 of the slot, as the row kernels do
+    const QkvPostParams& Q = P.post;
+    const int slots = Q.H + 2 * Q.K;
+    if (!dead)
+      for (int it = warp; it < 2 * rows_per; it += NT / 32) {
+        const int bl = kr * rows_per + (it >> 1), b = b0 + bl, hs = 2 * ft + (it & 1);
+        if (b >= P.M || hs >= slots) continue;  // warp-uniform
+        float2 acc;
+        if (P.ksplit > 1) {
+          float2 q[8];
+          const uint32_t a = t32_addr + (uint32_t)(bl * SW_PITCH + (it & 1) * 64 + 2 * lane) * 4u;
+#pragma unroll
+          for (int p = 0; p < 8; ++p)
+            if (p < P.ksplit) q[p] = sw_ld_peer_f2(a, (uint32_t)p);
+          acc = q[0];
+#pragma unroll
+          for (int p = 1; p < 8; ++p)
+            if (p < P.ksplit) acc.x += q[p].x, acc.y += q[p].y;
+        } else {
+          acc = *reinterpret_cast<const float2*>(T32 + bl * SW_PITCH + (it & 1) * 64 + 2 * lane);
+        }
+        const float rs = row_factor(bl);
+        float x[2] = {rnd<T>(acc.x * rs), rnd<T>(acc.y * rs)};  // the projection as the reference holds it (rounded)
+        qkv_post_compute<T, 64, true>(Q, b, hs, lane, x, rs, true);
+        T* vec = static_cast<T*>(Q.qkv) + ((int64_t)b * slots + hs) * 64;
+        *reinterpret_cast<__nv_bfloat162*>(vec + 2 * lane) = __floats2bfloat162_rn(x[0], x[1]);
+        if (hs >= Q.H && Q.k_cache != nullptr) qkv_post_append<T, 64>(Q, b, hs, lane, x);
+        if (hs < Q.H && Q.gate_out != nullptr) {
+          const float gt = head_gate<T>(static_cast<const T*>(Q.xn) + (int64_t)b * Q.d,
+                                        static_cast<const T*>(Q.gate_w) + (int64_t)hs * Q.gate_ch, Q.gate_ch, lane,
+                                        rs, true);
+          if (lane == 0) Q.gate_out[(int64_t)b * Q.H + hs] = gt;
+        }
+      }
+  } else if (!dead)
+    for (int rr = warp; rr < rows_per; rr += NT / 32) {
       const int bl = kr * rows_per + rr, b = b0 + bl;
       if (b >= P.M) continue;  // warp-uniform
       float4 acc;
@@ -236,7 +387,7 @@ __global__ void __launch_bounds__(SW_THREADS) gemm_sw_kernel(const __grid_consta
       } else {
         acc = *reinterpret_cast<const float4*>(T32 + bl * SW_PITCH + 4 * lane);
       }
-      const float rs = rs_sm[bl];
+      const float rs = row_factor(bl);
       // the GEMM result as the reference holds it: rounded to the activation dtype
       float c[4] = {rnd<T>(acc.x * rs), rnd<T>(acc.y * rs), rnd<T>(acc.z * rs), rnd<T>(acc.w * rs)};
       if constexpr (EPI == SW_EPI_STORE) {
@@ -279,34 +430,6 @@ __global__ void __launch_bounds__(SW_THREADS) gemm_sw_kernel(const __grid_consta
           *reinterpret_cast<uint2*>(o) =
               make_uint2(*reinterpret_cast<const uint32_t*>(&h0), *reinterpret_cast<const uint32_t*>(&h1));
         }
-      } else {  // SW_EPI_QKV: lanes 0..15 hold head slot 2*ft, lanes 16..31 slot 2*ft + 1 (4 features per lane)
-        // regroup to the row kernels' layout -- a full warp per 64-wide slot, 2 features per lane -- one slot at
-        // a time: lane l of slot s takes features 2l, 2l + 1 = element (2l % 4) .. of source lane 16 s + l / 2
-        const QkvPostParams& Q = P.post;
-        const int slots = Q.H + 2 * Q.K;
-#pragma unroll
-        for (int sl = 0; sl < 2; ++sl) {
-          const int hs = 2 * ft + sl;
-          const int src = 16 * sl + (lane >> 1);
-          float x[2];
-          {
-            const float c0 = __shfl_sync(0xffffffffu, c[0], src), c1 = __shfl_sync(0xffffffffu, c[1], src);
-            const float c2 = __shfl_sync(0xffffffffu, c[2], src), c3 = __shfl_sync(0xffffffffu, c[3], src);
-            x[0] = (lane & 1) ? c2 : c0;
-            x[1] = (lane & 1) ? c3 : c1;
-          }
-          if (hs >= slots) continue;
-          qkv_post_compute<T, 64, true>(Q, b, hs, lane, x, rs, true);
-          T* vec = static_cast<T*>(Q.qkv) + ((int64_t)b * slots + hs) * 64;
-          *reinterpret_cast<__nv_bfloat162*>(vec + 2 * lane) = __floats2bfloat162_rn(x[0], x[1]);
-          if (hs >= Q.H && Q.k_cache != nullptr) qkv_post_append<T, 64>(Q, b, hs, lane, x);
-          if (hs < Q.H && Q.gate_out != nullptr) {
-            const float gt = head_gate<T>(static_cast<const T*>(Q.xn) + (int64_t)b * Q.d,
-                                          static_cast<const T*>(Q.gate_w) + (int64_t)hs * Q.gate_ch, Q.gate_ch, lane,
-                                          rs, true);
-            if (lane == 0) Q.gate_out[(int64_t)b * Q.H + hs] = gt;
-          }
-        }
       }
     }
   if (P.ksplit > 1) sw_cluster_sync();  // peers may still be reading this CTA's partial
@@ -314,7 +437,9 @@ __global__ void __launch_bounds__(SW_THREADS) gemm_sw_kernel(const __grid_consta
 
 template <int BN, int EPI>
 static int launch_sw(const CUtensorMap& tw, const CUtensorMap& tx, const GemmSwParams& P, dim3 grid, cudaStream_t st) {
-  auto kern = gemm_sw_kernel<BN, EPI>;
+  // QKV epilogue: one warp per (row, slot) item of the CTA where the register file allows (2 * BN / ksplit items)
+  constexpr int NT = EPI == SW_EPI_QKV ? 512 : SW_THREADS;
+  auto kern = gemm_sw_kernel<BN, EPI, NT>;
   const size_t ring = (size_t)P.stages * (128 * TC_BK * 2 + BN * TC_BK * 2);
   const size_t t32 = (size_t)BN * SW_PITCH * sizeof(float);
   const size_t smem = ring + t32 + 1024;
@@ -323,7 +448,7 @@ static int launch_sw(const CUtensorMap& tw, const CUtensorMap& tx, const GemmSwP
     set_last_cuda_error((int)e);
     return UV_ERR_CUDA;
   }
-  launch_cluster(kern, grid, dim3(SW_THREADS), dim3(1, 1, (unsigned)P.ksplit), smem, st, tw, tx, P);
+  launch_cluster_pdl(P.pdl, kern, grid, dim3(NT), dim3(1, 1, (unsigned)P.ksplit), smem, st, tw, tx, P);
   return check_launch();
 }
 
@@ -383,6 +508,7 @@ extern "C" int uv_gemm_sw(const void* x, int64_t ldx, const void* w, void* c, in
   CUtensorMap tw, tx;
   if (!make_map(&tw, w, N, K, K, 128) || !make_map(&tx, x, M, K, ldx, bn)) return UV_ERR_CUDA;
   GemmSwParams P{};
+  P.pdl = -1;
   P.M = M, P.N = N, P.K = K, P.stages = stages, P.ksplit = ks, P.status = status, P.out = c, P.ldo = ldc;
   sw_norm_in(P, ss_in, ss_parts, ss_ld, K);
   const dim3 grid((unsigned)(N / 128), (unsigned)((M + bn - 1) / bn), (unsigned)ks);
@@ -403,6 +529,7 @@ extern "C" int uv_gemm_sw_resid(const void* a, int64_t lda, const void* w, const
   CUtensorMap tw, tx;
   if (!make_map(&tw, w, N, K, K, 128) || !make_map(&tx, a, M, K, lda, bn)) return UV_ERR_CUDA;
   GemmSwParams P{};
+  P.pdl = -1;
   P.M = M, P.N = N, P.K = K, P.stages = stages, P.ksplit = ks, P.status = status, P.out = h, P.ldo = ldh;
   P.resid = x, P.lambdas = lambdas, P.ss_out = ss_out, P.ss_out_ld = ss_out_ld;
   const dim3 grid((unsigned)(N / 128), (unsigned)((M + bn - 1) / bn), (unsigned)ks);
@@ -423,6 +550,7 @@ extern "C" int uv_gemm_sw_swiglu(const void* h, int64_t ldh, const void* w_gu, v
   CUtensorMap tw, tx;
   if (!make_map(&tw, w_gu, 2 * (int64_t)f, K, K, 64) || !make_map(&tx, h, M, K, ldh, bn)) return UV_ERR_CUDA;
   GemmSwParams P{};
+  P.pdl = -1;
   P.M = M, P.N = 2 * f, P.K = K, P.stages = stages, P.ksplit = 1, P.status = status, P.out = act, P.ldo = f, P.f = f;
   sw_norm_in(P, ss_in, ss_parts, ss_ld, K);
   const dim3 grid((unsigned)(f / 64), (unsigned)((M + bn - 1) / bn), 1u);
@@ -441,8 +569,9 @@ extern "C" int uv_gemm_sw_qkv(const void* x, int64_t ldx, const void* wqkv, cons
   if ((slots & 1) != 0) return UV_ERR_SHAPE;     // (the weight rows of such a tile would not exist)
   int rc = sw_checks(x, ldx, wqkv, M, N, K);
   if (rc != UV_OK) return rc;
-  if (!ss_in || (qa->inv_freq && !qa->rope_cs)) return UV_ERR_ARG;  // RoPE layers need the step's table
+  if (qa->inv_freq && !qa->rope_cs) return UV_ERR_ARG;  // RoPE layers need the step's table
   GemmSwParams P{};
+  P.pdl = -1;
   rc = qkv_post_params(&P.post, qa->qkv, x, qa->tok, qa->value_embed, qa->ve_gate, qa->inv_freq, qa->pos, qa->k_cache,
                        qa->v_cache, qa->k_scale, qa->v_scale, qa->row_map, qa->oob_count, qa->vocab, qa->B, qa->H,
                        qa->K, qa->hd, qa->d, qa->S, qa->S_alloc, qa->ring, qa->ve_ch, qa->n_pairs);
@@ -459,6 +588,18 @@ extern "C" int uv_gemm_sw_qkv(const void* x, int64_t ldx, const void* wqkv, cons
   if (!make_map(&tw, wqkv, N, K, K, 128) || !make_map(&tx, x, M, K, ldx, bn)) return UV_ERR_CUDA;
   P.M = M, P.N = N, P.K = K, P.stages = stages, P.ksplit = ks, P.status = status;
   sw_norm_in(P, ss_in, ss_parts, ss_ld, K);
+  if (!ss_in) {
+    // no producer of sums of squares (the residual stream was updated by a library GEMM): the kernel forms them
+    // from its own activation tiles, which must all stay resident; its weight tiles are worth requesting while the
+    // predecessor drains, so this launch carries the PDL attribute whatever the process default is
+    while (stages < (K / TC_BK + ks - 1) / ks && ks < 8 && ks_hint <= 0) {  // cut K further until a CTA's share fits
+      sw_plan(M, N / 128, K, bn, ks * 2, &bn, &ks, &stages);
+      P.stages = stages, P.ksplit = ks;
+    }
+    if (stages < (K / TC_BK + ks - 1) / ks) return UV_ERR_SHAPE;
+    P.ss_self = 1, P.ss_in_dim = K;
+    P.pdl = ss_parts < 0 ? 0 : 1;   // ss_parts = -1 with a null ss_in: launch without the attribute (A/B switch)
+  }
   const dim3 grid((unsigned)(N / 128), (unsigned)((M + bn - 1) / bn), (unsigned)ks);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   UV_SW_DISPATCH(SW_EPI_QKV, grid);

@@ -107,6 +107,12 @@ class DecodeEngine:
         # reference's literal op order (separate uv_resid_norm launches).
         self.fold = (os.environ.get("UVDECODE_FOLD", "1") != "0" and not self.fused_gemm and not self.tc_gemm
                      and not self.qkv_in_attn and d % 8 == 0)
+        # Folded step only: the QKV projection and everything uv_qkv_post does in ONE launch of this library's tcgen05
+        # kernel (uv_gemm_sw_qkv with self-computed row sums of squares) instead of library GEMM + uv_qkv_post_args.
+        # "1": with the PDL attribute on that launch, "nopdl": without, "0": off.
+        self.sw_qkv = os.environ.get("UVDECODE_SW_QKV", "0")
+        if not (self.fold and self.tc_gemm_ok and d // 64 <= 12):
+            self.sw_qkv = "0"
         self.n_sm = torch.cuda.get_device_properties(self.device).multi_processor_count
         _lib.lib()
 
@@ -227,7 +233,7 @@ class DecodeEngine:
         if self.fused_gemm:
             return 1 + 5 * n + 1
         if self.fold:
-            return 1 + 7 * n + 2
+            return 1 + (6 if self.sw_qkv != "0" else 7) * n + 2
         return 1 + (8 if self.qkv_in_attn else 9) * n + 1
 
     def _workspace(self, s: dict, B: int, splits: int) -> Tensor | None:
@@ -296,7 +302,10 @@ class DecodeEngine:
                                                *post_args), "uv_gemm_qkv")
                 else:
                     gin = x if fold else xn   # folded: the GEMM reads the un-normalised stream, uv_qkv_post norms
-                    torch.mm(gin, w[f"l{l}.wqkv"].t(), out=s["qkv"])
+                    sw_qkv = (fold and self.sw_qkv != "0" and packed is None and not qkv_in_attn and B <= 1024
+                              and (use_table or not (rope and cfg.rope_pairs)))
+                    if not sw_qkv:
+                        torch.mm(gin, w[f"l{l}.wqkv"].t(), out=s["qkv"])
                     qa = _lib.QkvArgs()
                     (qa.qkv, qa.xn, qa.tok, qa.value_embed, qa.ve_gate, qa.inv_freq, qa.pos, qa.k_cache,
                      qa.v_cache, qa.k_scale, qa.v_scale, qa.row_map, qa.oob_count, qa.dtype, qa.vocab,
@@ -313,7 +322,13 @@ class DecodeEngine:
                             qa.gate_w = w[f"l{l}.attn_gate"].data_ptr()  # computed off the attention kernel's tail
                             qa.gate_out, qa.gate_ch = s["gate"].data_ptr(), cfg.gate_channels
                             gate_vals = s["gate"]
-                        _lib.check(lib.uv_qkv_post_args(C.byref(qa), sp), "uv_qkv_post")
+                        if sw_qkv:
+                            _lib.check(lib.uv_gemm_sw_qkv(gin.data_ptr(), d, w[f"l{l}.wqkv"].data_ptr(), C.byref(qa),
+                                                          None, -1 if self.sw_qkv == "nopdl" else 0, 0,
+                                                          self.tc_hints["qkv"][0], self.tc_hints["qkv"][1],
+                                                          s["status"].data_ptr(), sp), "uv_gemm_sw_qkv")
+                        else:
+                            _lib.check(lib.uv_qkv_post_args(C.byref(qa), sp), "uv_qkv_post")
                 if glob:
                     ctx = min(g_len or S, S)
                     splits = ns.get("global") or default_splits(B * K, ctx, self.device)
