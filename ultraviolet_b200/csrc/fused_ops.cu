@@ -255,16 +255,20 @@ __global__ void __launch_bounds__(SWR_THREADS) swiglu_rs_kernel(const T* __restr
 
 // ------------------------------------------------------------------------------------------------ QKV post
 // One warp per (row b, head slot), in place on the packed GEMM output; the arithmetic lives in qkv_post.cuh.
-template <typename T, int HD, bool TABLE>
-__global__ void __launch_bounds__(128) qkv_post_kernel(const __grid_constant__ QkvPostParams P) {
+// W warps per CTA, one (row, item) per warp.  COOP (xn_raw launches whose items per row are a multiple of W): the W
+// items of a CTA belong to ONE row, whose sum of squares the CTA forms once -- every thread one 16-byte piece -- instead
+// of each warp reading the whole row for itself (18 readers per 1.3 KB row otherwise: at a few thousand rows that
+// redundant L2 traffic is what the launch costs).
+template <typename T, int HD, bool TABLE, int W, bool COOP>
+__global__ void __launch_bounds__(W * 32) qkv_post_kernel(const __grid_constant__ QkvPostParams P) {
   constexpr int E = HD >= 32 ? HD / 32 : 1;
   const int lane = threadIdx.x & 31;
   const int slots = P.H + 2 * P.K;
   const int per_row = slots + (P.gate_out ? P.H : 0);  // head slots, then one gate item per query head
-  const int item = blockIdx.x * 4 + (threadIdx.x >> 5);
+  const int item = blockIdx.x * W + (threadIdx.x >> 5);
   pdl_wait();
   pdl_trigger();
-  if (item >= P.B * per_row) return;
+  if (item >= P.B * per_row) return;  // (COOP: the item count is a multiple of W, so this is CTA-uniform)
   const int b = item / per_row, hs = item % per_row;
   const bool raw = P.xn_raw != 0;
   // the slot's own values are requested before the row reduction below needs its loads: one round trip, not two
@@ -279,7 +283,30 @@ __global__ void __launch_bounds__(128) qkv_post_kernel(const __grid_constant__ Q
   QkvSlot dest{};
   const bool appends = hs >= P.H && hs < slots && P.k_cache != nullptr;
   if (appends) dest = qkv_post_slot(P, b);
-  const float rs = raw ? row_rms_factor<T>(static_cast<const T*>(P.xn) + (int64_t)b * P.d, P.d, lane) : 1.0f;
+  float rs = 1.0f;
+  if constexpr (COOP) {
+    __shared__ float part[W];
+    const uint4* row = reinterpret_cast<const uint4*>(static_cast<const T*>(P.xn) + (int64_t)b * P.d);
+    float ss = 0.f;
+    for (int p = threadIdx.x; p * 8 < P.d; p += W * 32) {
+      const uint4 u = row[p];
+      const T* v = reinterpret_cast<const T*>(&u);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        const float f = to_f32<T>(v[k]);
+        ss += f * f;
+      }
+    }
+    ss = warp_sum(ss);
+    if (lane == 0) part[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    float tot = 0.f;
+#pragma unroll
+    for (int w = 0; w < W; ++w) tot += part[w];
+    rs = rsqrtf(tot / (float)P.d + RMS_EPS);
+  } else {
+    if (raw) rs = row_rms_factor<T>(static_cast<const T*>(P.xn) + (int64_t)b * P.d, P.d, lane);
+  }
   if (hs >= slots) {
     const int head = hs - slots;
     const float g = head_gate<T>(static_cast<const T*>(P.xn) + (int64_t)b * P.d,
@@ -306,12 +333,27 @@ __global__ void __launch_bounds__(128) qkv_post_kernel(const __grid_constant__ Q
 
 template <typename T>
 static int launch_qkv_post(const QkvPostParams& P, int hd, cudaStream_t st) {
-  const unsigned grid = (unsigned)(((int64_t)P.B * (P.H + 2 * P.K + (P.gate_out ? P.H : 0)) + 3) / 4);
+  const int per_row = P.H + 2 * P.K + (P.gate_out ? P.H : 0);
+  const int64_t items = (int64_t)P.B * per_row;
+  // cooperative row reduction when the launch defers the norm and a row's items fill whole CTAs of 6 or 4 warps
+  static const bool coop_on = [] {
+    const char* v = getenv("UVDECODE_QKV_POST_COOP");
+    return !(v && v[0] == '0');
+  }();
+  const int coop = (P.xn_raw && coop_on) ? (per_row % 6 == 0 ? 6 : (per_row % 4 == 0 ? 4 : 0)) : 0;
+  const int wpc = coop ? coop : 4;
+  const unsigned grid = (unsigned)((items + wpc - 1) / wpc);
   // with the step's RoPE table the kernel carries no cosf / sinf code at all
-#define UV_QKV_POST(HD_)                                                                        \
-  case HD_:                                                                                     \
-    if (P.rope_cs) launch_pdl(qkv_post_kernel<T, HD_, true>, dim3(grid), dim3(128), 0, st, P);  \
-    else launch_pdl(qkv_post_kernel<T, HD_, false>, dim3(grid), dim3(128), 0, st, P);           \
+#define UV_QKV_POST_W(HD_, TABLE_)                                                                              \
+  do {                                                                                                          \
+    if (coop == 6) launch_pdl(qkv_post_kernel<T, HD_, TABLE_, 6, true>, dim3(grid), dim3(192), 0, st, P);       \
+    else if (coop == 4) launch_pdl(qkv_post_kernel<T, HD_, TABLE_, 4, true>, dim3(grid), dim3(128), 0, st, P);  \
+    else launch_pdl(qkv_post_kernel<T, HD_, TABLE_, 4, false>, dim3(grid), dim3(128), 0, st, P);                \
+  } while (0)
+#define UV_QKV_POST(HD_)                       \
+  case HD_:                                    \
+    if (P.rope_cs) UV_QKV_POST_W(HD_, true);   \
+    else UV_QKV_POST_W(HD_, false);            \
     break;
   switch (hd) {
     UV_QKV_POST(16)
@@ -321,6 +363,7 @@ static int launch_qkv_post(const QkvPostParams& P, int hd, cudaStream_t st) {
     default: return UV_ERR_SHAPE;
   }
 #undef UV_QKV_POST
+#undef UV_QKV_POST_W
   return check_launch();
 }
 
