@@ -449,7 +449,7 @@ def rollout_job(m, rank, world, dev, *, prompts_all, stops_all, slots, max_new, 
     log-probs fp32, lengths and start versions int32) are gathered to rank 0 afterwards, each collective timed.
     overlap: each window of steps is launched before the payload of the requests that finished in the window before
     it is gathered (GpuScheduler.window), so the device does not wait for the host's harvest.
-    Windows of 16 (packed admission) or 64 steps are timed separately so that the steady state (slot occupancy >=
+    Windows of 32 (packed admission) or 64 steps are timed separately so that the steady state (slot occupancy >=
     0.95) can be told from the
     straggler tail.  Returns a dict on every rank (aggregates are all-reduced)."""
     import torch
@@ -470,7 +470,9 @@ def rollout_job(m, rank, world, dev, *, prompts_all, stops_all, slots, max_new, 
                        max_prompt=max_prompt, force_eos=force_eos, tok_cap=int(lens[mine].sum()) + 1,
                        out_cap=int(lim[mine].sum()) + 1, prefill_lanes=lanes, lane_chunk=lane_chunk,
                        packed_prefill=packed, compact=compact)
-    W_STEPS = 16 if packed else 64   # steps between harvests (= between admission passes in packed mode)
+    # steps between harvests (= between admission passes in packed mode: a pass costs 0.4-0.9 ms whatever it admits,
+    # a freed slot idles half a window on average; 32 measured best of 16 / 24 / 32 / 48 on config 3)
+    W_STEPS = 32 if packed else 64
     sch.warm()                       # every step / admission graph captured before the job, as a server would
     sch.enqueue([prompts_all[i] for i in mine], limits=None if stops_all is None else lim[mine].tolist(), keys=mine,
                 metas=mine)
