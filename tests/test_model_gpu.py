@@ -225,6 +225,19 @@ def test_seed_rule_top_k_and_skip_attn():
     runner = DecodeRunner(m, st, bucket=32, use_graph=False, temperature=0.0, skip_attn=True)
     tok = runner.step(torch.tensor([1, 2, 3], device=DEV)).clone()
     assert tok.shape == (3,) and int(st.pos[0]) == 1
+    # step_host: tokens in and out through pinned host buffers (copies inside the step's graph) = step on device
+    # tensors, token for token and log-prob for log-prob
+    first = torch.tensor([4, 5, 6])
+    for graph in (False, True):
+        ra = DecodeRunner(m, m.new_state(3, 32), bucket=32, use_graph=graph, temperature=1.3, seed=9)
+        rb = DecodeRunner(m, m.new_state(3, 32), bucket=32, use_graph=graph, temperature=1.3, seed=9)
+        ta, tb = first.to(DEV), first.clone()
+        for _ in range(6):
+            ta = ra.step(ta).clone()
+            la = ra.out_logp.clone()
+            tb = rb.step_host(tb)
+            assert tb.is_pinned() and not tb.is_cuda and tb.tolist() == ta.tolist()
+            assert torch.equal(rb.host_logp, la.cpu())
 
 
 @pytest.mark.parametrize("name", ["uv50m", "tiny_hd64"])

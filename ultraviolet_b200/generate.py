@@ -68,8 +68,9 @@ class DecodeRunner:
         self.want_logp = True
         self.row_keys = torch.arange(st.B, dtype=torch.int64, device=dev)
         self.steps = torch.zeros(st.B, dtype=torch.int64, device=dev)
-        self.graphs: dict[int, torch.cuda.CUDAGraph] = {}
+        self.graphs: dict[tuple, torch.cuda.CUDAGraph] = {}
         self.skip_attn = skip_attn
+        self.host_in = self.host_out = self.host_logp = None   # pinned buffers of step_host, made on first use
 
     def g_len(self, p: int) -> int:
         return min(self.st.max_len, ((p + 1 + self.bucket - 1) // self.bucket) * self.bucket)
@@ -97,26 +98,67 @@ class DecodeRunner:
         if not self.use_graph:
             self._body(gl)
         else:
-            g = self.graphs.get(gl)
-            if g is None:
-                dev = self.st.pos.device
-                pos0, steps0, tok0 = self.st.pos.clone(), self.steps.clone(), self.tok.clone()
-                s = torch.cuda.Stream(dev)
-                s.wait_stream(torch.cuda.current_stream(dev))
-                with torch.cuda.stream(s):  # warm-up: the slot written now is rewritten by the real replay
-                    self._body(gl)
-                    self.st.pos.copy_(pos0)
-                    self.steps.copy_(steps0)
-                    self.tok.copy_(tok0)
-                torch.cuda.current_stream(dev).wait_stream(s)
-                g = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(g, capture_error_mode="thread_local"):
-                    self._body(gl)
-                self.graphs[gl] = g
-                self.eng.check_status(self.st.B)  # the warm-up run of a new bucket is also the failure check
-            g.replay()
+            self._graph(gl, host=False).replay()
         self.st.host_pos += 1
         return self.out_tok
+
+    def _graph(self, gl: int, host: bool) -> torch.cuda.CUDAGraph:
+        """The step's graph for global-context bucket gl; host: with the copy of the input tokens from the pinned
+        host buffer in front and the copy of the sampled tokens (and log-probs) to pinned host buffers behind."""
+        g = self.graphs.get((gl, host))
+        if g is None:
+            dev = self.st.pos.device
+
+            def body():
+                if host:
+                    self.tok.copy_(self.host_in, non_blocking=True)
+                self._body(gl)
+                if host:
+                    self.host_out.copy_(self.out_tok, non_blocking=True)
+                    self.host_logp.copy_(self.out_logp, non_blocking=True)
+            pos0, steps0, tok0 = self.st.pos.clone(), self.steps.clone(), self.tok.clone()
+            s = torch.cuda.Stream(dev)
+            s.wait_stream(torch.cuda.current_stream(dev))
+            with torch.cuda.stream(s):  # warm-up: the slot written now is rewritten by the real replay
+                self._body(gl)
+                self.st.pos.copy_(pos0)
+                self.steps.copy_(steps0)
+                self.tok.copy_(tok0)
+            torch.cuda.current_stream(dev).wait_stream(s)
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, capture_error_mode="thread_local"):
+                body()
+            self.graphs[(gl, host)] = g
+            self.eng.check_status(self.st.B)  # the warm-up run of a new bucket is also the failure check
+        return g
+
+    def step_host(self, tok: Tensor | None = None) -> Tensor:
+        """``step`` for callers whose tokens live on the host: the input tokens are read from the pinned buffer
+        ``host_in`` (tok, if given, is copied there first; writing into ``host_in`` directly saves that), the
+        sampled tokens and their log-probs land in the pinned buffers ``host_out`` / ``host_logp``, and the call
+        returns ``host_out`` after the device has finished.  Both copies are nodes of the step's CUDA graph: one
+        graph launch and one synchronisation per step."""
+        if self.host_in is None:
+            B = self.st.B
+            self.host_in = torch.zeros(B, dtype=torch.long).pin_memory()
+            self.host_out = torch.zeros(B, dtype=torch.long).pin_memory()
+            self.host_logp = torch.zeros(B, dtype=torch.float32).pin_memory()
+        if tok is not None and tok.data_ptr() != self.host_in.data_ptr():
+            self.host_in.copy_(tok)
+        p = int(self.st.host_pos.max())
+        assert p < self.st.max_len, "cache full"
+        gl = self.g_len(p)
+        dev = self.st.pos.device
+        if not self.use_graph:
+            self.tok.copy_(self.host_in, non_blocking=True)
+            self._body(gl)
+            self.host_out.copy_(self.out_tok, non_blocking=True)
+            self.host_logp.copy_(self.out_logp, non_blocking=True)
+        else:
+            self._graph(gl, host=True).replay()
+        torch.cuda.current_stream(dev).synchronize()
+        self.st.host_pos += 1
+        return self.host_out
 
 
 def _new_state(model, rows, max_len, eng, ring_extra):
