@@ -141,6 +141,39 @@ def graph_ms(body, reps=5):
     return float(np.median(ts))
 
 
+def cupti_kernel_times(replay, n=20):
+    """Per-kernel device time of `replay()` (a CUDA-graph replay) from CUPTI activity records (torch.profiler with
+    the CUDA activity only): kernels run back to back as in the real step, not serialised as under ncu.  Returns
+    {"kernels": {name: {"per_replay": launches, "us_each": mean duration}}, "kernel_us_per_replay": sum of kernel
+    time, "replay_us": wall time of a replay by CUDA events without the profiler}."""
+    import collections
+    import torch
+    from torch.profiler import ProfilerActivity, profile
+    replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(n):
+        replay()
+    e1.record()
+    torch.cuda.synchronize()
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        for _ in range(n):
+            replay()
+        torch.cuda.synchronize()
+    agg = collections.defaultdict(lambda: [0, 0.0])
+    for ev in prof.events():
+        if (ev.device_type == torch.autograd.DeviceType.CUDA and ev.name and "Memcpy" not in ev.name
+                and "Memset" not in ev.name):
+            k = ev.name.split("(")[0][:72]
+            agg[k][0] += 1
+            agg[k][1] += ev.device_time
+    kernels = {k: {"per_replay": c / n, "us_each": round(t / c, 2)} for k, (c, t) in
+               sorted(agg.items(), key=lambda kv: -kv[1][1])}
+    return {"kernels": kernels, "kernel_us_per_replay": round(sum(t for _, t in agg.values()) / n, 1),
+            "replay_us": round(e0.elapsed_time(e1) * 1e3 / n, 1)}
+
+
 def time_attention_layers(eng, st, pos, starts, rounds=4):
     """Average device time of one decode-attention launch at the cache state of the run, per layer kind, exactly as
     the step issues it (XSA + precomputed head gates in the epilogue).  The run's own layer caches plus clones of
@@ -442,7 +475,8 @@ def run_gemm_workload(args, dev):
 
 # ------------------------------------------------------------------------------------------------ rollout jobs
 def rollout_job(m, rank, world, dev, *, prompts_all, stops_all, slots, max_new, max_prompt, lanes, lane_chunk, seed,
-                force_eos, timed_steps=0, warmup=3, broadcast=False, gather=False, packed=True, compact=True, overlap=True):
+                force_eos, timed_steps=0, warmup=3, broadcast=False, gather=False, packed=True, compact=True, overlap=True,
+                kernel_times=False):
     """One rollout round on the device-resident scheduler: the requests are sharded i % W == rank, every rank runs
     its replica until its share is drained (timed_steps > 0: that many steps only), finished rollouts are harvested
     as device tensors.  Optionally the weight arena is broadcast from rank 0 first and the rollouts (tokens int32,
@@ -550,6 +584,11 @@ def rollout_job(m, rank, world, dev, *, prompts_all, stops_all, slots, max_new, 
            "steps_by_batch_rows_rank0": {str(k): v for k, v in sorted(sch.bucket_steps.items())},
            "weight_broadcast_ms": t_bcast * 1e3, "rollout_gather_ms": t_gather * 1e3,
            "device_status": eng.device_status(), "sched_status": c_prev["status"]}
+    if kernel_times and rank == 0 and slots in sch._graphs:
+        # per-kernel device times of the full-batch step at the job's current cache state (CUPTI; the extra replays
+        # advance the job, which is over)
+        res["kernel_times_cupti"] = cupti_kernel_times(sch._graphs[slots].replay)
+        res["kernel_times_cupti"]["mean_context"] = float(st.pos[:slots].float().mean().item())
     if gathered is not None:
         res["gathered"] = {"requests": int(sum(int(g[2].numel()) for g in gathered)),
                            "tokens": int(sum(int(g[0].numel()) for g in gathered)),
@@ -583,7 +622,7 @@ def run_continuous(args, m, rank, world, dev):
     r = rollout_job(m, rank, world, dev, prompts_all=prompts, stops_all=stops, slots=512, max_new=max_new,
                     max_prompt=max_prompt, lanes=args.lanes, lane_chunk=args.lane_chunk, seed=7, force_eos=True,
                     timed_steps=args.steps, warmup=args.warmup, broadcast=True, packed=args.prefill == "packed",
-                    compact=not args.no_compact, overlap=not args.no_overlap)
+                    compact=not args.no_compact, overlap=not args.no_overlap, kernel_times=args.kernel_times)
     if rank == 0:
         line = {"metric": "rollout decode tokens/s", "value": r["tokens_per_s"], "unit": "tokens/s",
                 "n_gpus": world, "steps": r["steps_all_ranks"] // world, "warmup": max(args.warmup, 3),
@@ -620,6 +659,8 @@ def main():
     ap.add_argument("--prefill", default="packed", choices=["packed", "lanes"],
                     help="rollout jobs: how prompts enter the cache (packed admission passes, or prefill lanes through "
                          "the decode step)")
+    ap.add_argument("--kernel-times", action="store_true",
+                    help="add per-kernel device times of the step from CUPTI records (taken after the timed region)")
     ap.add_argument("--no-overlap", action="store_true",
                     help="rollout jobs: harvest after every window of steps instead of while the next one runs")
     ap.add_argument("--no-compact", action="store_true",
@@ -721,6 +762,13 @@ def main():
             block_ms.append(float(t.item()))
     ms = float(np.median(block_ms))
     value = world * SLOTS * K / (ms / 1e3)
+    kernel_times = None
+    if args.kernel_times and rank == 0:   # per-kernel device times of this step (CUPTI), after the timed region
+        gl = runner.g_len(int(st.host_pos.max()))
+        g = runner._graph(gl, host=False)
+        pos0, steps0, tok0 = st.pos.clone(), runner.steps.clone(), runner.tok.clone()
+        kernel_times = cupti_kernel_times(g.replay)
+        st.pos.copy_(pos0), runner.steps.copy_(steps0), runner.tok.copy_(tok0)   # the replays advanced the device side only
 
     # ---- rollout gather (token ids of every rank to rank 0)
     t_gather = uvdist.gather_rollouts(all_tok.t().contiguous())[1] if world > 1 else 0.0
@@ -801,6 +849,7 @@ def main():
         "e2e": {"value": e2e, "unit": "tokens/s", "h2d_bytes_per_step": SLOTS * 8, "d2h_bytes_per_step": SLOTS * 12,
                 "steps": K2},
         "gpu_launches": (eng.launches_per_step() + 1) * K,
+        **({"kernel_times_cupti": kernel_times} if kernel_times is not None else {}),
         "clocks": clk.summary(),
         "roofline": {"bound": "hbm", "kernel": "attn_split_kernel (local-layer launches, 8 per step)"
                      if att_mid is att["local"] else "attn_split_kernel (global-layer launches, 2 per step)",
