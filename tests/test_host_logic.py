@@ -93,3 +93,18 @@ def test_device_handoff_layout_matches_reference_micro_batches():
     bins = pack_bins([5, 900, 200, 100, 1024], 1024)
     assert sorted(sum(bins, [])) == [0, 1, 2, 3, 4] and all(sum([5, 900, 200, 100, 1024][i] for i in b) <= 1024
                                                            for b in bins)
+
+
+def test_admission_pass_capacities():
+    """Capacities an admission pass is captured at: ascending multiples of 64 from 256 to the limit, never more than
+    a quarter above the one before, powers of two included."""
+    from ultraviolet_b200.scheduler import _pass_caps
+    for limit in (256, 1024, 16384):
+        caps = _pass_caps(limit)
+        assert caps[0] == 256 and caps[-1] == limit and caps == sorted(set(caps))
+        assert all(c % 64 == 0 for c in caps)
+        assert all(b <= a * 1.25 + 1e-9 for a, b in zip(caps, caps[1:]))
+        p = 256
+        while p <= limit:
+            assert p in caps
+            p *= 2

@@ -23,6 +23,20 @@ def _pow2(n: int) -> int:
     return 1 << max(1, (n - 1).bit_length())
 
 
+def _pass_caps(limit: int) -> list[int]:
+    """Packed-row capacities an admission pass may be captured at: 256, then four steps per octave (1.25 x, 1.5 x,
+    1.75 x, 2 x of each power of two, all multiples of 64) up to `limit` -- a pass is padded by a fifth at most
+    instead of up to a factor of two."""
+    caps, p = [256], 256
+    while p < limit:
+        for f in (5, 6, 7, 8):
+            c = p * f // 4
+            if c <= limit:
+                caps.append(c)
+        p *= 2
+    return caps
+
+
 class GpuScheduler:
     def __init__(self, engine, st, *, max_new: int, temperature: float, top_p: float = 1.0, eos_id: int | None = 0,
                  pad_id: int = 0, seed: int = 0, q_cap: int = 8192, tok_cap: int | None = None,
@@ -73,6 +87,7 @@ class GpuScheduler:
         if self.packed:
             st.pos, st.starts = i64(B), i64(B)      # the decode step runs on the B slots (cache rows 0 .. B - 1)
             self.prefill_cap = max(256, _pow2(int(prefill_cap)))
+            self.pass_caps = _pass_caps(self.prefill_cap)
             cap = self.prefill_cap
             self.pk_tok, self.pk_pos, self.pk_row, self.pk_last = i64(cap), i64(cap), i64(cap, B), i64(cap)
             self.pk_zero = i64(cap)
@@ -232,7 +247,7 @@ class GpuScheduler:
                               last_pos=self.pk_last[:cap]))
 
     def _admit_pass(self, cap: int) -> None:
-        """One admission pass of `cap` packed rows (a power of two): captured once per size, replayed after."""
+        """One admission pass of `cap` packed rows (one of pass_caps): captured once per size, replayed after."""
         if not self.use_graph:
             self._admit_body(cap)
         else:
@@ -263,14 +278,14 @@ class GpuScheduler:
 
     def _plan_admission(self) -> int:
         """Packed rows the next pass should get (0: nothing to admit), from the host's copy of the queue and the
-        counters of the last read: the first min(free slots, queued) requests, rounded up to a power of two."""
+        counters of the last read: the first min(free slots, queued) requests, rounded up to the next pass capacity."""
         pending = self.n_enqueued - self._head_h
         free = self.B - (self._head_h - self._fin_h)
         k = min(pending, free)
         if k <= 0:
             return 0
         need = sum(self._plen[self._head_h + i] - 1 for i in range(k))
-        return min(self.prefill_cap, max(256, _pow2(max(need, 1))))
+        return next((c for c in self.pass_caps if c >= need), self.prefill_cap)
 
     def admit(self, drain: bool = False) -> None:
         """Launch an admission pass if the last counters say requests are waiting and slots are free.  drain: keep
@@ -313,10 +328,8 @@ class GpuScheduler:
         for n in self.buckets:
             self._step_graph(n)
         if self.packed:
-            cap = 256
-            while cap <= self.prefill_cap:
+            for cap in self.pass_caps:
                 self._admit_pass(cap)
-                cap *= 2
             self.n_admit_passes = 0
         self.steps_run = 0
         self.bucket_steps.clear()
