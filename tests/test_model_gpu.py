@@ -398,3 +398,40 @@ def test_window_harvest_and_compaction_change_no_rollout():
         else:
             assert same > 0.97, (route, same)
             assert min(buckets) < B, buckets    # the tail of the job stepped fewer rows
+
+
+@pytest.mark.parametrize("lanes", [0, 6])
+def test_window_harvest_without_admission_passes(lanes):
+    """window() on the scheduler modes that admit inside the step kernel (prompts through the decode step, with and
+    without prefill lanes): the same rollouts as run + harvest_packed, bit for bit."""
+    from ultraviolet_b200.scheduler import GpuScheduler
+    spec = gi.model_specs()["tiny_hd64"]
+    m = _gpu_model(spec)
+    r = np.random.default_rng(41)
+    n, B = 40, 8
+    prompts = [r.integers(1, m.cfg.vocab_size, r.integers(1, 12)).tolist() for _ in range(n)]
+    limits = r.integers(1, 16, n).tolist()
+
+    def drive(route):
+        st = m.new_state(GpuScheduler.state_rows(B, lanes, False), 48, ring_extra=GpuScheduler.ring_extra(lanes, 4))
+        sch = GpuScheduler(m.engine, st, max_new=16, temperature=0.9, eos_id=None, seed=3, q_cap=64, max_prompt=16,
+                           prefill_lanes=lanes, lane_chunk=4)
+        sch.enqueue(prompts, limits=limits)
+        out = {}
+        for _ in range(200):
+            if route == "window":
+                p = sch.window(4)
+            else:
+                sch.run(4)
+                p = sch.harvest_packed()
+            for meta, toks, lps, _v in GpuScheduler.unpack(p):
+                out[meta] = (toks, lps.tolist())
+            if len(out) == n:
+                break
+        for meta, toks, lps, _v in sch.harvest():
+            out[meta] = (toks, lps.tolist())
+        m.engine.check_status()
+        return out
+
+    a, b = drive("run"), drive("window")
+    assert len(a) == n and a == b

@@ -405,6 +405,14 @@ __global__ void __launch_bounds__(NTHREAD) attn_split_kernel(const __grid_consta
   const int G = P.G;
   pdl_wait();     // positions, q and the newest cache entries come from the kernels before this one
   pdl_trigger();
+  // what the epilogue will read at the very end of the chain (the current token's v, the head gates, the XSA
+  // coefficients): pulled towards the SM now, while the tiles stream
+  if (tid == 0 && P.xsa_alpha != nullptr && P.v_cur != nullptr)
+    asm volatile("prefetch.global.L1 [%0];" ::"l"(static_cast<const QT*>(P.v_cur) + (int64_t)b * P.v_cur_sb +
+                                                   (int64_t)h * P.v_cur_sh));
+  if (tid == 32 && P.gate_vals != nullptr)
+    asm volatile("prefetch.global.L1 [%0];" ::"l"(P.gate_vals + (int64_t)b * P.H + (int64_t)h * G));
+  if (tid == 64 && P.xsa_alpha != nullptr) asm volatile("prefetch.global.L1 [%0];" ::"l"(P.xsa_alpha + (int64_t)h * G));
 
   // ---- the row's key range and this split's tiles
   const int64_t p = P.pos[b];
