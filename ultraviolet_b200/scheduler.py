@@ -276,20 +276,29 @@ class GpuScheduler:
         self._head_h, self._fin_h = int(c[CTL_HEAD]), int(c[CTL_FIN])
         self._ctl_fresh = True
 
-    def _plan_admission(self) -> int:
-        """Packed rows the next pass should get (0: nothing to admit), from the host's copy of the queue and the
-        counters of the last read: the first min(free slots, queued) requests, rounded up to the next pass capacity."""
-        pending = self.n_enqueued - self._head_h
-        free = self.B - (self._head_h - self._fin_h)
-        k = min(pending, free)
-        if k <= 0:
-            return 0
-        need = sum(self._plen[self._head_h + i] - 1 for i in range(k))
-        return next((c for c in self.pass_caps if c >= need), self.prefill_cap)
+    def _plan_admission(self, head: int, free: int) -> tuple[int, int]:
+        """(packed rows the next pass should get, requests it will take) for a queue head and a free-slot count --
+        (0, 0): nothing to admit.  The pass takes the longest queue prefix of at most `free` requests whose prompts
+        fit prefill_cap packed rows (what uv_sched_admit does on the device), padded to the next captured capacity."""
+        k = min(self.n_enqueued - head, free)
+        need = taken = 0
+        for i in range(max(k, 0)):
+            w = self._plen[head + i] - 1
+            if need + w > self.prefill_cap:
+                break
+            need, taken = need + w, taken + 1
+        if taken == 0:
+            return 0, 0
+        return next(c for c in self.pass_caps if c >= need), taken
+
+    MAX_PASSES_PER_CALL = 8
 
     def admit(self, drain: bool = False) -> None:
-        """Launch an admission pass if the last counters say requests are waiting and slots are free.  drain: keep
-        going (one counter read per pass) until nothing more can be admitted -- used when the batch is first filled."""
+        """Launch admission passes while the last counters say requests are waiting and slots are free: as many
+        back-to-back passes as it takes to fill the free slots (a wave of rollouts that ended together frees more
+        prompt tokens than one pass holds), planned on the host from the counters of the last read and its own
+        copy of the queue -- no read-back in between.  drain: afterwards read the counters again and repeat until
+        nothing more can be admitted (used when the batch is first filled)."""
         if not self.packed:
             return
         while True:
@@ -297,11 +306,15 @@ class GpuScheduler:
                 if not drain:
                     return
                 self._read_ctl()
-            cap = self._plan_admission()
-            if cap == 0:
-                return
-            self._admit_pass(cap)
-            if not drain:
+            head, free = self._head_h, self.B - (self._head_h - self._fin_h)
+            launched = 0
+            while launched < self.MAX_PASSES_PER_CALL:
+                cap, taken = self._plan_admission(head, free)
+                if cap == 0:
+                    break
+                self._admit_pass(cap)
+                head, free, launched = head + taken, free - taken, launched + 1
+            if launched == 0 or not drain:
                 return
 
     def prime(self) -> None:
