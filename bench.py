@@ -296,7 +296,7 @@ def step_shape_attention(eng, rounds=4):
 
 def workload_config(K: int) -> dict:
     """The workload both arms run (identical dictionaries in the two JSON lines)."""
-    return {"workload": "UV-50M fixed-batch decode (BASELINE configs[1]): 256 sequences/GPU, prompts U[32,128] of "
+    return {"workload": "UV-50M fixed-batch decode (benchmark configuration 2): 256 sequences/GPU, prompts U[32,128] of "
                         "uniform token ids, greedy, int8 KV, decode steps after prefill (step = 256 tokens/GPU)",
             "slots_per_gpu": SLOTS, "vocab": VOCAB, "weights": "random init seed 0",
             "prompts": "numpy default_rng(100 + rank): lengths then ids"}
@@ -599,7 +599,7 @@ def rollout_job(m, rank, world, dev, *, prompts_all, stops_all, slots, max_new, 
 
 
 def config3_requests():
-    """BASELINE configs[2]: 4096 requests, prompts U[16,256], stop length Geometric(mean 600) capped at 2048."""
+    """benchmark configuration 3: 4096 requests, prompts U[16,256], stop length Geometric(mean 600) capped at 2048."""
     r = np.random.default_rng(3)
     n_req, max_prompt, max_new = 4096, 256, 2048
     lens = r.integers(16, max_prompt + 1, n_req)
@@ -608,7 +608,7 @@ def config3_requests():
 
 
 def config5_requests():
-    """BASELINE configs[4]: 256 prompts U[64,256] x group 8 = 2048 sequences, max_new 2048, T = 1, top-p 1."""
+    """benchmark configuration 5: 256 prompts U[64,256] x group 8 = 2048 sequences, max_new 2048, T = 1, top-p 1."""
     r = np.random.default_rng(5)
     lens = r.integers(64, 257, 256)
     base = [r.integers(1, VOCAB, int(L)).tolist() for L in lens]
@@ -616,7 +616,7 @@ def config5_requests():
 
 
 def run_continuous(args, m, rank, world, dev):
-    """`--workload continuous`: BASELINE configs[2] as the headline line (whole job, or --steps timed steps)."""
+    """`--workload continuous`: benchmark configuration 3 as the headline line (whole job, or --steps timed steps)."""
     import torch.distributed as dist
     prompts, stops, max_prompt, max_new = config3_requests()
     r = rollout_job(m, rank, world, dev, prompts_all=prompts, stops_all=stops, slots=512, max_new=max_new,
@@ -812,7 +812,7 @@ def main():
         cont = rollout_job(m, rank, world, dev, prompts_all=prompts3, stops_all=stops3, slots=512, max_new=mn3,
                            max_prompt=mp3, lanes=args.lanes, lane_chunk=args.lane_chunk, seed=7, force_eos=True,
                            packed=args.prefill == "packed", compact=not args.no_compact, overlap=not args.no_overlap)
-        cont["workload"] = ("BASELINE configs[2]: 4096 requests sharded i % W, prompts U[16,256], stop ~ "
+        cont["workload"] = ("benchmark configuration 3: 4096 requests sharded i % W, prompts U[16,256], stop ~ "
                             "Geometric(600) <= 2048 (EOS forced), 512 slots/GPU, T = 1.0; whole job until drained")
         torch.cuda.empty_cache()
         prompts5, mp5, mn5 = config5_requests()
@@ -820,7 +820,7 @@ def main():
                            max_prompt=mp5, lanes=args.lanes, lane_chunk=args.lane_chunk, seed=11, force_eos=False,
                            broadcast=True, gather=True, packed=args.prefill == "packed",
                            compact=not args.no_compact, overlap=not args.no_overlap)
-        grpo["workload"] = ("BASELINE configs[4]: 256 prompts U[64,256] x group 8 = 2048 sequences sharded i % W, "
+        grpo["workload"] = ("benchmark configuration 5: 256 prompts U[64,256] x group 8 = 2048 sequences sharded i % W, "
                             "max_new 2048, T = 1.0, top-p 1.0, Philox key per sequence; arena broadcast before the "
                             "round, rollouts (tokens, log-probs, versions) gathered to rank 0 after it")
 

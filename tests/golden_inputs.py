@@ -149,7 +149,7 @@ def model_specs() -> dict:
         # MQA, hd 64, XSA: the production head geometry at toy width
         "tiny_hd64": dict(preset="tiny", over=dict(xsa=True, head_dim=64, n_kv_heads=1), seed=0, perturb="outputs",
                           B=6, P=5, N=30, cache_layers=[0, 3]),
-        # UV-50M at BASELINE sizes, random init seed 0, every 2-D weight perturbed so no projection is zero
+        # UV-50M at the benchmark's sizes, random init seed 0, every 2-D weight perturbed so no projection is zero
         "uv50m": dict(preset="uv-50m-alpha", over=dict(vocab_size=16384), seed=0, perturb="all2d", B=4, P=40, N=6,
                       cache_layers=[0, 4]),
     }
