@@ -344,6 +344,20 @@ class GpuScheduler:
             for cap in self.pass_caps:
                 self._admit_pass(cap)
             self.n_admit_passes = 0
+        # the harvest's device ops (index, scan, repeat_interleave, the small D2H copies), on both streams they
+        # run on: their one-time module loads would otherwise land in the first window that has a finisher.  A
+        # stand-in record (request 0 with one prompt token and one output token) is gathered and put back.
+        if self._side is None:
+            self._side = torch.cuda.Stream(self.dev, priority=-1)
+        keep = (self.fin_ring[0].clone(), self.out_len[0].clone(), self.prompt_len[0].clone())
+        self.fin_ring[0], self.out_len[0], self.prompt_len[0] = 0, 1, 1
+        for stream in (torch.cuda.current_stream(self.dev), self._side):
+            stream.wait_stream(torch.cuda.current_stream(self.dev))
+            with torch.cuda.stream(stream):
+                p = self._gather(0, 1, True)
+                p["requests"].cpu(), p["tokens"].cpu(), p["offsets"].cpu()
+            torch.cuda.current_stream(self.dev).wait_stream(stream)
+        self.fin_ring[0], self.out_len[0], self.prompt_len[0] = keep
         self.steps_run = 0
         self.bucket_steps.clear()
         for w in (CTL_STEPS, CTL_SLOT_STEPS, CTL_PREFILL_ROWS, CTL_ADMIT_PASSES, CTL_GENERATED, CTL_ACTIVE):
@@ -453,7 +467,21 @@ class GpuScheduler:
         """Payload of the requests [n_harvested, fin) of the finishing order, gathered on the current stream."""
         # rollouts from a step (or an admission pass) whose kernels flagged a failure are not handed out
         self.eng.check_status(None if self.packed else self.st_rows)
-        k = torch.arange(self.n_harvested, fin, device=self.dev) % self.q_cap
+        p = self._gather(self.n_harvested, fin, with_prompts)
+        rid_h = p["requests"].cpu().tolist()
+        p["metas"] = [self.meta.pop(r) for r in rid_h]
+        for r in rid_h:
+            self._span.pop(r, None)
+            if self.packed:
+                self._plen.pop(r, None)
+        self.n_harvested = fin
+        while self._oldest < self.n_enqueued and self._oldest not in self._span:
+            self._oldest += 1
+        return p
+
+    def _gather(self, lo: int, hi: int, with_prompts: bool) -> dict:
+        """Device tensors of the finished requests [lo, hi) of the finishing order (no host bookkeeping)."""
+        k = torch.arange(lo, hi, device=self.dev) % self.q_cap
         rid = self.fin_ring[k].long()
         ri = rid % self.q_cap
         lens, offs, ver = self.out_len[ri].long(), self.out_off[ri], self.start_version[ri]
@@ -470,17 +498,8 @@ class GpuScheduler:
             pseg = torch.repeat_interleave(torch.arange(rid.numel(), device=self.dev), pl, output_size=ptotal)
             pflat = (po[pseg] + torch.arange(ptotal, device=self.dev) - (pends - pl)[pseg]) % self.tok_cap
             extra = dict(prompt_tokens=self.tokens[pflat], prompt_offsets=torch.cat([pends.new_zeros(1), pends]))
-        rid_h = rid.cpu().tolist()
-        metas = [self.meta.pop(r) for r in rid_h]
-        for r in rid_h:
-            self._span.pop(r, None)
-            if self.packed:
-                self._plen.pop(r, None)
-        self.n_harvested = fin
-        while self._oldest < self.n_enqueued and self._oldest not in self._span:
-            self._oldest += 1
         return dict(tokens=self.out_tok[flat], logp=self.out_lp[flat],
-                    offsets=torch.cat([ends.new_zeros(1), ends]), versions=ver, requests=rid, metas=metas, **extra)
+                    offsets=torch.cat([ends.new_zeros(1), ends]), versions=ver, requests=rid, **extra)
 
     def harvest(self):
         """Return the requests that finished since the last call as [(meta, tokens list, logp float32 array,
