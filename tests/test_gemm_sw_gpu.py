@@ -194,7 +194,7 @@ def _steps(m, B, steps, seed):
 
 @pytest.mark.parametrize("B", [5, 256])
 def test_three_step_paths_agree(B):
-    """One model, three ways to run the step: the reference's literal op order (library GEMMs + separate residual /
+    """One model, three ways (and one hybrid) to run the step: the reference's literal op order (library GEMMs + separate residual /
     norm kernels), the folded residual stream with deferred norms (the default), and the tcgen05 GEMMs with fused
     epilogues.  Logits agree within the path's 2e-2 tolerance; first-layer cache bytes within a step."""
     from tests import golden_inputs as gi
@@ -204,15 +204,17 @@ def test_three_step_paths_agree(B):
     eng = m.engine
     assert eng.fold and eng.tc_gemm_ok
     res = {}
-    for name, fold, tc in (("fold", True, False), ("literal", False, False), ("tc", False, True)):
-        eng.fold, eng.tc_gemm = fold, tc
+    # (fold_sw: the folded step with QKV GEMM + uv_qkv_post as one launch of the own tcgen05 kernel)
+    for name, fold, tc, sw in (("fold", True, False, "0"), ("literal", False, False, "0"), ("tc", False, True, "0"),
+                               ("fold_sw", True, False, "1")):
+        eng.fold, eng.tc_gemm, eng.sw_qkv = fold, tc, sw
         eng.load_from(m)
         res[name] = _steps(m, B, 5, 3)
         assert eng.device_status() == {"attn_status": 0, "kv_oob": 0}
-    eng.fold, eng.tc_gemm = True, False
+    eng.fold, eng.tc_gemm, eng.sw_qkv = True, False, "0"
     eng.load_from(m)
     ref, sref = res["literal"]
-    for name in ("fold", "tc"):
+    for name in ("fold", "tc", "fold_sw"):
         lg, st = res[name]
         assert np.isfinite(lg).all()
         err = np.abs(lg - ref)

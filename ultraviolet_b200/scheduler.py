@@ -345,12 +345,17 @@ class GpuScheduler:
                 self._admit_pass(cap)
             self.n_admit_passes = 0
         # the harvest's device ops (index, scan, repeat_interleave, the small D2H copies), on both streams they
-        # run on: their one-time module loads would otherwise land in the first window that has a finisher.  A
-        # stand-in record (request 0 with one prompt token and one output token) is gathered and put back.
+        # run on, at the size of a whole batch of rollouts finishing together: their one-time module loads and --
+        # worse -- the allocator's first cudaMalloc calls for buffers of that size (each of which waits for the
+        # steps in flight) would otherwise land in the first windows that have finishers.  A stand-in record
+        # (request 0 owning that many output tokens) is gathered and put back; the blocks stay in the allocator's
+        # per-stream pools.
         if self._side is None:
             self._side = torch.cuda.Stream(self.dev, priority=-1)
         keep = (self.fin_ring[0].clone(), self.out_len[0].clone(), self.prompt_len[0].clone())
-        self.fin_ring[0], self.out_len[0], self.prompt_len[0] = 0, 1, 1
+        self.fin_ring[0] = 0
+        self.out_len[0] = min(self.out_cap, self.B * self.max_new)
+        self.prompt_len[0] = min(self.tok_cap, self.B * 256)
         for stream in (torch.cuda.current_stream(self.dev), self._side):
             stream.wait_stream(torch.cuda.current_stream(self.dev))
             with torch.cuda.stream(stream):
