@@ -257,10 +257,14 @@ def generate_continuous(model, prompts, max_new: int, batch: int, temperature: f
     results = [None] * n
     got = 0
     while got < n:
-        sched.run(check_every)
-        for i, toks, _, _ in sched.harvest():
+        # check_every steps go to the device first; what had finished before them is collected while they run
+        for i, toks, _, _ in sched.unpack(sched.window(check_every)):
             results[i] = toks
             got += 1
+        if got < n and sched.live_bound() == 0:   # every request is known to have finished: collect without stepping
+            for i, toks, _, _ in sched.harvest():
+                results[i] = toks
+                got += 1
     if stats is not None:
         stats.update(steps=sched.steps_run, prefilled=n, slots=B)
     return results

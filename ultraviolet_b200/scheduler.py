@@ -435,7 +435,7 @@ class GpuScheduler:
             self._read_ctl()
             fin = self._fin_h
         else:
-            fin = int(self.ctl[CTL_FIN].item())
+            fin = self._fin_h = int(self.ctl[CTL_FIN].item())
         self.run(n_steps)
         if fin == self.n_harvested:
             return None
@@ -463,7 +463,7 @@ class GpuScheduler:
             self._read_ctl()   # head and finished count in one small D2H: the next admission pass is planned on them
             fin = self._fin_h
         else:
-            fin = int(self.ctl[CTL_FIN].item())
+            fin = self._fin_h = int(self.ctl[CTL_FIN].item())
         if fin == self.n_harvested:
             return None
         return self._collect(fin, with_prompts)
