@@ -40,6 +40,11 @@ def warmup(device) -> None:
     dist.gather(t, out, dst=0)
     lst = [torch.empty_like(t) for _ in range(W)]
     dist.all_gather(lst, t)
+    # a rollout-sized gather too: the first large message sets up the transport's big-buffer protocol (tens of
+    # milliseconds once), which would otherwise be charged to the first real rollout gather
+    big = torch.zeros(1 << 21, dtype=torch.int32, device=device)
+    out = [torch.empty_like(big) for _ in range(W)] if rank == 0 else None
+    dist.gather(big, out, dst=0)
     _sync(t)
 
 
