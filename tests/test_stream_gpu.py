@@ -252,3 +252,98 @@ def test_device_handoff_of_a_real_harvest_and_direct_weight_publication():
     a = eng.arena.clone()
     sync_weights_inplace(m, raw)
     assert eng.arena.data_ptr() == ptr and torch.equal(a, eng.arena) and eng.version == v0 + 2
+
+
+def _uv50m():
+    from ultraviolet_b200.model import MathLM, make_config
+    torch.manual_seed(0)
+    m = MathLM(make_config("uv-50m-alpha", vocab_size=16384))
+    return m.to(DEV).to(torch.bfloat16).fuse_for_inference(torch.bfloat16)
+
+
+def test_continuous_batching_job_at_full_size_properties():
+    """The continuous-batching benchmark job at its full size (UV-50M, 4096 requests, prompts U[16,256], stop length
+    ~ Geometric(600) <= 2048 with EOS forced there, 512 slots, T = 1) through the device scheduler with admission
+    passes, slot compaction and the overlapped harvest.  Too large for the oracle, so size-independent properties:
+    every request comes back exactly once; it ends with EOS and holds no EOS before its end; it is no longer than its
+    stop length and exactly that long unless the model drew EOS earlier (rare: a 1-in-16384 event per token); one
+    finite log-prob <= 0 per token; the device counters agree with the payload; compaction really shrank the step;
+    nothing flagged a failure."""
+    from ultraviolet_b200.scheduler import GpuScheduler
+    r = np.random.default_rng(3)
+    n, slots, max_prompt, max_new, V = 4096, 512, 256, 2048, 16384
+    lens = r.integers(16, max_prompt + 1, n)
+    stops = np.minimum(r.geometric(1.0 / 600.0, n), max_new)
+    prompts = [r.integers(1, V, int(L)).tolist() for L in lens]
+    m = _uv50m()
+    st = m.new_state(GpuScheduler.state_rows(slots, 0, True), max_prompt + max_new + 16)
+    sch = GpuScheduler(m.engine, st, max_new=max_new, temperature=1.0, eos_id=0, seed=7, q_cap=n, max_prompt=max_prompt,
+                       force_eos=True, tok_cap=int(lens.sum()) + 1, out_cap=int(stops.sum()) + 1, packed_prefill=True)
+    sch.warm()
+    sch.enqueue(prompts, limits=stops.tolist())
+    got, windows = {}, 0
+    while len(got) < n and windows < 400:
+        windows += 1
+        for meta, toks, lps, ver in sch.unpack(sch.window(32)):
+            assert meta not in got
+            got[meta] = (toks, lps, ver)
+    for meta, toks, lps, ver in sch.harvest():
+        assert meta not in got
+        got[meta] = (toks, lps, ver)
+    assert sorted(got) == list(range(n))
+    early = 0
+    for i in range(n):
+        toks, lps, ver = got[i]
+        assert 1 <= len(toks) <= stops[i] and len(lps) == len(toks) and ver == 0
+        assert toks[-1] == 0 and 0 not in toks[:-1]
+        assert np.isfinite(lps).all() and (lps <= 0).all()
+        early += len(toks) < stops[i]
+    assert early < 0.08 * n, early          # expected about 0.035 n early stops
+    c = sch.counters()
+    total = sum(len(got[i][0]) for i in range(n))
+    assert c["generated"] == total and c["finished"] == n and c["head"] == n and c["status"] == 0
+    # a slot is counted as occupied after every step it survives: all of a request's tokens but its last
+    assert c["slot_steps"] == total - n and min(sch.bucket_steps) < slots
+    assert m.engine.device_status() == {"attn_status": 0, "kv_oob": 0}
+
+
+def test_grpo_round_at_full_size_properties():
+    """The GRPO benchmark round at its full size (256 prompts U[64,256] x group 8 = 2048 sequences, max_new 2048,
+    T = 1, one Philox key per sequence): every sequence comes back once with at most max_new tokens, EOS only as a
+    last token; the 8 members of a group share a prompt and differ in their text (distinct keys); members of a group
+    agree on their FIRST token's log-prob distribution support (same prompt, same weights: the first log-prob is the
+    log-probability of a token under one and the same distribution, so equal first tokens carry equal log-probs)."""
+    from ultraviolet_b200.scheduler import GpuScheduler
+    r = np.random.default_rng(5)
+    lens = r.integers(64, 257, 256)
+    base = [r.integers(1, 16384, int(L)).tolist() for L in lens]
+    prompts = [p for p in base for _ in range(8)]
+    n, slots, max_new = len(prompts), 512, 2048
+    m = _uv50m()
+    st = m.new_state(GpuScheduler.state_rows(slots, 0, True), 256 + max_new + 16)
+    sch = GpuScheduler(m.engine, st, max_new=max_new, temperature=1.0, eos_id=0, seed=11, q_cap=n, max_prompt=256,
+                       tok_cap=sum(len(p) for p in prompts) + 1, out_cap=n * max_new + 1, packed_prefill=True)
+    sch.warm()
+    sch.enqueue(prompts, keys=list(range(n)))
+    got, windows = {}, 0
+    while len(got) < n and windows < 400:
+        windows += 1
+        for meta, toks, lps, ver in sch.unpack(sch.window(32)):
+            got[meta] = (toks, lps)
+    for meta, toks, lps, ver in sch.harvest():
+        got[meta] = (toks, lps)
+    assert sorted(got) == list(range(n))
+    for i in range(n):
+        toks, lps = got[i]
+        assert 1 <= len(toks) <= max_new and len(lps) == len(toks)
+        assert 0 not in toks[:-1] and (len(toks) == max_new or toks[-1] == 0)
+        assert np.isfinite(lps).all() and (lps <= 0).all()
+    for g in range(256):
+        members = [got[8 * g + c] for c in range(8)]
+        assert len({tuple(t[:64]) for t, _ in members}) == 8, g       # 8 keys, 8 different continuations
+        first = {}
+        for t, l in members:                                          # same first token -> same log-prob (bf16 GEMMs
+            first.setdefault(t[0], []).append(float(l[0]))            # at one batch size: up to rounding)
+        for v in first.values():
+            assert max(v) - min(v) < 0.05, (g, v)
+    assert m.engine.device_status() == {"attn_status": 0, "kv_oob": 0}
