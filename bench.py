@@ -476,7 +476,7 @@ def run_gemm_workload(args, dev):
 # ------------------------------------------------------------------------------------------------ rollout jobs
 def rollout_job(m, rank, world, dev, *, prompts_all, stops_all, slots, max_new, max_prompt, lanes, lane_chunk, seed,
                 force_eos, timed_steps=0, warmup=3, broadcast=False, gather=False, packed=True, compact=True, overlap=True,
-                kernel_times=False):
+                kernel_times=False, overlap_admit=False, window=0):
     """One rollout round on the device-resident scheduler: the requests are sharded i % W == rank, every rank runs
     its replica until its share is drained (timed_steps > 0: that many steps only), finished rollouts are harvested
     as device tensors.  Optionally the weight arena is broadcast from rank 0 first and the rollouts (tokens int32,
@@ -503,10 +503,10 @@ def rollout_job(m, rank, world, dev, *, prompts_all, stops_all, slots, max_new, 
     sch = GpuScheduler(eng, st, max_new=max_new, temperature=1.0, eos_id=0, seed=seed, q_cap=max(len(mine), 2),
                        max_prompt=max_prompt, force_eos=force_eos, tok_cap=int(lens[mine].sum()) + 1,
                        out_cap=int(lim[mine].sum()) + 1, prefill_lanes=lanes, lane_chunk=lane_chunk,
-                       packed_prefill=packed, compact=compact)
+                       packed_prefill=packed, compact=compact, overlap_admit=overlap_admit and overlap)
     # steps between harvests (= between admission passes in packed mode: a pass costs 0.4-0.9 ms whatever it admits,
     # a freed slot idles half a window on average; 32 measured best of 16 / 24 / 32 / 48 on config 3)
-    W_STEPS = 32 if packed else 64
+    W_STEPS = window or (32 if packed else 64)
     sch.warm()                       # every step / admission graph captured before the job, as a server would
     sch.enqueue([prompts_all[i] for i in mine], limits=None if stops_all is None else lim[mine].tolist(), keys=mine,
                 metas=mine)
@@ -581,6 +581,7 @@ def rollout_job(m, rank, world, dev, *, prompts_all, stops_all, slots, max_new, 
            "steady_state": f"{W_STEPS}-step windows with slot occupancy >= 0.95 (max window time over ranks)",
            "prefill": "packed admission passes" if packed else (f"{lanes} prefill lanes" if lanes else "decode step"),
            "admission_passes": getattr(sch, "n_admit_passes", 0),
+           "admission_passes_beside_steps": sch.n_deferred_passes,
            "steps_by_batch_rows_rank0": {str(k): v for k, v in sorted(sch.bucket_steps.items())},
            "weight_broadcast_ms": t_bcast * 1e3, "rollout_gather_ms": t_gather * 1e3,
            "device_status": eng.device_status(), "sched_status": c_prev["status"]}
@@ -622,7 +623,8 @@ def run_continuous(args, m, rank, world, dev):
     r = rollout_job(m, rank, world, dev, prompts_all=prompts, stops_all=stops, slots=512, max_new=max_new,
                     max_prompt=max_prompt, lanes=args.lanes, lane_chunk=args.lane_chunk, seed=7, force_eos=True,
                     timed_steps=args.steps, warmup=args.warmup, broadcast=True, packed=args.prefill == "packed",
-                    compact=not args.no_compact, overlap=not args.no_overlap, kernel_times=args.kernel_times)
+                    compact=not args.no_compact, overlap=not args.no_overlap, kernel_times=args.kernel_times,
+                    overlap_admit=args.overlap_admit, window=args.window)
     if rank == 0:
         line = {"metric": "rollout decode tokens/s", "value": r["tokens_per_s"], "unit": "tokens/s",
                 "n_gpus": world, "steps": r["steps_all_ranks"] // world, "warmup": max(args.warmup, 3),
@@ -661,6 +663,10 @@ def main():
                          "the decode step)")
     ap.add_argument("--kernel-times", action="store_true",
                     help="add per-kernel device times of the step from CUPTI records (taken after the timed region)")
+    ap.add_argument("--window", type=int, default=0,
+                    help="rollout jobs: steps between harvests / admissions (default 32 with admission passes, else 64)")
+    ap.add_argument("--overlap-admit", action="store_true",
+                    help="rollout jobs: admission passes on a second stream beside the decode steps")
     ap.add_argument("--no-overlap", action="store_true",
                     help="rollout jobs: harvest after every window of steps instead of while the next one runs")
     ap.add_argument("--no-compact", action="store_true",
@@ -811,7 +817,8 @@ def main():
         prompts3, stops3, mp3, mn3 = config3_requests()
         cont = rollout_job(m, rank, world, dev, prompts_all=prompts3, stops_all=stops3, slots=512, max_new=mn3,
                            max_prompt=mp3, lanes=args.lanes, lane_chunk=args.lane_chunk, seed=7, force_eos=True,
-                           packed=args.prefill == "packed", compact=not args.no_compact, overlap=not args.no_overlap)
+                           packed=args.prefill == "packed", compact=not args.no_compact, overlap=not args.no_overlap,
+                           overlap_admit=args.overlap_admit, window=args.window)
         cont["workload"] = ("benchmark configuration 3: 4096 requests sharded i % W, prompts U[16,256], stop ~ "
                             "Geometric(600) <= 2048 (EOS forced), 512 slots/GPU, T = 1.0; whole job until drained")
         torch.cuda.empty_cache()
@@ -819,7 +826,8 @@ def main():
         grpo = rollout_job(m, rank, world, dev, prompts_all=prompts5, stops_all=None, slots=512, max_new=mn5,
                            max_prompt=mp5, lanes=args.lanes, lane_chunk=args.lane_chunk, seed=11, force_eos=False,
                            broadcast=True, gather=True, packed=args.prefill == "packed",
-                           compact=not args.no_compact, overlap=not args.no_overlap)
+                           compact=not args.no_compact, overlap=not args.no_overlap,
+                           overlap_admit=args.overlap_admit, window=args.window)
         grpo["workload"] = ("benchmark configuration 5: 256 prompts U[64,256] x group 8 = 2048 sequences sharded i % W, "
                             "max_new 2048, T = 1.0, top-p 1.0, Philox key per sequence; arena broadcast before the "
                             "round, rollouts (tokens, log-probs, versions) gathered to rank 0 after it")

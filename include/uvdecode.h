@@ -26,7 +26,7 @@
 extern "C" {
 #endif
 
-#define UV_ABI_VERSION 1
+#define UV_ABI_VERSION 2
 
 enum { UV_F32 = 0, UV_F16 = 1, UV_BF16 = 2, UV_I8 = 3 };
 
@@ -409,6 +409,16 @@ typedef struct uv_sched_args {
    * row of batch row b (a permutation of [0, B); uv_sched_admit hands it to the packed prefill), so the caller can
    * run the decode step on the first n >= active rows only.  Request outputs do not depend on it. */
   int compact;
+  /* Deferred admission (all optional, no_admit mode).  step_row (B,) is the cache row the decode step should use
+   * for batch row b: row_map[b] while the slot is live, the spare row B otherwise (pass it to uv_decode_attn /
+   * uv_qkv_post as their row_map), so that parked rows never write into a cache row an admission pass is filling.
+   * With ctl[14] (defer) = 1, uv_sched_admit leaves the admitted requests in the pend_* arrays (B,) instead of the
+   * slot state; uv_sched_commit, launched after that pass's prefill, makes them live.  The caller sets ctl[13]
+   * (in flight) = 1 on the step's stream before it launches such a pass on another stream: the step kernel then
+   * does not compact and notes the owed compaction in ctl[15]. */
+  int64_t* step_row;
+  int* pend_req; int* pend_fed;
+  int64_t* pend_tok; int64_t* pend_pos; int64_t* pend_key;
 } uv_sched_args;
 
 int uv_sched_step(const uv_sched_args* args, void* stream);
@@ -428,6 +438,9 @@ typedef struct uv_sched_admit_args {
   int reserved_;
 } uv_sched_admit_args;
 int uv_sched_admit(const uv_sched_args* args, const uv_sched_admit_args* pass, void* stream);
+/* uv_sched_commit: the slots a deferred admission pass filled (pend_req[s] >= 0) go live; clears ctl[13] / ctl[14],
+ * sets ctl[15].  Order it after the pass's prefill kernels. */
+int uv_sched_commit(const uv_sched_args* args, void* stream);
 int uv_sched_enqueue(const uv_sched_args* args, int n, void* stream);
 
 #ifdef __cplusplus

@@ -34,7 +34,8 @@ def test_every_declared_symbol_is_exported_and_bound(lib):
 
 
 def test_version_and_error_strings(lib):
-    assert lib.uv_abi_version() == 1
+    from ultraviolet_b200 import _lib
+    assert lib.uv_abi_version() == _lib.UV_ABI_VERSION == 2
     for code in range(0, -7, -1):
         assert lib.uv_error_string(code)
     assert b"unknown" in lib.uv_error_string(-99)

@@ -346,3 +346,61 @@ def test_compaction_keeps_live_slots_dense_and_changes_no_output(B, n):
     (a, steps_a), (b, steps_b) = drive(False), drive(True)
     assert len(a) == n and len(b) == n
     assert a == b
+
+
+@pytest.mark.parametrize("B,n", [(6, 60), (64, 400), (1500, 5000)])
+def test_deferred_admission_beside_the_steps_changes_no_output(B, n):
+    """Admission passes launched beside the steps (shadow state + uv_sched_commit), on the scheduler alone with the
+    fake sampler: per-request outputs equal the run with ordinary passes; at every step a slot is either live (its
+    step row is its cache row), or not (its step row is the spare row B, whether it is free or reserved by a pass
+    in flight); no request sits in two slots; the compaction owed while a pass was in flight is made up after the
+    commit (dense again once the queue has drained); every launched pass is committed."""
+    from ultraviolet_b200.scheduler import GpuScheduler
+    r = np.random.default_rng(B + 1)
+    prompts = [r.integers(1, 900, r.integers(1, 12)).tolist() for _ in range(n)]
+    limits = r.integers(1, 14, n).tolist()
+
+    class _Eng(_FakeEngine):
+        def trunk(self, *a, **k):
+            return None
+
+    def drive(overlap):
+        st, eng = _FakeState(B + 1, 32), _Eng(B)
+        sch = GpuScheduler(eng, st, max_new=14, temperature=1.0, eos_id=0, q_cap=max(8192, n), max_prompt=16,
+                           use_graph=False, packed_prefill=True, prefill_cap=4096, overlap_admit=overlap)
+        sch.enqueue(prompts, limits=limits)
+        sch.st.pos.zero_()
+        sch.admit(drain=True)
+        sch._primed = True
+        out, step = {}, 0
+        while len(out) < n and step < 6000:
+            # one "window" of 3 steps, as window() runs it
+            full = sch._commit_pending()
+            sch._read_ctl()
+            full = sch._admit_beside() or full
+            rows = B if full else sch.rows_needed()
+            for _ in range(3):
+                torch.cuda.synchronize()
+                req, gen = sch.req.cpu().numpy(), sch.gen.cpu().numpy()
+                pend = sch.pend_req.cpu().numpy()
+                rm, sr = sch.row_map.cpu().numpy(), sch.step_row.cpu().numpy()
+                live = req >= 0
+                assert sorted(rm.tolist()) == list(range(B))
+                assert (sr[live] == rm[live]).all() and (sr[~live] == B).all(), step
+                assert not (live & (pend >= 0)).any()
+                both = np.concatenate([req[live], pend[pend >= 0]])
+                assert len(set(both.tolist())) == both.size
+                assert not live[rows:].any(), (step, rows)          # everything live is inside the stepped rows
+                eng._s["tok"].copy_(torch.from_numpy(_fake_token(req.astype(np.int64), gen.astype(np.int64), 7)
+                                                     .astype(np.int64)))
+                eng._s["logp"].copy_(torch.from_numpy((-(req + 1) - gen / 100).astype(np.float32)))
+                sch._sched_step()
+                step += 1
+            for m, toks, lps, ver in sch.harvest():
+                out[m] = (toks, lps.tolist())
+        assert not sch._admit_pending and int(sch.ctl[13].item()) == 0
+        return out, sch.n_deferred_passes, sch.n_admit_passes
+
+    (a, da, pa), (b, db, pb) = drive(False), drive(True)
+    assert len(a) == n and len(b) == n and a == b
+    assert da == 0 and db > 0

@@ -13,7 +13,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.environ.get("UVDECODE_LIB") or os.path.join(HERE, "libuvdecode.so")
 
 UV_F32, UV_F16, UV_BF16, UV_I8 = 0, 1, 2, 3
-UV_ABI_VERSION = 1
+UV_ABI_VERSION = 2
 
 _lock = threading.Lock()
 _lib = None
@@ -73,7 +73,9 @@ class SchedArgs(C.Structure):
         "fin_ring", "ctl")] + [("B", C.c_int), ("q_cap", C.c_int), ("tok_cap", C.c_int64), ("out_cap", C.c_int64),
                                ("eos", C.c_int), ("pad", C.c_int), ("force_eos", C.c_int), ("max_len", C.c_int64),
                                ("row_map", C.c_void_p), ("lanes", C.c_int), ("lane_chunk", C.c_int),
-                               ("ring_len", C.c_int64), ("no_admit", C.c_int), ("compact", C.c_int)]
+                               ("ring_len", C.c_int64), ("no_admit", C.c_int), ("compact", C.c_int),
+                               ("step_row", C.c_void_p), ("pend_req", C.c_void_p), ("pend_fed", C.c_void_p),
+                               ("pend_tok", C.c_void_p), ("pend_pos", C.c_void_p), ("pend_key", C.c_void_p)]
 
 
 class SchedAdmitArgs(C.Structure):
@@ -134,6 +136,7 @@ SIGNATURES = {
     "uv_sched_step": (C.c_int, [C.POINTER(SchedArgs), C.c_void_p]),
     "uv_sched_admit": (C.c_int, [C.POINTER(SchedArgs), C.POINTER(SchedAdmitArgs), C.c_void_p]),
     "uv_sched_enqueue": (C.c_int, [C.POINTER(SchedArgs), C.c_int, C.c_void_p]),
+    "uv_sched_commit": (C.c_int, [C.POINTER(SchedArgs), C.c_void_p]),
     "uv_sample_topk": (C.c_int, [C.c_void_p, C.c_int, C.c_int64, C.c_int, C.c_int, C.c_int, C.c_float, C.c_float,
                                  C.c_float, C.c_float, C.c_int, C.c_float, C.c_void_p, C.c_uint64, C.c_void_p,
                                  C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),

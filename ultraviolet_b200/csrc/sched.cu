@@ -73,6 +73,19 @@ struct SchedParams {
   // request, not by slot, so nothing a request produces depends on the move.  The host can then run the decode
   // step on the first n >= active batch rows only.
   int compact;
+  // Deferred admission (optional; no_admit mode): an admission pass may run BESIDE the decode steps, on another
+  // stream.  It then writes the admitted requests into the pend_* arrays instead of the slot state (ctl[DEFER] = 1),
+  // and uv_sched_commit makes them live once the pass's prefill has finished.  While a pass is in flight
+  // (ctl[INFLIGHT]) the step kernel does not compact -- the pass has chosen slots and cache rows -- and remembers
+  // in ctl[DIRTY] that it owes a compaction.  step_row (B,) is what the decode step uses as the cache row of batch
+  // row b: row_map[b] while the slot is live, the spare row B otherwise, so that the parked rows of a step never
+  // write into a cache row that a pass is filling.
+  int64_t* step_row;
+  int* pend_req;       // (B,) request waiting in slot s for its commit, or -1
+  int* pend_fed;
+  int64_t* pend_tok;
+  int64_t* pend_pos;
+  int64_t* pend_key;
 };
 
 constexpr int COMPACT_MAX_SLOTS = 4096;  // the new row_map is staged in shared memory
@@ -90,7 +103,7 @@ struct AdmitParams {
 };
 
 enum { CTL_HEAD = 0, CTL_TAIL, CTL_FIN, CTL_VERSION, CTL_ACTIVE, CTL_STATUS, CTL_STEPS, CTL_TOK_TAIL, CTL_OUT_TAIL,
-       CTL_GENERATED, CTL_SLOT_STEPS, CTL_PREFILL_ROWS, CTL_ADMIT_PASSES };
+       CTL_GENERATED, CTL_SLOT_STEPS, CTL_PREFILL_ROWS, CTL_ADMIT_PASSES, CTL_INFLIGHT, CTL_DEFER, CTL_DIRTY };
 
 __device__ __forceinline__ int block_excl_scan(int v, int* warp_tot, int tid, int& total) {
   const int lane = tid & 31, warp = tid >> 5;
@@ -156,6 +169,7 @@ __global__ void __launch_bounds__(SCHED_THREADS) sched_step_kernel(const __grid_
   int64_t head = head0;
   const int64_t fin0 = P.ctl[CTL_FIN];
   int64_t fin_base = fin0;
+  const bool inflight = P.ctl[CTL_INFLIGHT] != 0, dirty = P.ctl[CTL_DIRTY] != 0;
   int active = 0, generated = 0;
   for (int base = 0; base < P.B; base += SCHED_THREADS) {  // uniform trip count: every thread joins every scan
     const int s = base + tid;
@@ -188,6 +202,7 @@ __global__ void __launch_bounds__(SCHED_THREADS) sched_step_kernel(const __grid_
             finished = 1, fin_req = r;
             if (full && g < lim)
               atomicOr(reinterpret_cast<unsigned long long*>(P.ctl + CTL_STATUS), 2ull);  // cut short: cache full
+            if (P.step_row) P.step_row[s] = P.B;  // from the next step on this batch row works on the spare cache row
             P.req[s] = -1;
             freed = 1;
           } else {
@@ -223,6 +238,7 @@ __global__ void __launch_bounds__(SCHED_THREADS) sched_step_kernel(const __grid_
         P.row_key[s] = P.key[ri];
         P.step_ctr[s] = 0;
         P.start_version[ri] = version;
+        if (P.step_row) P.step_row[s] = P.row_map ? P.row_map[s] : (int64_t)s;
       } else {  // nothing queued: park the slot at position 0 so it never overruns the cache (model.py:1345-1350)
         P.cur_tok[s] = P.pad;
         P.pos[s] = 0;
@@ -236,7 +252,9 @@ __global__ void __launch_bounds__(SCHED_THREADS) sched_step_kernel(const __grid_
     active += n_in - total_free + admitted;
   }
   // ---- compaction (see SchedParams::compact): stable partition of the slots into live ones, then free ones
-  if (P.compact && fin_base != fin0) {  // uniform: every thread has the same totals
+  const bool owes = fin_base != fin0 || dirty;
+  if (P.compact && owes && inflight && tid == 0) P.ctl[CTL_DIRTY] = 1;  // a pass holds slots and rows: later
+  if (P.compact && owes && !inflight) {  // uniform: every thread has the same totals and flags
     __shared__ int rm_new[COMPACT_MAX_SLOTS];
     int live_before = 0;
     for (int base = 0; base < P.B; base += SCHED_THREADS) {
@@ -265,8 +283,10 @@ __global__ void __launch_bounds__(SCHED_THREADS) sched_step_kernel(const __grid_
     __syncthreads();
     for (int s = tid; s < P.B; s += SCHED_THREADS) {
       P.row_map[s] = rm_new[s];
+      if (P.step_row) P.step_row[s] = s < active ? (int64_t)rm_new[s] : (int64_t)P.B;
       if (s >= active) P.req[s] = -1, P.cur_tok[s] = P.pad, P.pos[s] = 0, P.starts[s] = 0;
     }
+    if (tid == 0) P.ctl[CTL_DIRTY] = 0;
   }
   // ---- prefill lanes (see SchedParams): hand out the lane rows in slot order by prefix sum
   if (P.lanes > 0) {
@@ -313,7 +333,7 @@ __global__ void __launch_bounds__(SCHED_THREADS) sched_step_kernel(const __grid_
     }
   }
   if (tid == 0) {
-    P.ctl[CTL_HEAD] = head;
+    if (!P.no_admit) P.ctl[CTL_HEAD] = head;  // (no_admit: only admission passes move the head, possibly meanwhile)
     __threadfence();  // ring entries and out_len before the count that publishes them
     P.ctl[CTL_FIN] = fin_base;
     P.ctl[CTL_ACTIVE] = active;
@@ -337,11 +357,12 @@ __global__ void __launch_bounds__(SCHED_THREADS) sched_admit_kernel(const __grid
   pdl_trigger();
   const int64_t head = P.ctl[CTL_HEAD], tail = P.ctl[CTL_TAIL];
   const int version = (int)P.ctl[CTL_VERSION];
+  const bool defer = P.pend_req != nullptr && P.ctl[CTL_DEFER] != 0;
   int nseq = 0, rows = 0, tiles = 0;
   bool stop = false;
   for (int base = 0; base < P.B; base += SCHED_THREADS) {  // uniform trip count and uniform `stop`
     const int s = base + tid;
-    const bool freed = s < P.B && P.req[s] < 0;
+    const bool freed = s < P.B && P.req[s] < 0 && !(P.pend_req != nullptr && P.pend_req[s] >= 0);
     unsigned long long tot;
     // (1) rank among the chunk's free slots -> candidate request
     const unsigned long long pre_a = block_excl_scan3(pack3(freed ? 1 : 0, 0, 0), warp_tot3, tid, tot);
@@ -369,14 +390,23 @@ __global__ void __launch_bounds__(SCHED_THREADS) sched_admit_kernel(const __grid
         A.row[row0 + j] = P.row_map ? P.row_map[s] : (int64_t)s;  // the slot's cache row
         A.last_pos[row0 + j] = w - 1;
       }
-      P.req[s] = (int)r;
-      P.fed[s] = plen;
-      P.gen[s] = 0;
-      P.cur_tok[s] = P.tokens[(toff + plen - 1) % P.tok_cap];
-      P.pos[s] = plen - 1;
-      P.starts[s] = 0;
-      P.row_key[s] = P.key[ri];
-      P.step_ctr[s] = 0;
+      if (defer) {  // the slot goes live at uv_sched_commit, after this pass's prefill
+        P.pend_fed[s] = plen;
+        P.pend_tok[s] = P.tokens[(toff + plen - 1) % P.tok_cap];
+        P.pend_pos[s] = plen - 1;
+        P.pend_key[s] = P.key[ri];
+        P.pend_req[s] = (int)r;
+      } else {
+        P.req[s] = (int)r;
+        P.fed[s] = plen;
+        P.gen[s] = 0;
+        P.cur_tok[s] = P.tokens[(toff + plen - 1) % P.tok_cap];
+        P.pos[s] = plen - 1;
+        P.starts[s] = 0;
+        P.row_key[s] = P.key[ri];
+        P.step_ctr[s] = 0;
+        if (P.step_row) P.step_row[s] = P.row_map ? P.row_map[s] : (int64_t)s;
+      }
       P.start_version[ri] = version;
     }
     rows += field(tot, 0);
@@ -400,6 +430,31 @@ __global__ void __launch_bounds__(SCHED_THREADS) sched_admit_kernel(const __grid
     P.ctl[CTL_HEAD] = head + nseq;
     P.ctl[CTL_PREFILL_ROWS] += rows;
     P.ctl[CTL_ADMIT_PASSES] += 1;
+  }
+}
+
+// Deferred admission, second half: the slots a deferred pass filled go live (their prefill is complete: the caller
+// orders this launch after the pass), the in-flight mark is cleared and the step kernel is told that it owes a
+// compaction.
+__global__ void __launch_bounds__(SCHED_THREADS) sched_commit_kernel(const __grid_constant__ SchedParams P) {
+  for (int s = threadIdx.x; s < P.B; s += SCHED_THREADS) {
+    const int r = P.pend_req[s];
+    if (r < 0) continue;
+    P.req[s] = r;
+    P.fed[s] = P.pend_fed[s];
+    P.gen[s] = 0;
+    P.cur_tok[s] = P.pend_tok[s];
+    P.pos[s] = P.pend_pos[s];
+    P.starts[s] = 0;
+    P.row_key[s] = P.pend_key[s];
+    P.step_ctr[s] = 0;
+    if (P.step_row) P.step_row[s] = P.row_map ? P.row_map[s] : (int64_t)s;
+    P.pend_req[s] = -1;
+  }
+  if (threadIdx.x == 0) {
+    P.ctl[CTL_INFLIGHT] = 0;
+    P.ctl[CTL_DEFER] = 0;
+    P.ctl[CTL_DIRTY] = 1;
   }
 }
 
@@ -482,5 +537,16 @@ extern "C" int uv_sched_enqueue(const uv_sched_args* a, int n, void* stream) {
   SchedParams P;
   memcpy(&P, a, sizeof(P));
   sched_enqueue_kernel<<<1, SCHED_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(P, n);
+  return check_launch();
+}
+
+extern "C" int uv_sched_commit(const uv_sched_args* a, void* stream) {
+  using namespace uv;
+  if (!a || a->B < 1) return UV_ERR_ARG;
+  if (!a->pend_req || !a->pend_fed || !a->pend_tok || !a->pend_pos || !a->pend_key || !a->req || !a->ctl)
+    return UV_ERR_ARG;
+  SchedParams P;
+  memcpy(&P, a, sizeof(P));
+  sched_commit_kernel<<<1, SCHED_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(P);
   return check_launch();
 }

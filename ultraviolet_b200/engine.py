@@ -171,17 +171,20 @@ class DecodeEngine:
     # ------------------------------------------------------------------------------------------------ scratch
     BIG_ROWS = 2048  # batches above this (packed prompt prefill) share bucketed buffers instead of one set per size
 
-    def scratch(self, B: int) -> dict:
+    def scratch(self, B: int, tag: str = "") -> dict:
+        """The buffers of a B-row trunk call.  tag names a second, independent family of buffers for calls that may
+        run beside the untagged ones on another stream (admission passes next to decode steps)."""
         if B > self.BIG_ROWS:
             # prefill batches come in every size: one allocation per 4096-row bucket, handed out as [:B] views
             cap = (B + 4095) // 4096 * 4096
-            big = self._scratch.get(cap) or self.scratch_exact(cap)
+            big = self._scratch.get((cap, tag) if tag else cap) or self.scratch_exact(cap, tag)
             return {k: (v[:B] if isinstance(v, Tensor) and v.dim() >= 1 and v.size(0) == cap and k not in
                         ("flags", "status", "oob") else v) for k, v in big.items()}
-        return self.scratch_exact(B)
+        return self.scratch_exact(B, tag)
 
-    def scratch_exact(self, B: int) -> dict:
-        s = self._scratch.get(B)
+    def scratch_exact(self, B: int, tag: str = "") -> dict:
+        key = (B, tag) if tag else B
+        s = self._scratch.get(key)
         if s is None:
             cfg, dt, dev = self.cfg, self.dtype, self.device
             d, hd, H, K, f = cfg.d_model, cfg.head_dim, cfg.n_heads, cfg.n_kv_heads, cfg.d_ff
@@ -199,14 +202,14 @@ class DecodeEngine:
             # device words the kernels raise on silent failures: [0] attention status (bit 0: a bulk copy did not
             # land in time, outputs of that launch are undefined), [1] count of skipped out-of-range KV writes
             s["status"], s["oob"] = s["flags"][0:1], s["flags"][1:2]
-            self._scratch[B] = s
+            self._scratch[key] = s
         return s
 
     def device_status(self, B: int | None = None) -> dict:
         """The failure words of the scratch set of batch size B (default: all sets), one small D2H each."""
         out = {"attn_status": 0, "kv_oob": 0}
         for b, s in self._scratch.items():
-            if B is None or b == B:
+            if B is None or b == B or (isinstance(b, tuple) and b[0] == B):
                 st, oob = s["flags"].tolist()
                 out["attn_status"] |= st
                 out["kv_oob"] += oob
@@ -218,7 +221,7 @@ class DecodeEngine:
         d = self.device_status(B)
         if d["attn_status"] or d["kv_oob"]:
             for b, s in self._scratch.items():
-                if B is None or b == B:
+                if B is None or b == B or (isinstance(b, tuple) and b[0] == B):
                     s["flags"].zero_()
             raise _lib.UvError(f"decode kernels reported a device-side failure: attention status word "
                                f"{d['attn_status']:#x} (bit 0 = a cache tile copy timed out), {d['kv_oob']} KV "
@@ -248,7 +251,7 @@ class DecodeEngine:
     # ------------------------------------------------------------------------------------------------ one step
     def trunk(self, tok: Tensor, st, pos: Tensor, starts: Tensor, g_len: int | None = None,
               num_splits: dict | None = None, row_map: Tensor | None = None, skip_attn: bool = False,
-              packed: dict | None = None) -> Tensor:
+              packed: dict | None = None, scratch_tag: str = "") -> Tensor:
         """One token for every batch entry: writes K/V at `pos` and returns the final normed hidden (B, d) (a view
         of engine scratch, overwritten by the next call).  pos/starts are batch-indexed (B,) int64; row_map
         optionally maps batch entries to cache rows.
@@ -260,7 +263,7 @@ class DecodeEngine:
         only the newest positions of each prompt."""
         cfg, lib, dt = self.cfg, _lib.lib(), DTYPE_CODE[self.dtype]
         B = tok.size(0)
-        s = self.scratch(B)
+        s = self.scratch(B, scratch_tag)
         d, hd, H, K, f = cfg.d_model, cfg.head_dim, cfg.n_heads, cfg.n_kv_heads, cfg.d_ff
         sp = stream_ptr(self.device)
         w = self.w

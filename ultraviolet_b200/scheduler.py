@@ -16,7 +16,7 @@ from . import _lib
 from .kernels._util import stream_ptr
 
 (CTL_HEAD, CTL_TAIL, CTL_FIN, CTL_VERSION, CTL_ACTIVE, CTL_STATUS, CTL_STEPS, CTL_TOK_TAIL, CTL_OUT_TAIL,
- CTL_GENERATED, CTL_SLOT_STEPS, CTL_PREFILL_ROWS, CTL_ADMIT_PASSES) = range(13)
+ CTL_GENERATED, CTL_SLOT_STEPS, CTL_PREFILL_ROWS, CTL_ADMIT_PASSES, CTL_INFLIGHT, CTL_DEFER, CTL_DIRTY) = range(16)
 
 
 def _pow2(n: int) -> int:
@@ -42,7 +42,8 @@ class GpuScheduler:
                  pad_id: int = 0, seed: int = 0, q_cap: int = 8192, tok_cap: int | None = None,
                  out_cap: int | None = None, max_prompt: int = 256, force_eos: bool = False, use_graph: bool = True,
                  num_splits: dict | None = None, prefill_lanes: int = 0, lane_chunk: int = 8, top_k: int = 0,
-                 packed_prefill: bool = False, prefill_cap: int = 16384, compact: bool = True):
+                 packed_prefill: bool = False, prefill_cap: int = 16384, compact: bool = True,
+                 overlap_admit: bool = False):
         """prefill_lanes > 0: the decode step runs on slots + prefill_lanes batch rows; the extra rows carry further
         prompt tokens of slots that are still prefilling (up to lane_chunk tokens per slot per step).  The state must
         then hold one spare cache row: st.B == slots + 1 (see ``state_rows``).
@@ -53,6 +54,11 @@ class GpuScheduler:
         cache written on the way) in a single pass of up to prefill_cap rows.  The host only chooses how many packed
         rows the pass gets, from the queue's prompt lengths and the head / finished counters it read at the last
         harvest.  Needs the spare cache row too; excludes prefill_lanes.
+
+        overlap_admit (packed_prefill only; takes effect in ``window``): an admission pass that refills the free
+        slots in one go is launched on a second stream and runs BESIDE the window's decode steps; its requests
+        wait in a shadow state and go live (uv_sched_commit) at the start of the next window.  A slot then idles
+        one window longer, but the device never stops stepping for a prefill.
 
         compact (packed_prefill only, up to 4096 slots): the step kernel keeps the live slots in batch rows
         [0, active) (a slot's cache row follows it through ``row_map``), and ``run`` replays a step graph over the
@@ -97,6 +103,14 @@ class GpuScheduler:
             self._admit_graphs: dict[int, torch.cuda.CUDAGraph] = {}
             self.n_admit_passes = 0
             self.row_map = torch.arange(B, dtype=torch.int64, device=dev)   # batch row -> cache row
+            # what the decode step uses as cache row: row_map while a slot is live, the spare row B while it is not
+            self.step_row = i64(B, B)
+            self.pend_req, self.pend_fed = i32(B, -1), i32(B)
+            self.pend_tok, self.pend_pos, self.pend_key = i64(B), i64(B), i64(B)
+            self._flag_on = torch.ones(2, dtype=torch.int64, device=dev)   # ctl[INFLIGHT], ctl[DEFER] = 1, 1
+        self.overlap_admit = bool(overlap_admit) and self.packed
+        self._admit_pending, self._admit_ev, self._admit_stream = False, None, None
+        self.n_deferred_passes = 0
         self.compact = bool(compact) and self.packed and B <= 4096
         # batch rows a step may run on: all slots, or (compact) a halving ladder down to 32 rows
         self.buckets = sorted({B} | ({B >> k for k in range(1, 12) if (B >> k) >= 32} if self.compact else set()))
@@ -137,6 +151,9 @@ class GpuScheduler:
         a.no_admit = int(self.packed)
         if self.packed:
             a.row_map, a.compact = self.row_map.data_ptr(), int(self.compact)
+            a.step_row = self.step_row.data_ptr()
+            for name in ("pend_req", "pend_fed", "pend_tok", "pend_pos", "pend_key"):
+                setattr(a, name, getattr(self, name).data_ptr())
         # host mirrors
         self.n_enqueued = 0       # == ctl[TAIL]
         self.n_harvested = 0      # finished requests already returned
@@ -226,7 +243,7 @@ class GpuScheduler:
                           num_splits=self.num_splits, row_map=self.row_map)[:self.B]  # only slots are sampled
         else:
             h = eng.trunk(self.cur_tok[:n], st, st.pos[:n], st.starts[:n], g_len=st.max_len,
-                          num_splits=self.num_splits, row_map=self.row_map[:n] if self.packed else None)
+                          num_splits=self.num_splits, row_map=self.step_row[:n] if self.packed else None)
         head = eng.head(h)
         eng.sample(head, self.T, self.top_p, seed=self.seed, row_keys=self.row_key[:n], steps=self.step_ctr[:n],
                    tok_out=self.samp_tok[:n], logp_out=self.samp_lp[:n], top_k=self.top_k)
@@ -242,7 +259,7 @@ class GpuScheduler:
             _lib.check(_lib.lib().uv_sched_admit(C.byref(self.args), C.byref(p), stream_ptr(self.dev)),
                        "uv_sched_admit")
         eng.trunk(self.pk_tok[:cap], st, self.pk_pos[:cap], self.pk_zero[:cap], g_len=st.max_len,
-                  row_map=self.pk_row[:cap],
+                  row_map=self.pk_row[:cap], scratch_tag="admit",   # buffers of its own: it may run beside a step
                   packed=dict(cu=self.pk_cu, tile_cu=self.pk_tile_cu, n_seq=self.B, max_tiles=cap // 16 + self.B,
                               last_pos=self.pk_last[:cap]))
 
@@ -301,6 +318,9 @@ class GpuScheduler:
         nothing more can be admitted (used when the batch is first filled)."""
         if not self.packed:
             return
+        if self._commit_pending():       # a deferred pass moved the head: the counters in hand are stale
+            if not drain:
+                return
         while True:
             if not self._ctl_fresh:
                 if not drain:
@@ -316,6 +336,46 @@ class GpuScheduler:
                 head, free, launched = head + taken, free - taken, launched + 1
             if launched == 0 or not drain:
                 return
+
+    def _commit_pending(self) -> bool:
+        """If a deferred admission pass is outstanding: order the caller's stream after it and make its requests
+        live.  Returns whether it did (the window that follows must then step every slot: the step kernel compacts
+        at its first step, not before)."""
+        if not self._admit_pending:
+            return False
+        main = torch.cuda.current_stream(self.dev)
+        main.wait_event(self._admit_ev)
+        with torch.cuda.device(self.dev):
+            _lib.check(_lib.lib().uv_sched_commit(C.byref(self.args), stream_ptr(self.dev)), "uv_sched_commit")
+        self._admit_pending = False
+        self._ctl_fresh = False
+        return True
+
+    def _admit_beside(self) -> bool:
+        """window()'s admission: if ONE pass refills the free slots and something is live to step meanwhile, launch it
+        deferred on the admission stream (returns True); otherwise admit on the caller's stream as ``admit`` does."""
+        head, live = self._head_h, self._head_h - self._fin_h
+        free = self.B - live
+        cap, taken = self._plan_admission(head, free)
+        if cap == 0:
+            return False
+        more, _ = self._plan_admission(head + taken, free - taken)
+        if not self.overlap_admit or live <= 0 or more:
+            self.admit()
+            return False
+        main = torch.cuda.current_stream(self.dev)
+        # the step kernels of this window must see "a pass is in flight" (no compaction under it) before the pass
+        # starts: the marks are written on their stream, and the pass waits for that write
+        self.ctl[CTL_INFLIGHT:CTL_DEFER + 1].copy_(self._flag_on, non_blocking=True)
+        if self._admit_stream is None:
+            self._admit_stream = torch.cuda.Stream(self.dev)
+        self._admit_stream.wait_event(main.record_event())
+        with torch.cuda.stream(self._admit_stream):
+            self._admit_pass(cap)
+            self._admit_ev = self._admit_stream.record_event()
+        self._admit_pending = True
+        self.n_deferred_passes += 1
+        return True
 
     def prime(self) -> None:
         """First scheduling pass (admits queued requests into the idle slots) and graph capture."""
@@ -365,7 +425,8 @@ class GpuScheduler:
         self.fin_ring[0], self.out_len[0], self.prompt_len[0] = keep
         self.steps_run = 0
         self.bucket_steps.clear()
-        for w in (CTL_STEPS, CTL_SLOT_STEPS, CTL_PREFILL_ROWS, CTL_ADMIT_PASSES, CTL_GENERATED, CTL_ACTIVE):
+        for w in (CTL_STEPS, CTL_SLOT_STEPS, CTL_PREFILL_ROWS, CTL_ADMIT_PASSES, CTL_GENERATED, CTL_ACTIVE,
+                  CTL_INFLIGHT, CTL_DEFER, CTL_DIRTY):
             self.ctl[w] = 0
         self.st.pos.zero_()
         self._ctl_fresh = True
@@ -402,8 +463,11 @@ class GpuScheduler:
 
     def run(self, n_steps: int) -> None:
         self.prime()
+        full = self._commit_pending()   # the step kernel compacts at its first step after a commit, not before it
         self.admit()   # packed prefill mode: refill the slots that the last harvest saw free
-        n = self.rows_needed()
+        self._steps(n_steps, self.B if full else self.rows_needed())
+
+    def _steps(self, n_steps: int, n: int) -> None:
         if self.use_graph:
             n_steps -= min(n_steps, self._step_graph(n))
             g = self._graphs[n]
@@ -431,12 +495,15 @@ class GpuScheduler:
         ``harvest_packed`` returns (requests that finish during the steps launched here come with the next call;
         call ``harvest_packed`` after the last window)."""
         self.prime()
+        full = self._commit_pending()    # (before the read: the counters then include what the pass admitted)
         if self.packed:
             self._read_ctl()
             fin = self._fin_h
+            full = self._admit_beside() or full
+            self._steps(n_steps, self.B if full else self.rows_needed())
         else:
             fin = self._fin_h = int(self.ctl[CTL_FIN].item())
-        self.run(n_steps)
+            self.run(n_steps)
         if fin == self.n_harvested:
             return None
         if self._side is None:
