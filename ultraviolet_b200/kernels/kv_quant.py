@@ -76,6 +76,8 @@ def kv_append(k_cache: Tensor, v_cache: Tensor, k_scale: Tensor, v_scale: Tensor
 def kv_write_rows(cache: Tensor, scale: Tensor | None, new: Tensor, slots, rows: Tensor | None = None) -> None:
     """kv_quant.py:39-54: prefill-time write of new (n, K, T', hd) into cache[rows][:, :, slots]."""
     need_cuda(cache, scale, new)
+    if scale is not None and _write_rows_fused(cache, scale, new, slots, rows):
+        return
     if scale is None:
         vals = [(cache, new.to(cache.dtype))]
     else:
@@ -88,3 +90,36 @@ def kv_write_rows(cache: Tensor, scale: Tensor | None, new: Tensor, slots, rows:
             dst[rows, :, slots] = src
         else:
             dst[rows[:, None], :, slots[None, :]] = src.transpose(1, 2)
+
+
+def _write_rows_fused(cache: Tensor, scale: Tensor, new: Tensor, slots, rows: Tensor | None) -> bool:
+    """kv_write_rows as ONE launch of the fused quantise + scatter kernel: the destination of every (row, head,
+    token) vector is computed as a flat cache-row index (integer arithmetic on a few small tensors) and handed to
+    uv_kv_quant_scatter, so the payload is read once and written once.  Returns False when the layout is not the
+    (B, K, S_alloc, hd) / (B, K, S_alloc) pair of a decode state (the caller then scatters with torch indexing)."""
+    Bc, K, S, hd = cache.shape
+    n, Kn, T, hdn = new.shape
+    pitch = cache.stride(1) // hd if hd else 0
+    if (Kn != K or hdn != hd or cache.stride(3) != 1 or cache.stride(2) != hd or cache.stride(1) != pitch * hd
+            or cache.stride(0) != K * pitch * hd or scale.stride(2) != 1 or scale.stride(1) != pitch
+            or scale.stride(0) != K * pitch or pitch < S or T == 0 or n == 0):
+        return False
+    dev = cache.device
+    if isinstance(slots, slice):
+        sl = torch.arange(S, device=dev)[slots]
+    else:
+        sl = torch.as_tensor(slots, device=dev).to(torch.int64).reshape(-1)
+        sl = torch.where(sl < 0, sl + S, sl)
+    if sl.numel() != T:
+        return False
+    r = torch.arange(Bc, device=dev) if rows is None else rows.to(dev, torch.int64).reshape(-1)
+    if r.numel() != n:
+        return False
+    idx = ((r[:, None, None] * K + torch.arange(K, device=dev)[None, :, None]) * pitch + sl[None, None, :]).reshape(-1)
+    x2 = _rows(new, hd)
+    with torch.cuda.device(dev):
+        rc = _lib.lib().uv_kv_quant_scatter(x2.data_ptr(), DTYPE_CODE[x2.dtype], x2.stride(0), x2.size(0), hd,
+                                            cache.data_ptr(), scale.data_ptr(), idx.contiguous().data_ptr(),
+                                            Bc * K * pitch, None, stream_ptr(dev))
+    _lib.check(rc, "uv_kv_quant_scatter")
+    return True
