@@ -589,3 +589,15 @@ def test_appended_key_changes_only_its_row():
     assert torch.equal(kq2, kq) and torch.equal(vq2, vq) and torch.equal(ks2, ks) and torch.equal(vs2, vs)
     again = decode_attention(q, kq2, vq2, pos, starts, 0.14125, k_scale=ks2, v_scale=vs2)
     assert torch.equal(again, full)
+
+
+def test_default_splits_with_the_references_knobs():
+    """default_splits without min_chunk / waves is the library's heuristic; with either of them it is the reference's
+    rule (decode_attn.py:121-129) on those values."""
+    from ultraviolet_b200.kernels import default_splits
+    n_sm = torch.cuda.get_device_properties(0).multi_processor_count
+    ref = lambda n_bk, ctx, mc, w: max(1, min(-(-w * n_sm // max(n_bk, 1)), max(1, ctx // mc), 64))
+    for n_bk, ctx, mc, w in ((64, 8192, 128, 8), (256, 256, 64, 4), (1, 100000, 128, 8), (4096, 512, 128, 8)):
+        assert default_splits(n_bk, ctx, "cuda", min_chunk=mc, waves=w) == ref(n_bk, ctx, mc, w)
+    assert default_splits(64, 8192, "cuda", waves=4) == ref(64, 8192, 128, 4)
+    assert default_splits(64, 8192, "cuda") == 8 if n_sm == 148 else default_splits(64, 8192, "cuda") >= 1

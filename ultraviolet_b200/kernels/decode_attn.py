@@ -20,11 +20,16 @@ def _n_sm(dev: torch.device) -> int:
 
 
 def default_splits(n_bk: int, ctx: int, device=None, min_chunk: int | None = None, waves: int | None = None) -> int:
-    """Splits per (row, kv head) (role of decode_attn.py:121-129).  min_chunk / waves are accepted for signature
-    compatibility and not used: the heuristic is the library's own (uv_default_splits: 128-key tiles, every CTA
-    resident in one wave, a split only when it takes at least four tiles off every CTA)."""
+    """Splits per (row, kv head) (role of decode_attn.py:121-129).  Without min_chunk / waves the heuristic is the
+    library's own (uv_default_splits: 128-key tiles, every CTA resident in one wave, a split only when it takes at
+    least four tiles off every CTA).  A caller that passes either one gets the reference's rule with those values
+    (about `waves` programs per SM, chunks of at least min_chunk keys, at most 64 splits; defaults 8 and 128)."""
     dev = torch.device(device or "cuda")
-    return int(_lib.lib().uv_default_splits(int(n_bk), int(ctx), _n_sm(dev)))
+    if min_chunk is None and waves is None:
+        return int(_lib.lib().uv_default_splits(int(n_bk), int(ctx), _n_sm(dev)))
+    waves, min_chunk = 8 if waves is None else int(waves), 128 if min_chunk is None else int(min_chunk)
+    want = -(-waves * _n_sm(dev) // max(int(n_bk), 1))
+    return int(max(1, min(want, max(1, int(ctx) // max(min_chunk, 1)), 64)))
 
 
 def _row_alloc(k_cache: Tensor, v_cache: Tensor, k_scale: Tensor, v_scale: Tensor, S: int) -> int:
