@@ -133,6 +133,9 @@ size_t uv_decode_attn_workspace_bytes(int B, int KH, int G, int hd, int num_spli
  * decode_attn.py:121-129): every CTA resident in one wave (4 per SM), at least two 128-key tiles per split, and at
  * most 8 splits (the cluster merge) unless the batch is so small that 8 per row leave most SMs idle. */
 int uv_default_splits(int n_bk, int ctx, int n_sm);
+/* A row whose key range is empty (starts[b] > pos[b], or pos[b] < 0) attends to nothing: its output is all zeros
+ * (the reference's softmax over an empty set is NaN there; the case does not occur on the decode path, where the
+ * current token's key is always in range).  Such rows do not affect the others. */
 int uv_decode_attn(const uv_attn_args* args, void* stream);
 /* Which copy path uv_decode_attn takes for these arguments: 1 = bulk-copy (TMA) tiles (linear rows allocated to a
  * multiple of 8 slots, or a ring whose length is a multiple of 8; 16-byte aligned rows and scale rows), 0 = the

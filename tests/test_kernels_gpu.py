@@ -601,3 +601,27 @@ def test_default_splits_with_the_references_knobs():
         assert default_splits(n_bk, ctx, "cuda", min_chunk=mc, waves=w) == ref(n_bk, ctx, mc, w)
     assert default_splits(64, 8192, "cuda", waves=4) == ref(64, 8192, 128, 4)
     assert default_splits(64, 8192, "cuda") == 8 if n_sm == 148 else default_splits(64, 8192, "cuda") >= 1
+
+
+@pytest.mark.parametrize("splits", [1, 3])
+def test_rows_without_a_valid_key_give_zeros_and_leave_the_others_alone(splits):
+    """Edge case of the ragged batch: rows whose key range is empty (starts > pos) produce zeros, with or without a
+    split merge, and every other row of the launch equals the launch without them."""
+    from ultraviolet_b200.kernels import decode_attention, quantize_kv
+    g = torch.Generator(device=DEV).manual_seed(9)
+    B, S = 12, 640
+    k = torch.randn(B, 1, S, 64, device=DEV, generator=g)
+    v = torch.randn(B, 1, S, 64, device=DEV, generator=g)
+    q = torch.randn(B, 8, 64, device=DEV, generator=g).half()
+    kq, ks = quantize_kv(k)
+    vq, vs = quantize_kv(v)
+    pos = torch.randint(50, S, (B,), device=DEV, generator=g)
+    starts = torch.zeros(B, dtype=torch.long, device=DEV)
+    full = decode_attention(q, kq, vq, pos, starts, 0.14125, k_scale=ks, v_scale=vs, num_splits=splits)
+    empty = [1, 6, 11]
+    starts2 = starts.clone()
+    starts2[empty] = pos[empty] + 1
+    out = decode_attention(q, kq, vq, pos, starts2, 0.14125, k_scale=ks, v_scale=vs, num_splits=splits)
+    keep = [b for b in range(B) if b not in empty]
+    assert torch.equal(out[keep], full[keep])
+    assert torch.isfinite(out).all() and (out[empty] == 0).all()
