@@ -625,3 +625,23 @@ def test_rows_without_a_valid_key_give_zeros_and_leave_the_others_alone(splits):
     keep = [b for b in range(B) if b not in empty]
     assert torch.equal(out[keep], full[keep])
     assert torch.isfinite(out).all() and (out[empty] == 0).all()
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16, torch.float32])
+def test_sampler_edges_of_the_uniform(dtype):
+    """The reference sampler's edge cases (tests/test_perf_fz.py:66-71): with (almost) all of the mass on one token,
+    u -> 1 (target -> 0) and u = 0 (target = the whole sum) still give valid ids with finite log-probs -- the softcap
+    leaves every other token a mass of about 1e-9 of the total, so the extreme targets may land on those -- and any
+    u away from the ends draws the token that holds the mass, wherever it sits in the vocabulary."""
+    from ultraviolet_b200.kernels import fused_sample
+    V = 4096
+    for hot in (0, 40, 2047, 2048, V - 1):
+        x = torch.full((5, V), -1e4, device=DEV, dtype=dtype)
+        x[:, hot] = 10.0
+        u = torch.tensor([0.0, 1.0 - 2.0 ** -24, 0.5, 1e-3, 0.999], device=DEV)
+        tok, lp = fused_sample(x, u, (23.0, 5.0, 7.5), 1.0)
+        assert int(tok.min()) >= 0 and int(tok.max()) < V
+        assert tok[2:].tolist() == [hot] * 3
+        assert torch.isfinite(lp).all() and (lp <= 0).all() and (lp[2:] > -1e-3).all()
+        if hot == 0:
+            assert int(tok[1]) == 0          # target -> 0: the first token that has any mass

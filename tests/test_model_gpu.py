@@ -440,3 +440,29 @@ def test_window_harvest_without_admission_passes(lanes):
 
     a, b = drive("run"), drive("window")
     assert len(a) == n and a == b
+
+
+def test_runner_logp_across_graph_bucket_boundaries():
+    """DecodeRunner.out_logp is log softmax(out_logits / T)[sampled token] at every step, also on the steps where the
+    global-context bucket -- and with it the replayed graph -- changes (the reference's own check,
+    tests/test_perf_opt.py:194-222); graph and eager runs draw the same tokens."""
+    from ultraviolet_b200.generate import DecodeRunner
+    spec = gi.model_specs()["tiny_hd64"]
+    m = _gpu_model(spec)
+    T, B = 0.9, 4
+    res = []
+    for graph in (False, True):
+        st = m.new_state(B, 80)
+        st.set_pos(10)                      # positions 10 .. 49: buckets of 16 change at 16, 32 and 48
+        run = DecodeRunner(m, st, bucket=16, use_graph=graph, temperature=T, seed=21)
+        tok = torch.arange(1, B + 1, device=DEV)
+        toks, buckets = [], set()
+        for _ in range(40):
+            buckets.add(run.g_len(int(st.host_pos.max())))
+            tok = run.step(tok).clone()
+            ref = torch.log_softmax(run.out_logits.float() / T, -1).gather(1, tok[:, None])[:, 0]
+            assert (run.out_logp - ref).abs().max().item() < 2e-3
+            toks.append(tok)
+        assert len(buckets) >= 3
+        res.append(torch.stack(toks))
+    assert torch.equal(res[0], res[1])
