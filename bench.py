@@ -749,23 +749,24 @@ def main():
     # ---- timed region: K decode steps, device resident (R such blocks, each bracketed; median block reported)
     all_tok = torch.empty(K, SLOTS, dtype=torch.long, device=dev)
     block_ms = []
-    with ClockSampler(local) as clk:
-        for _ in range(R):
-            if world > 1:
-                dist.barrier()
-            torch.cuda.synchronize()
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record()
-            for i in range(K):
-                tok = runner.step(tok)
-                all_tok[i].copy_(tok)
-            e1.record()
-            torch.cuda.synchronize()
-            t = torch.tensor([e0.elapsed_time(e1)], device=dev)
-            if world > 1:
-                dist.all_reduce(t, op=dist.ReduceOp.MAX)
-                dist.barrier()
-            block_ms.append(float(t.item()))
+    clk = ClockSampler(local)
+    clk.__enter__()   # samples until the end-to-end loop below is over: both are the same step under load
+    for _ in range(R):
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(K):
+            tok = runner.step(tok)
+            all_tok[i].copy_(tok)
+        e1.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1)], device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            dist.barrier()
+        block_ms.append(float(t.item()))
     ms = float(np.median(block_ms))
     value = world * SLOTS * K / (ms / 1e3)
     kernel_times = None
@@ -799,6 +800,7 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e_s = float(t.item())
     e2e = world * SLOTS * K2 / e2e_s
+    clk.__exit__(None, None, None)
 
     # ---- roofline of the dominant kernel of this library (decode attention), at the run's final cache state
     #      (rank 0 measures; the other ranks wait at the next job's barrier)
