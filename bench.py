@@ -47,18 +47,18 @@ def measured_peaks():
 
 # ------------------------------------------------------------------------------------------------ clocks
 class ClockSampler:
-    """nvidia-smi clocks / throttle reasons sampled every 200 ms while the timed region runs (read-only)."""
+    """nvidia-smi clocks / throttle reasons sampled every interval_ms while the timed region runs (read-only)."""
     Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
          "clocks_event_reasons.sw_power_cap")
 
-    def __init__(self, index: int):
-        self.index, self.rows, self.proc = index, [], None
+    def __init__(self, index: int, interval_ms: int = 200):
+        self.index, self.rows, self.proc, self.interval_ms = index, [], None, int(interval_ms)
 
     def __enter__(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                                          "-lms", "200", "-i", str(self.index)], stdout=subprocess.PIPE, text=True)
+                                          "-lms", str(self.interval_ms), "-i", str(self.index)], stdout=subprocess.PIPE, text=True)
             self.t = threading.Thread(target=self._read, daemon=True)
             self.t.start()
         except Exception:
@@ -518,6 +518,8 @@ def rollout_job(m, rank, world, dev, *, prompts_all, stops_all, slots, max_new, 
     harvested, windows, steps, n_done = [], [], 0, 0
     ev = lambda: torch.cuda.Event(enable_timing=True)
     e_begin, e_end = ev(), ev()
+    clk = ClockSampler(dev.index if dev.index is not None else 0)
+    clk.__enter__()
     e_begin.record()
     last = None   # (start event, end event, steps) of the window in flight
 
@@ -557,6 +559,7 @@ def rollout_job(m, rank, world, dev, *, prompts_all, stops_all, slots, max_new, 
             n_done += len(p["metas"])
     e_end.record()
     torch.cuda.synchronize()
+    clk.__exit__(None, None, None)
     ms = e_begin.elapsed_time(e_end)
     steady = [(t, g) for t, g, occ in windows if occ >= 0.95]
     agg = torch.tensor([c_prev["generated"] - c0["generated"], c_prev["slot_steps"] - c0["slot_steps"], steps,
@@ -584,7 +587,7 @@ def rollout_job(m, rank, world, dev, *, prompts_all, stops_all, slots, max_new, 
            "admission_passes_beside_steps": sch.n_deferred_passes,
            "steps_by_batch_rows_rank0": {str(k): v for k, v in sorted(sch.bucket_steps.items())},
            "weight_broadcast_ms": t_bcast * 1e3, "rollout_gather_ms": t_gather * 1e3,
-           "device_status": eng.device_status(), "sched_status": c_prev["status"]}
+           "device_status": eng.device_status(), "sched_status": c_prev["status"], "clocks_rank0": clk.summary()}
     if kernel_times and rank == 0 and slots in sch._graphs:
         # per-kernel device times of the full-batch step at the job's current cache state (CUPTI; the extra replays
         # advance the job, which is over)
@@ -749,7 +752,7 @@ def main():
     # ---- timed region: K decode steps, device resident (R such blocks, each bracketed; median block reported)
     all_tok = torch.empty(K, SLOTS, dtype=torch.long, device=dev)
     block_ms = []
-    clk = ClockSampler(local)
+    clk = ClockSampler(local, interval_ms=50)   # the region is tens of milliseconds long at the default --steps
     clk.__enter__()   # samples until the end-to-end loop below is over: both are the same step under load
     for _ in range(R):
         if world > 1:
