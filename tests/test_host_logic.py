@@ -108,3 +108,35 @@ def test_admission_pass_capacities():
         while p <= limit:
             assert p in caps
             p *= 2
+
+
+def test_bench_workload_definitions_are_deterministic_and_match_their_configurations():
+    """bench.py's synthetic workloads: the same requests every time (both benchmark arms and every rank build them
+    independently), with the shapes the configurations name; the algorithmic-bytes formula of an attention launch."""
+    import importlib.util
+    import os
+    spec = importlib.util.spec_from_file_location(
+        "uv_bench", os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "bench.py"))
+    bench = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(bench)
+    p3, stops, max_prompt, max_new = bench.config3_requests()
+    q3, stops2, _, _ = bench.config3_requests()
+    assert p3 == q3 and (stops == stops2).all()
+    assert len(p3) == 4096 and (max_prompt, max_new) == (256, 2048)
+    lens = np.array([len(p) for p in p3])
+    assert lens.min() >= 16 and lens.max() <= 256 and stops.min() >= 1 and stops.max() == 2048
+    assert 500 < stops.mean() < 620                       # Geometric(mean 600) capped at 2048
+    assert all(0 < t < bench.VOCAB for p in p3[:50] for t in p)          # EOS (0) never inside a prompt
+    p5, mp5, mn5 = bench.config5_requests()
+    assert len(p5) == 2048 and (mp5, mn5) == (256, 2048)
+    assert all(p5[8 * g + c] == p5[8 * g] for g in range(256) for c in range(8))   # groups of 8 identical prompts
+    assert len({tuple(p5[8 * g]) for g in range(256)}) == 256
+    assert min(len(p) for p in p5) >= 64 and max(len(p) for p in p5) <= 256
+    a = bench.make_prompts(256, 32, 128, 100)
+    assert a == bench.make_prompts(256, 32, 128, 100) and 32 <= min(map(len, a)) and max(map(len, a)) <= 128
+    # 132 bytes per attended key (64 + 64 int8 + two fp16 scales) + q and out of 8 heads x 64 x 2 bytes per row
+    pos, starts = np.array([9, 300, 5]), np.array([0, 0, 3])
+    assert bench.attn_bytes(pos, starts, 0) == (10 + 301 + 3) * 132 + 2 * 3 * 8 * 64 * 2
+    assert bench.attn_bytes(pos, starts, 256, S=256, ring=True) == (10 + 256 + 3) * 132 + 2 * 3 * 8 * 64 * 2
+    cfg = bench.workload_config(20)
+    assert cfg == bench.workload_config(20) and "workload" in cfg
